@@ -1,0 +1,270 @@
+// Elementwise stages: unary math, binary arithmetic with NumPy broadcast,
+// scalar ops, cast, copy and rope. One implementation replaces the
+// reference's Broadcast1/Broadcast2 tile walkers
+// (ark/include/kernels/common/broadcast.h:22-553, arithmetic.h, math_functions.h,
+// cast.h, copy.h, scalar.h, embedding.h:14-37): every thread moves 128-bit
+// vectors, the arithmetic is fp32 and the result is rounded once.
+#include "dev_common.cuh"
+#include "dev_funcs.h"
+
+namespace arkb {
+
+template <int N>
+__device__ __forceinline__ void ewise_math(int op, float scalar, const float (&x)[N], const float (&y)[N],
+                                           float (&r)[N]) {
+    switch (op) {
+        case EW_GELU:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = gelu_f(x[i]);
+            break;
+        case EW_EXP:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = expf(x[i]);
+            break;
+        case EW_RELU:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] > 0.0f ? x[i] : 0.0f;
+            break;
+        case EW_RSQRT:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = 1.0f / sqrtf(x[i]);
+            break;
+        case EW_SIGMOID:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = sigmoid_f(x[i]);
+            break;
+        case EW_SILU:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] * sigmoid_f(x[i]);
+            break;
+        case EW_SQRT:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = sqrtf(x[i]);
+            break;
+        case EW_ADD:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] + y[i];
+            break;
+        case EW_SUB:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] - y[i];
+            break;
+        case EW_MUL:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] * y[i];
+            break;
+        case EW_DIV:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] / y[i];
+            break;
+        case EW_SCALAR_ASSIGN:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = scalar;
+            break;
+        case EW_SCALAR_ADD:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] + scalar;
+            break;
+        case EW_SCALAR_MUL:
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i] * scalar;
+            break;
+        case EW_ROPE:
+            // complex multiply on adjacent pairs (ark/include/kernels/embedding.h:14-37)
+            if constexpr (N >= 2) {
+#pragma unroll
+                for (int i = 0; i < N; i += 2) {
+                    r[i] = x[i] * y[i] - x[i + 1] * y[i + 1];
+                    r[i + 1] = x[i] * y[i + 1] + x[i + 1] * y[i];
+                }
+            }
+            break;
+        default:  // EW_COPY / EW_CAST
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = x[i];
+            break;
+    }
+}
+
+__device__ __forceinline__ bool ewise_is_binary(int op) { return (op >= EW_ADD && op <= EW_DIV) || op == EW_ROPE; }
+__device__ __forceinline__ bool ewise_reads_in0(int op) { return op != EW_SCALAR_ASSIGN; }
+
+
+// Same-type path: TIn == TOut, V elements per access.
+template <typename TI, typename TO, int V>
+__device__ void ewise_walk(const EwiseArgs &a, int p, int P) {
+    const int op = a.op;
+    const bool bin = ewise_is_binary(op);
+    const bool rd0 = ewise_reads_in0(op);
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x;
+    const int64_t nth = (int64_t)P * kThreads;
+    TO *out = reinterpret_cast<TO *>(a.out.ptr);
+    const TI *in0 = reinterpret_cast<const TI *>(a.in0.ptr);
+    const TI *in1 = reinterpret_cast<const TI *>(a.in1.ptr);
+    if (a.flat) {
+        constexpr int U = 4;  // independent accesses in flight per thread
+        for (int64_t u0 = tid; u0 < a.n_units; u0 += nth * U) {
+            float x[U][V], y[U][V], r[V];
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                int64_t u = u0 + j * nth;
+                if (u < a.n_units) {
+                    if (rd0) load_vec<TI, V>(in0 + u * V, x[j]);
+                    if (bin) load_vec<TI, V>(in1 + u * V, y[j]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                int64_t u = u0 + j * nth;
+                if (u < a.n_units) {
+                    ewise_math<V>(op, a.scalar, x[j], y[j], r);
+                    store_vec<TO, V>(out + u * V, r);
+                }
+            }
+        }
+        return;
+    }
+    const int64_t WV = (a.out.shape[3] + V - 1) / V;
+    const int64_t H = a.out.shape[2], C = a.out.shape[1];
+    for (int64_t u = tid; u < a.n_units; u += nth) {
+        int64_t wv = u % WV, row = u / WV;
+        int64_t h = row % H;
+        row /= H;
+        int64_t c = row % C, n = row / C;
+        int64_t w = wv * V;
+        float x[V], y[V], r[V];
+        if (rd0) {
+            const TI *p0 = in0 + tref_off(a.in0, n, c, h, a.in0.stride[3] ? w : 0);
+            if (a.in0.stride[3]) {
+                load_vec<TI, V>(p0, x);
+            } else {
+                float s = to_f32(*p0);
+#pragma unroll
+                for (int i = 0; i < V; ++i) x[i] = s;
+            }
+        }
+        if (bin) {
+            const TI *p1 = in1 + tref_off(a.in1, n, c, h, a.in1.stride[3] ? w : 0);
+            if (a.in1.stride[3]) {
+                load_vec<TI, V>(p1, y);
+            } else {
+                float s = to_f32(*p1);
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = s;
+            }
+        }
+        ewise_math<V>(op, a.scalar, x, y, r);
+        store_vec<TO, V>(out + tref_off(a.out, n, c, h, w), r);
+    }
+}
+
+template <typename TI, typename TO>
+__device__ __forceinline__ void ewise_typed(const EwiseArgs &a, int p, int P) {
+    constexpr int VS = 16 / (sizeof(TI) > sizeof(TO) ? sizeof(TI) : sizeof(TO));
+    if (a.vec > 1)
+        ewise_walk<TI, TO, VS>(a, p, P);
+    else
+        ewise_walk<TI, TO, 1>(a, p, P);
+}
+
+// Raw copy of integer data (no fp32 round trip): 16 or 1 bytes per access.
+__device__ void ewise_bytes(const EwiseArgs &a, int p, int P, int esize) {
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x;
+    const int64_t nth = (int64_t)P * kThreads;
+    if (a.flat && a.vec > 1) {
+        const uint4 *s = reinterpret_cast<const uint4 *>(a.in0.ptr);
+        uint4 *d = reinterpret_cast<uint4 *>(a.out.ptr);
+        for (int64_t u = tid; u < a.n_units; u += nth) d[u] = s[u];
+        return;
+    }
+    // generic strided element copy
+    const int64_t W = a.out.shape[3], H = a.out.shape[2], C = a.out.shape[1];
+    const int64_t total = (int64_t)a.out.shape[0] * C * H * W;
+    const char *s = reinterpret_cast<const char *>(a.in0.ptr);
+    char *d = reinterpret_cast<char *>(a.out.ptr);
+    for (int64_t i = tid; i < total; i += nth) {
+        int64_t w = i % W, r = i / W;
+        int64_t h = r % H;
+        r /= H;
+        int64_t c = r % C, n = r / C;
+        int64_t so = tref_off(a.in0, n, c, h, w) * esize, dof = tref_off(a.out, n, c, h, w) * esize;
+        for (int b = 0; b < esize; ++b) d[dof + b] = s[so + b];
+    }
+}
+
+// Conversions between any two storage types go through one generic walker
+// whose loads and stores dispatch on the runtime dtype (keeps the code size
+// additive in the number of types instead of quadratic).
+template <int V>
+__device__ __forceinline__ void load_any(const void *base, int dt, int64_t e, float (&f)[V]) {
+    switch (dt) {
+        case DT_F32: load_vec<float, V>(reinterpret_cast<const float *>(base) + e, f); break;
+        case DT_F16: load_vec<__half, V>(reinterpret_cast<const __half *>(base) + e, f); break;
+        case DT_BF16: load_vec<__nv_bfloat16, V>(reinterpret_cast<const __nv_bfloat16 *>(base) + e, f); break;
+        case DT_I32: load_vec<int32_t, V>(reinterpret_cast<const int32_t *>(base) + e, f); break;
+        case DT_U32: load_vec<uint32_t, V>(reinterpret_cast<const uint32_t *>(base) + e, f); break;
+        case DT_I8: load_vec<int8_t, V>(reinterpret_cast<const int8_t *>(base) + e, f); break;
+        default: load_vec<uint8_t, V>(reinterpret_cast<const uint8_t *>(base) + e, f); break;
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_any(void *base, int dt, int64_t e, const float (&f)[V]) {
+    switch (dt) {
+        case DT_F32: store_vec<float, V>(reinterpret_cast<float *>(base) + e, f); break;
+        case DT_F16: store_vec<__half, V>(reinterpret_cast<__half *>(base) + e, f); break;
+        case DT_BF16: store_vec<__nv_bfloat16, V>(reinterpret_cast<__nv_bfloat16 *>(base) + e, f); break;
+        case DT_I32: store_vec<int32_t, V>(reinterpret_cast<int32_t *>(base) + e, f); break;
+        case DT_U32: store_vec<uint32_t, V>(reinterpret_cast<uint32_t *>(base) + e, f); break;
+        case DT_I8: store_vec<int8_t, V>(reinterpret_cast<int8_t *>(base) + e, f); break;
+        default: store_vec<uint8_t, V>(reinterpret_cast<uint8_t *>(base) + e, f); break;
+    }
+}
+
+template <int V>
+__device__ void ewise_convert(const EwiseArgs &a, int p, int P) {
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x;
+    const int64_t nth = (int64_t)P * kThreads;
+    const int idt = a.in0.dtype, odt = a.out.dtype;
+    if (a.flat) {
+        for (int64_t u = tid; u < a.n_units; u += nth) {
+            float x[V];
+            load_any<V>(a.in0.ptr, idt, u * V, x);
+            store_any<V>(a.out.ptr, odt, u * V, x);
+        }
+        return;
+    }
+    const int64_t WV = (a.out.shape[3] + V - 1) / V;
+    const int64_t H = a.out.shape[2], C = a.out.shape[1];
+    for (int64_t u = tid; u < a.n_units; u += nth) {
+        int64_t wv = u % WV, row = u / WV;
+        int64_t h = row % H;
+        row /= H;
+        int64_t c = row % C, n = row / C;
+        float x[V];
+        load_any<V>(a.in0.ptr, idt, tref_off(a.in0, n, c, h, wv * V), x);
+        store_any<V>(a.out.ptr, odt, tref_off(a.out, n, c, h, wv * V), x);
+    }
+}
+
+__device__ void run_ewise(const EwiseArgs &a, int p, int P) {
+    const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
+    if (a.op == EW_COPY && idt == a.out.dtype) {
+        const int es = (idt == DT_F32 || idt == DT_I32 || idt == DT_U32) ? 4 : (idt == DT_F16 || idt == DT_BF16) ? 2 : 1;
+        ewise_bytes(a, p, P, es);
+        return;
+    }
+    if (a.op == EW_CAST || idt != a.out.dtype) {
+        // vector mode moves 4 elements per access (16 bytes of the widest type)
+        if (a.vec > 1) ewise_convert<4>(a, p, P);
+        else ewise_convert<1>(a, p, P);
+        return;
+    }
+    switch (idt) {
+        case DT_F32: ewise_typed<float, float>(a, p, P); break;
+        case DT_F16: ewise_typed<__half, __half>(a, p, P); break;
+        case DT_BF16: ewise_typed<__nv_bfloat16, __nv_bfloat16>(a, p, P); break;
+        default: break;
+    }
+}
+
+}  // namespace arkb

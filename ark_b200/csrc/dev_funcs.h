@@ -1,0 +1,19 @@
+// Device entry points of the op implementations. Each group lives in its own
+// translation unit (relocatable device code) so the compiler works on them
+// separately and in parallel.
+#pragma once
+#include "dev_common.cuh"
+
+namespace arkb {
+struct GemmPipe;
+__device__ void run_ewise(const EwiseArgs &a, int p, int P);
+__device__ void run_reduce(const ReduceArgs &a, int p, int P);
+__device__ void run_rowop(const RowOpArgs &a, int p, int P);
+__device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem);
+__device__ void run_embed(const EmbedArgs &a, int p, int P);
+__device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
+                         int stage_idx, unsigned long long spin_limit);
+__device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
+__device__ void run_put(const PutArgs &a, int p, int P);
+__device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no);
+}  // namespace arkb

@@ -1,0 +1,170 @@
+// Tiled matmul on the 5th-generation tensor cores (sm_100a).
+//
+// Replaces the reference's matmul -> gemm_cutlass -> CUTLASS 2.x mma.sync path
+// (ark/include/kernels/matmul.h:36-115, gemm_cutlass.h:900-965). One CTA runs a
+// list of 128 x tile_n output tiles with three warp roles:
+//   warp 4      : TMA producer  — cp.async.bulk.tensor loads of A and B
+//                 k-blocks (64 elements of K) into a 4-deep shared-memory ring;
+//   warp 5      : MMA issuer    — one elected lane issues tcgen05.mma
+//                 (M=128, N=tile_n, K=16, fp32 accumulators in TMEM);
+//   warps 0..3  : epilogue      — tcgen05.ld of the accumulator (each warp owns
+//                 the 32 TMEM lanes of its quarter), activation / bias, one
+//                 rounding to the storage type, 128-bit stores.
+// Two accumulators (2 x 256 TMEM columns) let the epilogue of tile i overlap
+// the mainloop of tile i+1. No cluster launch, no multicast: every CTA loads
+// its own operands, so the same code runs on any number of GPUs.
+//
+// Every wait is bounded; on expiry the CTA records a status and leaves.
+#pragma once
+#include "dev_common.cuh"
+#include "dev_funcs.h"
+
+namespace arkb {
+
+constexpr int kGemmStages = 4;
+constexpr int kGemmBK = 64;                       // K elements per stage (128 bytes of fp16/bf16)
+constexpr int kGemmTileM = 128;
+constexpr int kGemmABytes = kGemmTileM * kGemmBK * 2;   // 16 KiB
+constexpr int kGemmBBytes = 256 * kGemmBK * 2;          // 32 KiB (tile_n up to 256)
+constexpr int kGemmStageBytes = kGemmABytes + kGemmBBytes;
+constexpr int kGemmSmemBytes = kGemmStages * kGemmStageBytes;  // 192 KiB
+constexpr int kTmemCols = 512;
+constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5;
+
+struct GemmPipe {
+    unsigned long long full[kGemmStages];
+    unsigned long long empty[kGemmStages];
+    unsigned long long acc_full[2];
+    unsigned long long acc_empty[2];
+    unsigned int kb_count;    // k-blocks this CTA has pushed through the ring since launch
+    unsigned int tile_count;  // tiles this CTA has finished since launch
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(void *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void *bar) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void *bar, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// Bounded wait on an mbarrier phase; false when `limit_ns` nanoseconds ran out.
+__device__ __forceinline__ bool mbar_wait(void *bar, uint32_t parity, unsigned long long limit_ns) {
+    const uint32_t a = smem_u32(bar);
+    unsigned long long t0 = 0;
+    for (unsigned long long i = 1;; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 255) == 0) {
+            const unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit_ns) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *tm, void *bar, int c0, int c1, int c2,
+                                            int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+// Bits: [0,14) start>>4, [16,30) leading byte offset>>4, [32,46) stride byte
+// offset>>4, [46,48) version = 1, [61,64) layout = 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, A/B fp16 or bf16.
+__device__ __forceinline__ uint32_t umma_idesc(int bf16, int a_mn, int b_mn, int n) {
+    uint32_t d = 0;
+    d |= 1u << 4;                        // D format: F32
+    d |= (uint32_t)(bf16 ? 1 : 0) << 7;  // A format
+    d |= (uint32_t)(bf16 ? 1 : 0) << 10; // B format
+    d |= (uint32_t)(a_mn ? 1 : 0) << 15; // A major: 0 K, 1 MN
+    d |= (uint32_t)(b_mn ? 1 : 0) << 16; // B major
+    d |= (uint32_t)(n >> 3) << 17;       // N / 8
+    d |= (uint32_t)(kGemmTileM >> 4) << 24;  // M / 16
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "  tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(void *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// TMEM allocation for the whole CTA lifetime (one warp executes these).
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, int cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void gemm_pipe_init(GemmPipe *pp) {
+    for (int s = 0; s < kGemmStages; ++s) {
+        mbar_init(&pp->full[s], 1);
+        mbar_init(&pp->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+        mbar_init(&pp->acc_full[a], 1);
+        mbar_init(&pp->acc_empty[a], kEpiWarps);
+    }
+    pp->kb_count = 0;
+    pp->tile_count = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+}  // namespace arkb

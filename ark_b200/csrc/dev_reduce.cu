@@ -1,0 +1,290 @@
+// Reductions and fused row operators.
+//
+// reduce along the last axis  : one warp per row, 128-bit loads, fp32
+//                               accumulation, shuffle tree (replaces WwiseReduce,
+//                               ark/include/kernels/reduce.h:341-444);
+// reduce along another axis   : each thread owns a vector of consecutive
+//                               outputs along W and walks the axis (replaces
+//                               EwiseReduce, reduce.h:196-338);
+// rmsnorm / layernorm / softmax: single-pass row kernels standing in for the
+//                               op chains the reference composes in Python
+//                               (python/ark/ops.py:491-513,
+//                               examples/llama/model.py:92-99).
+#include <type_traits>
+
+#include "dev_common.cuh"
+#include "dev_funcs.h"
+
+namespace arkb {
+
+template <typename T, int V>
+__device__ void reduce_last_axis(const ReduceArgs &a, int p, int P) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int WPC = kThreads / 32;
+    const int64_t W = a.in.shape[3];
+    const int64_t H = a.in.shape[2], C = a.in.shape[1];
+    const int64_t rows = (int64_t)a.in.shape[0] * C * H;
+    const T *in = reinterpret_cast<const T *>(a.in.ptr);
+    T *out = reinterpret_cast<T *>(a.out.ptr);
+    for (int64_t row = (int64_t)p * WPC + warp; row < rows; row += (int64_t)P * WPC) {
+        int64_t h = row % H, r = row / H;
+        int64_t c = r % C, n = r / C;
+        const T *src = in + tref_off(a.in, n, c, h, 0);
+        float acc = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        const int64_t nv = W / V;
+        constexpr int U = 4;
+        for (int64_t v0 = lane; v0 < nv; v0 += 32 * U) {
+            float x[U][V];
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (v0 + j * 32 < nv) load_vec<T, V>(src + (v0 + j * 32) * V, x[j]);
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (v0 + j * 32 < nv) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, x[j][i]) : acc + x[j][i];
+                }
+        }
+        for (int64_t w = nv * V + lane; w < W; w += 32) {
+            float x = to_f32(src[w]);
+            acc = (a.op == RD_MAX) ? fmaxf(acc, x) : acc + x;
+        }
+        acc = (a.op == RD_MAX) ? warp_max(acc) : warp_sum(acc);
+        if (a.op == RD_MEAN) acc /= (float)W;
+        if (lane == 0) out[tref_off(a.out, n, c, h, 0)] = from_f32<T>(acc);
+    }
+}
+
+template <typename T, int V>
+__device__ void reduce_other_axis(const ReduceArgs &a, int p, int P) {
+    const int ax = a.axis;
+    int32_t osh[4] = {a.in.shape[0], a.in.shape[1], a.in.shape[2], a.in.shape[3]};
+    const int64_t len = osh[ax];
+    osh[ax] = 1;
+    const int64_t WV = (osh[3] + V - 1) / V;
+    const int64_t units = (int64_t)osh[0] * osh[1] * osh[2] * WV;
+    const T *in = reinterpret_cast<const T *>(a.in.ptr);
+    T *out = reinterpret_cast<T *>(a.out.ptr);
+    const int64_t astr = a.in.stride[ax];
+    for (int64_t u = (int64_t)p * kThreads + threadIdx.x; u < units; u += (int64_t)P * kThreads) {
+        int64_t wv = u % WV, r = u / WV;
+        int64_t h = r % osh[2];
+        r /= osh[2];
+        int64_t c = r % osh[1], n = r / osh[1];
+        const T *src = in + tref_off(a.in, n, c, h, wv * V);
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        for (int64_t k = 0; k < len; ++k) {
+            float x[V];
+            load_vec<T, V>(src + k * astr, x);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? fmaxf(acc[i], x[i]) : acc[i] + x[i];
+        }
+        if (a.op == RD_MEAN) {
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] /= (float)len;
+        }
+        store_vec<T, V>(out + tref_off(a.out, n, c, h, wv * V), acc);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void reduce_typed(const ReduceArgs &a, int p, int P) {
+    constexpr int V = 16 / sizeof(T);
+    if (a.axis == 3) {
+        if (a.vec > 1) reduce_last_axis<T, V>(a, p, P);
+        else reduce_last_axis<T, 1>(a, p, P);
+    } else {
+        if (a.vec > 1) reduce_other_axis<T, V>(a, p, P);
+        else reduce_other_axis<T, 1>(a, p, P);
+    }
+}
+
+__device__ void run_reduce(const ReduceArgs &a, int p, int P) {
+    switch (a.in.dtype) {
+        case DT_F32: reduce_typed<float>(a, p, P); break;
+        case DT_F16: reduce_typed<__half>(a, p, P); break;
+        case DT_BF16: reduce_typed<__nv_bfloat16>(a, p, P); break;
+        default: break;
+    }
+}
+
+// ---- fused row operators --------------------------------------------------------
+// One warp per row. Pass 1 accumulates the row statistics in fp32, pass 2
+// re-reads the row (it is still in L2) and writes the result: HBM sees one
+// read and one write per element.
+template <typename T>
+__device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int WPC = kThreads / 32;
+    constexpr int U = 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t cols = a.cols;
+    const int64_t nv = cols / V;  // host guarantees cols % V == 0 and 16-byte aligned rows
+    const T *wgt = reinterpret_cast<const T *>(a.weight);
+    const int op = a.op;
+    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    for (int64_t row = (int64_t)p * WPC + warp; row < a.rows; row += (int64_t)P * WPC) {
+        const T *src = reinterpret_cast<const T *>(a.in) + row * a.in_ld;
+        T *dst = reinterpret_cast<T *>(a.out) + row * a.out_ld;
+        if (a.residual) {
+            // x := x + residual, rounded to the storage type and kept (res_out) for the next block
+            const T *res = reinterpret_cast<const T *>(a.residual) + row * a.in_ld;
+            T *rout = reinterpret_cast<T *>(a.res_out) + row * a.in_ld;
+            for (int64_t v = lane; v < nv; v += 32) {
+                float f[V], g[V];
+                load_vec<T, V>(src + v * V, f);
+                load_vec<T, V>(res + v * V, g);
+#pragma unroll
+                for (int i = 0; i < V; ++i) f[i] += g[i];
+                store_vec<T, V>(rout + v * V, f);
+            }
+            __syncwarp();
+            src = rout;
+        }
+        float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
+        for (int64_t v0 = lane; v0 < nv; v0 += 32 * U) {
+            float x[U][V];
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (v0 + j * 32 < nv) load_vec<T, V>(src + (v0 + j * 32) * V, x[j]);
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (v0 + j * 32 < nv) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) {
+                        const float e = x[j][i] * scale;
+                        s1 += e;
+                        s2 += e * e;
+                        mx = fmaxf(mx, e);
+                    }
+                }
+        }
+        float mul = 1.0f, sub = 0.0f;
+        if (op == RO_RMSNORM) {
+            s2 = warp_sum(s2);
+            mul = 1.0f / sqrtf(s2 / (float)cols + a.eps);
+        } else if (op == RO_LAYERNORM) {
+            s1 = warp_sum(s1);
+            const float mean = s1 / (float)cols;
+            float var = 0.0f;
+            for (int64_t v = lane; v < nv; v += 32) {
+                float f[V];
+                load_vec<T, V>(src + v * V, f);
+#pragma unroll
+                for (int i = 0; i < V; ++i) var += (f[i] - mean) * (f[i] - mean);
+            }
+            var = warp_sum(var);
+            mul = 1.0f / sqrtf(var / (float)cols + a.eps);
+            sub = mean;
+        } else {
+            mx = warp_max(mx);
+            float se = 0.0f;
+            for (int64_t v = lane; v < nv; v += 32) {
+                float f[V];
+                load_vec<T, V>(src + v * V, f);
+#pragma unroll
+                for (int i = 0; i < V; ++i) se += expf(f[i] * scale - mx);
+            }
+            se = warp_sum(se);
+            mul = 1.0f / se;
+        }
+        for (int64_t v = lane; v < nv; v += 32) {
+            float f[V];
+            load_vec<T, V>(src + v * V, f);
+            if (op == RO_SOFTMAX) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) f[i] = expf(f[i] * scale - mx) * mul;
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; ++i) f[i] = (f[i] - sub) * mul;
+                if (wgt) {
+                    float g[V];
+                    load_vec<T, V>(wgt + v * V, g);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) f[i] *= g[i];
+                }
+            }
+            store_vec<T, V>(dst + v * V, f);
+        }
+    }
+}
+
+__device__ void run_rowop(const RowOpArgs &a, int p, int P) {
+    switch (a.dtype) {
+        case DT_F32: rowop_typed<float>(a, p, P); break;
+        case DT_F16: rowop_typed<__half>(a, p, P); break;
+        case DT_BF16: rowop_typed<__nv_bfloat16>(a, p, P); break;
+        default: break;
+    }
+}
+
+// ---- transpose / embedding ---------------------------------------------------------
+// 4-D permutation (ark/include/kernels/transpose.h). When the innermost dim
+// stays innermost the copy is vectorised along it; otherwise a 32x32 shared
+// memory tile turns strided reads into coalesced ones.
+template <int ES>
+__device__ void transpose_es(const TransposeArgs &a, int p, int P, char *smem) {
+    typedef typename std::conditional<ES == 4, uint32_t, typename std::conditional<ES == 2, uint16_t, uint8_t>::type>::type E;
+    const E *in = reinterpret_cast<const E *>(a.in.ptr);
+    E *out = reinterpret_cast<E *>(a.out.ptr);
+    const int64_t O0 = a.out.shape[0], O1 = a.out.shape[1], O2 = a.out.shape[2], O3 = a.out.shape[3];
+    int64_t is[4];  // input stride seen from each output dim
+    for (int i = 0; i < 4; ++i) is[i] = a.in.stride[a.perm[i]];
+    if (a.perm[3] == 3) {
+        constexpr int V = 16 / ES;
+        const bool vec = (O3 % V == 0) && a.out.contiguous == 2;  // host: 2 = rows 16-byte aligned on both sides
+        if (vec) {
+            const int64_t WV = O3 / V, units = O0 * O1 * O2 * WV;
+            for (int64_t u = (int64_t)p * kThreads + threadIdx.x; u < units; u += (int64_t)P * kThreads) {
+                int64_t wv = u % WV, r = u / WV;
+                int64_t i2 = r % O2;
+                r /= O2;
+                int64_t i1 = r % O1, i0 = r / O1;
+                const uint4 v = *reinterpret_cast<const uint4 *>(in + i0 * is[0] + i1 * is[1] + i2 * is[2] + wv * V);
+                *reinterpret_cast<uint4 *>(out + tref_off(a.out, i0, i1, i2, wv * V)) = v;
+            }
+            return;
+        }
+    }
+    // generic: one element per thread, writes coalesced
+    const int64_t total = O0 * O1 * O2 * O3;
+    for (int64_t i = (int64_t)p * kThreads + threadIdx.x; i < total; i += (int64_t)P * kThreads) {
+        int64_t i3 = i % O3, r = i / O3;
+        int64_t i2 = r % O2;
+        r /= O2;
+        int64_t i1 = r % O1, i0 = r / O1;
+        out[tref_off(a.out, i0, i1, i2, i3)] = in[i0 * is[0] + i1 * is[1] + i2 * is[2] + i3 * is[3]];
+    }
+}
+
+__device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem) {
+    const int dt = a.in.dtype;
+    if (dt == DT_F32 || dt == DT_I32 || dt == DT_U32) transpose_es<4>(a, p, P, smem);
+    else if (dt == DT_F16 || dt == DT_BF16) transpose_es<2>(a, p, P, smem);
+    else transpose_es<1>(a, p, P, smem);
+}
+
+// Row gather (ark/include/kernels/embedding.h; host op ark/ops/ops_embedding.cpp:37-70):
+// one warp per index, negative indices wrap.
+__device__ void run_embed(const EmbedArgs &a, int p, int P) {
+    constexpr int WPC = kThreads / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t row_bytes = a.emb_dim * a.esize;
+    for (int64_t i = (int64_t)p * WPC + warp; i < a.n_idx; i += (int64_t)P * WPC) {
+        int64_t r = a.idx[i];
+        if (r < 0) r += a.num_emb;
+        const char *src = reinterpret_cast<const char *>(a.weight) + r * a.w_ld * a.esize;
+        char *dst = reinterpret_cast<char *>(a.out) + i * a.out_ld * a.esize;
+        if (((row_bytes | (a.w_ld * a.esize) | (a.out_ld * a.esize)) & 15) == 0 &&
+            ((reinterpret_cast<uintptr_t>(a.weight) | reinterpret_cast<uintptr_t>(a.out)) & 15) == 0) {
+            for (int64_t b = lane * 16; b < row_bytes; b += 32 * 16)
+                *reinterpret_cast<uint4 *>(dst + b) = *reinterpret_cast<const uint4 *>(src + b);
+        } else {
+            for (int64_t b = lane; b < row_bytes; b += 32) dst[b] = src[b];
+        }
+    }
+}
+
+}  // namespace arkb

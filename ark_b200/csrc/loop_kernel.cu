@@ -1,0 +1,157 @@
+// The persistent loop kernel: one CTA per processor walks the stage list of a
+// lowered plan, once per iteration, and in loop mode stays resident waiting
+// for run requests on a host-mapped flag. Counterpart of the reference's
+// generated ark_loop_kernel / ark_kernel
+// (ark/include/kernels/kernel_template.in:40-78).
+#include "dev_comm.cuh"
+#include "dev_common.cuh"
+#include "dev_funcs.h"
+#include "dev_gemm.cuh"
+#include "loop_kernel.h"
+
+namespace arkb {
+
+__device__ __forceinline__ bool in_range(const Stage &S, int cta, int &p, int &Pn) {
+    const int b = S.proc_b, e = S.proc_e, s = S.proc_s;
+    Pn = (e - b + s - 1) / s;
+    if (cta < b || cta >= e) return false;
+    const int d = cta - b;
+    if (d % s) return false;
+    p = d / s;
+    return true;
+}
+
+// One pass over the stage list. iter_local counts iterations since this
+// launch (barrier phases); iter_no is the 1-based iteration number over the
+// executor's life (cross-rank epochs and channel flags).
+__device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, GemmPipe *pipe, CtaCtl *ctl,
+                                         unsigned long long iter_local, unsigned long long iter_no) {
+    const int cta = blockIdx.x;
+    for (int s = 0; s < P.n_stages; ++s) {
+        const Stage &S = P.stages[s];
+        int p = 0, Pn = 1;
+        if (!in_range(S, cta, p, Pn)) continue;
+        __syncthreads();
+        if (ctl->abort) return;
+        switch (S.kind) {
+            case SK_SYNC: {
+                const unsigned long long k = iter_local * (unsigned long long)P.syncs_per_iter[S.sync_group] + S.sync_ord;
+                if (!grid_barrier(&P.state->barrier[S.sync_group], k * (unsigned long long)S.sync_count, P.spin_limit,
+                                  ctl, P.state, s))
+                    return;
+                break;
+            }
+            case SK_EWISE: run_ewise(S.ew, p, Pn); break;
+            case SK_REDUCE: run_reduce(S.rd, p, Pn); break;
+            case SK_ROWOP: run_rowop(S.ro, p, Pn); break;
+            case SK_GEMM: run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit); break;
+            case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
+            case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;
+            case SK_EMBED: run_embed(S.em, p, Pn); break;
+            case SK_PUT: run_put(S.put, p, Pn); break;
+            case SK_SIGNAL: if (p == 0) run_signal(P, S.sg, iter_no); break;
+            case SK_WAITFLAG: if (p == 0) run_wait(P, S.wt, iter_no, ctl, s); break;
+            case SK_PEERSYNC:
+                if (p == 0)
+                    run_peersync(P, (iter_no - 1) * (unsigned long long)P.peersyncs_per_iter + S.ps.ord, ctl, s);
+                break;
+            case SK_ALLREDUCE: run_allreduce(P, S.ar, p, Pn, iter_no); break;
+            default: break;
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const __grid_constant__ LaunchParams P) {
+    extern __shared__ __align__(1024) char dyn_smem[];
+    __shared__ CtaCtl ctl;
+    __shared__ GemmPipe pipe;
+    // dynamic shared memory base rounded up to 1 KiB (128-byte swizzle atoms)
+    char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~(uintptr_t)1023);
+
+    if (threadIdx.x == 0) {
+        ctl.abort = 0;
+        ctl.run_iters = 0;
+        gemm_pipe_init(&pipe);
+    }
+    if (threadIdx.x < 32) tmem_alloc(&ctl.tmem_base, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+
+    DeviceState *st = P.state;
+    const int whole = kMaxSyncGroups - 1;  // barrier counter reserved for the run protocol
+    unsigned long long whole_k = 0;        // whole-grid barriers passed since launch
+    unsigned long long iter_local = 0;
+    unsigned long long iter_no = st->iter_total;  // stable: only advanced after the last barrier of a run
+
+    for (;;) {
+        int iters = P.iters;
+        if (P.loop_mode) {
+            if (blockIdx.x == 0 && threadIdx.x == 0) {
+                const unsigned long long t0 = globaltimer();
+                int v;
+                for (;;) {
+                    v = *P.run_flag;
+                    if (v != 0) break;
+                    if (globaltimer() - t0 > P.idle_limit_ns) {
+                        v = -2;  // idle for too long: leave, the host relaunches on the next run
+                        break;
+                    }
+                    __nanosleep(200);
+                }
+                st->run_iters = v;
+                __threadfence();
+            }
+            ++whole_k;
+            if (!grid_barrier(&st->barrier[whole], whole_k * gridDim.x, P.spin_limit, &ctl, st, -1)) break;
+            iters = *reinterpret_cast<volatile int32_t *>(&st->run_iters);
+            if (iters < 0) {
+                if (iters == -2 && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(&st->status, ST_OK, ST_IDLE_EXIT);
+                break;
+            }
+        }
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->t_begin = globaltimer();
+        bool ok = true;
+        for (int i = 0; i < iters && ok; ++i) {
+            run_body(P, smem, &pipe, &ctl, iter_local, iter_no + 1);
+            ++whole_k;
+            ok = grid_barrier(&st->barrier[whole], whole_k * gridDim.x, P.spin_limit, &ctl, st, -2);
+            ++iter_local;
+            ++iter_no;
+        }
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            st->t_end = globaltimer();
+            st->iter_total = iter_no;
+            __threadfence_system();
+            if (P.loop_mode) *P.run_flag = 0;
+        }
+        if (!ok || !P.loop_mode) break;
+    }
+
+    __syncthreads();
+    if (ctl.abort && threadIdx.x == 0) {
+        // give bulk copies still in flight time to land before the CTA's shared memory goes away
+        for (int i = 0; i < 64; ++i) __nanosleep(2000);
+        if (P.loop_mode && blockIdx.x == 0) *P.run_flag = 0;
+    }
+    __syncthreads();
+    tc_fence_after();
+    if (threadIdx.x < 32) tmem_dealloc(ctl.tmem_base, kTmemCols);
+}
+
+}  // namespace arkb
+
+// ---- host-side launch shim (keeps <<<>>> syntax inside the .cu file) ----------------
+namespace arkb {
+size_t loop_kernel_smem_bytes() { return kGemmSmemBytes + 1024; }
+
+cudaError_t loop_kernel_prepare() {
+    return cudaFuncSetAttribute(arkb_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)loop_kernel_smem_bytes());
+}
+
+cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream) {
+    arkb_loop_kernel<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
+    return cudaGetLastError();
+}
+}  // namespace arkb

@@ -1,0 +1,11 @@
+// Host-visible entry points of the loop kernel translation unit.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "program.h"
+
+namespace arkb {
+size_t loop_kernel_smem_bytes();
+cudaError_t loop_kernel_prepare();
+cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream);
+}  // namespace arkb

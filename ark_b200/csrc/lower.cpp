@@ -1,0 +1,698 @@
+// Plan -> stage program. This is the engine's code generator: where the
+// reference emits CUDA source per plan (ark/codegen.cpp:79-429) this emits a
+// table of stages for the prebuilt sm_100a loop kernel.
+//
+// What is kept from the plan: the processor ranges (which CTAs run what, and
+// therefore which groups run concurrently), the order of processor groups,
+// the barrier rule between them (codegen.cpp:109-158) and the task ranges.
+// What is not kept: the mapping of task ids to warps/shared-memory slots
+// inside a CTA (WarpRange, SramRange, NumWarps, SramBytes are validated and
+// otherwise ignored) — here a whole CTA works on one stage at a time and an
+// op's work is split over the CTAs of its range by the op's own kernel.
+#include <algorithm>
+#include <cstring>
+#include <set>
+#include <sstream>
+
+#include "plan.hpp"
+
+namespace arkb {
+
+namespace {
+
+struct Lowerer {
+    const Plan &plan;
+    const Layout &lay;
+    const LowerEnv &env;
+    Program prog;
+    std::map<std::tuple<int64_t, int64_t, int64_t>, int> sync_ids;
+    int oneshot_ord = 0;
+
+    Lowerer(const Plan &p, const Layout &l, const LowerEnv &e) : plan(p), lay(l), env(e) {}
+
+    // ---- helpers ---------------------------------------------------------------
+    char *tensor_ptr(const TensorDesc &t) const {
+        const BufferInfo &b = lay.buffers.at(t.buffer_id);
+        if (!b.resolved) throw Error(E_PLAN, "buffer " + std::to_string(b.id) + " has no address");
+        int r = (b.rank == -1) ? env.rank : b.rank;
+        if (r < 0 || r >= env.nranks || !env.arena[r]) throw Error(E_PLAN, "tensor on unmapped rank " + std::to_string(r));
+        int64_t es[4], org;
+        t.elem_strides(es, org);
+        return env.arena[r] + b.offset + (size_t)org * dtype_size(t.dtype);
+    }
+
+    // View of `t` broadcast to the 4-D shape `osh` (NumPy rules on dims4).
+    TRef make_ref(const TensorDesc &t, const std::vector<int64_t> *osh = nullptr) const {
+        TRef r;
+        std::memset(&r, 0, sizeof(r));
+        r.ptr = tensor_ptr(t);
+        r.dtype = t.dtype;
+        int64_t es[4], org;
+        t.elem_strides(es, org);
+        auto sh = t.shape4();
+        for (int i = 0; i < 4; ++i) {
+            int64_t target = osh ? (*osh)[i] : sh[i];
+            if (sh[i] != target && sh[i] != 1) throw Error(E_MODEL, "shapes do not broadcast");
+            r.shape[i] = (int32_t)target;
+            r.stride[i] = (sh[i] == 1 && target != 1) ? 0 : es[i];
+            if (sh[i] == 1) r.stride[i] = (target == 1) ? es[i] : 0;
+        }
+        r.contiguous = t.dense() ? 1 : 0;
+        return r;
+    }
+
+    static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+    Stage new_stage(int kind, const Range &proc) {
+        Stage s;
+        std::memset(&s, 0, sizeof(s));
+        s.kind = kind;
+        s.proc_b = (int32_t)proc.b;
+        s.proc_e = (int32_t)proc.e;
+        s.proc_s = (int32_t)proc.s;
+        return s;
+    }
+    void push(const Stage &s, const std::string &note) {
+        prog.stages.push_back(s);
+        std::ostringstream os;
+        os << "[" << s.proc_b << "," << s.proc_e << (s.proc_s != 1 ? "," + std::to_string(s.proc_s) : "") << ") " << note;
+        prog.notes.push_back(os.str());
+    }
+
+    void emit_sync(const Range &r) {
+        if (r.count() <= 0) return;
+        auto key = std::make_tuple(r.b, r.e, r.s);
+        auto it = sync_ids.find(key);
+        int id;
+        if (it == sync_ids.end()) {
+            id = (int)sync_ids.size();
+            if (id >= kMaxSyncGroups - 1) throw Error(E_UNSUPPORTED, "too many distinct processor ranges need a barrier");
+            sync_ids[key] = id;
+        } else {
+            id = it->second;
+        }
+        Stage s = new_stage(SK_SYNC, r);
+        s.sync_group = id;
+        s.sync_count = (int32_t)r.count();
+        s.sync_ord = ++prog.syncs_per_iter[id];
+        push(s, "sync group " + std::to_string(id) + " #" + std::to_string(s.sync_ord));
+    }
+
+    static bool full_range(const Range &tr, int64_t num_tasks) { return tr.b == 0 && tr.s == 1 && tr.e >= num_tasks; }
+
+    int64_t num_tasks(const OpDesc &op) const {
+        if (op.config.is_object() && op.config.contains("NumTasks")) return op.config.at("NumTasks").as_int();
+        return 1;
+    }
+
+    // ---- elementwise -----------------------------------------------------------
+    static int ewise_code(const std::string &t) {
+        static const std::map<std::string, int> m = {
+            {"Copy", EW_COPY}, {"Gelu", EW_GELU}, {"Exp", EW_EXP}, {"Relu", EW_RELU}, {"Rsqrt", EW_RSQRT},
+            {"Sigmoid", EW_SIGMOID}, {"Sqrt", EW_SQRT}, {"Cast", EW_CAST}, {"Add", EW_ADD}, {"Sub", EW_SUB},
+            {"Mul", EW_MUL}, {"Div", EW_DIV}, {"ScalarAssign", EW_SCALAR_ASSIGN}, {"ScalarAdd", EW_SCALAR_ADD},
+            {"ScalarMul", EW_SCALAR_MUL}, {"Rope", EW_ROPE}, {"Silu", EW_SILU}};
+        auto it = m.find(t);
+        return it == m.end() ? -1 : it->second;
+    }
+
+    void lower_ewise(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        const int code = ewise_code(op.type);
+        const bool binary = (code >= EW_ADD && code <= EW_DIV) || code == EW_ROPE;
+        const bool has_in = code != EW_SCALAR_ASSIGN;
+        if (!full_range(tg.task_range, num_tasks(op)))
+            throw Error(E_UNSUPPORTED, op.type + ": partial TaskRange is supported for Matmul only");
+        const TensorDesc &out = op.results.at(0);
+        if ((has_in && op.reads.size() < (binary ? 2u : 1u))) throw Error(E_MODEL, op.type + ": missing operand");
+        Stage s = new_stage(SK_EWISE, proc);
+        EwiseArgs &a = s.ew;
+        auto osh = out.shape4();
+        a.out = make_ref(out);
+        if (has_in) a.in0 = make_ref(op.reads[0], &osh);
+        if (binary) a.in1 = make_ref(op.reads[1], &osh);
+        a.op = code;
+        if (code == EW_SCALAR_ASSIGN) a.scalar = (float)op.arg_float("Value");
+        if (code == EW_SCALAR_ADD || code == EW_SCALAR_MUL) a.scalar = (float)op.arg_float("Factor");
+        const int idt = has_in ? op.reads[0].dtype : out.dtype;
+        if (binary && op.reads[1].dtype != idt) throw Error(E_MODEL, op.type + ": operand data types differ");
+        const bool convert = (code == EW_CAST) || idt != out.dtype;
+        if (!convert && code != EW_COPY && !(idt == DT_F32 || idt == DT_F16 || idt == DT_BF16))
+            throw Error(E_UNSUPPORTED, op.type + ": arithmetic on integer tensors is not supported");
+        int V = convert ? 4 : (int)(16 / dtype_size(out.dtype));
+        if (code == EW_COPY && !convert) V = (int)(16 / dtype_size(out.dtype));
+        const int64_t nelem = out.nelems();
+        bool same = has_in ? (op.reads[0].shape4() == osh) : true;
+        if (binary) same = same && (op.reads[1].shape4() == osh);
+        bool dense = out.dense() && (!has_in || op.reads[0].dense()) && (!binary || op.reads[1].dense());
+        auto ptr_ok = [&](const TRef &r, int dt) {
+            size_t bytes = (size_t)V * dtype_size(dt);
+            size_t al = bytes > 16 ? 16 : bytes;
+            return (reinterpret_cast<uintptr_t>(r.ptr) % al) == 0;
+        };
+        a.flat = (same && dense) ? 1 : 0;
+        bool vec_ok = ptr_ok(a.out, out.dtype) && (!has_in || ptr_ok(a.in0, idt)) && (!binary || ptr_ok(a.in1, idt));
+        if (a.flat) {
+            vec_ok = vec_ok && (nelem % V == 0);
+        } else {
+            vec_ok = vec_ok && (osh[3] % V == 0);
+            auto strides_ok = [&](const TRef &r) {
+                if (r.stride[3] != 0 && r.stride[3] != 1) return false;
+                for (int i = 0; i < 3; ++i)
+                    if (r.stride[i] % V) return false;
+                return true;
+            };
+            vec_ok = vec_ok && strides_ok(a.out) && (!has_in || strides_ok(a.in0)) && (!binary || strides_ok(a.in1));
+        }
+        if (code == EW_ROPE && !vec_ok && (osh[3] % 2)) throw Error(E_MODEL, "Rope needs an even innermost dimension");
+        if (code == EW_ROPE && !vec_ok) {
+            // pairs must stay together: fall back to 2-element units via the scalar walker is not
+            // possible, so require vectorisable layouts
+            throw Error(E_UNSUPPORTED, "Rope needs 16-byte aligned rows");
+        }
+        a.vec = vec_ok ? V : 1;
+        if (a.flat) a.n_units = nelem / a.vec;
+        else a.n_units = osh[0] * osh[1] * osh[2] * ((osh[3] + a.vec - 1) / a.vec);
+        push(s, op.type + " " + op.name + " units=" + std::to_string(a.n_units) + " vec=" + std::to_string(a.vec) +
+                    (a.flat ? " flat" : " strided"));
+    }
+
+    // ---- reduce ------------------------------------------------------------------
+    void lower_reduce(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        if (!full_range(tg.task_range, num_tasks(op)))
+            throw Error(E_UNSUPPORTED, op.type + ": partial TaskRange is supported for Matmul only");
+        const TensorDesc &in = op.reads.at(0);
+        TensorDesc out = op.results.at(0);
+        int axis = (int)op.arg_int("Axis");
+        const bool keep = op.arg_bool("KeepDim");
+        const int nd = (int)in.shape.size();
+        if (axis < 0) axis += nd;
+        if (axis < 0 || axis >= nd) throw Error(E_MODEL, "invalid reduction axis");
+        if (!keep) {  // re-insert the reduced dim (ark/ops/ops_reduce.cpp:93-98)
+            out.shape.insert(out.shape.begin() + axis, 1);
+            out.strides.insert(out.strides.begin() + axis, 1);
+            out.offsets.insert(out.offsets.begin() + axis, 0);
+            out.padded.insert(out.padded.begin() + axis, 1);
+        }
+        const int ax4 = axis + 4 - nd;
+        if (in.dtype != out.dtype) throw Error(E_MODEL, "reduce: data types differ");
+        if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16))
+            throw Error(E_UNSUPPORTED, "reduce: floating-point tensors only");
+        Stage s = new_stage(SK_REDUCE, proc);
+        ReduceArgs &a = s.rd;
+        a.in = make_ref(in);
+        a.out = make_ref(out);
+        a.op = op.type == "ReduceSum" ? RD_SUM : op.type == "ReduceMax" ? RD_MAX : RD_MEAN;
+        a.axis = ax4;
+        const int V = (int)(16 / dtype_size(in.dtype));
+        bool ok = aligned16(a.in.ptr) && a.in.stride[3] == 1;
+        for (int i = 0; i < 3; ++i) ok = ok && (a.in.stride[i] % V == 0);
+        if (ax4 != 3) {
+            ok = ok && aligned16(a.out.ptr) && (in.shape4()[3] % V == 0) && a.out.stride[3] == 1;
+            for (int i = 0; i < 3; ++i) ok = ok && (a.out.stride[i] % V == 0);
+        }
+        a.vec = ok ? V : 1;
+        push(s, op.type + " " + op.name + " axis=" + std::to_string(ax4) + " vec=" + std::to_string(a.vec));
+    }
+
+    // ---- fused row operators (engine extensions) -----------------------------------------
+    void lower_rowop(const OpDesc &op, const Range &proc) {
+        const TensorDesc &in = op.reads.at(0);
+        const TensorDesc &out = op.results.at(0);
+        Stage s = new_stage(SK_ROWOP, proc);
+        RowOpArgs &a = s.ro;
+        a.op = op.type == "RMSNorm" ? RO_RMSNORM : op.type == "LayerNorm" ? RO_LAYERNORM : RO_SOFTMAX;
+        a.dtype = in.dtype;
+        auto sh = in.shape4();
+        auto ist = in.strides4();
+        auto ost = out.strides4();
+        a.cols = sh[3];
+        a.rows = sh[0] * sh[1] * sh[2];
+        a.in_ld = ist[3];
+        a.out_ld = ost[3];
+        // rows must be uniformly spaced: leading dims dense over H (and C, N)
+        auto rows_uniform = [&](const TensorDesc &t) {
+            auto s4 = t.shape4();
+            auto st4 = t.strides4();
+            auto of4 = t.offsets4();
+            (void)of4;
+            return (s4[0] * s4[1] == 1 || st4[2] == s4[2]) && (s4[0] == 1 || st4[1] == s4[1]);
+        };
+        if (!rows_uniform(in) || !rows_uniform(out)) throw Error(E_UNSUPPORTED, op.type + ": rows must be evenly spaced");
+        a.in = tensor_ptr(in);
+        a.out = tensor_ptr(out);
+        a.eps = op.has_arg("Eps") ? (float)op.arg_float("Eps") : 1e-5f;
+        a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
+        size_t ri = 1;
+        if (a.op == RO_RMSNORM && op.reads.size() > ri && op.reads[ri].nelems() == a.cols) a.weight = tensor_ptr(op.reads[ri++]);
+        if (op.has_arg("Residual") && op.arg_bool("Residual")) {
+            if (op.reads.size() <= ri || op.results.size() < 2) throw Error(E_MODEL, op.type + ": residual form needs 2 results");
+            a.residual = tensor_ptr(op.reads[ri]);
+            a.res_out = tensor_ptr(op.results[1]);
+        }
+        const int V = (int)(16 / dtype_size(in.dtype));
+        bool ok = (a.cols % V == 0) && aligned16(a.in) && aligned16(a.out) && (a.in_ld % V == 0) && (a.out_ld % V == 0);
+        if (a.weight) ok = ok && aligned16(a.weight);
+        if (a.residual) ok = ok && aligned16(a.residual) && aligned16(a.res_out);
+        if (!ok) throw Error(E_UNSUPPORTED, op.type + ": rows must be 16-byte aligned and a multiple of 16 bytes long");
+        if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16)) throw Error(E_UNSUPPORTED, op.type + ": floating-point only");
+        push(s, op.type + " " + op.name + " rows=" + std::to_string(a.rows) + " cols=" + std::to_string(a.cols));
+    }
+
+    // ---- matmul --------------------------------------------------------------------
+    struct MM {
+        int64_t M, N, K;
+        bool ta, tb;
+        int64_t bc, bn;
+    };
+
+    static int act_code(const std::string &t) {
+        if (t == "Relu") return ACT_RELU;
+        if (t == "Gelu") return ACT_GELU;
+        if (t == "Sigmoid") return ACT_SIGMOID;
+        if (t == "Silu") return ACT_SILU;
+        return -1;
+    }
+
+    // Number of ops of the plan (other than `except`) that read buffer `buf`.
+    int other_readers(int64_t buf, const OpDesc *except) const {
+        int n = 0;
+        for (auto &ti : plan.task_infos)
+            for (auto &op : ti.ops) {
+                if (&op == except) continue;
+                for (auto &t : op.reads)
+                    if (t.buffer_id == buf) ++n;
+            }
+        return n;
+    }
+
+    void lower_matmul(const OpDesc &op, const Range &proc, const TaskGroup &tg, int act, const TensorDesc *act_out) {
+        const TensorDesc &A = op.reads.at(0), &B = op.reads.at(1);
+        const TensorDesc &C = act_out ? *act_out : op.results.at(0);
+        const bool ta = op.arg_bool("TransposeInput");
+        // a 1-D `other` is a column vector [K]: the same memory as a K-major [1, K] matrix
+        const bool tb = B.shape.size() == 1 ? true : op.arg_bool("TransposeOther");
+        if (A.dtype != B.dtype || A.dtype != C.dtype) throw Error(E_MODEL, "Matmul: operand data types differ");
+        auto ash = A.shape4(), bsh = B.shape4(), csh = C.shape4();
+        auto ast = A.strides4(), bst = B.strides4(), cst = C.strides4();
+        // problem size (ark/ops/ops_matmul.cpp:13-42)
+        int64_t M = A.shape.size() == 1 ? 1 : ash[2], K = ash[3];
+        if (ta) std::swap(M, K);
+        int64_t N = bsh[3], K2 = bsh[2];
+        if (tb) std::swap(N, K2);
+        if (K != K2) throw Error(E_MODEL, "Matmul: inner dimensions mismatch");
+        if (csh[2] != M || csh[3] != N) throw Error(E_MODEL, "Matmul: output shape mismatch");
+        const int64_t bn = csh[0], bc = csh[1];
+        for (int d = 0; d < 2; ++d) {
+            if ((ash[d] != 1 && ash[d] != csh[d]) || (bsh[d] != 1 && bsh[d] != csh[d]))
+                throw Error(E_MODEL, "Matmul: batch dimensions do not broadcast");
+        }
+        const size_t es = dtype_size(A.dtype);
+        const int64_t lda = ast[3], ldb = bst[3], ldc = cst[3];
+        char *pa = tensor_ptr(A), *pb = tensor_ptr(B), *pc = tensor_ptr(C);
+        const bool tma_ok = (A.dtype == DT_F16 || A.dtype == DT_BF16) && aligned16(pa) && aligned16(pb) &&
+                            (lda * es) % 16 == 0 && (ldb * es) % 16 == 0 && (ast[2] * lda * es) % 16 == 0 &&
+                            (bst[2] * ldb * es) % 16 == 0 && env.encode_tmap;
+        const int64_t ntasks = num_tasks(op);
+        const bool full = full_range(tg.task_range, ntasks);
+        if (!tma_ok) {
+            if (!full) throw Error(E_UNSUPPORTED, "Matmul: partial TaskRange needs 16-byte aligned fp16/bf16 operands");
+            Stage s = new_stage(SK_GEMM_SIMT, proc);
+            GemmSimtArgs &g = s.gs;
+            g.A = pa; g.B = pb; g.C = pc;
+            g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+            g.a_stride_c = ash[1] > 1 ? ast[2] * ast[3] : 0;
+            g.a_stride_n = ash[0] > 1 ? ast[1] * ast[2] * ast[3] : 0;
+            g.b_stride_c = bsh[1] > 1 ? bst[2] * bst[3] : 0;
+            g.b_stride_n = bsh[0] > 1 ? bst[1] * bst[2] * bst[3] : 0;
+            g.c_stride_c = cst[2] * cst[3];
+            g.c_stride_n = cst[1] * cst[2] * cst[3];
+            g.M = (int32_t)M; g.N = (int32_t)N; g.K = (int32_t)K;
+            g.batch_c = (int32_t)bc; g.batch_n = (int32_t)bn;
+            g.trans_a = ta; g.trans_b = tb;
+            g.dtype = A.dtype; g.act = act;
+            push(s, "Matmul(simt) " + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" + std::to_string(K));
+            return;
+        }
+        Stage s = new_stage(SK_GEMM, proc);
+        GemmArgs &g = s.gm;
+        g.C = pc;
+        g.ldc = ldc;
+        g.c_stride_c = cst[2] * cst[3];
+        g.c_stride_n = cst[1] * cst[2] * cst[3];
+        g.M = (int32_t)M; g.N = (int32_t)N; g.K = (int32_t)K;
+        g.batch_c = (int32_t)bc; g.batch_n = (int32_t)bn;
+        g.a_bc = ash[1] > 1; g.a_bn = ash[0] > 1; g.b_bc = bsh[1] > 1; g.b_bn = bsh[0] > 1;
+        g.a_mn_major = ta ? 1 : 0;   // A stored [K, M]: M is the inner dim
+        g.b_mn_major = tb ? 0 : 1;   // B stored [K, N]: N is the inner dim
+        g.dtype = A.dtype;
+        g.act = act < 0 ? ACT_NONE : act;
+        g.c_vec = (aligned16(pc) && ldc % 8 == 0 && g.c_stride_c % 8 == 0 && g.c_stride_n % 8 == 0) ? 1 : 0;
+        const int64_t P = proc.count();
+        const int64_t tiles_m = (M + 127) / 128;
+        if (full) {
+            std::vector<int> cand = {256, 128, 64};
+            if (!g.b_mn_major) { cand.push_back(32); cand.push_back(16); }
+            int tile_n = cand.back();
+            for (int c : cand) {
+                int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
+                if (units >= P) { tile_n = c; break; }
+            }
+            if (N < tile_n) tile_n = (int)((N + 15) / 16 * 16);  // narrow outputs: one tile covers N
+            g.tile_n = tile_n;
+            g.plan_tiles = 0;
+            g.tiles_m = (int32_t)tiles_m;
+            g.tiles_n = (int32_t)((N + tile_n - 1) / tile_n);
+            g.raster_group = (int32_t)std::min<int64_t>(tiles_m, 8);
+            g.n_units = (int32_t)(bn * bc * tiles_m * g.tiles_n);
+        } else {
+            // honour the plan's task ids: tile id -> (n, c, tile_h, tile_w), w fastest
+            auto tile = op.config.at("TileShapeMNK").as_int_vec();
+            if (tile.size() != 3) throw Error(E_PLAN, "TileShapeMNK should have 3 elements");
+            const int64_t ptm = tile[0], ptn = tile[1];
+            if (ptm <= 0 || ptn <= 0) throw Error(E_PLAN, "TileShapeMNK must be positive");
+            int tile_n = 0;
+            for (int c = 256; c >= 16; c -= 16)
+                if (ptn % c == 0) { tile_n = c; break; }
+            if (!tile_n) throw Error(E_UNSUPPORTED, "Matmul: tile N of a partial TaskRange must be a multiple of 16");
+            g.tile_n = tile_n;
+            g.plan_tiles = 1;
+            g.ptm = (int32_t)ptm; g.ptn = (int32_t)ptn;
+            auto pad = C.padded.size() >= 2 ? C.padded : C.shape;
+            const int64_t pM = pad[pad.size() - 2], pN = pad[pad.size() - 1];
+            g.p_tiles_h = (int32_t)((pM + ptm - 1) / ptm);
+            g.p_tiles_w = (int32_t)((pN + ptn - 1) / ptn);
+            g.sub_m = (int32_t)((ptm + 127) / 128);
+            g.sub_n = (int32_t)(ptn / tile_n);
+            g.task_b = (int32_t)tg.task_range.b;
+            g.task_s = (int32_t)tg.task_range.s;
+            g.n_units = (int32_t)(tg.task_range.count() * g.sub_m * g.sub_n);
+        }
+        // tensor maps: dims {inner, rows, C, N}
+        auto mk = [&](const TensorDesc &T, const std::vector<int64_t> &sh, const std::vector<int64_t> &st, char *base,
+                      uint32_t box_inner, uint32_t box_rows, CUtensorMap *out) {
+            TmapSpec sp;
+            sp.base = base;
+            sp.dtype = T.dtype;
+            sp.dims[0] = (uint64_t)sh[3];
+            sp.dims[1] = (uint64_t)sh[2];
+            sp.dims[2] = (uint64_t)sh[1];
+            sp.dims[3] = (uint64_t)sh[0];
+            sp.strides_bytes[0] = (uint64_t)st[3] * es;
+            sp.strides_bytes[1] = (uint64_t)st[2] * st[3] * es;
+            sp.strides_bytes[2] = (uint64_t)st[1] * st[2] * st[3] * es;
+            sp.box[0] = box_inner; sp.box[1] = box_rows; sp.box[2] = 1; sp.box[3] = 1;
+            env.encode_tmap(out, sp);
+        };
+        // 1-D operands ([K] vectors) are viewed as one row / one column
+        std::vector<int64_t> ash2 = ash, bsh2 = bsh;
+        mk(A, ash2, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
+        mk(B, bsh2, bst, pb, 64, g.b_mn_major ? 64 : (uint32_t)g.tile_n, &g.tmB);
+        push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
+                    std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
+                    (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
+                    (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K"));
+    }
+
+    // ---- transpose / embedding ---------------------------------------------------------
+    void lower_transpose(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Transpose: partial TaskRange");
+        const TensorDesc &in = op.reads.at(0), &out = op.results.at(0);
+        auto perm = op.arg_dims("Permutation");
+        const int nd = (int)in.shape.size();
+        if ((int)perm.size() != nd) throw Error(E_MODEL, "Transpose: permutation rank mismatch");
+        Stage s = new_stage(SK_TRANSPOSE, proc);
+        TransposeArgs &a = s.tp;
+        a.in = make_ref(in);
+        a.out = make_ref(out);
+        for (int i = 0; i < 4 - nd; ++i) a.perm[i] = i;
+        for (int i = 0; i < nd; ++i) a.perm[4 - nd + i] = (int32_t)perm[i] + 4 - nd;
+        for (int i = 0; i < 4; ++i)
+            if (a.out.shape[i] != a.in.shape[a.perm[i]]) throw Error(E_MODEL, "Transpose: output shape mismatch");
+        const int V = (int)(16 / dtype_size(in.dtype));
+        bool vec = a.perm[3] == 3 && aligned16(a.in.ptr) && aligned16(a.out.ptr) && a.out.shape[3] % V == 0;
+        for (int i = 0; i < 3; ++i) vec = vec && a.in.stride[i] % V == 0 && a.out.stride[i] % V == 0;
+        a.out.contiguous = vec ? 2 : a.out.contiguous;
+        push(s, "Transpose " + op.name + (vec ? " vec" : ""));
+    }
+
+    void lower_embedding(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Embedding: partial TaskRange");
+        const TensorDesc &idx = op.reads.at(0), &w = op.reads.at(1), &out = op.results.at(0);
+        if (idx.dtype != DT_I32) throw Error(E_MODEL, "Embedding: indices must be INT32");
+        if (!idx.dense()) throw Error(E_UNSUPPORTED, "Embedding: strided index tensor");
+        auto osh = out.shape4(), ost = out.strides4(), wsh = w.shape4(), wst = w.strides4();
+        if (!((osh[0] * osh[1] == 1 || ost[2] == osh[2]) && (osh[0] == 1 || ost[1] == osh[1])))
+            throw Error(E_UNSUPPORTED, "Embedding: output rows must be evenly spaced");
+        Stage s = new_stage(SK_EMBED, proc);
+        EmbedArgs &a = s.em;
+        a.out = tensor_ptr(out);
+        a.idx = reinterpret_cast<const int32_t *>(tensor_ptr(idx));
+        a.weight = tensor_ptr(w);
+        a.n_idx = idx.nelems();
+        a.num_emb = wsh[2];
+        a.emb_dim = wsh[3];
+        a.w_ld = wst[3];
+        a.out_ld = ost[3];
+        a.esize = (int32_t)dtype_size(w.dtype);
+        push(s, "Embedding " + op.name + " n=" + std::to_string(a.n_idx));
+    }
+
+    // ---- communication ------------------------------------------------------------------
+    static int channel_of(int tag) { return (int)(((uint32_t)tag) % kChannels); }
+
+    void lower_send(const OpDesc &op, const Range &proc) {
+        const TensorDesc &src = op.reads.at(0), &dst = op.writes.at(0);
+        const int peer = dst.buffer_rank;
+        if (peer < 0 || peer >= env.nranks || peer == env.rank) throw Error(E_MODEL, "Send: invalid remote rank");
+        if (!src.dense() || !dst.dense() || src.nelems() != dst.nelems() || src.dtype != dst.dtype)
+            throw Error(E_UNSUPPORTED, "Send: dense tensors of equal size only");
+        if (dst.recv_tags.empty()) throw Error(E_MODEL, "Send: destination buffer carries no tag");
+        Stage s = new_stage(SK_PUT, proc);
+        s.put.dst = tensor_ptr(dst);
+        s.put.src = tensor_ptr(src);
+        s.put.bytes = src.nelems() * (int64_t)dtype_size(src.dtype);
+        s.put.peer = peer;
+        push(s, "Send " + op.name + " -> rank " + std::to_string(peer) + " bytes=" + std::to_string(s.put.bytes));
+        const bool signal = !op.config.is_object() || !op.config.contains("Signal") || op.config.at("Signal").as_bool();
+        if (signal) {
+            emit_sync(proc);
+            Stage g = new_stage(SK_SIGNAL, proc);
+            g.sg.peer = peer;
+            g.sg.channel = channel_of(dst.recv_tags[0].second);
+            push(g, "  signal rank " + std::to_string(peer) + " ch " + std::to_string(g.sg.channel));
+        }
+    }
+
+    void lower_recv(const OpDesc &op, const Range &proc) {
+        const TensorDesc &stand_in = op.reads.at(0);
+        const int peer = stand_in.buffer_rank;
+        if (peer < 0 || peer >= env.nranks || peer == env.rank) throw Error(E_MODEL, "Recv: invalid remote rank");
+        const bool wait = !op.config.is_object() || !op.config.contains("Wait") || op.config.at("Wait").as_bool();
+        if (!wait) return;  // placeholder op expressing a dependency only (ops_all_reduce_test.cpp:210-215)
+        if (stand_in.send_tags.empty()) throw Error(E_MODEL, "Recv: source buffer carries no tag");
+        Stage s = new_stage(SK_WAITFLAG, proc);
+        s.wt.peer = peer;
+        s.wt.channel = channel_of(stand_in.send_tags[0].second);
+        push(s, "Recv " + op.name + " <- rank " + std::to_string(peer) + " ch " + std::to_string(s.wt.channel));
+    }
+
+    void emit_peersync(const Range &proc, const std::string &why) {
+        Stage s = new_stage(SK_PEERSYNC, proc);
+        s.ps.ord = ++prog.peersyncs_per_iter;
+        push(s, "peer barrier #" + std::to_string(s.ps.ord) + " (" + why + ")");
+    }
+
+    void lower_device_sync(const OpDesc &op, const Range &proc) {
+        if (env.nranks == 1) return;
+        emit_sync(proc);
+        emit_peersync(proc, "DeviceSync " + op.name);
+        emit_sync(proc);
+    }
+
+    void lower_all_reduce(const OpDesc &op, const Range &proc) {
+        if (env.nranks == 1) return;
+        const TensorDesc &t = op.results.at(0);
+        if (!t.dense()) throw Error(E_UNSUPPORTED, "AllReduce: dense tensors only");
+        const int tag = (int)op.arg_int("Tag");
+        auto it = lay.coll_offsets.find(tag);
+        if (it == lay.coll_offsets.end() || (int)it->second.size() != env.nranks)
+            throw Error(E_PLAN, "AllReduce: tag " + std::to_string(tag) + " was not published by every rank");
+        const size_t es = dtype_size(t.dtype);
+        const int V = (int)(16 / es);
+        const int64_t n = t.nelems();
+        const size_t bytes = (size_t)n * es;
+        Stage s = new_stage(SK_ALLREDUCE, proc);
+        AllReduceArgs &a = s.ar;
+        for (int r = 0; r < env.nranks; ++r) {
+            a.buf_off[r] = it->second[r];
+            if (a.buf_off[r] % 16) throw Error(E_UNSUPPORTED, "AllReduce: tensor must be 16-byte aligned");
+        }
+        if (n % V) throw Error(E_UNSUPPORTED, "AllReduce: element count must be a multiple of 16 bytes");
+        a.nelem = n;
+        a.dtype = t.dtype;
+        std::string algo = op.config.is_object() && op.config.contains("Algo") ? op.config.at("Algo").as_string() : "auto";
+        const size_t slot = lay.comm_stage_bytes / kMaxPeers;
+        const bool one = (algo == "oneshot") || (algo == "auto" && bytes <= 256 * 1024);
+        if (one && bytes > slot) throw Error(E_PLAN, "AllReduce: tensor exceeds the one-shot staging area");
+        if (one) {
+            a.algo = 0;
+            a.stage_bytes = lay.comm_stage_bytes;
+            a.ord = oneshot_ord++;
+            a.phase = 0;
+            push(s, "AllReduce " + op.name + " one-shot push bytes=" + std::to_string(bytes));
+            emit_sync(proc);
+            emit_peersync(proc, "all_reduce data pushed");
+            emit_sync(proc);
+            Stage s2 = s;
+            s2.ar.phase = 1;
+            push(s2, "AllReduce " + op.name + " one-shot reduce");
+        } else {
+            a.algo = 1;
+            emit_sync(proc);
+            emit_peersync(proc, "all_reduce inputs ready");
+            emit_sync(proc);
+            push(s, "AllReduce " + op.name + " two-shot bytes=" + std::to_string(bytes));
+            emit_sync(proc);
+            emit_peersync(proc, "all_reduce outputs stored");
+            emit_sync(proc);
+        }
+    }
+
+    // ---- task dispatch --------------------------------------------------------------------
+    void lower_op(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        if (op.is_virtual) return;
+        const std::string &t = op.type;
+        if (t == "Noop" || t == "SendDone" || t == "Tensor" || t == "Refer" || t == "Reshape" || t == "Identity") return;
+        if (ewise_code(t) >= 0) return lower_ewise(op, proc, tg);
+        if (t == "ReduceSum" || t == "ReduceMax" || t == "ReduceMean") return lower_reduce(op, proc, tg);
+        if (t == "Matmul") return lower_matmul(op, proc, tg, -1, nullptr);
+        if (t == "Transpose") return lower_transpose(op, proc, tg);
+        if (t == "Embedding") return lower_embedding(op, proc, tg);
+        if (t == "RMSNorm" || t == "LayerNorm" || t == "Softmax") return lower_rowop(op, proc);
+        if (t == "Send") return lower_send(op, proc);
+        if (t == "Recv") return lower_recv(op, proc);
+        if (t == "DeviceSync") return lower_device_sync(op, proc);
+        if (t == "AllReduce") return lower_all_reduce(op, proc);
+        throw Error(E_UNSUPPORTED, "operator type not supported by this engine: " + t);
+    }
+
+    void lower_task_group(const TaskGroup &tg, const Range &proc) {
+        const TaskInfo &ti = plan.task(tg.task_id);
+        if (tg.task_range.count() == 0) return;
+        bool first = true;
+        for (size_t i = 0; i < ti.ops.size(); ++i) {
+            const OpDesc &op = ti.ops[i];
+            if (op.is_virtual) continue;
+            // Matmul followed by a unary activation on its result, merged into one task
+            // by the planner (Sync=false): run the activation in the GEMM epilogue.
+            if (op.type == "Matmul" && i + 1 < ti.ops.size()) {
+                const OpDesc &nx = ti.ops[i + 1];
+                const int act = act_code(nx.type);
+                if (act > 0 && nx.reads.size() == 1 && nx.reads[0].id == op.results.at(0).id &&
+                    nx.reads[0].shape == nx.results.at(0).shape && nx.results[0].dtype == op.results[0].dtype &&
+                    (other_readers(op.results[0].buffer_id, &nx) == 0 || nx.results[0].buffer_id == op.results[0].buffer_id)) {
+                    if (!first) emit_sync(proc);
+                    lower_matmul(op, proc, tg, act, &nx.results[0]);
+                    first = false;
+                    ++i;
+                    continue;
+                }
+            }
+            const size_t before = prog.stages.size();
+            if (!first) emit_sync(proc);  // ops of one task depend on each other; the split over CTAs differs per op
+            const size_t mid = prog.stages.size();
+            lower_op(op, proc, tg);
+            if (prog.stages.size() == mid && mid != before) {  // op lowered to nothing: drop the barrier again
+                const Stage &sy = prog.stages.back();
+                --prog.syncs_per_iter[sy.sync_group];
+                prog.stages.pop_back();
+                prog.notes.pop_back();
+            } else if (prog.stages.size() != mid) {
+                first = false;
+            }
+        }
+    }
+
+    static void touched(const TaskInfo &ti, std::set<int64_t> &reads, std::set<int64_t> &writes) {
+        for (auto &op : ti.ops) {
+            for (auto &t : op.reads) reads.insert(t.buffer_id);
+            for (auto &t : op.writes) writes.insert(t.buffer_id);
+            for (auto &t : op.results) writes.insert(t.buffer_id);
+        }
+    }
+
+    void run() {
+        if (plan.num_processors > env.num_sm)
+            throw Error(E_UNSUPPORTED, "plan needs " + std::to_string(plan.num_processors) + " processors, the device has " +
+                                           std::to_string(env.num_sm) + " SMs (the loop kernel keeps one CTA per processor resident)");
+        prog.grid = plan.num_processors;
+        std::vector<Range> unsynced;
+        bool first_pg = true;
+        for (auto &pg : plan.processor_groups) {
+            const Range &pr = pg.proc;
+            if (pr.count() == 0) continue;
+            if (!first_pg) {
+                // barrier rule of the reference code generator (ark/codegen.cpp:109-158)
+                bool need_sync = false;
+                for (auto it = unsynced.begin(); it != unsynced.end();) {
+                    if (!pr.overlaps(*it)) {
+                        ++it;
+                        continue;
+                    }
+                    const bool range_inside_pr = it->b >= pr.b && it->e <= pr.e && pr.s == 1;
+                    if (!range_inside_pr) {
+                        emit_sync(*it);
+                        const bool pr_inside_range = pr.b >= it->b && pr.e <= it->e && it->s == 1;
+                        if (!pr_inside_range) need_sync = true;
+                    } else {
+                        need_sync = true;
+                    }
+                    it = unsynced.erase(it);
+                }
+                if (need_sync) emit_sync(pr);
+            }
+            for (auto &rg : pg.resource_groups) {
+                std::set<int64_t> prev_w;
+                bool any = false;
+                for (auto &tg : rg.task_groups) {
+                    std::set<int64_t> r, w;
+                    touched(plan.task(tg.task_id), r, w);
+                    bool conflict = false;
+                    for (auto b : prev_w)
+                        if (r.count(b) || w.count(b)) conflict = true;
+                    // The reference runs task groups of one resource group back to back on each
+                    // processor with no barrier, relying on its task->processor mapping. This
+                    // engine splits work differently, so dependent groups get a barrier.
+                    if (any && conflict) emit_sync(rg.proc);
+                    lower_task_group(tg, rg.proc);
+                    prev_w.insert(w.begin(), w.end());
+                    any = true;
+                }
+            }
+            unsynced.push_back(pr);
+            first_pg = false;
+        }
+        prog.n_sync_groups = (int)sync_ids.size();
+        prog.oneshots_per_iter = oneshot_ord;
+        for (auto &s : prog.stages)
+            if (s.kind == SK_ALLREDUCE && s.ar.algo == 0) s.ar.per_iter = oneshot_ord;
+    }
+};
+
+}  // namespace
+
+std::string Program::dump() const {
+    std::ostringstream os;
+    os << "grid=" << grid << " stages=" << stages.size() << " sync_groups=" << n_sync_groups
+       << " peer_barriers=" << peersyncs_per_iter << "\n";
+    for (size_t i = 0; i < notes.size(); ++i) os << i << ": " << notes[i] << "\n";
+    return os.str();
+}
+
+Program lower_plan(const Plan &plan, const Layout &lay, const LowerEnv &env) {
+    Lowerer lw(plan, lay, env);
+    lw.run();
+    return lw.prog;
+}
+
+}  // namespace arkb

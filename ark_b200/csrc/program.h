@@ -1,0 +1,262 @@
+// Device program: what the host lowers a plan into and what the persistent
+// loop kernel walks. Shared between host C++ and CUDA device code.
+//
+// A plan (reference format: docs/plan_file.md) is lowered to a flat list of
+// stages. Every CTA of the grid walks the whole list once per iteration and
+// executes the stages whose processor range contains it. This is the
+// counterpart of the reference's generated `ark_body` (a straight-line list
+// of `task_seq<...>` calls and `sync_gpu` barriers, ark/codegen.cpp:119-151,
+// ark/include/kernels/kernel_template.in:6-69), held as data instead of
+// generated source so that one prebuilt sm_100a kernel runs any plan.
+#pragma once
+#include <stdint.h>
+
+#include <cuda.h>  // CUtensorMap
+
+namespace arkb {
+
+constexpr int kThreads = 512;       // threads per CTA of the loop kernel
+constexpr int kMaxSyncGroups = 64;  // distinct processor ranges that get a barrier
+constexpr int kMaxPeers = 8;
+
+enum DType : int32_t { DT_F32 = 0, DT_F16 = 1, DT_BF16 = 2, DT_I32 = 3, DT_U32 = 4, DT_I8 = 5, DT_U8 = 6 };
+
+enum StageKind : int32_t {
+    SK_SYNC = 0,       // barrier over a processor range
+    SK_EWISE = 1,      // unary / binary / scalar / cast / copy / rope, NumPy broadcast
+    SK_REDUCE = 2,     // sum / mean / max along one axis
+    SK_GEMM = 3,       // tcgen05 tiled matmul (+ fused epilogue)
+    SK_GEMV = 4,       // skinny matmul (few rows): weight streaming
+    SK_TRANSPOSE = 5,  // 4-D permutation
+    SK_EMBED = 6,      // row gather
+    SK_ROWOP = 7,      // fused row kernels: rmsnorm / layernorm / softmax
+    SK_PUT = 8,        // copy a local tensor into a peer's arena (data phase of send)
+    SK_WAITFLAG = 9,   // wait until a peer raised a channel flag (recv)
+    SK_PEERSYNC = 10,  // barrier across ranks (device_sync)
+    SK_ALLREDUCE = 11, // data phase of the in-kernel all_reduce
+    SK_GEMM_SIMT = 12, // CUDA-core matmul for shapes the TMA path cannot take
+    SK_SIGNAL = 13,    // raise a channel flag on a peer (after the put's data is complete)
+};
+
+enum EwiseOp : int32_t {
+    EW_COPY = 0, EW_GELU, EW_EXP, EW_RELU, EW_RSQRT, EW_SIGMOID, EW_SQRT, EW_CAST,
+    EW_ADD, EW_SUB, EW_MUL, EW_DIV,
+    EW_SCALAR_ASSIGN, EW_SCALAR_ADD, EW_SCALAR_MUL,
+    EW_ROPE, EW_SILU,
+};
+enum ReduceOp : int32_t { RD_SUM = 0, RD_MAX = 1, RD_MEAN = 2 };
+enum RowOp : int32_t { RO_RMSNORM = 0, RO_LAYERNORM = 1, RO_SOFTMAX = 2 };
+enum ActOp : int32_t { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2, ACT_SIGMOID = 3, ACT_SILU = 4 };
+
+// A strided view of up to 4 dims. `stride` is in elements and already 0 for
+// broadcast dims; `ptr` already includes the view's offsets.
+struct TRef {
+    void *ptr;
+    int32_t shape[4];
+    int64_t stride[4];
+    int32_t dtype;
+    int32_t contiguous;  // 1 when the view covers a dense row-major block
+};
+
+struct EwiseArgs {
+    TRef out, in0, in1;
+    int32_t op;
+    int32_t vec;        // elements per thread access along W (1 or 16/sizeof)
+    int32_t flat;       // 1: all operands dense and same shape -> 1-D walk
+    float scalar;
+    int64_t n_units;    // number of vec units
+};
+
+struct ReduceArgs {
+    TRef out, in;       // out has shape 1 along `axis`
+    int32_t op;
+    int32_t axis;       // 0..3 in 4-D form
+    int32_t vec;        // vector width usable on the innermost dim
+    int32_t pad;
+};
+
+struct RowOpArgs {
+    void *out;
+    const void *in;
+    const void *weight;    // optional (rmsnorm scale), broadcast over rows
+    const void *residual;  // optional: in := in + residual before the norm (also written to res_out)
+    void *res_out;
+    int64_t rows, cols;
+    int64_t in_ld, out_ld;
+    int32_t op, dtype;
+    float eps;
+    float scale;           // softmax: logits are multiplied by this first
+};
+
+struct GemmArgs {
+    CUtensorMap tmA;  // dims {inner, rows, C, N}; box {64, 128 or 64, 1, 1}, 128-byte swizzle
+    CUtensorMap tmB;  // dims {inner, rows, C, N}; box {64, tile_n or 64, 1, 1}
+    void *C;
+    const void *bias;     // optional tensor added in the epilogue (same layout as C)
+    int64_t ldc;
+    int64_t c_stride_c, c_stride_n;  // batch strides of C in elements
+    int32_t M, N, K;
+    int32_t batch_c, batch_n;        // output batch dims
+    int32_t a_bc, a_bn, b_bc, b_bn;  // 1 when the operand has that batch dim (else broadcast: coordinate 0)
+    int32_t a_mn_major, b_mn_major;  // 0: K-major (inner dim = K), 1: MN-major (inner dim = M or N)
+    int32_t dtype;                   // DT_F16 / DT_BF16
+    int32_t act;
+    int32_t tile_n;                  // UMMA N (multiple of 16, <= 256)
+    int32_t c_vec;                   // 1: C rows allow 16-byte stores
+    // Unit enumeration. plan_tiles == 0: units are this engine's own tiles
+    // (128 x tile_n) over the whole output, rasterised in groups of
+    // `raster_group` m-tiles. plan_tiles == 1: units follow the plan's task ids
+    // (task id -> (n, c, tile_h, tile_w), w fastest, as the reference's UnitOp
+    // does, ark/include/kernels/common/unit_op.h), each plan tile of
+    // ptm x ptn being cut into sub_m x sub_n sub-tiles of 128 x tile_n.
+    int32_t plan_tiles;
+    int32_t tiles_m, tiles_n, raster_group;
+    int32_t ptm, ptn, p_tiles_h, p_tiles_w, sub_m, sub_n, task_b, task_s;
+    int32_t n_units;
+    int32_t pad;
+};
+
+struct GemvArgs {
+    // y[m, n] = sum_k x[m,k] * W, m <= 16; W is [N,K] (K-major) or [K,N].
+    void *out;
+    const void *x;
+    const void *w;
+    int64_t ldx, ldw, ldo;
+    int32_t M, N, K;
+    int32_t w_is_nk;  // 1: W stored [N,K]
+    int32_t dtype, act;
+};
+
+struct GemmSimtArgs {
+    void *C;
+    const void *A;
+    const void *B;
+    int64_t lda, ldb, ldc;
+    int64_t a_stride_c, a_stride_n, b_stride_c, b_stride_n, c_stride_c, c_stride_n;
+    int32_t M, N, K;
+    int32_t batch_c, batch_n;
+    int32_t trans_a, trans_b;
+    int32_t dtype, act;
+};
+
+struct TransposeArgs {
+    TRef out, in;      // out.shape[i] == in.shape[perm[i]]
+    int32_t perm[4];
+};
+
+struct EmbedArgs {
+    void *out;
+    const int32_t *idx;
+    const void *weight;
+    int64_t n_idx, num_emb, emb_dim;  // emb_dim in elements
+    int64_t w_ld, out_ld;
+    int32_t esize, pad;
+};
+
+struct PutArgs {
+    void *dst;           // points into the peer's arena mapping
+    const void *src;
+    int64_t bytes;       // dense copy
+    int32_t peer, pad;
+};
+struct SignalArgs {
+    int32_t peer;        // rank whose comm block gets the flag
+    int32_t channel;     // flag index on the receiver: sender_rank * kChannels + channel
+};
+struct WaitArgs {
+    int32_t peer;        // sender rank
+    int32_t channel;
+};
+struct PeerSyncArgs {
+    int32_t ord;         // 1-based ordinal of this cross-rank barrier within an iteration
+    int32_t pad;
+};
+// Data phase of all_reduce over a dense tensor that sits at the same arena
+// offset on every rank.
+//   algo 0 (one-shot, small): phase 0 pushes the local tensor into slot
+//     [rank] of every peer's staging area; phase 1 (after a cross-rank
+//     barrier) sums the slots in rank order into the local tensor.
+//   algo 1 (two-shot, large): after a cross-rank barrier every rank sums its
+//     1/p shard from all ranks' tensors (peer loads, rank order, fp32) and
+//     stores the rounded result into every rank's tensor (peer stores).
+struct AllReduceArgs {
+    uint64_t buf_off[kMaxPeers];  // byte offset of the tensor in each rank's arena
+    int64_t nelem;
+    int32_t dtype;
+    int32_t algo, phase;
+    int32_t ord, per_iter;    // one-shot: ordinal among the one-shot all_reduces of an iteration, and their count
+                              // (consecutive invocations alternate between two staging buffers)
+    uint64_t stage_bytes;     // one-shot: bytes of one staging buffer (nranks slots)
+};
+
+struct alignas(128) Stage {
+    int32_t kind;
+    int32_t proc_b, proc_e, proc_s;  // processor (CTA) range [b, e) step s
+    int32_t sync_group;              // SK_SYNC: which barrier counter
+    int32_t sync_count;              // SK_SYNC: CTAs taking part
+    int32_t sync_ord;                // SK_SYNC: 1-based ordinal of this barrier within an iteration
+    int32_t pad0;
+    union {
+        EwiseArgs ew;
+        ReduceArgs rd;
+        RowOpArgs ro;
+        GemmArgs gm;
+        GemvArgs gv;
+        GemmSimtArgs gs;
+        TransposeArgs tp;
+        EmbedArgs em;
+        PutArgs put;
+        WaitArgs wt;
+        PeerSyncArgs ps;
+        SignalArgs sg;
+        AllReduceArgs ar;
+    };
+};
+
+// Status word written by the device when a bounded wait gives up.
+enum StatusCode : int32_t {
+    ST_OK = 0,
+    ST_BARRIER_TIMEOUT = 1,
+    ST_MBAR_TIMEOUT = 2,
+    ST_PEER_TIMEOUT = 3,
+    ST_IDLE_EXIT = 4,  // loop kernel saw no run request for a long time and returned (not an error)
+};
+
+constexpr int kChannels = 64;  // send/recv flag channels per rank pair
+
+struct DeviceState {
+    unsigned long long barrier[kMaxSyncGroups];  // monotonic arrive counters (host zeroes them at launch)
+    unsigned long long iter_total;               // iterations completed over the executor's life (never reset)
+    int32_t status;                              // StatusCode (first failure wins)
+    int32_t status_stage;                        // stage index where it happened
+    int32_t status_cta;
+    int32_t run_iters;                           // iterations requested by the current run (broadcast)
+    unsigned long long t_begin, t_end;           // %globaltimer stamps around the last run
+    volatile int32_t *host_status;               // host-mapped mirror of `status`
+};
+
+// Per-rank communication block, mapped into every peer. It sits at the start
+// of each rank's comm allocation; the all_reduce staging area follows it.
+struct CommBlock {
+    unsigned long long barrier_flag[kMaxPeers];             // [r]: written by rank r
+    unsigned long long chan_flag[kMaxPeers * kChannels];    // [src_rank * kChannels + channel]
+};
+constexpr uint64_t kCommDataOff = 8192;  // staging area offset inside the comm allocation
+
+struct LaunchParams {
+    const Stage *stages;
+    DeviceState *state;
+    volatile int32_t *run_flag;   // host-mapped; >0: run that many iterations; <0: exit
+    int32_t n_stages;
+    int32_t loop_mode;            // 1: persistent, wait on run_flag; 0: run `iters` once and return
+    int32_t iters;
+    int32_t rank, nranks;
+    int32_t peersyncs_per_iter;
+    int32_t syncs_per_iter[kMaxSyncGroups];
+    char *arena[kMaxPeers];       // arena base of every rank as mapped here (own included)
+    char *comm[kMaxPeers];        // comm allocation of every rank as mapped here (own included)
+    unsigned long long spin_limit;     // nanoseconds a device-side wait may last before it gives up
+    unsigned long long idle_limit_ns;  // loop mode: return after this long without a run request
+};
+
+}  // namespace arkb

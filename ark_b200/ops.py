@@ -1,0 +1,454 @@
+"""Functional operator API — same names and argument meaning as the reference
+front end (python/ark/ops.py), building ops on the global Model.
+
+Engine extensions (no counterpart op in the reference, which composes them
+from several ops): `rmsnorm`, `silu`, fused `softmax`/`layernorm` row kernels
+(selected with `fused=True`), and `all_reduce` as one collective op.
+"""
+import math
+
+from . import data_type as dt
+from .error import ModelError
+from .model import Model, Tensor, Buffer
+
+NullTensor = None
+
+
+def _m():
+    return Model.get_model()
+
+
+def _broadcast_shape(a, b):
+    ra, rb = list(a)[::-1], list(b)[::-1]
+    out = []
+    for i in range(max(len(ra), len(rb))):
+        x = ra[i] if i < len(ra) else 1
+        y = rb[i] if i < len(rb) else 1
+        if x != y and x != 1 and y != 1:
+            raise ModelError(f"shapes {a} and {b} do not broadcast")
+        out.append(max(x, y))
+    return out[::-1]
+
+
+def _out_like(shape, dtype, output, padded_shape=None):
+    m = _m()
+    if output is not None:
+        if list(output.shape) != list(shape):
+            raise ModelError(f"output shape {output.shape} does not match {shape}")
+        return output
+    return Tensor(m, dtype, Buffer(m), shape, padded_shape=padded_shape)
+
+
+def _result_of(output):
+    return output.clone_view()
+
+
+# ---- tensors -----------------------------------------------------------------
+def tensor(shape, dtype=dt.fp32, strides=None, offsets=None, padded_shape=None, rank=-1, name="tensor"):
+    """ark.tensor (python/ark/ops.py:418-431)."""
+    return _m().new_tensor(list(shape), dtype, strides, offsets, padded_shape, rank, name)
+
+
+def parameter(shape, dtype=dt.fp32, strides=None, offsets=None, padded_shape=None, name="parameter"):
+    return tensor(shape, dtype, strides, offsets, padded_shape, -1, name)
+
+
+def reshape(input, shape, allowzero=False, name="reshape"):
+    """View with a new shape over the same buffer (ark/ops/ops_reshape.cpp). Dense inputs only."""
+    shape = list(shape)
+    n = input.nelems()
+    if -1 in shape:
+        known = 1
+        for s in shape:
+            if s != -1:
+                known *= s
+        shape[shape.index(-1)] = n // known
+    p = 1
+    for s in shape:
+        p *= s
+    if p != n:
+        raise ModelError(f"cannot reshape {input.shape} to {shape}")
+    if not input.is_dense():
+        raise ModelError("reshape needs a dense tensor")
+    t = Tensor(_m(), input.dtype, input.buffer, shape)
+    _m().add_op("Reshape", name, [input], [], [t], virtual=True)
+    return t
+
+
+def identity(input, deps=(), name="identity"):
+    """Same view, new id; `deps` only express ordering (ark/ops/ops_identity.cpp)."""
+    t = input.clone_view()
+    _m().add_op("Identity", name, [input] + list(deps), [], [t], virtual=True)
+    return t
+
+
+def refer(input, shape, strides, offsets, padded_shape, dtype=None, name="refer"):
+    t = Tensor(_m(), dtype or input.dtype, input.buffer, shape, strides, offsets, padded_shape)
+    _m().add_op("Refer", name, [input], [], [t], virtual=True)
+    return t
+
+
+def sharding(input, axis, dim_per_shard, name="sharding"):
+    """Splits a tensor along `axis` into views (ark/ops/ops_sharding.cpp)."""
+    if axis < 0:
+        axis += len(input.shape)
+    out = []
+    pos = 0
+    while pos < input.shape[axis]:
+        d = min(dim_per_shard, input.shape[axis] - pos)
+        shape = list(input.shape)
+        shape[axis] = d
+        offs = list(input.offsets)
+        offs[axis] += pos
+        out.append(refer(input, shape, input.strides, offs, shape, name=f"{name}_{len(out)}"))
+        pos += d
+    return out
+
+
+def noop(input, name="noop"):
+    _m().add_op("Noop", name, [input], [], [])
+
+
+# ---- elementwise ----------------------------------------------------------------
+def _unary(type_, input, output, name):
+    out = _out_like(input.shape, input.dtype, output)
+    res = _result_of(out)
+    _m().add_op(type_, name, [input], [out], [res])
+    return res
+
+
+def _binary(type_, input, other, output, name):
+    if isinstance(other, (int, float)):
+        raise ModelError("scalar operands go through scalar ops")
+    if input.dtype is not other.dtype:
+        raise ModelError("operand data types differ")
+    out = _out_like(_broadcast_shape(input.shape, other.shape), input.dtype, output)
+    res = _result_of(out)
+    _m().add_op(type_, name, [input, other], [out], [res])
+    return res
+
+
+def add(input, other, output=None, name="add"):
+    if isinstance(other, (int, float)):
+        return _scalar("ScalarAdd", input, float(other), output, name)
+    return _binary("Add", input, other, output, name)
+
+
+def sub(input, other, output=None, name="sub"):
+    if isinstance(other, (int, float)):
+        return _scalar("ScalarAdd", input, -float(other), output, name)
+    return _binary("Sub", input, other, output, name)
+
+
+def mul(input, other, output=None, name="mul"):
+    if isinstance(other, (int, float)):
+        return _scalar("ScalarMul", input, float(other), output, name)
+    return _binary("Mul", input, other, output, name)
+
+
+def div(input, other, output=None, name="div"):
+    if isinstance(other, (int, float)):
+        return _scalar("ScalarMul", input, 1.0 / float(other), output, name)
+    return _binary("Div", input, other, output, name)
+
+
+def _scalar(type_, input, factor, output, name):
+    out = _out_like(input.shape, input.dtype, output)
+    res = _result_of(out)
+    _m().add_op(type_, name, [input], [out], [res], {"Factor": float(factor)})
+    return res
+
+
+def constant(value, shape, dtype=dt.fp32, name="constant"):
+    out = Tensor(_m(), dtype, Buffer(_m()), list(shape))
+    res = _result_of(out)
+    _m().add_op("ScalarAssign", name, [], [out], [res], {"Value": float(value)})
+    return res
+
+
+def ones(shape, dtype=dt.fp32, name="ones"):
+    return constant(1.0, shape, dtype, name)
+
+
+def zeros(shape, dtype=dt.fp32, name="zeros"):
+    return constant(0.0, shape, dtype, name)
+
+
+def exp(input, output=None, name="exp"):
+    return _unary("Exp", input, output, name)
+
+
+def gelu(input, output=None, name="gelu"):
+    return _unary("Gelu", input, output, name)
+
+
+def relu(input, output=None, name="relu"):
+    return _unary("Relu", input, output, name)
+
+
+def rsqrt(input, output=None, name="rsqrt"):
+    return _unary("Rsqrt", input, output, name)
+
+
+def sigmoid(input, output=None, name="sigmoid"):
+    return _unary("Sigmoid", input, output, name)
+
+
+def sqrt(input, output=None, name="sqrt"):
+    return _unary("Sqrt", input, output, name)
+
+
+def silu(input, output=None, name="silu"):
+    """x * sigmoid(x) in one pass (engine extension; the reference composes sigmoid and mul)."""
+    return _unary("Silu", input, output, name)
+
+
+def copy(input, output=None, name="copy"):
+    return _unary("Copy", input, output, name)
+
+
+def cast(input, dtype, output=None, name="cast"):
+    """ark.cast (ark/ops/ops_cast.cpp). Casting to/from `byte` reinterprets the bytes."""
+    if dtype is input.dtype:
+        return input
+    if dtype is dt.byte or input.dtype is dt.byte:
+        if not input.is_dense():
+            raise ModelError("byte casts need a dense tensor")
+        shape = list(input.shape)
+        if dtype is dt.byte:
+            shape[-1] *= input.dtype.nbytes
+        else:
+            if shape[-1] % dtype.nbytes:
+                raise ModelError("byte tensor length is not a multiple of the element size")
+            shape[-1] //= dtype.nbytes
+        t = Tensor(_m(), dtype, input.buffer, shape)
+        _m().add_op("Refer", name, [input], [], [t], virtual=True)
+        return t
+    out = _out_like(input.shape, dtype, output)
+    res = _result_of(out)
+    _m().add_op("Cast", name, [input], [out], [res])
+    return res
+
+
+def rope(input, other, output=None, name="rope"):
+    return _binary("Rope", input, other, output, name)
+
+
+# ---- reductions ----------------------------------------------------------------------
+def _reduce(type_, input, axis, keepdims, output, name):
+    nd = len(input.shape)
+    ax = axis + nd if axis < 0 else axis
+    if ax < 0 or ax >= nd:
+        raise ModelError(f"invalid reduction axis {axis}")
+    shape = list(input.shape)
+    if keepdims:
+        shape[ax] = 1
+    else:
+        shape.pop(ax)
+    out = _out_like(shape, input.dtype, output)
+    if out is input:
+        raise ModelError("output tensor cannot be the same as input tensor for a reduce op")
+    res = _result_of(out)
+    _m().add_op(type_, name, [input], [out], [res], {"Axis": int(ax), "KeepDim": bool(keepdims)})
+    return res
+
+
+def reduce_sum(input, axis, keepdims=True, output=None, name="reduce_sum"):
+    return _reduce("ReduceSum", input, axis, keepdims, output, name)
+
+
+def reduce_mean(input, axis, keepdims=True, output=None, name="reduce_mean"):
+    return _reduce("ReduceMean", input, axis, keepdims, output, name)
+
+
+def reduce_max(input, axis, keepdims=True, output=None, name="reduce_max"):
+    return _reduce("ReduceMax", input, axis, keepdims, output, name)
+
+
+def mean(input, axis, keepdims=True, output=None, name="mean"):
+    return reduce_mean(input, axis, keepdims, output, name)
+
+
+# ---- matmul -----------------------------------------------------------------------------
+def matmul(input, other, output=None, transpose_input=False, transpose_other=False, name="matmul"):
+    """ark.matmul (ark/ops/ops_matmul.cpp:13-106): [N,C,H,W] batches broadcast over N and C."""
+    if input.dtype is not other.dtype:
+        raise ModelError("operand data types differ")
+
+    def mnk(a, b):
+        m = 1 if len(a) == 1 else a[-2]
+        k = a[-1]
+        n = 1 if len(b) == 1 else b[-1]
+        k2 = b[0] if len(b) == 1 else b[-2]
+        if transpose_input:
+            m, k = k, m
+        if transpose_other:
+            n, k2 = k2, n
+        if k != k2:
+            raise ModelError(f"inner dimensions mismatch: {k} and {k2}")
+        return m, n, k
+
+    def oshape(a, b):
+        m, n, _ = mnk(a, b)
+        nd = max(len(a), len(b))
+        if nd < 3:
+            return [m, n]
+        a4 = [1] * (4 - len(a)) + list(a)
+        b4 = [1] * (4 - len(b)) + list(b)
+        nc = _broadcast_shape(a4[:2], b4[:2])
+        return [nc[0], nc[1], m, n] if nd == 4 else [nc[1], m, n]
+
+    shape = oshape(input.shape, other.shape)
+    padded = oshape(input.padded_shape, other.padded_shape)
+    out = _out_like(shape, input.dtype, output, padded)
+    res = _result_of(out)
+    _m().add_op("Matmul", name, [input, other], [out], [res],
+                {"TransposeInput": bool(transpose_input), "TransposeOther": bool(transpose_other)})
+    return res
+
+
+# ---- layout ------------------------------------------------------------------------------
+def transpose(input, perm, output=None, name="transpose"):
+    nd = len(input.shape)
+    perm = [int(p) for p in perm]
+    if sorted(perm) != list(range(nd)):
+        raise ModelError(f"invalid permutation {perm}")
+    shape = [input.shape[p] for p in perm]
+    out = _out_like(shape, input.dtype, output)
+    res = _result_of(out)
+    _m().add_op("Transpose", name, [input], [out], [res], {"Permutation": perm})
+    return res
+
+
+def embedding(input, weight, output=None, name="embedding"):
+    """Row gather (ark/ops/ops_embedding.cpp:11-70): input INT32 indices, weight [num_emb, dim]."""
+    if input.dtype is not dt.int32:
+        raise ModelError("embedding indices must be int32")
+    if len(input.shape) > 3:
+        raise ModelError("embedding input has at most 3 dimensions")
+    shape = list(input.shape) + [weight.shape[-1]]
+    out = _out_like(shape, weight.dtype, output)
+    res = _result_of(out)
+    _m().add_op("Embedding", name, [input, weight], [out], [res])
+    return res
+
+
+# ---- compositions / fused rows ----------------------------------------------------------------
+def softmax(input, output=None, name="softmax", fused=True, scale=1.0):
+    """Softmax over the last axis. The reference composes five ops
+    (python/ark/ops.py:491-500); `fused=True` runs one row kernel instead."""
+    if fused:
+        out = _out_like(input.shape, input.dtype, output)
+        res = _result_of(out)
+        _m().add_op("Softmax", name, [input], [out], [res], {"Scale": float(scale)})
+        return res
+    x = input if scale == 1.0 else mul(input, float(scale))
+    mx = reduce_max(x, axis=-1)
+    e = exp(sub(x, mx))
+    s = reduce_sum(e, axis=-1)
+    return div(e, s, output)
+
+
+def layernorm(input, eps=1e-5, output=None, name="layernorm", fused=True):
+    """Layer normalisation over the last axis (python/ark/ops.py:503-513 composes six ops)."""
+    if fused:
+        out = _out_like(input.shape, input.dtype, output)
+        res = _result_of(out)
+        _m().add_op("LayerNorm", name, [input], [out], [res], {"Eps": float(eps)})
+        return res
+    mu = reduce_mean(input, axis=-1)
+    x = sub(input, mu)
+    var = reduce_mean(mul(x, x), axis=-1)
+    return mul(x, rsqrt(add(var, float(eps))), output)
+
+
+def rmsnorm(input, weight=None, eps=1e-5, output=None, residual=None, name="rmsnorm"):
+    """RMSNorm row kernel for the pattern examples/llama/model.py:92-99 builds
+    from cast/mul/reduce_mean/rsqrt/mul. With `residual`, normalises
+    input + residual and also returns the sum: (normed, summed)."""
+    out = _out_like(input.shape, input.dtype, output)
+    res = _result_of(out)
+    reads = [input] + ([weight] if weight is not None else [])
+    args = {"Eps": float(eps)}
+    if residual is None:
+        _m().add_op("RMSNorm", name, reads, [out], [res], args)
+        return res
+    summed = Tensor(_m(), input.dtype, Buffer(_m()), input.shape)
+    sres = _result_of(summed)
+    args["Residual"] = True
+    _m().add_op("RMSNorm", name, reads + [residual], [out, summed], [res, sres], args)
+    return res, sres
+
+
+# ---- communication ------------------------------------------------------------------------------
+def send(input, remote_rank, tag, output=None, name="send"):
+    """ark::Model::send (ark/ops/ops_communication.cpp:18-43)."""
+    m = _m()
+    if output is None:
+        output = Tensor(m, input.dtype, Buffer(m, remote_rank), input.shape, input.strides, input.offsets,
+                        input.padded_shape)
+    elif output.buffer.rank != remote_rank:
+        raise ModelError(f"invalid buffer rank: {output.buffer.rank}, expected: {remote_rank}")
+    input.buffer.tag_send(remote_rank, tag)
+    output.buffer.tag_recv(-1, tag)
+    res = _result_of(output)
+    m.add_op("Send", name, [input], [output], [res])
+    return res
+
+
+def send_done(input, name="send_done"):
+    res = input.clone_view()
+    _m().add_op("SendDone", name, [input], [], [res])
+    return res
+
+
+def recv(output, remote_rank, tag, name="recv"):
+    """ark::Model::recv (ark/ops/ops_communication.cpp:122-139)."""
+    m = _m()
+    res = _result_of(output)
+    stand_in = Tensor(m, output.dtype, Buffer(m, remote_rank), output.shape, output.strides, output.offsets,
+                      output.padded_shape)
+    stand_in.buffer.tag_send(-1, tag)
+    output.buffer.tag_recv(remote_rank, tag)
+    m.add_op("Recv", name, [stand_in], [output], [res])
+    return res
+
+
+def device_sync(input, rank, rank_num, name="device_sync"):
+    res = input.clone_view()
+    _m().add_op("DeviceSync", name, [input], [input], [res], {"Rank": int(rank), "PeerNum": int(rank_num) - 1})
+    return res
+
+
+def all_reduce(input, rank, world_size, output=None, name="all_reduce", naive=False):
+    """Sum over ranks. The reference composes world_size-1 rounds of
+    send/send_done/recv/add (ark/ops/ops_all_reduce.cpp:8-37, kept as
+    `naive=True`); by default this is one in-kernel collective on `output`
+    (in place on a copy of `input` when `output` is None)."""
+    m = _m()
+    if output is None:
+        output = copy(input)
+    elif output is not input:
+        output = copy(input, output)
+    if world_size == 1:
+        return output
+    if naive:
+        tags = [m.unique_tag() for _ in range(world_size)]
+        prev_recv = None
+        cumulate = output
+        for i in range(1, world_size):
+            dst = (rank + i) % world_size
+            src = (rank + world_size - i) % world_size
+            send_data = input if prev_recv is None else identity(input, [prev_recv])
+            send_data = send(send_data, dst, tags[rank])
+            sd = send_done(send_data)
+            recv_buf = tensor(output.shape, output.dtype)
+            recv_t = identity(recv_buf, [sd])
+            recv_t = recv(recv_buf, src, tags[src])
+            prev_recv = recv_t
+            cumulate = add(cumulate, recv_t, cumulate)
+        return cumulate
+    res = output.clone_view()
+    tag = m.unique_tag()
+    m.add_op("AllReduce", name, [output], [output], [res], {"Tag": int(tag), "Rank": int(rank), "RankNum": int(world_size)})
+    return res

@@ -1,0 +1,121 @@
+"""GPU parity: tensor-core matmul (tcgen05) and the CUDA-core fallback against
+the oracle's fp32-accumulate restatement. Cases follow
+ark/ops/ops_matmul_test.cpp:330-561 (plain, transposed, batched with N/C
+broadcast, padded/offset operands, constant inputs)."""
+import numpy as np
+import pytest
+
+import ark_b200 as ark
+from oracle import oracle as O
+from tests.ark_util import NAME, assert_matmul_close, execute, rand
+
+pytestmark = pytest.mark.gpu
+
+
+def run_mm(ash, bsh, dt, ta=False, tb=False, seed=31, fuse=None):
+    rng = np.random.default_rng(seed)
+    a, b = rand(rng, ash, dt), rand(rng, bsh, dt)
+    ark.init()
+    t_a, t_b = ark.tensor(list(ash), NAME[dt]), ark.tensor(list(bsh), NAME[dt])
+    if fuse:
+        with ark.PlannerContext(sync=False):
+            out = getattr(ark, fuse)(ark.matmul(t_a, t_b, transpose_input=ta, transpose_other=tb))
+    else:
+        out = ark.matmul(t_a, t_b, transpose_input=ta, transpose_other=tb)
+    (got,) = execute([out], {t_a: a, t_b: b})
+    want = O.matmul(a, b, dt, ta, tb, act=fuse)
+    return got, want
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 256, 256), (256, 512, 1024), (128, 64, 64), (4096, 256, 128),
+                                 (64, 48, 96), (1, 256, 512), (200, 1000, 136)])
+def test_matmul_nn(dt, mnk):
+    m, n, k = mnk
+    got, want = run_mm((m, k), (k, n), dt)
+    assert_matmul_close(got, want, dt, f"nn {mnk}")
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (256, 384, 512), (72, 200, 264)])
+def test_matmul_transposed(dt, ta, tb, mnk):
+    m, n, k = mnk
+    got, want = run_mm((k, m) if ta else (m, k), (n, k) if tb else (k, n), dt, ta, tb)
+    assert_matmul_close(got, want, dt, f"t{int(ta)}{int(tb)} {mnk}")
+
+
+@pytest.mark.parametrize("dt", ["fp16"])
+@pytest.mark.parametrize("ash,bsh", [((3, 128, 64), (3, 64, 256)), ((2, 3, 128, 64), (1, 3, 64, 128)),
+                                     ((2, 1, 64, 64), (1, 3, 64, 64)), ((4, 128, 128), (128, 64))])
+def test_matmul_batched_broadcast(dt, ash, bsh):
+    got, want = run_mm(ash, bsh, dt)
+    assert got.shape == want.shape
+    assert_matmul_close(got, want, dt, f"batched {ash}x{bsh}")
+
+
+@pytest.mark.parametrize("fuse", ["relu", "gelu"])
+def test_matmul_fused_activation(fuse):
+    got, want = run_mm((256, 512), (512, 768), "fp16", fuse=fuse)
+    assert_matmul_close(got, want, "fp16", f"fused {fuse}")
+
+
+def test_matmul_constant_inputs():
+    # ops_matmul_test.cpp:343-360: all 0.1 -> every output is k * 0.01
+    ark.init()
+    m, n, k = 256, 256, 512
+    t_a, t_b = ark.tensor([m, k], ark.fp16), ark.tensor([k, n], ark.fp16)
+    out = ark.matmul(t_a, t_b)
+    a = np.full((m, k), 0.1, np.float16)
+    b = np.full((k, n), 0.1, np.float16)
+    (got,) = execute([out], {t_a: a, t_b: b})
+    want = O.matmul(a, b, "fp16")
+    assert np.array_equal(got, want)  # exact: identical products, fp32 accumulation
+
+
+def test_matmul_padded_offset_operands():
+    """Operands that are windows of larger buffers (ops_matmul_test.cpp:527-561)."""
+    rng = np.random.default_rng(33)
+    a, b = rand(rng, (128, 64), "fp16"), rand(rng, (64, 256), "fp16")
+    ark.init()
+    t_a = ark.tensor([128, 64], ark.fp16, strides=[256, 128], offsets=[128, 64], padded_shape=[128, 64])
+    t_b = ark.tensor([64, 256], ark.fp16, strides=[128, 512], offsets=[64, 256], padded_shape=[64, 256])
+    out = ark.matmul(t_a, t_b)
+    (got,) = execute([out], {t_a: a, t_b: b})
+    assert_matmul_close(got, O.matmul(a, b, "fp16"), "fp16", "padded/offset")
+
+
+@pytest.mark.parametrize("dt,mnk", [("fp32", (128, 256, 64)), ("fp32", (100, 70, 130)), ("fp16", (64, 50, 70))])
+def test_matmul_cuda_core_fallback(dt, mnk):
+    """fp32, and fp16 rows that are not 16-byte multiples, run on the CUDA-core path."""
+    m, n, k = mnk
+    got, want = run_mm((m, k), (k, n), dt)
+    if dt == "fp32":
+        assert np.allclose(got, want, rtol=1e-4, atol=1e-5)
+    else:
+        assert_matmul_close(got, want, dt, "simt fp16")
+
+
+def test_matmul_partial_task_range_follows_plan_tiles():
+    """A hand-written plan that splits one Matmul's tiles over two processor groups
+    (as examples/tutorial/plan_tutorial.py does) must compute the same result."""
+    import json
+    rng = np.random.default_rng(34)
+    a, b = rand(rng, (256, 128), "fp16"), rand(rng, (128, 512), "fp16")
+    ark.init()
+    t_a, t_b = ark.tensor([256, 128], ark.fp16), ark.tensor([128, 512], ark.fp16)
+    out = ark.matmul(t_a, t_b)
+    plan = ark.Planner(0).plan().plan
+    assert plan["TaskInfos"][0]["Ops"][0]["Config"]["NumTasks"] == 4  # 128x256 tiles
+    pg = plan["ProcessorGroups"][0]
+    rg = pg["ResourceGroups"][0]
+    pg["ProcessorRange"] = [0, 4]
+    rg["ProcessorRange"] = [0, 2]
+    rg["TaskGroups"][0]["TaskRange"] = [0, 4, 2]
+    rg2 = json.loads(json.dumps(rg))
+    rg2["ProcessorRange"] = [2, 4]
+    rg2["TaskGroups"][0]["TaskRange"] = [1, 4, 2]
+    pg["ResourceGroups"].append(rg2)
+    plan["NumProcessors"] = 4
+    (got,) = execute([out], {t_a: a, t_b: b}, plan=ark.Plan(plan))
+    assert_matmul_close(got, O.matmul(a, b, "fp16"), "fp16", "partial ranges")

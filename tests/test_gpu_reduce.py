@@ -1,0 +1,104 @@
+"""GPU parity: reductions, fused row operators, transpose and embedding
+(reference tests: ark/ops/ops_reduce_test.cpp, ops_transpose_test.cpp,
+ops_embedding_test.cpp)."""
+import numpy as np
+import pytest
+
+import ark_b200 as ark
+from oracle import oracle as O
+from tests.ark_util import NAME, assert_close, execute, rand
+
+pytestmark = pytest.mark.gpu
+FLOATS = ["fp32", "fp16", "bf16"]
+
+
+def red_tol(dt, k):
+    # reduction_abs_error_bound (ark/ops/ops_test_common.hpp:52-69), halved: the oracle is exact fp32
+    bits = {"fp32": 23, "fp16": 10, "bf16": 7}[dt]
+    return k * 2 * 0.1 / (1 << (bits + 1)) * 2
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+@pytest.mark.parametrize("axis", [0, 1, 2, 3])
+@pytest.mark.parametrize("kind", ["sum", "mean", "max"])
+def test_reduce_axes(kind, axis, dt):
+    rng = np.random.default_rng(21)
+    shape = (7, 2, 4, 1024)
+    x = rand(rng, shape, dt)
+    ark.init()
+    t = ark.tensor(list(shape), NAME[dt])
+    out = getattr(ark, "reduce_" + kind)(t, axis=axis)
+    (got,) = execute([out], {t: x})
+    want = O.reduce(kind, x, axis, dt)
+    assert_close(got, want, dt, rtol=2 * (2.0 ** -9 if dt == "fp16" else 2.0 ** -7 if dt == "bf16" else 1e-6),
+                 atol=red_tol(dt, shape[axis]), what=f"reduce_{kind}_axis{axis}_{dt}")
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+def test_reduce_no_keepdims_and_odd_width(dt):
+    rng = np.random.default_rng(22)
+    x = rand(rng, (5, 3, 1001), dt)
+    ark.init()
+    t = ark.tensor([5, 3, 1001], NAME[dt])
+    o1 = ark.reduce_sum(t, axis=-1, keepdims=False)
+    o2 = ark.reduce_sum(t, axis=0, keepdims=False)
+    g1, g2 = execute([o1, o2], {t: x})
+    assert g1.shape == (5, 3) and g2.shape == (3, 1001)
+    assert_close(g1, O.reduce("sum", x, 2, dt, keepdims=False), dt, rtol=4e-3 if dt != "fp32" else 1e-5,
+                 atol=red_tol(dt, 1001), what="sum -1")
+    assert_close(g2, O.reduce("sum", x, 0, dt, keepdims=False), dt, rtol=1e-2 if dt == "bf16" else 4e-3, atol=red_tol(dt, 5), what="sum 0")
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (7, 8192), (2048, 128), (3, 40000)])
+def test_rmsnorm_softmax_layernorm(dt, rows, cols):
+    rng = np.random.default_rng(23)
+    x = O.to_storage(rng.normal(0, 1, (rows, cols)).astype(np.float32), dt)
+    w = O.to_storage(rng.normal(1, 0.1, (cols,)).astype(np.float32), dt)
+    ark.init()
+    t, tw = ark.tensor([rows, cols], NAME[dt]), ark.tensor([cols], NAME[dt])
+    o1 = ark.rmsnorm(t, tw, eps=1e-5)
+    o2 = ark.softmax(t)
+    o3 = ark.layernorm(t)
+    g1, g2, g3 = execute([o1, o2, o3], {t: x, tw: w})
+    tol = {"fp32": 2e-5, "fp16": 2e-3, "bf16": 1.6e-2}[dt]
+    assert_close(g1, O.rmsnorm(x, w, dt, 1e-5), dt, rtol=tol, atol=tol, what="rmsnorm")
+    assert_close(g2, O.softmax(x, dt), dt, rtol=tol, atol=1e-7 if dt == "fp32" else 1e-5, what="softmax")
+    assert_close(g3, O.layernorm(x, dt), dt, rtol=tol, atol=tol, what="layernorm")
+
+
+def test_fused_rows_match_the_reference_compositions():
+    """softmax/layernorm as the reference composes them (python/ark/ops.py:491-513) vs the fused kernels."""
+    rng = np.random.default_rng(24)
+    x = rng.normal(0, 1, (16, 512)).astype(np.float32)
+    ark.init()
+    t = ark.tensor([16, 512], ark.fp32)
+    f1, f2 = ark.softmax(t, fused=True), ark.layernorm(t, fused=True)
+    c1, c2 = ark.softmax(t, fused=False), ark.layernorm(t, fused=False)
+    g = execute([f1, f2, c1, c2], {t: x})
+    assert np.allclose(g[0], g[2], rtol=1e-5, atol=1e-7)
+    assert np.allclose(g[1], g[3], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("dt", ["fp32", "fp16"])
+@pytest.mark.parametrize("perm", [[0, 1, 3, 2], [0, 2, 3, 1], [0, 2, 1, 3], [3, 2, 1, 0], [1, 0, 2, 3], [2, 3, 0, 1]])
+def test_transpose_exact(dt, perm):
+    rng = np.random.default_rng(25)
+    x = rand(rng, (5, 3, 32, 128), dt)
+    ark.init()
+    t = ark.tensor([5, 3, 32, 128], NAME[dt])
+    out = ark.transpose(t, perm)
+    (got,) = execute([out], {t: x})
+    assert np.array_equal(got, O.transpose(x, perm))
+
+
+@pytest.mark.parametrize("dt", FLOATS)
+def test_embedding_exact(dt):
+    rng = np.random.default_rng(26)
+    w = rand(rng, (100, 4096), dt)
+    idx = rng.integers(-100, 100, size=(8, 3, 64)).astype(np.int32)
+    ark.init()
+    ti, tw = ark.tensor([8, 3, 64], ark.int32), ark.tensor([100, 4096], NAME[dt])
+    out = ark.embedding(ti, tw)
+    (got,) = execute([out], {ti: idx, tw: w})
+    assert np.array_equal(got.view(np.uint8), O.embedding(idx, w).view(np.uint8))

@@ -1,0 +1,107 @@
+"""GPU tests of the executor protocol through the C ABI: loop mode, repeated
+runs, error behaviour pinned by the reference's executor tests
+(ark/api/executor_test.cpp:47-59, 149-155, 171-183) and the bounded-wait
+status path."""
+import numpy as np
+import pytest
+
+import ark_b200 as ark
+from oracle import oracle as O
+from tests.ark_util import assert_close, execute, rand
+
+pytestmark = pytest.mark.gpu
+
+
+def build_chain():
+    ark.init()
+    t = ark.tensor([64, 1024], ark.fp16)
+    o = ark.add(t, 1.0, t)  # in place: x += 1 every iteration
+    return t, o
+
+
+def test_device_info():
+    di = ark.device_info(0)
+    assert di["arch"] == "CUDA_100" and di["num_sm"] >= 100
+
+
+@pytest.mark.parametrize("loop_mode", [False, True])
+def test_iterations_accumulate(loop_mode):
+    t, o = build_chain()
+    x = np.zeros((64, 1024), np.float16)
+    ex = ark.Executor(0, 0, "t", str(ark.Planner(0).plan()), loop_mode)
+    ex.set_wait_limit(3_000_000_000)
+    ex.compile()
+    ex.tensor_from_numpy(t, x)
+    ex.launch()
+    ex.run(3)
+    ex.wait()
+    ex.run(2)
+    ex.wait()
+    got = ex.tensor_to_numpy(o)
+    ms = ex.stop()
+    st = ex.status()
+    ex.destroy()
+    assert np.all(got == 5.0)
+    assert ms >= 0 and st["code"] == 0 and st["iterations"] == 5
+    assert st["n_launches"] == (1 if loop_mode else 2)
+
+
+def test_relaunch_after_stop():
+    t, o = build_chain()
+    ex = ark.Executor(0, 0, "t", str(ark.Planner(0).plan()), True)
+    ex.compile()
+    ex.tensor_from_numpy(t, np.zeros((64, 1024), np.float16))
+    for expect in (1.0, 2.0):
+        ex.launch()
+        ex.run(1)
+        ex.wait()
+        ex.stop()
+        assert np.all(ex.tensor_to_numpy(o) == expect)
+    ex.destroy()
+    assert ex.destroyed()
+
+
+def test_usage_errors():
+    t, o = build_chain()
+    plan = str(ark.Planner(0).plan())
+    with pytest.raises(ark.InvalidUsageError):
+        ark.Executor(-1, 0, "t", plan, True)
+    ex = ark.Executor(0, 0, "t", plan, True)
+    with pytest.raises(ark.InvalidUsageError):
+        ex.launch()  # launch before compile
+    ex.compile()
+    ex.launch()
+    ex.launch()  # second launch is ignored
+    with pytest.raises(ark.InvalidUsageError):
+        ex.tensor_to_numpy(o, np.zeros(3, np.float16))  # size mismatch
+    ex.stop()
+    ex.destroy()
+    with pytest.raises(ark.PlanError):
+        ark.Executor(0, 0, "t", "{not json", True)
+
+
+def test_tensor_io_strided_roundtrip():
+    ark.init()
+    t = ark.tensor([4, 3, 10, 20], ark.fp32, strides=[4, 3, 16, 32], offsets=[0, 0, 2, 8], padded_shape=[4, 3, 10, 20])
+    o = ark.mul(t, 2.0)
+    x = np.random.default_rng(41).normal(size=(4, 3, 10, 20)).astype(np.float32)
+    (got,) = execute([o], {t: x})
+    assert np.array_equal(got, x * 2)
+
+
+def test_multi_op_plan_ffn_block():
+    """Config 1 of the benchmark set: Y = ReLU(X W1) W2, fp16 with fp32 accumulate."""
+    rng = np.random.default_rng(0)
+    x = O.to_storage(rng.normal(0, 1, (128, 1024)).astype(np.float32), "fp16")
+    w1 = O.to_storage(rng.normal(0, 0.02, (1024, 4096)).astype(np.float32), "fp16")
+    w2 = O.to_storage(rng.normal(0, 0.02, (4096, 1024)).astype(np.float32), "fp16")
+    ark.init()
+    tx, t1, t2 = ark.tensor([128, 1024], ark.fp16), ark.tensor([1024, 4096], ark.fp16), ark.tensor([4096, 1024], ark.fp16)
+    with ark.PlannerContext(sync=False):
+        h = ark.relu(ark.matmul(tx, t1))
+    y = ark.matmul(h, t2)
+    (got,) = execute([y], {tx: x, t1: w1, t2: w2}, loop_mode=True)
+    hh = O.matmul(x, w1, "fp16", act="relu")
+    want = O.matmul(hh, w2, "fp16")
+    from tests.ark_util import assert_matmul_close
+    assert_matmul_close(got, want, "fp16", "ffn block")
