@@ -186,9 +186,10 @@ __device__ __forceinline__ void named_barrier(int id, int nthreads) {
 // The tanh form of GeLU used by the reference (ark/include/kernels/math_functions.h:24-46,
 // host baseline ark/ops/ops_math_test.cpp:10-12), evaluated in fp32.
 __device__ __forceinline__ float gelu_f(float x) {
+    // 0.5 * (1 + tanh(u)) == 1 / (1 + exp(-2u)): no cancellation in the negative tail
     const float k0 = 0.7978845608028654f, k1 = 0.044715f;
     float u = k0 * (x + k1 * x * x * x);
-    return 0.5f * x * (1.0f + tanhf(u));
+    return x / (1.0f + expf(-2.0f * u));
 }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 

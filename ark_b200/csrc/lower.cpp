@@ -61,6 +61,36 @@ struct Lowerer {
         return r;
     }
 
+    // fp32 value after a round trip through the storage type (round to nearest even)
+    static float round_to_dtype(float v, int dt) {
+        uint32_t x;
+        std::memcpy(&x, &v, 4);
+        if (dt == DT_BF16) {
+            if ((x & 0x7f800000u) != 0x7f800000u) x += 0x7fffu + ((x >> 16) & 1u);
+            x &= 0xffff0000u;
+            std::memcpy(&v, &x, 4);
+            return v;
+        }
+        if (dt == DT_F16) {
+            const uint32_t sign = x & 0x80000000u;
+            const int32_t e = (int32_t)((x >> 23) & 0xff) - 127;
+            if (e > 15) return v;                 // overflow/inf/nan: leave to the device conversion
+            if (e < -25 || (e == -25 && (x & 0x7fffffu) == 0)) { x = sign; std::memcpy(&v, &x, 4); return v; }
+            if (e == -25) { x = sign | 0x33800000u; std::memcpy(&v, &x, 4); return v; }  // rounds up to 2^-24
+            // keep 10 mantissa bits (fewer for subnormal halves)
+            const int drop = e >= -14 ? 13 : 13 + (-14 - e);
+            const uint32_t mant = x & 0x7fffffffu;
+            const uint32_t half = 1u << (drop - 1), mask = (1u << drop) - 1;
+            uint32_t r = mant & ~mask;
+            const uint32_t rem = mant & mask;
+            if (rem > half || (rem == half && (r >> drop & 1u))) r += (1u << drop);
+            x = sign | r;
+            std::memcpy(&v, &x, 4);
+            return v;
+        }
+        return v;
+    }
+
     static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
     Stage new_stage(int kind, const Range &proc) {
@@ -131,8 +161,10 @@ struct Lowerer {
         if (has_in) a.in0 = make_ref(op.reads[0], &osh);
         if (binary) a.in1 = make_ref(op.reads[1], &osh);
         a.op = code;
-        if (code == EW_SCALAR_ASSIGN) a.scalar = (float)op.arg_float("Value");
-        if (code == EW_SCALAR_ADD || code == EW_SCALAR_MUL) a.scalar = (float)op.arg_float("Factor");
+        // the scalar is rounded to the tensor's storage type first, as the reference's
+        // host baselines do with T(factor) (ark/ops/ops_scalar_test.cpp:11-62)
+        if (code == EW_SCALAR_ASSIGN) a.scalar = round_to_dtype((float)op.arg_float("Value"), out.dtype);
+        if (code == EW_SCALAR_ADD || code == EW_SCALAR_MUL) a.scalar = round_to_dtype((float)op.arg_float("Factor"), out.dtype);
         const int idt = has_in ? op.reads[0].dtype : out.dtype;
         if (binary && op.reads[1].dtype != idt) throw Error(E_MODEL, op.type + ": operand data types differ");
         const bool convert = (code == EW_CAST) || idt != out.dtype;

@@ -1,0 +1,218 @@
+"""CPU tests of the host side: the C ABI library loads and exports what the
+header declares, plans in the reference's JSON format are parsed, validated and
+lowered without a GPU, the planner follows the reference's config precedence
+and task-merging rules, and the multi-rank bootstrap plumbing works over gloo."""
+import ctypes
+import glob
+import json
+import os
+import re
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import ark_b200 as ark
+from ark_b200.executor import LIB_PATH, lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "ark_b200.h")).read()
+    names = sorted(n for n in set(re.findall(r"\b(arkb_[a-z_]+)\s*\(", hdr)) if n not in ("arkb_status", "arkb_allgather_fn"))
+    assert len(names) >= 20
+    L = ctypes.CDLL(LIB_PATH)
+    for n in names:
+        assert hasattr(L, n), f"{n} is declared in include/ark_b200.h but not exported"
+    assert ark.version().count(".") == 2
+
+
+def _ffn_plan(num_sm=148):
+    ark.init()
+    x, w1, w2 = ark.tensor([128, 1024], ark.fp16), ark.tensor([1024, 4096], ark.fp16), ark.tensor([4096, 1024], ark.fp16)
+    with ark.PlannerContext(sync=False):
+        h = ark.relu(ark.matmul(x, w1))
+    y = ark.matmul(h, w2)
+    return ark.Planner(0, num_sm=num_sm).plan()
+
+
+def test_plan_has_reference_fields_and_merges_unsynced_ops():
+    plan = _ffn_plan().plan
+    for k in ("Rank", "WorldSize", "Architecture", "NumProcessors", "NumWarpsPerProcessor", "TaskInfos", "ProcessorGroups"):
+        assert k in plan
+    assert plan["Architecture"] == "CUDA_100"
+    assert [len(t["Ops"]) for t in plan["TaskInfos"]] == [2, 1]  # matmul+relu share a task (Sync=false)
+    op = plan["TaskInfos"][0]["Ops"][0]
+    assert op["Type"] == "Matmul" and op["Args"]["TransposeOther"] == {"BOOL": False}
+    assert op["Config"]["TileShapeMNK"] == [128, 256, 64] and op["Config"]["NumTasks"] == 16
+    t = op["ReadTensors"][0]
+    assert set(t) == {"Id", "DataType", "Shape", "Strides", "Offsets", "PaddedShape", "Buffer"}
+    assert set(t["Buffer"]) == {"Id", "Rank", "SendTags", "RecvTags"}
+
+
+def test_plan_lowering_fuses_activation_and_places_barriers():
+    plan = _ffn_plan()
+    n_stages, arena, procs = ark.plan_check(str(plan))
+    text = ark.plan_dump(str(plan))
+    assert procs == 148 and n_stages == 3
+    assert "act=1" in text and text.count("sync group") == 1
+    assert arena >= (128 * 1024 + 2 * 1024 * 4096 + 128 * 4096 + 128 * 1024) * 2
+
+
+def test_barrier_rule_between_processor_groups():
+    """Disjoint processor groups run without a barrier; overlapping ones get one (ark/codegen.cpp:109-158)."""
+    ark.init()
+    a, b = ark.tensor([64, 64], ark.fp32), ark.tensor([64, 64], ark.fp32)
+    with ark.PlannerContext(processor_range=[0, 8]):
+        c = ark.add(a, b)
+    with ark.PlannerContext(processor_range=[8, 16]):
+        d = ark.mul(a, b)
+    with ark.PlannerContext(processor_range=[0, 16]):
+        e = ark.add(c, d)
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    lines = text.strip().split("\n")[1:]
+    kinds = [("sync" if "sync group" in l else "op") for l in lines]
+    assert kinds == ["op", "op", "sync", "op"]
+    assert "[0,16) sync" in lines[2]
+
+
+def test_config_precedence_context_over_rule_over_default():
+    ark.init()
+    a = ark.tensor([64, 64], ark.fp32)
+    with ark.PlannerContext(config={"Tile": [2, 32]}):
+        ark.exp(a)
+    ark.relu(a)
+    pl = ark.Planner(0, num_sm=148)
+    pl.install_config_rule(lambda op, arch: json.dumps({"NumWarps": 2, "SramBytes": 0, "NumTasks": 7, "Tile": [4, 16]})
+                           if json.loads(op)["Type"] == "Relu" else "")
+    plan = pl.plan().plan
+    assert plan["TaskInfos"][0]["Ops"][0]["Config"]["Tile"] == [2, 32]
+    assert plan["TaskInfos"][1]["Ops"][0]["Config"]["Tile"] == [4, 16]
+
+
+@pytest.mark.parametrize("mutate,err", [
+    (lambda p: p.__setitem__("Rank", 3), ark.InvalidUsageError),
+    (lambda p: p.pop("TaskInfos"), ark.PlanError),
+    (lambda p: p["ProcessorGroups"][0].__setitem__("ProcessorRange", [0, 4096]), ark.PlanError),
+    (lambda p: p["TaskInfos"][0]["Ops"][0].__setitem__("Type", "Conv9000"), ark.UnsupportedError),
+    (lambda p: p["ProcessorGroups"][0]["ResourceGroups"][0]["TaskGroups"][0].__setitem__("TaskId", 77), ark.PlanError),
+    (lambda p: p.__setitem__("NumProcessors", 500), ark.UnsupportedError),
+])
+def test_plan_errors(mutate, err):
+    plan = _ffn_plan().plan
+    mutate(plan)
+    if plan.get("NumProcessors") == 500:
+        plan["ProcessorGroups"][0]["ProcessorRange"] = [0, 500]
+        plan["ProcessorGroups"][0]["ResourceGroups"][0]["ProcessorRange"] = [0, 500]
+    with pytest.raises(err):
+        ark.plan_check(json.dumps(plan))
+
+
+def test_not_json_is_a_plan_error():
+    with pytest.raises(ark.PlanError):
+        ark.plan_check("{oops")
+
+
+def test_model_errors():
+    ark.init()
+    a, b = ark.tensor([4, 8], ark.fp32), ark.tensor([5, 8], ark.fp32)
+    with pytest.raises(ark.ModelError):
+        ark.add(a, b)
+    with pytest.raises(ark.ModelError):
+        ark.matmul(a, b)
+    with pytest.raises(ark.ModelError):
+        ark.reduce_sum(a, axis=5)
+    with pytest.raises(ark.ModelError):
+        ark.tensor([1, 2, 3, 4, 5], ark.fp32)
+
+
+def test_multi_rank_plan_lowering_all_reduce_and_send_recv():
+    for algo_elems, expect in ((4096, "one-shot"), (4 * 1024 * 1024, "two-shot")):
+        ark.init()
+        ark.set_rank(1)
+        ark.set_world_size(4)
+        t = ark.tensor([algo_elems], ark.fp16)
+        ark.all_reduce(t, 1, 4, output=t)
+        text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+        assert expect in text and "peer barrier" in text
+    ark.init()
+    ark.set_rank(0)
+    ark.set_world_size(2)
+    t = ark.tensor([1024], ark.fp16)
+    s = ark.send(t, 1, tag=5)
+    ark.send_done(s)
+    r = ark.recv(ark.tensor([1024], ark.fp16), 1, tag=6)
+    plan = ark.Planner(0, num_sm=148).plan()
+    ops = [o for ti in plan.plan["TaskInfos"] for o in ti["Ops"]]
+    assert ops[0]["WriteTensors"][0]["Buffer"]["Rank"] == 1
+    assert ops[0]["WriteTensors"][0]["Buffer"]["RecvTags"] == [[-1, 5]]
+    assert ops[0]["ReadTensors"][0]["Buffer"]["SendTags"] == [[1, 5]]
+    ark.set_rank(0)
+    ark.set_world_size(1)
+
+
+def test_naive_all_reduce_composition_matches_reference_structure():
+    """Model::all_reduce of the reference: world_size-1 rounds of send/send_done/recv/add (ops_all_reduce.cpp:8-37)."""
+    ark.init()
+    ark.set_rank(0)
+    ark.set_world_size(4)
+    t = ark.tensor([1024], ark.fp16)
+    ark.all_reduce(t, 0, 4, naive=True)
+    types = [o.type for o in ark.Model.get_model().ops if not o.virtual]
+    assert types == ["Copy"] + ["Send", "SendDone", "Recv", "Add"] * 3
+    ark.set_world_size(1)
+
+
+@pytest.mark.skipif(not os.path.isdir("/root/reference/examples/tutorial"), reason="reference checkout not present")
+def test_reference_tutorial_plans_load_unmodified():
+    """Plan files written for the reference (CUDA_80, 108 processors) lower as they are."""
+    n = 0
+    for f in sorted(glob.glob("/root/reference/examples/tutorial/*.json")):
+        s = open(f).read()
+        if '"TaskInfos"' not in s:
+            continue
+        stages, arena, procs = ark.plan_check(s)
+        assert stages > 0 and procs == 108
+        n += 1
+    assert n >= 4
+
+
+_GLOO_WORKER = r"""
+import os, sys, ctypes
+import numpy as np
+import torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from ark_b200.executor import torch_allgather
+dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{sys.argv[2]}", rank=int(sys.argv[3]), world_size=2)
+rank = dist.get_rank()
+fn = torch_allgather()
+send = (ctypes.c_uint8 * 64)(*[(rank * 100 + i) % 256 for i in range(64)])
+recv = (ctypes.c_uint8 * 128)()
+rc = fn(None, ctypes.addressof(send), ctypes.addressof(recv), 64)
+got = np.frombuffer(recv, dtype=np.uint8)
+want = np.concatenate([np.array([(r * 100 + i) % 256 for i in range(64)], dtype=np.uint8) for r in range(2)])
+assert rc == 0 and np.array_equal(got, want), (rc, got[:8])
+# rank-specific shards of the benchmark operands: disjoint column / row blocks of the same matrices
+import ark_b200 as ark
+ark.init(); ark.set_rank(rank); ark.set_world_size(2)
+from ark_b200.ffn import build_ffn
+x, w1, w2, y = build_ffn(256, 512, 2048, ark.fp16, rank, 2)
+assert w1.shape == [512, 1024] and w2.shape == [1024, 512]
+stages, arena, procs = ark.plan_check(str(ark.Planner(0, num_sm=148).plan()))
+assert stages > 3
+dist.barrier(); dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_bootstrap_allgather_over_gloo_world_size_2(tmp_path):
+    script = tmp_path / "w.py"
+    script.write_text(_GLOO_WORKER)
+    port = 29500 + (os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), ROOT, str(port), str(r)], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240)[0] for p in procs]
+    for p, o in zip(procs, outs):
+        assert p.returncode == 0, o
