@@ -18,7 +18,7 @@ __device__ __forceinline__ TileCoord gemm_unit(const GemmArgs &g, int u) {
         const int gi = r / gsz, ri = r % gsz;
         const int first_m = gi * g.raster_group;
         const int gm = min(g.raster_group, g.tiles_m - first_m);
-        t.m0 = (first_m + ri % gm) * kGemmTileM;
+        t.m0 = (first_m + ri % gm) * g.tile_m;
         t.n0 = (ri / gm) * g.tile_n;
     } else {
         const int subs = g.sub_m * g.sub_n;
@@ -30,7 +30,7 @@ __device__ __forceinline__ TileCoord gemm_unit(const GemmArgs &g, int u) {
         id /= g.p_tiles_h;
         t.bc = id % g.batch_c;
         t.bn = id / g.batch_c;
-        t.m0 = th * g.ptm + (sub / g.sub_n) * kGemmTileM;
+        t.m0 = th * g.ptm + (sub / g.sub_n) * g.tile_m;
         t.n0 = tw * g.ptn + (sub % g.sub_n) * g.tile_n;
     }
     return t;
@@ -101,56 +101,90 @@ __device__ void gemm_epilogue_tile(const GemmArgs &g, const TileCoord &tc, uint3
 
 // Runs the tiles of one GEMM stage assigned to CTA p of P. All threads of the
 // CTA call this; it returns with the pipeline drained.
-__device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
-                                      DeviceState *st, int stage_idx, unsigned long long spin_limit) {
+//
+// PAIR == false: the CTA owns 128 x tile_n tiles (tcgen05 cta_group::1).
+// PAIR == true : CTAs 2q and 2q+1 form a cluster and own 256 x tile_n tiles
+//   (cta_group::2). Each CTA stages its 128 rows of A and its half of the B
+//   columns; the leader (even CTA) issues the MMAs, which read both CTAs'
+//   shared memory and write both CTAs' TMEM. TMA completions of both CTAs are
+//   credited to the leader's `full` barrier; the leader's commits release the
+//   `empty` slot and publish `acc_full` in both CTAs; the epilogue warps of
+//   both CTAs arrive on the leader's `acc_empty`.
+template <bool PAIR>
+__device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
+                           int stage_idx, unsigned long long lim) {
+    using Cfg = GemmCfg<PAIR>;
+    constexpr int STAGES = Cfg::kStages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kblocks = (g.K + kGemmBK - 1) / kGemmBK;
     const unsigned int kb0 = pp->kb_count, t0 = pp->tile_count;
+    const int crank = PAIR ? (p & 1) : 0;          // rank inside the CTA pair
+    const int up = PAIR ? (p >> 1) : p;             // which tile walker this CTA belongs to
+    const int UP = PAIR ? (P >> 1) : P;
+    const int n_half = PAIR ? g.tile_n / 2 : g.tile_n;  // B columns staged by this CTA
     int my_tiles = 0;
-    for (int u = p; u < g.n_units; u += P) ++my_tiles;
+    for (int u = up; u < g.n_units; u += UP) ++my_tiles;
     const uint32_t tmem_base = ctl->tmem_base;
-    const unsigned long long lim = spin_limit;
 
     if (warp == kProducerWarp) {
         if (lane == 0) {
-            const int a_chunks = g.a_mn_major ? 2 : 1;                      // 64-wide M chunks
-            const int b_chunks = g.b_mn_major ? (g.tile_n + 63) / 64 : 1;   // 64-wide N chunks
+            const int a_chunks = g.a_mn_major ? 2 : 1;                     // 64-wide M chunks
+            const int b_chunks = g.b_mn_major ? (n_half + 63) / 64 : 1;    // 64-wide N chunks
             const uint32_t a_bytes = kGemmABytes;
-            const uint32_t b_bytes = g.b_mn_major ? (uint32_t)b_chunks * 64 * kGemmBK * 2 : (uint32_t)g.tile_n * kGemmBK * 2;
+            const uint32_t b_bytes = g.b_mn_major ? (uint32_t)b_chunks * 64 * kGemmBK * 2 : (uint32_t)n_half * kGemmBK * 2;
             unsigned int kb = kb0;
-            for (int u = p; u < g.n_units; u += P) {
-                const TileCoord tc = gemm_unit(g, u);
+            for (int u = up; u < g.n_units; u += UP) {
+                TileCoord tc = gemm_unit(g, u);
+                tc.m0 += crank * kGemmTileM;
+                tc.n0 += crank * n_half;
                 const int a_c = g.a_bc ? tc.bc : 0, a_n = g.a_bn ? tc.bn : 0;
                 const int b_c = g.b_bc ? tc.bc : 0, b_n = g.b_bn ? tc.bn : 0;
                 for (int k = 0; k < kblocks; ++k, ++kb) {
-                    const int s = kb % kGemmStages;
-                    const uint32_t par = ((kb / kGemmStages) & 1) ^ 1;
+                    const int s = kb % STAGES;
+                    const uint32_t par = ((kb / STAGES) & 1) ^ 1;
                     if (!mbar_wait(&pp->empty[s], par, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
-                    char *sa = smem + s * kGemmStageBytes;
+                    char *sa = smem + s * Cfg::kStageBytes;
                     char *sb = sa + kGemmABytes;
-                    mbar_expect_tx(&pp->full[s], a_bytes + b_bytes);
-                    if (!g.a_mn_major) {
-                        tma_load_4d(sa, &g.tmA, &pp->full[s], k * kGemmBK, tc.m0, a_c, a_n);
+                    if constexpr (!PAIR) {
+                        mbar_expect_tx(&pp->full[s], a_bytes + b_bytes);
+                        if (!g.a_mn_major) {
+                            tma_load_4d(sa, &g.tmA, &pp->full[s], k * kGemmBK, tc.m0, a_c, a_n);
+                        } else {
+                            for (int c = 0; c < a_chunks; ++c)
+                                tma_load_4d(sa + c * 64 * kGemmBK * 2, &g.tmA, &pp->full[s], tc.m0 + c * 64, k * kGemmBK, a_c, a_n);
+                        }
+                        if (!g.b_mn_major) {
+                            tma_load_4d(sb, &g.tmB, &pp->full[s], k * kGemmBK, tc.n0, b_c, b_n);
+                        } else {
+                            for (int c = 0; c < b_chunks; ++c)
+                                tma_load_4d(sb + c * 64 * kGemmBK * 2, &g.tmB, &pp->full[s], tc.n0 + c * 64, k * kGemmBK, b_c, b_n);
+                        }
                     } else {
-                        for (int c = 0; c < a_chunks; ++c)
-                            tma_load_4d(sa + c * 64 * kGemmBK * 2, &g.tmA, &pp->full[s], tc.m0 + c * 64, k * kGemmBK, a_c, a_n);
-                    }
-                    if (!g.b_mn_major) {
-                        tma_load_4d(sb, &g.tmB, &pp->full[s], k * kGemmBK, tc.n0, b_c, b_n);
-                    } else {
-                        for (int c = 0; c < b_chunks; ++c)
-                            tma_load_4d(sb + c * 64 * kGemmBK * 2, &g.tmB, &pp->full[s], tc.n0 + c * 64, k * kGemmBK, b_c, b_n);
+                        const uint32_t full_leader = mapa_u32(smem_u32(&pp->full[s]), 0);
+                        if (crank == 0) mbar_expect_tx(&pp->full[s], 2 * (a_bytes + b_bytes));
+                        if (!g.a_mn_major) {
+                            tma_load_4d_pair(sa, &g.tmA, full_leader, k * kGemmBK, tc.m0, a_c, a_n);
+                        } else {
+                            for (int c = 0; c < a_chunks; ++c)
+                                tma_load_4d_pair(sa + c * 64 * kGemmBK * 2, &g.tmA, full_leader, tc.m0 + c * 64, k * kGemmBK, a_c, a_n);
+                        }
+                        if (!g.b_mn_major) {
+                            tma_load_4d_pair(sb, &g.tmB, full_leader, k * kGemmBK, tc.n0, b_c, b_n);
+                        } else {
+                            for (int c = 0; c < b_chunks; ++c)
+                                tma_load_4d_pair(sb + c * 64 * kGemmBK * 2, &g.tmB, full_leader, tc.n0 + c * 64, k * kGemmBK, b_c, b_n);
+                        }
                     }
                 }
             }
         }
     } else if (warp == kMmaWarp) {
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc(g.dtype == DT_BF16, g.a_mn_major, g.b_mn_major, g.tile_n);
+        if (lane == 0 && crank == 0) {
+            const uint32_t idesc = umma_idesc(g.dtype == DT_BF16, g.a_mn_major, g.b_mn_major, g.tile_n, PAIR ? 256 : 128);
             // per-MMA (K=16) advance of the descriptor start address, in 16-byte units
             const uint32_t a_adv = g.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
             const uint32_t b_adv = g.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
@@ -166,30 +200,46 @@ __device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * 256;
                 for (int k = 0; k < kblocks; ++k, ++kb) {
-                    const int s = kb % kGemmStages;
-                    if (!mbar_wait(&pp->full[s], (kb / kGemmStages) & 1, lim)) {
+                    const int s = kb % STAGES;
+                    if (!mbar_wait(&pp->full[s], (kb / STAGES) & 1, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * kGemmStageBytes);
+                    const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
                     const uint32_t sb = sa + kGemmABytes;
                     const uint64_t da = g.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
                     const uint64_t db = g.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < kGemmBK / 16; ++kk)
-                        umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc,
-                                 (k > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(&pp->empty[s]);  // frees the smem slot when these MMAs have read it
+                    for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                        const uint32_t accum = (k > 0 || kk > 0) ? 1u : 0u;
+                        if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                        else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                    }
+                    // free the shared-memory slot once these MMAs have read it
+                    if constexpr (PAIR) {
+                        const uint32_t e = smem_u32(&pp->empty[s]);
+                        umma_commit_pair(mapa_u32(e, 0));
+                        umma_commit_pair(mapa_u32(e, 1));
+                    } else {
+                        umma_commit(&pp->empty[s]);
+                    }
                 }
-                umma_commit(&pp->acc_full[acc]);  // accumulator complete
+                if constexpr (PAIR) {  // accumulator complete, in both CTAs
+                    const uint32_t f = smem_u32(&pp->acc_full[acc]);
+                    umma_commit_pair(mapa_u32(f, 0));
+                    umma_commit_pair(mapa_u32(f, 1));
+                } else {
+                    umma_commit(&pp->acc_full[acc]);
+                }
             }
         }
     } else if (warp < kEpiWarps) {
         unsigned int t = t0;
-        for (int u = p; u < g.n_units; u += P, ++t) {
-            const TileCoord tc = gemm_unit(g, u);
+        for (int u = up; u < g.n_units; u += UP, ++t) {
+            TileCoord tc = gemm_unit(g, u);
+            tc.m0 += crank * kGemmTileM;
             const int acc = t & 1;
             bool ok = mbar_wait(&pp->acc_full[acc], (t >> 1) & 1, lim);
             ok = __all_sync(0xffffffffu, ok);
@@ -206,7 +256,10 @@ __device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *
             else gemm_epilogue_tile<__half>(g, tc, tmem_acc, warp, lane);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&pp->acc_empty[acc]);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&pp->acc_empty[acc]), 0));
+                else mbar_arrive(&pp->acc_empty[acc]);
+            }
         }
     }
 done:
@@ -215,7 +268,18 @@ done:
         pp->kb_count = kb0 + (unsigned int)my_tiles * (unsigned int)kblocks;
         pp->tile_count = t0 + (unsigned int)my_tiles;
     }
+    // the partner may still read this CTA's shared memory / signal its barriers
+    if constexpr (PAIR) cluster_sync_all();
     __syncthreads();
+}
+
+__device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
+                         int stage_idx, unsigned long long spin_limit) {
+    run_gemm_t<false>(g, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+}
+__device__ void run_gemm_pair(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
+                              int stage_idx, unsigned long long spin_limit) {
+    run_gemm_t<true>(g, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
 
 // ---- CUDA-core fallback -------------------------------------------------------------

@@ -21,19 +21,26 @@
 
 namespace arkb {
 
-constexpr int kGemmStages = 4;
 constexpr int kGemmBK = 64;                       // K elements per stage (128 bytes of fp16/bf16)
-constexpr int kGemmTileM = 128;
+constexpr int kGemmTileM = 128;                   // accumulator rows per CTA
 constexpr int kGemmABytes = kGemmTileM * kGemmBK * 2;   // 16 KiB
-constexpr int kGemmBBytes = 256 * kGemmBK * 2;          // 32 KiB (tile_n up to 256)
-constexpr int kGemmStageBytes = kGemmABytes + kGemmBBytes;
-constexpr int kGemmSmemBytes = kGemmStages * kGemmStageBytes;  // 192 KiB
+// One CTA per tile: B tile up to 256 columns (32 KiB), 4 stages.
+// CTA pair per tile (cta_group::2, 256 x tile_n): each CTA stages its 128 rows
+// of A and half of the B columns (16 KiB), 6 stages.
+template <bool PAIR>
+struct GemmCfg {
+    static constexpr int kStages = PAIR ? 6 : 4;
+    static constexpr int kBBytes = (PAIR ? 128 : 256) * kGemmBK * 2;
+    static constexpr int kStageBytes = kGemmABytes + kBBytes;
+};
+constexpr int kGemmMaxStages = 6;
+constexpr int kGemmSmemBytes = 4 * (kGemmABytes + 256 * kGemmBK * 2);  // 192 KiB in both modes
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5;
 
 struct GemmPipe {
-    unsigned long long full[kGemmStages];
-    unsigned long long empty[kGemmStages];
+    unsigned long long full[kGemmMaxStages];
+    unsigned long long empty[kGemmMaxStages];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
     unsigned int kb_count;    // k-blocks this CTA has pushed through the ring since launch
@@ -95,7 +102,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 // Instruction descriptor for kind::f16: fp32 accumulate, A/B fp16 or bf16.
-__device__ __forceinline__ uint32_t umma_idesc(int bf16, int a_mn, int b_mn, int n) {
+__device__ __forceinline__ uint32_t umma_idesc(int bf16, int a_mn, int b_mn, int n, int m = kGemmTileM) {
     uint32_t d = 0;
     d |= 1u << 4;                        // D format: F32
     d |= (uint32_t)(bf16 ? 1 : 0) << 7;  // A format
@@ -103,7 +110,7 @@ __device__ __forceinline__ uint32_t umma_idesc(int bf16, int a_mn, int b_mn, int
     d |= (uint32_t)(a_mn ? 1 : 0) << 15; // A major: 0 K, 1 MN
     d |= (uint32_t)(b_mn ? 1 : 0) << 16; // B major
     d |= (uint32_t)(n >> 3) << 17;       // N / 8
-    d |= (uint32_t)(kGemmTileM >> 4) << 24;  // M / 16
+    d |= (uint32_t)(m >> 4) << 24;       // M / 16
     return d;
 }
 
@@ -153,14 +160,61 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, int cols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
 
-__device__ __forceinline__ void gemm_pipe_init(GemmPipe *pp) {
-    for (int s = 0; s < kGemmStages; ++s) {
+// pair == true: the accumulator-empty barrier of the leader CTA collects the
+// epilogue warps of both CTAs.
+// ---- CTA-pair (cta_group::2) variants --------------------------------------------------
+// Address of `local` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void tma_load_4d_pair(void *smem_dst, const CUtensorMap *tm, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2, int c3) {
+    // data lands in this CTA's shared memory, the byte count is credited to the
+    // leader CTA's barrier; no multicast: every CTA loads its own operands
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "  tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p; }"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// Arrive on a barrier (given as a shared::cluster address, own or peer CTA) when
+// the MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, int cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, int cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void gemm_pipe_init(GemmPipe *pp, bool pair) {
+    for (int s = 0; s < kGemmMaxStages; ++s) {
         mbar_init(&pp->full[s], 1);
         mbar_init(&pp->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
         mbar_init(&pp->acc_full[a], 1);
-        mbar_init(&pp->acc_empty[a], kEpiWarps);
+        mbar_init(&pp->acc_empty[a], pair ? 2 * kEpiWarps : kEpiWarps);
     }
     pp->kb_count = 0;
     pp->tile_count = 0;

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <thread>
 
@@ -182,6 +183,7 @@ void Executor::compile() {
     }
     env.encode_tmap = encode_tmap_cuda;
     env.num_sm = num_sm_;
+    env.allow_pair = getenv("ARKB_NO_PAIR") == nullptr;
     program_ = lower_plan(plan_, layout_, env);
     if (!program_.stages.empty()) {
         CUDA_CHECK(cudaMalloc(&stages_dev_, program_.stages.size() * sizeof(Stage)));
@@ -203,6 +205,7 @@ void Executor::fill_params(LaunchParams &P, int iters) const {
     P.rank = plan_.rank;
     P.nranks = plan_.world_size;
     P.peersyncs_per_iter = program_.peersyncs_per_iter;
+    P.pair_mode = program_.pair_mode ? 1 : 0;
     for (int i = 0; i < kMaxSyncGroups; ++i) P.syncs_per_iter[i] = program_.syncs_per_iter[i];
     for (int r = 0; r < kMaxPeers; ++r) {
         P.arena[r] = peer_arena_[r];

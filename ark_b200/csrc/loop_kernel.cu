@@ -24,6 +24,7 @@ __device__ __forceinline__ bool in_range(const Stage &S, int cta, int &p, int &P
 // One pass over the stage list. iter_local counts iterations since this
 // launch (barrier phases); iter_no is the 1-based iteration number over the
 // executor's life (cross-rank epochs and channel flags).
+template <bool PAIR>
 __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, GemmPipe *pipe, CtaCtl *ctl,
                                          unsigned long long iter_local, unsigned long long iter_no) {
     const int cta = blockIdx.x;
@@ -44,7 +45,10 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             case SK_EWISE: run_ewise(S.ew, p, Pn); break;
             case SK_REDUCE: run_reduce(S.rd, p, Pn); break;
             case SK_ROWOP: run_rowop(S.ro, p, Pn); break;
-            case SK_GEMM: run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit); break;
+            case SK_GEMM:
+                if constexpr (PAIR) run_gemm_pair(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
+                else run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
+                break;
             case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
             case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;
             case SK_EMBED: run_embed(S.em, p, Pn); break;
@@ -61,7 +65,8 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
     }
 }
 
-extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const __grid_constant__ LaunchParams P) {
+template <bool PAIR>
+__device__ __forceinline__ void loop_main(const LaunchParams &P) {
     extern __shared__ __align__(1024) char dyn_smem[];
     __shared__ CtaCtl ctl;
     __shared__ GemmPipe pipe;
@@ -71,11 +76,15 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const
     if (threadIdx.x == 0) {
         ctl.abort = 0;
         ctl.run_iters = 0;
-        gemm_pipe_init(&pipe);
+        gemm_pipe_init(&pipe, PAIR);
     }
-    if (threadIdx.x < 32) tmem_alloc(&ctl.tmem_base, kTmemCols);
+    if (threadIdx.x < 32) {
+        if constexpr (PAIR) tmem_alloc_pair(&ctl.tmem_base, kTmemCols);
+        else tmem_alloc(&ctl.tmem_base, kTmemCols);
+    }
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
     tc_fence_after();
 
     DeviceState *st = P.state;
@@ -113,7 +122,7 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const
         if (blockIdx.x == 0 && threadIdx.x == 0) st->t_begin = globaltimer();
         bool ok = true;
         for (int i = 0; i < iters && ok; ++i) {
-            run_body(P, smem, &pipe, &ctl, iter_local, iter_no + 1);
+            run_body<PAIR>(P, smem, &pipe, &ctl, iter_local, iter_no + 1);
             ++whole_k;
             ok = grid_barrier(&st->barrier[whole], whole_k * gridDim.x, P.spin_limit, &ctl, st, -2);
             ++iter_local;
@@ -135,8 +144,22 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const
         if (P.loop_mode && blockIdx.x == 0) *P.run_flag = 0;
     }
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither CTA of a pair leaves while the other may still touch it
     tc_fence_after();
-    if (threadIdx.x < 32) tmem_dealloc(ctl.tmem_base, kTmemCols);
+    if (threadIdx.x < 32) {
+        if constexpr (PAIR) tmem_dealloc_pair(ctl.tmem_base, kTmemCols);
+        else tmem_dealloc(ctl.tmem_base, kTmemCols);
+    }
+}
+
+// One CTA per processor, tcgen05 cta_group::1.
+extern "C" __global__ void __launch_bounds__(kThreads, 1) arkb_loop_kernel(const __grid_constant__ LaunchParams P) {
+    loop_main<false>(P);
+}
+// Processors 2q and 2q+1 form a cluster (one SM pair); matmul tiles are shared by the pair (cta_group::2).
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    arkb_loop_kernel_pair(const __grid_constant__ LaunchParams P) {
+    loop_main<true>(P);
 }
 
 }  // namespace arkb
@@ -146,12 +169,16 @@ namespace arkb {
 size_t loop_kernel_smem_bytes() { return kGemmSmemBytes + 1024; }
 
 cudaError_t loop_kernel_prepare() {
-    return cudaFuncSetAttribute(arkb_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(arkb_loop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)loop_kernel_smem_bytes());
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(arkb_loop_kernel_pair, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)loop_kernel_smem_bytes());
 }
 
 cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream) {
-    arkb_loop_kernel<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
+    if (P.pair_mode) arkb_loop_kernel_pair<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
+    else arkb_loop_kernel<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
     return cudaGetLastError();
 }
 }  // namespace arkb

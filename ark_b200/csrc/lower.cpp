@@ -379,22 +379,25 @@ struct Lowerer {
         g.dtype = A.dtype;
         g.act = act < 0 ? ACT_NONE : act;
         g.c_vec = (aligned16(pc) && ldc % 8 == 0 && g.c_stride_c % 8 == 0 && g.c_stride_n % 8 == 0) ? 1 : 0;
-        const int64_t P = proc.count();
-        const int64_t tiles_m = (M + 127) / 128;
+        const int tile_m = prog.pair_mode ? 256 : 128;
+        g.tile_m = tile_m;
+        const int64_t P = prog.pair_mode ? proc.count() / 2 : proc.count();
+        const int64_t tiles_m = (M + tile_m - 1) / tile_m;
         if (full) {
             std::vector<int> cand = {256, 128, 64};
-            if (!g.b_mn_major) { cand.push_back(32); cand.push_back(16); }
+            if (!g.b_mn_major) { cand.push_back(32); if (!prog.pair_mode) cand.push_back(16); }
             int tile_n = cand.back();
             for (int c : cand) {
                 int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
                 if (units >= P) { tile_n = c; break; }
             }
             if (N < tile_n) tile_n = (int)((N + 15) / 16 * 16);  // narrow outputs: one tile covers N
+            if (prog.pair_mode && tile_n % 32) tile_n += 16;     // each CTA of a pair stages half the columns
             g.tile_n = tile_n;
             g.plan_tiles = 0;
             g.tiles_m = (int32_t)tiles_m;
             g.tiles_n = (int32_t)((N + tile_n - 1) / tile_n);
-            g.raster_group = (int32_t)std::min<int64_t>(tiles_m, 8);
+            g.raster_group = (int32_t)std::min<int64_t>(tiles_m, 16);  // ~sqrt(#CTAs * tile_n / tile_m): least A+B bytes per wave
             g.n_units = (int32_t)(bn * bc * tiles_m * g.tiles_n);
         } else {
             // honour the plan's task ids: tile id -> (n, c, tile_h, tile_w), w fastest
@@ -404,7 +407,7 @@ struct Lowerer {
             if (ptm <= 0 || ptn <= 0) throw Error(E_PLAN, "TileShapeMNK must be positive");
             int tile_n = 0;
             for (int c = 256; c >= 16; c -= 16)
-                if (ptn % c == 0) { tile_n = c; break; }
+                if (ptn % c == 0 && (!prog.pair_mode || c % 32 == 0)) { tile_n = c; break; }
             if (!tile_n) throw Error(E_UNSUPPORTED, "Matmul: tile N of a partial TaskRange must be a multiple of 16");
             g.tile_n = tile_n;
             g.plan_tiles = 1;
@@ -413,7 +416,7 @@ struct Lowerer {
             const int64_t pM = pad[pad.size() - 2], pN = pad[pad.size() - 1];
             g.p_tiles_h = (int32_t)((pM + ptm - 1) / ptm);
             g.p_tiles_w = (int32_t)((pN + ptn - 1) / ptn);
-            g.sub_m = (int32_t)((ptm + 127) / 128);
+            g.sub_m = (int32_t)((ptm + tile_m - 1) / tile_m);
             g.sub_n = (int32_t)(ptn / tile_n);
             g.task_b = (int32_t)tg.task_range.b;
             g.task_s = (int32_t)tg.task_range.s;
@@ -438,7 +441,8 @@ struct Lowerer {
         // 1-D operands ([K] vectors) are viewed as one row / one column
         std::vector<int64_t> ash2 = ash, bsh2 = bsh;
         mk(A, ash2, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
-        mk(B, bsh2, bst, pb, 64, g.b_mn_major ? 64 : (uint32_t)g.tile_n, &g.tmB);
+        // K-major B: one box holds the rows (output columns) this CTA stages — all of the tile, or half in a pair
+        mk(B, bsh2, bst, pb, 64, g.b_mn_major ? 64 : (uint32_t)(prog.pair_mode ? g.tile_n / 2 : g.tile_n), &g.tmB);
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
@@ -645,6 +649,28 @@ struct Lowerer {
         }
     }
 
+    // CTA pairs (clusters of 2) can share matmul tiles when the grid is even and every
+    // Matmul runs on a processor range made of whole pairs, over its full task range
+    // (or with plan tiles that are multiples of 256 rows).
+    bool pair_eligible() const {
+        if (plan.num_processors % 2) return false;
+        bool any = false;
+        for (auto &pg : plan.processor_groups)
+            for (auto &rg : pg.resource_groups)
+                for (auto &tg : rg.task_groups)
+                    for (auto &op : plan.task(tg.task_id).ops) {
+                        if (op.type != "Matmul") continue;
+                        any = true;
+                        if (rg.proc.s != 1 || rg.proc.b % 2 || rg.proc.count() % 2) return false;
+                        if (!full_range(tg.task_range, num_tasks(op))) {
+                            if (!op.config.is_object() || !op.config.contains("TileShapeMNK")) return false;
+                            auto tile = op.config.at("TileShapeMNK").as_int_vec();
+                            if (tile.size() != 3 || tile[0] % 256 || tile[1] % 32) return false;
+                        }
+                    }
+        return any;
+    }
+
     static void touched(const TaskInfo &ti, std::set<int64_t> &reads, std::set<int64_t> &writes) {
         for (auto &op : ti.ops) {
             for (auto &t : op.reads) reads.insert(t.buffer_id);
@@ -658,6 +684,7 @@ struct Lowerer {
             throw Error(E_UNSUPPORTED, "plan needs " + std::to_string(plan.num_processors) + " processors, the device has " +
                                            std::to_string(env.num_sm) + " SMs (the loop kernel keeps one CTA per processor resident)");
         prog.grid = plan.num_processors;
+        prog.pair_mode = env.allow_pair && pair_eligible();
         std::vector<Range> unsynced;
         bool first_pg = true;
         for (auto &pg : plan.processor_groups) {
@@ -715,7 +742,7 @@ struct Lowerer {
 
 std::string Program::dump() const {
     std::ostringstream os;
-    os << "grid=" << grid << " stages=" << stages.size() << " sync_groups=" << n_sync_groups
+    os << "grid=" << grid << (pair_mode ? " pairs" : "") << " stages=" << stages.size() << " sync_groups=" << n_sync_groups
        << " peer_barriers=" << peersyncs_per_iter << "\n";
     for (size_t i = 0; i < notes.size(); ++i) os << i << ": " << notes[i] << "\n";
     return os.str();

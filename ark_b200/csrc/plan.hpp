@@ -146,6 +146,7 @@ struct LowerEnv {
     char *comm[kMaxPeers] = {};
     TmapEncoder encode_tmap;
     int num_sm = 148;
+    bool allow_pair = true;  // let matmul tiles span CTA pairs (tcgen05 cta_group::2) when the plan permits
 };
 
 struct Program {
@@ -156,6 +157,7 @@ struct Program {
     int syncs_per_iter[kMaxSyncGroups] = {};
     int peersyncs_per_iter = 0;
     int oneshots_per_iter = 0;
+    bool pair_mode = false;  // launch clusters of 2 CTAs; matmul tiles are 256 x tile_n per pair
     std::string dump() const;
 };
 

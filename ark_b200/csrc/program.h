@@ -113,7 +113,7 @@ struct GemmArgs {
     int32_t tiles_m, tiles_n, raster_group;
     int32_t ptm, ptn, p_tiles_h, p_tiles_w, sub_m, sub_n, task_b, task_s;
     int32_t n_units;
-    int32_t pad;
+    int32_t tile_m;                  // 128 (one CTA per tile) or 256 (CTA pair per tile)
 };
 
 struct GemvArgs {
@@ -252,6 +252,7 @@ struct LaunchParams {
     int32_t iters;
     int32_t rank, nranks;
     int32_t peersyncs_per_iter;
+    int32_t pair_mode;            // 1: launched as clusters of 2 CTAs, matmul tiles are 256 rows per CTA pair
     int32_t syncs_per_iter[kMaxSyncGroups];
     char *arena[kMaxPeers];       // arena base of every rank as mapped here (own included)
     char *comm[kMaxPeers];        // comm allocation of every rank as mapped here (own included)

@@ -37,38 +37,54 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs
+    (one streaming nvidia-smi process, a line every 20 ms)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index=0):
-        self.index, self.rows, self.stop_flag, self.th = index, [], False, None
+        self.index, self.rows, self.proc, self.th = index, [], None, None
+        self.t_rows = []
 
     def _run(self):
-        while not self.stop_flag:
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
-                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
-            except Exception:
-                pass
-            time.sleep(0.1)
+        for line in self.proc.stdout:
+            c = [x.strip() for x in line.split(",")]
+            if len(c) >= 7:
+                self.rows.append(c)
+                self.t_rows.append(time.perf_counter())
 
     def start(self):
-        self.th = threading.Thread(target=self._run, daemon=True)
-        self.th.start()
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                                          str(self.index), "-lms", "20"], stdout=subprocess.PIPE, text=True)
+            self.th = threading.Thread(target=self._run, daemon=True)
+            self.th.start()
+            time.sleep(0.3)  # let the first lines arrive before the timed region starts
+        except Exception:
+            self.proc = None
 
-    def stop(self):
-        self.stop_flag = True
+    def stop(self, t_begin=None, t_end=None):
+        time.sleep(0.05)
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
         if self.th:
-            self.th.join(timeout=6)
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+            self.th.join(timeout=5)
+        rows = self.rows
+        if t_begin is not None:
+            sel = [r for r, t in zip(self.rows, self.t_rows) if t_begin <= t <= t_end]
+            rows = sel if sel else rows
+        sm = sorted(int(float(r[0])) for r in rows if r[0].replace(".", "").isdigit())
+        mx = [int(float(r[1])) for r in rows if r[1].replace(".", "").isdigit()]
+        pw = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].lower().startswith("active") for r in self.rows)]
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(self.rows)}
+        reasons = [n for i, n in enumerate(names) if any(r[3 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "power_w_max": max(pw) if pw else None, "reasons": reasons,
+                "samples": len(rows)}
 
 
 def synth(rank, world):
@@ -130,6 +146,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ark_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the loop-mode end-to-end leg (profiler captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="reduced size for profiler captures only")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -180,18 +197,29 @@ def main():
     barrier()
     if rank == 0:
         sampler.start()
+    t_b = time.perf_counter()
     e0.record(stream)
     ex.run(args.steps)
     e1.record(stream)
     ex.wait()
+    t_e = time.perf_counter()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(t_b, t_e) if rank == 0 else None
     st = ex.status()
     n_stages = st["n_stages"]
     ex.stop()
 
     # ---- end to end through the Executor API with host buffers (loop mode) ----
+    if args.no_e2e:
+        ex.destroy()
+        value = flops / (ms / args.steps * 1e-3) / 1e12
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms / args.steps,
+                              "tokens": tokens, "note": "device-timed leg only"}))
+        if world > 1:
+            torch.distributed.destroy_process_group()
+        return
     hx = torch.from_numpy(x.copy()).pin_memory()
     hy = torch.empty((tokens, D_MODEL), dtype=torch.float16).pin_memory()
     ex2 = ark.Executor(local, 0, "bench_e2e", str(plan), loop_mode=True, allgather=allgather)
