@@ -3,11 +3,11 @@
 # translation unit per op group, compiled in parallel) plus the host runtime.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-OUT="$HERE/../lib"
+OUT="${ARKB_OUT:-$HERE/../lib}"
 mkdir -p "$OUT/obj"
 NVCC=${NVCC:-nvcc}
 ARCH="-gencode arch=compute_100a,code=sm_100a"
-CUFLAGS="$ARCH -lineinfo -O3 -std=c++17 -rdc=true -maxrregcount=128 -Xcompiler -fPIC ${ARKB_PTXAS_V:+-Xptxas -v}"
+CUFLAGS="$ARCH ${ARKB_DEFS:-} -lineinfo -O3 -std=c++17 -rdc=true -maxrregcount=128 -Xcompiler -fPIC ${ARKB_PTXAS_V:+-Xptxas -v}"
 pids=()
 for f in loop_kernel dev_ewise dev_reduce dev_gemm dev_comm; do
   if [ "$HERE/$f.cu" -nt "$OUT/obj/$f.o" ] || [ -n "$(find "$HERE" -maxdepth 1 \( -name '*.h' -o -name '*.cuh' \) -newer "$OUT/obj/$f.o" 2>/dev/null)" ] || [ ! -f "$OUT/obj/$f.o" ]; then

@@ -193,7 +193,27 @@ __device__ __forceinline__ float gelu_f(float x) {
 }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
 
+// Activations for 16-bit outputs (GEMM epilogue): hardware exp2 / reciprocal
+// approximations, relative error ~1e-6, far below the storage rounding.
+__device__ __forceinline__ float fast_sigmoid(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+__device__ __forceinline__ float apply_act_fast(int act, float v) {
+    switch (act) {
+        case ACT_RELU: return fmaxf(v, 0.0f);
+        case ACT_GELU: {
+            const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+            const float u = k0 * (v + k1 * v * v * v);
+            return v * fast_sigmoid(2.0f * u);
+        }
+        case ACT_SIGMOID: return fast_sigmoid(v);
+        case ACT_SILU: return v * fast_sigmoid(v);
+        default: return v;
+    }
+}
+
 __device__ __forceinline__ float apply_act(int act, float v) {
+#ifdef ARKB_EXP_NO_ACT
+    return v;
+#endif
     switch (act) {
         case ACT_RELU: return fmaxf(v, 0.0f);
         case ACT_GELU: return gelu_f(v);

@@ -34,7 +34,11 @@ struct GemmCfg {
     static constexpr int kStageBytes = kGemmABytes + kBBytes;
 };
 constexpr int kGemmMaxStages = 6;
-constexpr int kGemmSmemBytes = 4 * (kGemmABytes + 256 * kGemmBK * 2);  // 192 KiB in both modes
+constexpr int kGemmPipeBytes = 4 * (kGemmABytes + 256 * kGemmBK * 2);  // 192 KiB of operand stages in both modes
+// epilogue staging: per epilogue warp two 32-row x 64-byte blocks (64-byte swizzle)
+constexpr int kEpiBlockBytes = 32 * 64;
+constexpr int kEpiStageBytes = 4 * 2 * kEpiBlockBytes;                  // 16 KiB
+constexpr int kGemmSmemBytes = kGemmPipeBytes + kEpiStageBytes;
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5;
 
@@ -125,6 +129,24 @@ __device__ __forceinline__ void umma_commit(void *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// TMA store of a staged block (shared -> global), tracked by bulk async-groups.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tm, const void *smem_src, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tm),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Wait until at most N of this thread's bulk groups are still reading shared memory / still in flight.
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -50,7 +50,8 @@ static void encode_tmap_cuda(CUtensorMap *out, const TmapSpec &sp) {
         if (strides[i] == 0 || strides[i] % 16) strides[i] = ((strides[i] + 15) / 16 + (strides[i] == 0)) * 16;
     CUtensorMapDataType dt = sp.dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUresult r = get_encode_fn()(out, dt, 4, const_cast<void *>(sp.base), dims, strides, box, estr,
-                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 sp.swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) throw Error(E_GPU, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
 }

@@ -424,8 +424,9 @@ struct Lowerer {
         }
         // tensor maps: dims {inner, rows, C, N}
         auto mk = [&](const TensorDesc &T, const std::vector<int64_t> &sh, const std::vector<int64_t> &st, char *base,
-                      uint32_t box_inner, uint32_t box_rows, CUtensorMap *out) {
+                      uint32_t box_inner, uint32_t box_rows, CUtensorMap *out, int swizzle = 128) {
             TmapSpec sp;
+            sp.swizzle_bytes = swizzle;
             sp.base = base;
             sp.dtype = T.dtype;
             sp.dims[0] = (uint64_t)sh[3];
@@ -443,6 +444,9 @@ struct Lowerer {
         mk(A, ash2, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
         // K-major B: one box holds the rows (output columns) this CTA stages — all of the tile, or half in a pair
         mk(B, bsh2, bst, pb, 64, g.b_mn_major ? 64 : (uint32_t)(prog.pair_mode ? g.tile_n / 2 : g.tile_n), &g.tmB);
+        // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
+        g.c_tma = (g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
+        if (g.c_tma) mk(C, csh, cst, pc, 32, 32, &g.tmC, 64);
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +

@@ -136,6 +136,7 @@ struct TmapSpec {
     uint64_t dims[4];
     uint64_t strides_bytes[3];  // strides of dims 1..3
     uint32_t box[4];
+    int swizzle_bytes = 128;  // 128 or 64
 };
 // Encodes a 128-byte-swizzled tiled tensor map; throws on failure.
 using TmapEncoder = std::function<void(CUtensorMap *out, const TmapSpec &spec)>;

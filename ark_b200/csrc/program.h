@@ -91,6 +91,7 @@ struct RowOpArgs {
 struct GemmArgs {
     CUtensorMap tmA;  // dims {inner, rows, C, N}; box {64, 128 or 64, 1, 1}, 128-byte swizzle
     CUtensorMap tmB;  // dims {inner, rows, C, N}; box {64, tile_n or 64, 1, 1}
+    CUtensorMap tmC;  // output, dims {N, M, C, N}; box {32, 32, 1, 1}, 64-byte swizzle (used when c_tma)
     void *C;
     const void *bias;     // optional tensor added in the epilogue (same layout as C)
     int64_t ldc;
@@ -103,6 +104,8 @@ struct GemmArgs {
     int32_t act;
     int32_t tile_n;                  // UMMA N (multiple of 16, <= 256)
     int32_t c_vec;                   // 1: C rows allow 16-byte stores
+    int32_t c_tma;                   // 1: the epilogue stages 32x32 blocks in shared memory and stores them with TMA
+    int32_t pad1;
     // Unit enumeration. plan_tiles == 0: units are this engine's own tiles
     // (128 x tile_n) over the whole output, rasterised in groups of
     // `raster_group` m-tiles. plan_tiles == 1: units follow the plan's task ids

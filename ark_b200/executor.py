@@ -12,7 +12,8 @@ import numpy as np
 from .error import STATUS_TO_ERROR, BaseError, InvalidUsageError
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libark_b200.so")
+# ARK_B200_LIB overrides the library location (e.g. an instrumented build)
+LIB_PATH = os.environ.get("ARK_B200_LIB") or os.path.join(_HERE, "lib", "libark_b200.so")
 _lib = None
 
 ALLGATHER_FN = ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t)

@@ -6,22 +6,23 @@ from . import ops
 from .planner import PlannerContext
 
 
-def build_ffn(tokens, d_model, d_ff, dtype, rank=0, world_size=1, act="gelu", fuse_act=True):
+def build_ffn(tokens, d_model, d_ff, dtype, rank=0, world_size=1, act="gelu", fuse_act=True, weights_nk=False):
     """Adds the block to the global model. Returns (x, w1_shard, w2_shard, out).
     w1_shard is [d_model, d_ff / world_size], w2_shard is [d_ff / world_size, d_model]."""
     if d_ff % world_size:
         raise ValueError("d_ff must be divisible by the world size")
     shard = d_ff // world_size
     x = ops.tensor([tokens, d_model], dtype, name="x")
-    w1 = ops.tensor([d_model, shard], dtype, name="w1")
-    w2 = ops.tensor([shard, d_model], dtype, name="w2")
+    # weights_nk stores the weights [out_features, in_features] (as nn.Linear / the llama example do)
+    w1 = ops.tensor([shard, d_model] if weights_nk else [d_model, shard], dtype, name="w1")
+    w2 = ops.tensor([d_model, shard] if weights_nk else [shard, d_model], dtype, name="w2")
     actf = getattr(ops, act)
     if fuse_act:
         with PlannerContext(sync=False):  # one task: the activation runs in the GEMM epilogue
-            h = actf(ops.matmul(x, w1))
+            h = actf(ops.matmul(x, w1, transpose_other=weights_nk))
     else:
-        h = actf(ops.matmul(x, w1))
-    y = ops.matmul(h, w2)
+        h = actf(ops.matmul(x, w1, transpose_other=weights_nk))
+    y = ops.matmul(h, w2, transpose_other=weights_nk)
     if world_size > 1:
         y = ops.all_reduce(y, rank, world_size, output=y)
     return x, w1, w2, y

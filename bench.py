@@ -148,6 +148,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the loop-mode end-to-end leg (profiler captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="reduced size for profiler captures only")
+    ap.add_argument("--weights-nk", action="store_true", help="store the weights [out, in] (K-major B operands)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -172,10 +173,12 @@ def main():
     ark.set_rank(rank)
     ark.set_world_size(world)
     from ark_b200.ffn import build_ffn
-    tx, t1, t2, ty = build_ffn(tokens, D_MODEL, D_FF, ark.fp16, rank, world, act="gelu")
+    tx, t1, t2, ty = build_ffn(tokens, D_MODEL, D_FF, ark.fp16, rank, world, act="gelu", weights_nk=args.weights_nk)
     plan = ark.Planner(local).plan()
     x, w1, w2 = synth(rank, world)
     x = x[:tokens]
+    if args.weights_nk:
+        w1, w2 = np.ascontiguousarray(w1.T), np.ascontiguousarray(w2.T)
 
     def barrier():
         if world > 1:
@@ -216,7 +219,7 @@ def main():
         value = flops / (ms / args.steps * 1e-3) / 1e12
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "ms_per_step": ms / args.steps,
-                              "tokens": tokens, "note": "device-timed leg only"}))
+                              "tokens": tokens, "clocks": clocks, "note": "device-timed leg only"}))
         if world > 1:
             torch.distributed.destroy_process_group()
         return
