@@ -211,9 +211,6 @@ __device__ __forceinline__ float apply_act_fast(int act, float v) {
 }
 
 __device__ __forceinline__ float apply_act(int act, float v) {
-#ifdef ARKB_EXP_NO_ACT
-    return v;
-#endif
     switch (act) {
         case ACT_RELU: return fmaxf(v, 0.0f);
         case ACT_GELU: return gelu_f(v);

@@ -40,7 +40,7 @@ constexpr int kEpiBlockBytes = 32 * 64;
 constexpr int kEpiStageBytes = 4 * 2 * kEpiBlockBytes;                  // 16 KiB
 constexpr int kGemmSmemBytes = kGemmPipeBytes + kEpiStageBytes;
 constexpr int kTmemCols = 512;
-constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5;
+constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5, kProducerWarpB = 6;  // warp 4 loads A, warp 6 loads B
 
 struct GemmPipe {
     unsigned long long full[kGemmMaxStages];
@@ -231,7 +231,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 __device__ __forceinline__ void gemm_pipe_init(GemmPipe *pp, bool pair) {
     for (int s = 0; s < kGemmMaxStages; ++s) {
-        mbar_init(&pp->full[s], 1);
+        mbar_init(&pp->full[s], 2);  // one arrival per producer warp (A and B)
         mbar_init(&pp->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {

@@ -10,6 +10,7 @@
 // otherwise ignored) — here a whole CTA works on one stage at a time and an
 // op's work is split over the CTAs of its range by the op's own kernel.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <set>
 #include <sstream>

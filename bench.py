@@ -148,6 +148,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the loop-mode end-to-end leg (profiler captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="reduced size for profiler captures only")
+    ap.add_argument("--procs", type=int, default=0, help="experiment: plan for this many SMs instead of all")
     ap.add_argument("--weights-nk", action="store_true", help="store the weights [out, in] (K-major B operands)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -174,7 +175,7 @@ def main():
     ark.set_world_size(world)
     from ark_b200.ffn import build_ffn
     tx, t1, t2, ty = build_ffn(tokens, D_MODEL, D_FF, ark.fp16, rank, world, act="gelu", weights_nk=args.weights_nk)
-    plan = ark.Planner(local).plan()
+    plan = ark.Planner(local, num_sm=args.procs or None).plan()
     x, w1, w2 = synth(rank, world)
     x = x[:tokens]
     if args.weights_nk:

@@ -1,0 +1,109 @@
+"""Worker of the multi-GPU tests: one process per GPU under torch.distributed.run.
+Checks, on every rank, the in-kernel all_reduce (one-shot and two-shot) against
+the exact fp32 sum of the rank inputs (bit-exact), send/recv between
+neighbours, the reference's naive all_reduce composition, and the
+tensor-parallel FFN block against the oracle."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import ark_b200 as ark  # noqa: E402
+from ark_b200.executor import torch_allgather  # noqa: E402
+from ark_b200.ffn import build_ffn  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ag = torch_allgather()
+
+    def run(outputs, feeds, iters=1, loop_mode=True):
+        plan = ark.Planner(local).plan()
+        ex = ark.Executor(local, 0, "multi", str(plan), loop_mode, allgather=ag)
+        ex.set_wait_limit(5_000_000_000)
+        ex.compile()
+        for t, a in feeds.items():
+            ex.tensor_from_numpy(t, a)
+        ex.barrier()
+        ex.launch()
+        ex.run(iters)
+        ex.wait()
+        outs = [ex.tensor_to_numpy(t) for t in outputs]
+        ex.barrier()
+        ex.stop()
+        ex.destroy()
+        return outs
+
+    def fresh():
+        ark.init()
+        ark.set_rank(rank)
+        ark.set_world_size(world)
+
+    # ---- all_reduce sweep: values ~ U(-1,1) from seed+rank, exact fp32 sum then one rounding ----
+    for n in (512, 4096, 64 * 1024, 128 * 1024, 1024 * 1024, 8 * 1024 * 1024):
+        for dt, adt in (("fp16", ark.fp16), ("bf16", ark.bf16), ("fp32", ark.fp32)):
+            if dt != "fp16" and n not in (4096, 1024 * 1024):
+                continue
+            ins = [O.to_storage(np.random.default_rng(1000 + r).uniform(-1, 1, n).astype(np.float32), dt) for r in range(world)]
+            fresh()
+            t = ark.tensor([n], adt)
+            out = ark.all_reduce(t, rank, world, output=t)
+            (got,) = run([out], {t: ins[rank]})
+            want = O.all_reduce(ins, dt)
+            assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), f"all_reduce {dt} n={n} rank {rank}"
+    # closed form of the reference tests: rank r holds r+1 (ops_all_reduce_test.cpp:9-24), 3 iterations in place
+    fresh()
+    t = ark.tensor([8192], ark.fp16)
+    out = ark.all_reduce(t, rank, world, output=t)
+    (got,) = run([out], {t: np.full(8192, rank + 1, np.float16)}, iters=1)
+    assert np.all(got == np.float16(world * (world + 1) / 2)), "closed-form all_reduce"
+
+    # ---- send / recv ring: every rank sends its tensor to rank+1 ----
+    fresh()
+    src = ark.tensor([4, 1024], ark.fp16)
+    dstbuf = ark.tensor([4, 1024], ark.fp16)
+    s = ark.send(src, (rank + 1) % world, tag=7)
+    ark.send_done(s)
+    r = ark.recv(dstbuf, (rank - 1) % world, tag=7)
+    res = ark.add(r, 0.0)
+    (got,) = run([res], {src: np.full((4, 1024), rank + 1, np.float16)})
+    assert np.all(got == np.float16((rank - 1) % world + 1)), f"send/recv on rank {rank}"
+
+    # ---- the reference's naive all_reduce composition (send/send_done/recv/add rounds) ----
+    fresh()
+    t = ark.tensor([2048], ark.fp16)
+    out = ark.all_reduce(t, rank, world, naive=True)
+    (got,) = run([out], {t: np.full(2048, rank + 1, np.float16)})
+    assert np.all(got == np.float16(world * (world + 1) / 2)), "naive all_reduce"
+
+    # ---- tensor-parallel FFN: partial products summed in-kernel ----
+    tokens, d, f = 256, 512, 2048
+    rng = np.random.default_rng(5)
+    x = O.to_storage(rng.normal(0, 1, (tokens, d)).astype(np.float32), "fp16")
+    w1 = O.to_storage(rng.normal(0, 0.02, (d, f)).astype(np.float32), "fp16")
+    w2 = O.to_storage(rng.normal(0, 0.02, (f, d)).astype(np.float32), "fp16")
+    sh = f // world
+    fresh()
+    tx, t1, t2, ty = build_ffn(tokens, d, f, ark.fp16, rank, world)
+    (got,) = run([ty], {tx: x, t1: np.ascontiguousarray(w1[:, rank * sh:(rank + 1) * sh]),
+                        t2: np.ascontiguousarray(w2[rank * sh:(rank + 1) * sh, :])})
+    parts = [O.matmul(O.matmul(x, np.ascontiguousarray(w1[:, r * sh:(r + 1) * sh]), "fp16", act="gelu"),
+                      np.ascontiguousarray(w2[r * sh:(r + 1) * sh, :]), "fp16") for r in range(world)]
+    want = O.all_reduce(parts, "fp16")
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert err.mean() <= 2e-3 and err.max() <= 5e-2, (err.mean(), err.max())
+
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank}: multi-GPU checks passed")
+
+
+if __name__ == "__main__":
+    main()
