@@ -111,6 +111,17 @@ __device__ __forceinline__ int8_t from_f32<int8_t>(float v) { return (int8_t)v; 
 template <>
 __device__ __forceinline__ uint8_t from_f32<uint8_t>(float v) { return (uint8_t)v; }
 
+// 16-byte global load that does not allocate a line in L1. The loop kernel gives
+// almost all of the SM's L1/shared storage to shared memory, so the few L1 lines
+// that are left would otherwise bound the number of loads in flight.
+__device__ __forceinline__ uint4 ldg16_stream(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
 // Load N consecutive elements (N*sizeof(T) is 4, 8, 16 or 32 bytes, address
 // aligned to min(16, N*sizeof(T))) and widen to fp32.
 template <typename T, int N>
@@ -122,13 +133,33 @@ __device__ __forceinline__ void load_vec(const T *p, float (&f)[N]) {
     } u;
     if constexpr (BYTES >= 16) {
 #pragma unroll
-        for (int i = 0; i < BYTES / 16; ++i) u.q[i] = reinterpret_cast<const uint4 *>(p)[i];
+        for (int i = 0; i < BYTES / 16; ++i) u.q[i] = ldg16_stream(reinterpret_cast<const uint4 *>(p) + i);
     } else if constexpr (BYTES == 8) {
         uint2 v = *reinterpret_cast<const uint2 *>(p);
         u.q[0].x = v.x;
         u.q[0].y = v.y;
     } else if constexpr (BYTES == 4) {
         u.q[0].x = *reinterpret_cast<const uint32_t *>(p);
+    } else {
+#pragma unroll
+        for (int i = 0; i < N; ++i) u.e[i] = p[i];
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = to_f32(u.e[i]);
+}
+
+// Same as load_vec but through L1: for small operands that are re-read many times
+// (norm weights, broadcast rows).
+template <typename T, int N>
+__device__ __forceinline__ void load_vec_cached(const T *p, float (&f)[N]) {
+    constexpr int BYTES = N * sizeof(T);
+    union {
+        uint4 q[(BYTES + 15) / 16];
+        T e[N];
+    } u;
+    if constexpr (BYTES >= 16) {
+#pragma unroll
+        for (int i = 0; i < BYTES / 16; ++i) u.q[i] = reinterpret_cast<const uint4 *>(p)[i];
     } else {
 #pragma unroll
         for (int i = 0; i < N; ++i) u.e[i] = p[i];
@@ -195,7 +226,7 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 
 // Activations for 16-bit outputs (GEMM epilogue): hardware exp2 / reciprocal
 // approximations, relative error ~1e-6, far below the storage rounding.
-__device__ __forceinline__ float fast_sigmoid(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float apply_act_fast(int act, float v) {
     switch (act) {
         case ACT_RELU: return fmaxf(v, 0.0f);

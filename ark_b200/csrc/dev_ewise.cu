@@ -9,13 +9,15 @@
 
 namespace arkb {
 
-template <int N>
+// FAST: results are rounded to a 16-bit type, so the hardware exp2 / reciprocal
+// approximations (relative error ~1e-6) are used for gelu / sigmoid / silu.
+template <int N, bool FAST>
 __device__ __forceinline__ void ewise_math(int op, float scalar, const float (&x)[N], const float (&y)[N],
                                            float (&r)[N]) {
     switch (op) {
         case EW_GELU:
 #pragma unroll
-            for (int i = 0; i < N; ++i) r[i] = gelu_f(x[i]);
+            for (int i = 0; i < N; ++i) r[i] = FAST ? apply_act_fast(ACT_GELU, x[i]) : gelu_f(x[i]);
             break;
         case EW_EXP:
 #pragma unroll
@@ -31,11 +33,11 @@ __device__ __forceinline__ void ewise_math(int op, float scalar, const float (&x
             break;
         case EW_SIGMOID:
 #pragma unroll
-            for (int i = 0; i < N; ++i) r[i] = sigmoid_f(x[i]);
+            for (int i = 0; i < N; ++i) r[i] = FAST ? fast_sigmoid(x[i]) : sigmoid_f(x[i]);
             break;
         case EW_SILU:
 #pragma unroll
-            for (int i = 0; i < N; ++i) r[i] = x[i] * sigmoid_f(x[i]);
+            for (int i = 0; i < N; ++i) r[i] = x[i] * (FAST ? fast_sigmoid(x[i]) : sigmoid_f(x[i]));
             break;
         case EW_SQRT:
 #pragma unroll
@@ -102,59 +104,144 @@ __device__ void ewise_walk(const EwiseArgs &a, int p, int P) {
     const TI *in0 = reinterpret_cast<const TI *>(a.in0.ptr);
     const TI *in1 = reinterpret_cast<const TI *>(a.in1.ptr);
     if (a.flat) {
-        constexpr int U = 4;  // independent accesses in flight per thread
-        for (int64_t u0 = tid; u0 < a.n_units; u0 += nth * U) {
-            float x[U][V], y[U][V], r[V];
+        const int64_t n_units = a.n_units;
+        const float scalar = a.scalar;
+        if constexpr (V * sizeof(TI) == 16) {
+            // 16-byte units kept packed in registers until they are consumed, so that eight
+            // (unary) or six (binary) loads per operand are in flight per thread: with one
+            // 512-thread CTA per SM the bytes in flight, not the issue rate, bound the bandwidth
+            if (!bin) {
+                constexpr int U = 8;
+                for (int64_t u0 = tid; u0 < n_units; u0 += nth * U) {
+                    uint4 rx[U];
 #pragma unroll
-            for (int j = 0; j < U; ++j) {
-                int64_t u = u0 + j * nth;
-                if (u < a.n_units) {
-                    if (rd0) load_vec<TI, V>(in0 + u * V, x[j]);
-                    if (bin) load_vec<TI, V>(in1 + u * V, y[j]);
+                    for (int j = 0; j < U; ++j)
+                        if (rd0 && u0 + j * nth < n_units) rx[j] = ldg16_stream(in0 + (u0 + j * nth) * V);
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const int64_t u = u0 + j * nth;
+                        if (u < n_units) {
+                            float x[V], r[V];
+                            const TI *e = reinterpret_cast<const TI *>(&rx[j]);
+#pragma unroll
+                            for (int i = 0; i < V; ++i) x[i] = to_f32(e[i]);
+                            ewise_math<V, sizeof(TO) == 2>(op, scalar, x, x, r);
+                            store_vec<TO, V>(out + u * V, r);
+                        }
+                    }
+                }
+            } else {
+                constexpr int U = 6;
+                for (int64_t u0 = tid; u0 < n_units; u0 += nth * U) {
+                    uint4 rx[U], ry[U];
+#pragma unroll
+                    for (int j = 0; j < U; ++j)
+                        if (u0 + j * nth < n_units) {
+                            rx[j] = ldg16_stream(in0 + (u0 + j * nth) * V);
+                            ry[j] = ldg16_stream(in1 + (u0 + j * nth) * V);
+                        }
+#pragma unroll
+                    for (int j = 0; j < U; ++j) {
+                        const int64_t u = u0 + j * nth;
+                        if (u < n_units) {
+                            float x[V], y[V], r[V];
+                            const TI *ex = reinterpret_cast<const TI *>(&rx[j]);
+                            const TI *ey = reinterpret_cast<const TI *>(&ry[j]);
+#pragma unroll
+                            for (int i = 0; i < V; ++i) {
+                                x[i] = to_f32(ex[i]);
+                                y[i] = to_f32(ey[i]);
+                            }
+                            ewise_math<V, sizeof(TO) == 2>(op, scalar, x, y, r);
+                            store_vec<TO, V>(out + u * V, r);
+                        }
+                    }
                 }
             }
-#pragma unroll
-            for (int j = 0; j < U; ++j) {
-                int64_t u = u0 + j * nth;
-                if (u < a.n_units) {
-                    ewise_math<V>(op, a.scalar, x[j], y[j], r);
-                    store_vec<TO, V>(out + u * V, r);
-                }
-            }
+            return;
+        }
+        for (int64_t u = tid; u < n_units; u += nth) {
+            float x[V], y[V], r[V];
+            if (rd0) load_vec<TI, V>(in0 + u * V, x);
+            if (bin) load_vec<TI, V>(in1 + u * V, y);
+            ewise_math<V, sizeof(TO) == 2>(op, scalar, x, y, r);
+            store_vec<TO, V>(out + u * V, r);
         }
         return;
     }
-    const int64_t WV = (a.out.shape[3] + V - 1) / V;
-    const int64_t H = a.out.shape[2], C = a.out.shape[1];
-    for (int64_t u = tid; u < a.n_units; u += nth) {
-        int64_t wv = u % WV, row = u / WV;
-        int64_t h = row % H;
-        row /= H;
-        int64_t c = row % C, n = row / C;
-        int64_t w = wv * V;
-        float x[V], y[V], r[V];
-        if (rd0) {
-            const TI *p0 = in0 + tref_off(a.in0, n, c, h, a.in0.stride[3] ? w : 0);
-            if (a.in0.stride[3]) {
-                load_vec<TI, V>(p0, x);
-            } else {
-                float s = to_f32(*p0);
+    // strided / broadcast walk: four units per thread in flight; 32-bit index arithmetic
+    // whenever the unit count allows it (64-bit division costs ~4x as many instructions)
+    const int64_t n_units = a.n_units;
+    const float scalar = a.scalar;
+    const TRef to = a.out, t0 = a.in0, t1 = a.in1;
+    const uint32_t WV = (uint32_t)((to.shape[3] + V - 1) / V), H = (uint32_t)to.shape[2], C = (uint32_t)to.shape[1];
+    const bool small = n_units <= 0xffffffffll;
+    // an operand with a broadcast dimension is re-read many times: keep it in L1
+    const bool bc0 = !(t0.stride[0] && t0.stride[1] && t0.stride[2] && t0.stride[3]);
+    const bool bc1 = !(t1.stride[0] && t1.stride[1] && t1.stride[2] && t1.stride[3]);
+    constexpr int U = 4;
+    for (int64_t u0 = tid; u0 < n_units; u0 += nth * U) {
+        int64_t oo[U], o0[U], o1[U];
 #pragma unroll
-                for (int i = 0; i < V; ++i) x[i] = s;
+        for (int k = 0; k < U; ++k) {
+            const int64_t u = u0 + k * nth;
+            int64_t wv, h, c, n;
+            if (small) {
+                const uint32_t uu = (uint32_t)u;
+                uint32_t row = uu / WV;
+                wv = uu - row * WV;
+                const uint32_t r2 = row / H;
+                h = row - r2 * H;
+                const uint32_t r3 = r2 / C;
+                c = r2 - r3 * C;
+                n = r3;
+            } else {
+                wv = u % WV;
+                int64_t row = u / WV;
+                h = row % H;
+                row /= H;
+                c = row % C;
+                n = row / C;
+            }
+            const int64_t w = wv * V;
+            oo[k] = tref_off(to, n, c, h, w);
+            o0[k] = tref_off(t0, n, c, h, t0.stride[3] ? w : 0);
+            o1[k] = tref_off(t1, n, c, h, t1.stride[3] ? w : 0);
+        }
+        float x[U][V], y[U][V];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            if (u0 + k * nth >= n_units) continue;
+            if (rd0) {
+                if (!t0.stride[3]) {
+                    const float sv = to_f32(in0[o0[k]]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) x[k][i] = sv;
+                } else if (bc0) {
+                    load_vec_cached<TI, V>(in0 + o0[k], x[k]);
+                } else {
+                    load_vec<TI, V>(in0 + o0[k], x[k]);
+                }
+            }
+            if (bin) {
+                if (!t1.stride[3]) {
+                    const float sv = to_f32(in1[o1[k]]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) y[k][i] = sv;
+                } else if (bc1) {
+                    load_vec_cached<TI, V>(in1 + o1[k], y[k]);
+                } else {
+                    load_vec<TI, V>(in1 + o1[k], y[k]);
+                }
             }
         }
-        if (bin) {
-            const TI *p1 = in1 + tref_off(a.in1, n, c, h, a.in1.stride[3] ? w : 0);
-            if (a.in1.stride[3]) {
-                load_vec<TI, V>(p1, y);
-            } else {
-                float s = to_f32(*p1);
 #pragma unroll
-                for (int i = 0; i < V; ++i) y[i] = s;
-            }
+        for (int k = 0; k < U; ++k) {
+            if (u0 + k * nth >= n_units) continue;
+            float r[V];
+            ewise_math<V, sizeof(TO) == 2>(op, scalar, x[k], y[k], r);
+            store_vec<TO, V>(out + oo[k], r);
         }
-        ewise_math<V>(op, a.scalar, x, y, r);
-        store_vec<TO, V>(out + tref_off(a.out, n, c, h, w), r);
     }
 }
 
@@ -174,7 +261,17 @@ __device__ void ewise_bytes(const EwiseArgs &a, int p, int P, int esize) {
     if (a.flat && a.vec > 1) {
         const uint4 *s = reinterpret_cast<const uint4 *>(a.in0.ptr);
         uint4 *d = reinterpret_cast<uint4 *>(a.out.ptr);
-        for (int64_t u = tid; u < a.n_units; u += nth) d[u] = s[u];
+        const int64_t n = a.n_units;
+        constexpr int U = 8;
+        for (int64_t u0 = tid; u0 < n; u0 += nth * U) {
+            uint4 r[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (u0 + j * nth < n) r[j] = ldg16_stream(s + u0 + j * nth);
+#pragma unroll
+            for (int j = 0; j < U; ++j)
+                if (u0 + j * nth < n) d[u0 + j * nth] = r[j];
+        }
         return;
     }
     // generic strided element copy

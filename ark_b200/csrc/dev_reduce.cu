@@ -32,18 +32,28 @@ __device__ void reduce_last_axis(const ReduceArgs &a, int p, int P) {
         const T *src = in + tref_off(a.in, n, c, h, 0);
         float acc = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
         const int64_t nv = W / V;
-        constexpr int U = 4;
-        for (int64_t v0 = lane; v0 < nv; v0 += 32 * U) {
-            float x[U][V];
+        constexpr int U = 8;
+        if constexpr (V * sizeof(T) == 16) {
+            for (int64_t v0 = lane; v0 < nv; v0 += 32 * U) {
+                uint4 rx[U];
 #pragma unroll
-            for (int j = 0; j < U; ++j)
-                if (v0 + j * 32 < nv) load_vec<T, V>(src + (v0 + j * 32) * V, x[j]);
+                for (int j = 0; j < U; ++j)
+                    if (v0 + j * 32 < nv) rx[j] = ldg16_stream(src + (v0 + j * 32) * V);
 #pragma unroll
-            for (int j = 0; j < U; ++j)
-                if (v0 + j * 32 < nv) {
+                for (int j = 0; j < U; ++j)
+                    if (v0 + j * 32 < nv) {
+                        const T *e = reinterpret_cast<const T *>(&rx[j]);
 #pragma unroll
-                    for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, x[j][i]) : acc + x[j][i];
-                }
+                        for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, to_f32(e[i])) : acc + to_f32(e[i]);
+                    }
+            }
+        } else {
+            for (int64_t v0 = lane; v0 < nv; v0 += 32) {
+                float x[V];
+                load_vec<T, V>(src + v0 * V, x);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, x[i]) : acc + x[i];
+            }
         }
         for (int64_t w = nv * V + lane; w < W; w += 32) {
             float x = to_f32(src[w]);
@@ -75,7 +85,19 @@ __device__ void reduce_other_axis(const ReduceArgs &a, int p, int P) {
         float acc[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
-        for (int64_t k = 0; k < len; ++k) {
+        constexpr int U = 8;  // independent loads in flight along the reduced axis
+        int64_t k = 0;
+        for (; k + U <= len; k += U) {
+            float x[U][V];
+#pragma unroll
+            for (int j = 0; j < U; ++j) load_vec<T, V>(src + (k + j) * astr, x[j]);
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? fmaxf(acc[i], x[j][i]) : acc[i] + x[j][i];
+            }
+        }
+        for (; k < len; ++k) {
             float x[V];
             load_vec<T, V>(src + k * astr, x);
 #pragma unroll
@@ -201,7 +223,7 @@ __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
                 for (int i = 0; i < V; ++i) f[i] = (f[i] - sub) * mul;
                 if (wgt) {
                     float g[V];
-                    load_vec<T, V>(wgt + v * V, g);
+                    load_vec_cached<T, V>(wgt + v * V, g);
 #pragma unroll
                     for (int i = 0; i < V; ++i) f[i] *= g[i];
                 }
@@ -211,11 +233,140 @@ __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
     }
 }
 
+// Single-read variant: G warps share a row and keep it packed in registers
+// (at most 8 16-byte vectors per lane); cross-warp sums go through a few floats
+// of shared memory and a named barrier per warp group. HBM sees exactly one
+// read and one write per element.
+template <typename T>
+__device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
+    constexpr int V = 16 / sizeof(T);
+    constexpr int MAXV = 8;
+    constexpr int WPC = kThreads / 32;
+    __shared__ float red[4][WPC];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = warp / G, wig = warp % G, groups = WPC / G;
+    const int li = wig * 32 + lane, lstride = 32 * G;
+    const int64_t cols = a.cols, nv = cols / V;
+    const int op = a.op;
+    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    const T *wgt = reinterpret_cast<const T *>(a.weight);
+    const int64_t in_ld = a.in_ld, out_ld = a.out_ld, rows = a.rows;
+    const float eps = a.eps, inv_cols = 1.0f / (float)cols;
+    const T *in = reinterpret_cast<const T *>(a.in);
+    const T *resid = reinterpret_cast<const T *>(a.residual);
+    T *res_out = reinterpret_cast<T *>(a.res_out);
+    T *out = reinterpret_cast<T *>(a.out);
+    auto group_sum = [&](float v, int slot, bool is_max) -> float {
+        v = is_max ? warp_max(v) : warp_sum(v);
+        if (G == 1) return v;
+        if (lane == 0) red[slot][warp] = v;
+        named_barrier(1 + group, G * 32);
+        float r = red[slot][group * G];
+        for (int i = 1; i < G; ++i) r = is_max ? fmaxf(r, red[slot][group * G + i]) : r + red[slot][group * G + i];
+        return r;
+    };
+    unsigned it = 0;
+    for (int64_t row = (int64_t)p * groups + group; row < rows; row += (int64_t)P * groups, ++it) {
+        const T *src = in + row * in_ld;
+        uint4 rx[MAXV];
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j)
+            if (li + j * lstride < nv) rx[j] = ldg16_stream(src + (int64_t)(li + j * lstride) * V);
+        if (resid) {
+            const T *rs = resid + row * in_ld;
+            T *ro = res_out + row * in_ld;
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j)
+                if (li + j * lstride < nv) {
+                    const uint4 g4 = ldg16_stream(rs + (int64_t)(li + j * lstride) * V);
+                    T *e = reinterpret_cast<T *>(&rx[j]);
+                    const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) e[i] = from_f32<T>(to_f32(e[i]) + to_f32(ge[i]));
+                    *reinterpret_cast<uint4 *>(ro + (int64_t)(li + j * lstride) * V) = rx[j];
+                }
+        }
+        float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j)
+            if (li + j * lstride < nv) {
+                const T *e = reinterpret_cast<const T *>(&rx[j]);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    const float x = to_f32(e[i]) * scale;
+                    s1 += x;
+                    s2 += x * x;
+                    mx = fmaxf(mx, x);
+                }
+            }
+        const int slot = (it & 1) * 2;
+        float mul = 1.0f, sub = 0.0f;
+        if (op == RO_RMSNORM) {
+            s2 = group_sum(s2, slot, false);
+            mul = 1.0f / sqrtf(s2 * inv_cols + eps);
+        } else if (op == RO_LAYERNORM) {
+            const float mean = group_sum(s1, slot, false) * inv_cols;
+            float var = 0.0f;
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j)
+                if (li + j * lstride < nv) {
+                    const T *e = reinterpret_cast<const T *>(&rx[j]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) var += (to_f32(e[i]) - mean) * (to_f32(e[i]) - mean);
+                }
+            var = group_sum(var, slot + 1, false);
+            mul = 1.0f / sqrtf(var * inv_cols + eps);
+            sub = mean;
+        } else {
+            mx = group_sum(mx, slot, true);
+            float se = 0.0f;
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j)
+                if (li + j * lstride < nv) {
+                    const T *e = reinterpret_cast<const T *>(&rx[j]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) se += (sizeof(T) == 2 ? __expf(to_f32(e[i]) * scale - mx) : expf(to_f32(e[i]) * scale - mx));
+                }
+            se = group_sum(se, slot + 1, false);
+            mul = 1.0f / se;
+        }
+        T *dst = out + row * out_ld;
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j)
+            if (li + j * lstride < nv) {
+                const int64_t v = li + j * lstride;
+                const T *e = reinterpret_cast<const T *>(&rx[j]);
+                float f[V];
+                if (op == RO_SOFTMAX) {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) f[i] = (sizeof(T) == 2 ? __expf(to_f32(e[i]) * scale - mx) : expf(to_f32(e[i]) * scale - mx)) * mul;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) f[i] = (to_f32(e[i]) - sub) * mul;
+                    if (wgt) {
+                        float g[V];
+                        load_vec_cached<T, V>(wgt + v * V, g);
+#pragma unroll
+                        for (int i = 0; i < V; ++i) f[i] *= g[i];
+                    }
+                }
+                store_vec<T, V>(dst + v * V, f);
+            }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void rowop_dispatch(const RowOpArgs &a, int p, int P) {
+    const int G = a.warps_per_row;
+    if (G > 0) rowop_regs<T>(a, p, P, G);
+    else rowop_typed<T>(a, p, P);
+}
+
 __device__ void run_rowop(const RowOpArgs &a, int p, int P) {
     switch (a.dtype) {
-        case DT_F32: rowop_typed<float>(a, p, P); break;
-        case DT_F16: rowop_typed<__half>(a, p, P); break;
-        case DT_BF16: rowop_typed<__nv_bfloat16>(a, p, P); break;
+        case DT_F32: rowop_dispatch<float>(a, p, P); break;
+        case DT_F16: rowop_dispatch<__half>(a, p, P); break;
+        case DT_BF16: rowop_dispatch<__nv_bfloat16>(a, p, P); break;
         default: break;
     }
 }

@@ -288,7 +288,15 @@ struct Lowerer {
         if (a.residual) ok = ok && aligned16(a.residual) && aligned16(a.res_out);
         if (!ok) throw Error(E_UNSUPPORTED, op.type + ": rows must be 16-byte aligned and a multiple of 16 bytes long");
         if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16)) throw Error(E_UNSUPPORTED, op.type + ": floating-point only");
-        push(s, op.type + " " + op.name + " rows=" + std::to_string(a.rows) + " cols=" + std::to_string(a.cols));
+        // warps that share a row so that each lane keeps at most 8 16-byte vectors of it in registers
+        {
+            const int64_t nv = a.cols / V;
+            int gw = 1;
+            while (gw < 16 && nv > (int64_t)32 * gw * 8) gw *= 2;
+            a.warps_per_row = nv <= (int64_t)32 * gw * 8 ? gw : 0;
+        }
+        push(s, op.type + " " + op.name + " rows=" + std::to_string(a.rows) + " cols=" + std::to_string(a.cols) +
+                    " warps/row=" + std::to_string(a.warps_per_row));
     }
 
     // ---- matmul --------------------------------------------------------------------
@@ -385,15 +393,26 @@ struct Lowerer {
         const int64_t P = prog.pair_mode ? proc.count() / 2 : proc.count();
         const int64_t tiles_m = (M + tile_m - 1) / tile_m;
         if (full) {
-            std::vector<int> cand = {256, 128, 64};
-            if (!g.b_mn_major) { cand.push_back(32); if (!prog.pair_mode) cand.push_back(16); }
-            int tile_n = cand.back();
-            for (int c : cand) {
-                int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
-                if (units >= P) { tile_n = c; break; }
+            // tile_n: with many waves of tiles the widest tile is the most efficient; with few,
+            // pick the width whose makespan (waves x tile width, plus a fixed cost per tile) is least,
+            // so that skinny and small problems spread evenly over the CTAs.
+            // a CTA stages whole 64-column chunks of a row-major (MN-major) B, so its share stays a multiple of 64
+            const int step = g.b_mn_major ? (prog.pair_mode ? 128 : 64) : (prog.pair_mode ? 32 : 16);
+            const int min_n = step;
+            int tile_n = 256;
+            {
+                const int64_t units256 = bn * bc * tiles_m * ((N + 255) / 256);
+                if (units256 < 4 * P) {
+                    double best = 1e30;
+                    for (int c = 256; c >= min_n; c -= step) {
+                        const int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
+                        const int64_t waves = (units + P - 1) / P;
+                        const double cost = (double)waves * (c + 24);
+                        if (cost < best - 1e-9) { best = cost; tile_n = c; }
+                    }
+                }
             }
-            if (N < tile_n) tile_n = (int)((N + 15) / 16 * 16);  // narrow outputs: one tile covers N
-            if (prog.pair_mode && tile_n % 32) tile_n += 16;     // each CTA of a pair stages half the columns
+            if (N < tile_n) tile_n = (int)((N + step - 1) / step * step);  // narrow outputs: one tile covers N
             g.tile_n = tile_n;
             g.plan_tiles = 0;
             g.tiles_m = (int32_t)tiles_m;

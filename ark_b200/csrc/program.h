@@ -86,6 +86,8 @@ struct RowOpArgs {
     int32_t op, dtype;
     float eps;
     float scale;           // softmax: logits are multiplied by this first
+    int32_t warps_per_row; // 1,2,4,8,16: the row is held in registers by that many warps; 0: two-pass fallback
+    int32_t pad;
 };
 
 struct GemmArgs {

@@ -1,0 +1,170 @@
+"""Per-kernel-class measurements of the loop-kernel engine on one GPU: achieved
+HBM GB/s for elementwise / reduce / norm / softmax / gemv-shaped matmul stages
+and TFLOP/s for matmul shapes, each as a fraction of the measured peak
+(MEASURED_PEAKS.json). One JSON line per case. bench.py remains the headline
+benchmark; this script produces the numbers quoted in profiles/.
+
+  python bench_ops.py [--iters 20] [--only name-substring]
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def time_plan(ark, torch, build, iters, warm=3):
+    """Builds a model with `build()` (returns algorithmic bytes, flops), runs `iters`
+    iterations in one launch and returns milliseconds per iteration."""
+    ark.init()
+    nbytes, flops = build()
+    plan = ark.Planner(0).plan()
+    ex = ark.Executor(0, 0, "bench_ops", str(plan), loop_mode=False)
+    ex.compile()
+    stream = torch.cuda.ExternalStream(ex.stream())
+    ex.launch()
+    ex.run(warm)
+    ex.wait()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    ex.run(iters)
+    e1.record(stream)
+    ex.wait()
+    ms = e0.elapsed_time(e1) / iters
+    n_stages = ex.status()["n_stages"]
+    ex.stop()
+    ex.destroy()
+    return ms, nbytes, flops, n_stages
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default="")
+    args = ap.parse_args()
+    import torch
+    import ark_b200 as ark
+    pk, which = peaks()
+    MB = 1 << 20
+    cases = []
+
+    def case(name, fn):
+        if args.only in name:
+            cases.append((name, fn))
+
+    # ---- HBM-bound stages: tensors of 256 MiB so that nothing fits in L2 ----
+    def ew_unary(op, dt, es):
+        def b():
+            n = 256 * MB // es
+            t = ark.tensor([n // 8192, 8192], dt)
+            getattr(ark, op)(t)
+            return 2 * n * es, 0
+        return b
+
+    def ew_binary(op, dt, es):
+        def b():
+            n = 256 * MB // es
+            a, c = ark.tensor([n // 8192, 8192], dt), ark.tensor([n // 8192, 8192], dt)
+            getattr(ark, op)(a, c)
+            return 3 * n * es, 0
+        return b
+    case("relu_fp16", ew_unary("relu", ark.fp16, 2))
+    case("gelu_fp16", ew_unary("gelu", ark.fp16, 2))
+    case("copy_fp32", ew_unary("copy", ark.fp32, 4))
+    case("add_fp16", ew_binary("add", ark.fp16, 2))
+    case("mul_bf16", ew_binary("mul", ark.bf16, 2))
+
+    def add_bcast():
+        a, c = ark.tensor([16384, 8192], ark.fp16), ark.tensor([1, 8192], ark.fp16)
+        ark.add(a, c)
+        return 2 * 16384 * 8192 * 2, 0
+    case("add_broadcast_row_fp16", add_bcast)
+
+    def reduce_last(rows, cols, dt, es):
+        def b():
+            t = ark.tensor([rows, cols], dt)
+            ark.reduce_sum(t, axis=-1)
+            return rows * cols * es, 0
+        return b
+    case("reduce_sum_w_fp16_32768x4096", reduce_last(32768, 4096, ark.fp16, 2))
+    case("reduce_sum_w_fp32_16384x4096", reduce_last(16384, 4096, ark.fp32, 4))
+
+    def reduce_h():
+        t = ark.tensor([64, 1024, 2048], ark.fp16)
+        ark.reduce_sum(t, axis=1)
+        return 64 * 1024 * 2048 * 2, 0
+    case("reduce_sum_h_fp16", reduce_h)
+
+    def rows(opname, r, c, dt, es):
+        def b():
+            t = ark.tensor([r, c], dt)
+            if opname == "rmsnorm":
+                w = ark.tensor([c], dt)
+                ark.rmsnorm(t, w)
+            elif opname == "softmax":
+                ark.softmax(t)
+            else:
+                ark.layernorm(t)
+            return 2 * r * c * es, 0
+        return b
+    case("rmsnorm_fp16_32768x4096", rows("rmsnorm", 32768, 4096, ark.fp16, 2))
+    case("rmsnorm_bf16_16384x8192", rows("rmsnorm", 16384, 8192, ark.bf16, 2))
+    case("softmax_fp16_65536x2048", rows("softmax", 65536, 2048, ark.fp16, 2))
+    case("layernorm_fp16_32768x4096", rows("layernorm", 32768, 4096, ark.fp16, 2))
+
+    # ---- weight-streaming matmuls (decode shapes): bytes = weights ----
+    def gemv(m, n, k, dt, es, nk=True):
+        def b():
+            x = ark.tensor([m, k], dt)
+            w = ark.tensor([n, k] if nk else [k, n], dt)
+            ark.matmul(x, w, transpose_other=nk)
+            return (n * k + m * k + m * n) * es, 2.0 * m * n * k
+        return b
+    case("gemv_m1_fp16_28672x8192", gemv(1, 28672, 8192, ark.fp16, 2))
+    case("gemv_m16_bf16_28672x8192", gemv(16, 28672, 8192, ark.bf16, 2))
+    case("gemv_m1_fp16_4096x4096", gemv(1, 4096, 4096, ark.fp16, 2))
+    case("gemv_m1_fp16_kn_8192x28672", gemv(1, 28672, 8192, ark.fp16, 2, nk=False))
+
+    # ---- tensor-core matmuls ----
+    def mm(m, n, k, dt, es, nk=False):
+        def b():
+            x = ark.tensor([m, k], dt)
+            w = ark.tensor([n, k] if nk else [k, n], dt)
+            ark.matmul(x, w, transpose_other=nk)
+            return (n * k + m * k + m * n) * es, 2.0 * m * n * k
+        return b
+    case("matmul_fp16_8192x8192x8192", mm(8192, 8192, 8192, ark.fp16, 2))
+    case("matmul_bf16_nk_4096x8192x8192", mm(4096, 8192, 8192, ark.bf16, 2, nk=True))
+    case("matmul_fp16_2048x4096x4096", mm(2048, 4096, 4096, ark.fp16, 2))
+    case("matmul_fp16_128x4096x1024", mm(128, 4096, 1024, ark.fp16, 2))
+
+    for name, fn in cases:
+        try:
+            ms, nbytes, flops, n_stages = time_plan(ark, torch, fn, args.iters)
+        except Exception as e:  # keep going: one failing case must not hide the others
+            print(json.dumps({"case": name, "error": f"{type(e).__name__}: {e}"[:300]}))
+            continue
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        line = {"case": name, "ms": ms, "stages": n_stages, "algorithmic_bytes": nbytes, "GB/s": gbs,
+                "hbm_frac": gbs / pk["hbm_gbs"], "peak": which}
+        if flops:
+            tf = flops / (ms * 1e-3) / 1e12
+            line["TFLOP/s"] = tf
+            line["tensor_frac"] = tf / pk["bf16_tflops"]
+        print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()
