@@ -169,78 +169,82 @@ __device__ void ewise_walk(const EwiseArgs &a, int p, int P) {
         }
         return;
     }
-    // strided / broadcast walk: four units per thread in flight; 32-bit index arithmetic
-    // whenever the unit count allows it (64-bit division costs ~4x as many instructions)
+    // strided / broadcast walk. The host has collapsed the dimensions, so the common
+    // cases are two-dimensional ([rows, W]); index arithmetic is 32-bit whenever the unit
+    // count allows it (64-bit division costs ~4x as many instructions).
     const int64_t n_units = a.n_units;
     const float scalar = a.scalar;
-    const TRef to = a.out, t0 = a.in0, t1 = a.in1;
-    const uint32_t WV = (uint32_t)((to.shape[3] + V - 1) / V), H = (uint32_t)to.shape[2], C = (uint32_t)to.shape[1];
-    const bool small = n_units <= 0xffffffffll;
+    const uint32_t WV = (uint32_t)((a.out.shape[3] + V - 1) / V), H = (uint32_t)a.out.shape[2], C = (uint32_t)a.out.shape[1];
+    const bool two_d = a.out.shape[0] == 1 && a.out.shape[1] == 1 && n_units <= 0xffffffffll;
+    const int64_t so2 = a.out.stride[2], s02 = a.in0.stride[2], s12 = a.in1.stride[2];
+    const int64_t s03 = a.in0.stride[3], s13 = a.in1.stride[3];
     // an operand with a broadcast dimension is re-read many times: keep it in L1
-    const bool bc0 = !(t0.stride[0] && t0.stride[1] && t0.stride[2] && t0.stride[3]);
-    const bool bc1 = !(t1.stride[0] && t1.stride[1] && t1.stride[2] && t1.stride[3]);
+    const bool bc0 = !(s02 && s03), bc1 = !(s12 && s13);
     constexpr int U = 4;
     for (int64_t u0 = tid; u0 < n_units; u0 += nth * U) {
         int64_t oo[U], o0[U], o1[U];
 #pragma unroll
         for (int k = 0; k < U; ++k) {
             const int64_t u = u0 + k * nth;
-            int64_t wv, h, c, n;
-            if (small) {
+            if (two_d) {
                 const uint32_t uu = (uint32_t)u;
-                uint32_t row = uu / WV;
-                wv = uu - row * WV;
-                const uint32_t r2 = row / H;
-                h = row - r2 * H;
-                const uint32_t r3 = r2 / C;
-                c = r2 - r3 * C;
-                n = r3;
+                const uint32_t row = uu / WV;
+                const int64_t w = (int64_t)(uu - row * WV) * V;
+                oo[k] = row * so2 + w;
+                o0[k] = row * s02 + (s03 ? w : 0);
+                o1[k] = row * s12 + (s13 ? w : 0);
             } else {
-                wv = u % WV;
+                const int64_t wv = u % WV;
                 int64_t row = u / WV;
-                h = row % H;
+                const int64_t h = row % H;
                 row /= H;
-                c = row % C;
-                n = row / C;
-            }
-            const int64_t w = wv * V;
-            oo[k] = tref_off(to, n, c, h, w);
-            o0[k] = tref_off(t0, n, c, h, t0.stride[3] ? w : 0);
-            o1[k] = tref_off(t1, n, c, h, t1.stride[3] ? w : 0);
-        }
-        float x[U][V], y[U][V];
-#pragma unroll
-        for (int k = 0; k < U; ++k) {
-            if (u0 + k * nth >= n_units) continue;
-            if (rd0) {
-                if (!t0.stride[3]) {
-                    const float sv = to_f32(in0[o0[k]]);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) x[k][i] = sv;
-                } else if (bc0) {
-                    load_vec_cached<TI, V>(in0 + o0[k], x[k]);
-                } else {
-                    load_vec<TI, V>(in0 + o0[k], x[k]);
-                }
-            }
-            if (bin) {
-                if (!t1.stride[3]) {
-                    const float sv = to_f32(in1[o1[k]]);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) y[k][i] = sv;
-                } else if (bc1) {
-                    load_vec_cached<TI, V>(in1 + o1[k], y[k]);
-                } else {
-                    load_vec<TI, V>(in1 + o1[k], y[k]);
-                }
+                const int64_t c = row % C, n = row / C;
+                const int64_t w = wv * V;
+                oo[k] = tref_off(a.out, n, c, h, w);
+                o0[k] = tref_off(a.in0, n, c, h, s03 ? w : 0);
+                o1[k] = tref_off(a.in1, n, c, h, s13 ? w : 0);
             }
         }
+        if constexpr (V * sizeof(TI) == 16) {
+            // operands stay packed (one 16-byte register quad per unit) until they are used
+            uint4 rx[U], ry[U];
+            float sx[U], sy[U];
 #pragma unroll
-        for (int k = 0; k < U; ++k) {
-            if (u0 + k * nth >= n_units) continue;
-            float r[V];
-            ewise_math<V, sizeof(TO) == 2>(op, scalar, x[k], y[k], r);
-            store_vec<TO, V>(out + oo[k], r);
+            for (int k = 0; k < U; ++k) {
+                if (u0 + k * nth >= n_units) continue;
+                if (rd0) {
+                    if (!s03) sx[k] = to_f32(in0[o0[k]]);
+                    else rx[k] = bc0 ? *reinterpret_cast<const uint4 *>(in0 + o0[k]) : ldg16_stream(in0 + o0[k]);
+                }
+                if (bin) {
+                    if (!s13) sy[k] = to_f32(in1[o1[k]]);
+                    else ry[k] = bc1 ? *reinterpret_cast<const uint4 *>(in1 + o1[k]) : ldg16_stream(in1 + o1[k]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < U; ++k) {
+                if (u0 + k * nth >= n_units) continue;
+                float x[V], y[V], r[V];
+                const TI *ex = reinterpret_cast<const TI *>(&rx[k]);
+                const TI *ey = reinterpret_cast<const TI *>(&ry[k]);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                    x[i] = s03 ? to_f32(ex[i]) : sx[k];
+                    y[i] = s13 ? to_f32(ey[i]) : sy[k];
+                }
+                ewise_math<V, sizeof(TO) == 2>(op, scalar, x, y, r);
+                store_vec<TO, V>(out + oo[k], r);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < U; ++k) {
+                if (u0 + k * nth >= n_units) continue;
+                float x[V], y[V], r[V];
+                if (rd0) load_vec_cached<TI, V>(in0 + o0[k], x);
+                if (bin) load_vec_cached<TI, V>(in1 + o1[k], y);
+                ewise_math<V, sizeof(TO) == 2>(op, scalar, x, y, r);
+                store_vec<TO, V>(out + oo[k], r);
+            }
         }
     }
 }

@@ -15,6 +15,7 @@ __device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *
                          int stage_idx, unsigned long long spin_limit);
 __device__ void run_gemm_pair(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
                               int stage_idx, unsigned long long spin_limit);
+__device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P);
 __device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no);

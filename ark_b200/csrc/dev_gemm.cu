@@ -43,7 +43,9 @@ struct GemmLocal {
     void *C;
     const void *bias;
     int64_t ldc, c_stride_c, c_stride_n;
-    int M, N, K, tile_n, act, c_vec, c_tma, dtype;
+    int M, N, K, tile_n, act, c_vec, c_tma, dtype, out_transposed, splits, batch_c;
+    float *ws;
+    int64_t splits_stride;  // elements between the partials of consecutive k-ranges
     int a_mn_major, b_mn_major, a_bc, a_bn, b_bc, b_bn;
 };
 
@@ -146,6 +148,68 @@ __device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint
     }
 }
 
+// Epilogue of the swapped form (A = weights, B = activations): accumulator row =
+// output column n (one per lane), accumulator column = output row m. For a fixed m
+// the 32 lanes of a warp write 32 consecutive n: coalesced without staging.
+// In this form g.M / g.N hold the swapped problem (M' = columns of C, N' = rows of C).
+template <typename T>
+__device__ void gemm_epilogue_tile_swapped(const GemmLocal &g, const TileCoord &tc, uint32_t tmem_acc, int warp, int lane) {
+    const int n = tc.m0 + warp * 32 + lane;
+    const bool n_ok = n < g.M;
+    const int64_t boff = (int64_t)tc.bn * g.c_stride_n + (int64_t)tc.bc * g.c_stride_c;
+    T *cbase = reinterpret_cast<T *>(g.C) + boff;
+    const T *bbase = g.bias ? reinterpret_cast<const T *>(g.bias) + boff : nullptr;
+    const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
+    const int rows = min(g.tile_n, g.N - tc.n0);
+    for (int c = 0; c < g.tile_n; c += 32) {
+        if (c >= rows) break;
+        uint32_t r[32];
+        const int cnt = (g.tile_n - c >= 32) ? 32 : 16;
+        if (cnt == 32) tmem_ld32(lane_addr + c, r);
+        else tmem_ld16(lane_addr + c, r);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int m = tc.n0 + c + i;
+                if (i < cnt && m < g.N) {
+                    float v = __uint_as_float(r[i]);
+                    if (bbase) v += to_f32(bbase[(int64_t)m * g.ldc + n]);
+                    cbase[(int64_t)m * g.ldc + n] = from_f32<T>(apply_act_fast(g.act, v));
+                }
+            }
+        }
+    }
+}
+
+// Split-K epilogue of the swapped form: the fp32 partial of k-range `split` goes to
+// ws[split][batch][m][n] unrounded; run_splitk_reduce finishes the job.
+__device__ void gemm_epilogue_tile_partial(const GemmLocal &g, const TileCoord &tc, int split, uint32_t tmem_acc, int warp,
+                                           int lane) {
+    const int n = tc.m0 + warp * 32 + lane;   // column of C
+    const bool n_ok = n < g.M;                // g.M / g.N hold the swapped problem
+    const int64_t ncols = g.M, nrows = g.N;
+    const int64_t batch = (int64_t)tc.bn * g.batch_c + tc.bc;
+    float *w = g.ws + (int64_t)split * g.splits_stride + batch * nrows * ncols;
+    const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
+    const int rows = min(g.tile_n, (int)nrows - tc.n0);
+    for (int c = 0; c < g.tile_n; c += 32) {
+        if (c >= rows) break;
+        uint32_t r[32];
+        const int cnt = (g.tile_n - c >= 32) ? 32 : 16;
+        if (cnt == 32) tmem_ld32(lane_addr + c, r);
+        else tmem_ld16(lane_addr + c, r);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const int m = tc.n0 + c + i;
+                if (i < cnt && m < nrows) w[(int64_t)m * ncols + n] = __uint_as_float(r[i]);
+            }
+        }
+    }
+}
+
 // Runs the tiles of one GEMM stage assigned to CTA p of P. All threads of the
 // CTA call this; it returns with the pipeline drained.
 //
@@ -160,13 +224,14 @@ __device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint
 template <bool PAIR>
 __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
                            int stage_idx, unsigned long long lim) {
-    using Cfg = GemmCfg<PAIR>;
-    constexpr int STAGES = Cfg::kStages;
+    const int STAGES = g.stages;
+    const int stage_bytes = kGemmABytes + g.stage_b_bytes;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     GemmLocal L;
     L.C = g.C; L.bias = g.bias; L.ldc = g.ldc; L.c_stride_c = g.c_stride_c; L.c_stride_n = g.c_stride_n;
     L.M = g.M; L.N = g.N; L.K = g.K; L.tile_n = g.tile_n; L.act = g.act; L.c_vec = g.c_vec; L.c_tma = g.c_tma;
-    L.dtype = g.dtype;
+    L.dtype = g.dtype; L.out_transposed = g.out_transposed; L.splits = g.splits; L.ws = g.ws; L.batch_c = g.batch_c;
+    L.splits_stride = (int64_t)g.batch_c * g.batch_n * g.M * g.N;
     L.a_mn_major = g.a_mn_major; L.b_mn_major = g.b_mn_major;
     L.a_bc = g.a_bc; L.a_bn = g.a_bn; L.b_bc = g.b_bc; L.b_bn = g.b_bn;
     const int n_units = g.n_units;
@@ -174,13 +239,25 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
     char *epi_stage = smem + kGemmPipeBytes;
     unsigned int epi_blk = 0;
     const int kblocks = (L.K + kGemmBK - 1) / kGemmBK;
-    const unsigned int kb0 = pp->kb_count, t0 = pp->tile_count;
+    const unsigned int t0 = pp->tile_count;
+    // phase bit of every ring slot at the start of this stage; inside the loops the slot index
+    // and a wrap bit are stepped by hand (no division on the MMA-issuing thread's critical path)
+    uint32_t base_par = 0;
+    for (int s = 0; s < STAGES; ++s) base_par |= (pp->use[s] & 1u) << s;
     const int crank = PAIR ? (p & 1) : 0;          // rank inside the CTA pair
     const int up = PAIR ? (p >> 1) : p;             // which tile walker this CTA belongs to
     const int UP = PAIR ? (P >> 1) : P;
     const int n_half = PAIR ? L.tile_n / 2 : L.tile_n;  // B columns staged by this CTA
+    // split-K: unit = tile * splits + range; a unit runs k-blocks [kb_lo, kb_hi) of its tile
+    const int splits = L.splits > 1 ? L.splits : 1;
+    const int kper = (kblocks + splits - 1) / splits;
     int my_tiles = 0;
-    for (int u = up; u < n_units; u += UP) ++my_tiles;
+    unsigned int my_kblocks = 0;
+    for (int u = up; u < n_units; u += UP) {
+        ++my_tiles;
+        const int lo = (u % splits) * kper;
+        my_kblocks += (unsigned int)(min(kblocks, lo + kper) - lo);
+    }
     const uint32_t tmem_base = ctl->tmem_base;
 
     if (warp == kProducerWarp || warp == kProducerWarpB) {
@@ -194,20 +271,21 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
             const uint32_t bytes = mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2;
             const CUtensorMap *tm = is_a ? tmA : tmB;
             const int has_c = is_a ? L.a_bc : L.b_bc, has_n = is_a ? L.a_bn : L.b_bn;
-            unsigned int kb = kb0;
+            int s = 0;
+            uint32_t wrap = 0;
             for (int u = up; u < n_units; u += UP) {
-                const TileCoord tc = gemm_unit(g, u);
+                const TileCoord tc = gemm_unit(g, u / splits);
                 const int mn0 = is_a ? tc.m0 + crank * kGemmTileM : tc.n0 + crank * n_half;
                 const int bc = has_c ? tc.bc : 0, bn = has_n ? tc.bn : 0;
-                for (int k = 0; k < kblocks; ++k, ++kb) {
-                    const int s = kb % STAGES;
-                    const uint32_t par = ((kb / STAGES) & 1) ^ 1;
+                const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
+                for (int k = kb_lo; k < kb_hi; ++k, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+                    const uint32_t par = (((base_par >> s) ^ wrap) & 1) ^ 1;
                     if (!mbar_wait(&pp->empty[s], par, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
-                    char *dst = smem + s * Cfg::kStageBytes + (is_a ? 0 : kGemmABytes);
+                    char *dst = smem + s * stage_bytes + (is_a ? 0 : kGemmABytes);
                     if constexpr (!PAIR) {
                         mbar_expect_tx(&pp->full[s], bytes);
                         if (!mn_major) {
@@ -237,8 +315,11 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
             const uint32_t a_adv = L.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
             const uint32_t b_adv = L.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
             const uint32_t chunk_bytes = 64 * kGemmBK * 2;  // one 64-wide MN chunk
-            unsigned int kb = kb0, t = t0;
-            for (int i = 0; i < my_tiles; ++i, ++t) {
+            unsigned int t = t0;
+            int s = 0;
+            uint32_t wrap = 0;
+            for (int u = up; u < n_units; u += UP, ++t) {
+                const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
                 const int acc = t & 1;
                 if (!mbar_wait(&pp->acc_empty[acc], ((t >> 1) & 1) ^ 1, lim)) {
                     ctl->abort = 1;
@@ -247,21 +328,20 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * 256;
-                for (int k = 0; k < kblocks; ++k, ++kb) {
-                    const int s = kb % STAGES;
-                    if (!mbar_wait(&pp->full[s], (kb / STAGES) & 1, lim)) {
+                for (int k = kb_lo; k < kb_hi; ++k, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+                    if (!mbar_wait(&pp->full[s], ((base_par >> s) ^ wrap) & 1, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * Cfg::kStageBytes);
+                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
                     const uint32_t sb = sa + kGemmABytes;
                     const uint64_t da = L.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
                     const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
 #pragma unroll
                     for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-                        const uint32_t accum = (k > 0 || kk > 0) ? 1u : 0u;
+                        const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
                         if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                         else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                     }
@@ -286,8 +366,9 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
     } else if (warp < kEpiWarps) {
         unsigned int t = t0;
         for (int u = up; u < n_units; u += UP, ++t) {
-            TileCoord tc = gemm_unit(g, u);
+            TileCoord tc = gemm_unit(g, u / splits);
             tc.m0 += crank * kGemmTileM;
+            const int split = u % splits;
             const int acc = t & 1;
             bool ok = mbar_wait(&pp->acc_full[acc], (t >> 1) & 1, lim);
             ok = __all_sync(0xffffffffu, ok);
@@ -300,7 +381,12 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
             }
             tc_fence_after();
             const uint32_t tmem_acc = tmem_base + acc * 256;
-            if (L.c_tma) {
+            if (L.splits > 1) {
+                gemm_epilogue_tile_partial(L, tc, split, tmem_acc, warp, lane);
+            } else if (L.out_transposed) {
+                if (L.dtype == DT_BF16) gemm_epilogue_tile_swapped<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
+                else gemm_epilogue_tile_swapped<__half>(L, tc, tmem_acc, warp, lane);
+            } else if (L.c_tma) {
                 if (L.dtype == DT_BF16) gemm_epilogue_tile_tma<__nv_bfloat16>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
                 else gemm_epilogue_tile_tma<__half>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
             } else {
@@ -320,7 +406,9 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
 done:
     __syncthreads();
     if (threadIdx.x == 0) {
-        pp->kb_count = kb0 + (unsigned int)my_tiles * (unsigned int)kblocks;
+        const unsigned int total = my_kblocks;
+        for (int s = 0; s < STAGES; ++s)
+            if (total > (unsigned int)s) pp->use[s] += (total - s + STAGES - 1) / STAGES;
         pp->tile_count = t0 + (unsigned int)my_tiles;
     }
     // the partner may still read this CTA's shared memory / signal its barriers
@@ -335,6 +423,42 @@ __device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *
 __device__ void run_gemm_pair(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
                               int stage_idx, unsigned long long spin_limit) {
     run_gemm_t<true>(g, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+}
+
+// Sums the split-K partials (fixed order: deterministic), adds the optional bias,
+// applies the activation and rounds once. Four outputs per thread step.
+template <typename T>
+__device__ void splitk_reduce_typed(const SplitKReduceArgs &a, int p, int P) {
+    const int64_t per = (int64_t)a.M * a.N, total = per * a.batch_c * a.batch_n;
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)P * kThreads;
+    const bool vec = (a.N % 4 == 0);
+    const int64_t step = vec ? 4 : 1;
+    for (int64_t e0 = tid * step; e0 < total; e0 += nth * step) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < a.splits; ++s) {
+            const float *w = a.ws + (int64_t)s * total + e0;
+            if (vec) {
+                const float4 v = *reinterpret_cast<const float4 *>(w);
+                acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+            } else {
+                acc[0] += w[0];
+            }
+        }
+        for (int i = 0; i < step; ++i) {
+            const int64_t e = e0 + i;
+            const int64_t b = e / per, r = e % per;
+            const int64_t m = r / a.N, n = r % a.N;
+            const int64_t off = (b / a.batch_c) * a.c_stride_n + (b % a.batch_c) * a.c_stride_c + m * a.ldc + n;
+            float v = acc[i];
+            if (a.bias) v += to_f32(reinterpret_cast<const T *>(a.bias)[off]);
+            reinterpret_cast<T *>(a.C)[off] = from_f32<T>(apply_act_fast(a.act, v));
+        }
+    }
+}
+
+__device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P) {
+    if (a.dtype == DT_BF16) splitk_reduce_typed<__nv_bfloat16>(a, p, P);
+    else splitk_reduce_typed<__half>(a, p, P);
 }
 
 // ---- CUDA-core fallback -------------------------------------------------------------

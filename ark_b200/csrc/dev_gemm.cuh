@@ -33,7 +33,7 @@ struct GemmCfg {
     static constexpr int kBBytes = (PAIR ? 128 : 256) * kGemmBK * 2;
     static constexpr int kStageBytes = kGemmABytes + kBBytes;
 };
-constexpr int kGemmMaxStages = 6;
+constexpr int kGemmMaxStages = 12;  // skinny (swapped) problems stage small B blocks and use more, smaller stages
 constexpr int kGemmPipeBytes = 4 * (kGemmABytes + 256 * kGemmBK * 2);  // 192 KiB of operand stages in both modes
 // epilogue staging: per epilogue warp two 32-row x 64-byte blocks (64-byte swizzle)
 constexpr int kEpiBlockBytes = 32 * 64;
@@ -47,7 +47,7 @@ struct GemmPipe {
     unsigned long long empty[kGemmMaxStages];
     unsigned long long acc_full[2];
     unsigned long long acc_empty[2];
-    unsigned int kb_count;    // k-blocks this CTA has pushed through the ring since launch
+    unsigned int use[kGemmMaxStages];  // completed uses of each ring slot since launch (gives the barrier phase)
     unsigned int tile_count;  // tiles this CTA has finished since launch
 };
 
@@ -238,7 +238,7 @@ __device__ __forceinline__ void gemm_pipe_init(GemmPipe *pp, bool pair) {
         mbar_init(&pp->acc_full[a], 1);
         mbar_init(&pp->acc_empty[a], pair ? 2 * kEpiWarps : kEpiWarps);
     }
-    pp->kb_count = 0;
+    for (int s = 0; s < kGemmMaxStages; ++s) pp->use[s] = 0;
     pp->tile_count = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }

@@ -185,7 +185,14 @@ void Executor::compile() {
     env.encode_tmap = encode_tmap_cuda;
     env.num_sm = num_sm_;
     env.allow_pair = getenv("ARKB_NO_PAIR") == nullptr;
+    // first pass sizes the scratch (split-K partials) against a stand-in address, second pass uses the real one
+    env.workspace = reinterpret_cast<char *>((uintptr_t)1 << 44);
     program_ = lower_plan(plan_, layout_, env);
+    if (program_.workspace_bytes > 0) {
+        CUDA_CHECK(cudaMalloc(&workspace_, program_.workspace_bytes));
+        env.workspace = reinterpret_cast<char *>(workspace_);
+        program_ = lower_plan(plan_, layout_, env);
+    }
     if (!program_.stages.empty()) {
         CUDA_CHECK(cudaMalloc(&stages_dev_, program_.stages.size() * sizeof(Stage)));
         CUDA_CHECK(cudaMemcpy(stages_dev_, program_.stages.data(), program_.stages.size() * sizeof(Stage),
@@ -353,6 +360,8 @@ void Executor::destroy() {
         peer_arena_[r] = peer_comm_[r] = nullptr;
     }
     if (stages_dev_) cudaFree(stages_dev_);
+    if (workspace_) cudaFree(workspace_);
+    workspace_ = nullptr;
     if (arena_) cudaFree(arena_);
     if (comm_) cudaFree(comm_);
     if (state_) cudaFree(state_);
@@ -445,6 +454,7 @@ void plan_check(const std::string &plan_json, int *n_stages, size_t *arena_bytes
     }
     env.encode_tmap = encode_tmap_check;
     env.num_sm = 148;
+    env.workspace = reinterpret_cast<char *>((uintptr_t)1 << 44);
     // every rank is assumed to publish the same records as this one (SPMD plans)
     std::vector<std::vector<TagRecord>> records(plan.world_size, lay.published);
     for (auto &kv : lay.buffers) {
@@ -472,6 +482,7 @@ std::string plan_dump(const std::string &plan_json) {
         env.comm[r] = reinterpret_cast<char *>(((uintptr_t)(r + 1) << 40) + ((uintptr_t)1 << 39));
     }
     env.encode_tmap = encode_tmap_check;
+    env.workspace = reinterpret_cast<char *>((uintptr_t)1 << 44);
     std::vector<std::vector<TagRecord>> records(plan.world_size, lay.published);
     for (auto &kv : lay.buffers)
         if (!kv.second.resolved) {

@@ -60,6 +60,7 @@ class Executor {
     cudaStream_t stream_ = nullptr, copy_stream_ = nullptr;
     bool own_stream_ = false;
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
+    void *workspace_ = nullptr;  // split-K partials
     void *arena_ = nullptr, *comm_ = nullptr, *state_ = nullptr, *stages_dev_ = nullptr;
     size_t arena_bytes_ = 0, comm_bytes_ = 0;
     int32_t *host_flags_ = nullptr;          // [0] run flag, [1] status mirror (mapped host memory)

@@ -50,6 +50,7 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
                 else run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
                 break;
             case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
+            case SK_SPLITK_REDUCE: run_splitk_reduce(S.sr, p, Pn); break;
             case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;
             case SK_EMBED: run_embed(S.em, p, Pn); break;
             case SK_PUT: run_put(S.put, p, Pn); break;

@@ -162,6 +162,45 @@ struct Lowerer {
         if (has_in) a.in0 = make_ref(op.reads[0], &osh);
         if (binary) a.in1 = make_ref(op.reads[1], &osh);
         a.op = code;
+        bool same = has_in ? (op.reads[0].shape4() == osh) : true;
+        if (binary) same = same && (op.reads[1].shape4() == osh);
+        // Collapse adjacent dimensions that every operand walks contiguously (or broadcasts
+        // together), so that e.g. [N,C,H,W] + [1,1,1,W] is walked as [rows, W] with one division.
+        {
+            TRef *refs[3] = {&a.out, has_in ? &a.in0 : nullptr, binary ? &a.in1 : nullptr};
+            int64_t shp[4] = {osh[0], osh[1], osh[2], osh[3]};
+            bool changed = true;
+            while (changed) {
+                changed = false;
+                for (int i = 2; i >= 0; --i) {
+                    if (shp[i] == 1) continue;
+                    if (shp[i + 1] == 1) {  // empty slot below: move the dimension down
+                        for (auto r : refs)
+                            if (r) {
+                                r->stride[i + 1] = r->stride[i];
+                                r->stride[i] = 0;
+                            }
+                        shp[i + 1] = shp[i];
+                        shp[i] = 1;
+                        changed = true;
+                        continue;
+                    }
+                    bool ok = true;
+                    for (auto r : refs)
+                        if (r && r->stride[i] != r->stride[i + 1] * shp[i + 1]) ok = false;
+                    if (!ok) continue;
+                    for (auto r : refs)
+                        if (r) r->stride[i] = 0;
+                    shp[i + 1] *= shp[i];
+                    shp[i] = 1;
+                    changed = true;
+                }
+            }
+            for (auto r : refs)
+                if (r)
+                    for (int i = 0; i < 4; ++i) r->shape[i] = (int32_t)shp[i];
+            osh = {shp[0], shp[1], shp[2], shp[3]};
+        }
         // the scalar is rounded to the tensor's storage type first, as the reference's
         // host baselines do with T(factor) (ark/ops/ops_scalar_test.cpp:11-62)
         if (code == EW_SCALAR_ASSIGN) a.scalar = round_to_dtype((float)op.arg_float("Value"), out.dtype);
@@ -174,8 +213,6 @@ struct Lowerer {
         int V = convert ? 4 : (int)(16 / dtype_size(out.dtype));
         if (code == EW_COPY && !convert) V = (int)(16 / dtype_size(out.dtype));
         const int64_t nelem = out.nelems();
-        bool same = has_in ? (op.reads[0].shape4() == osh) : true;
-        if (binary) same = same && (op.reads[1].shape4() == osh);
         bool dense = out.dense() && (!has_in || op.reads[0].dense()) && (!binary || op.reads[1].dense());
         auto ptr_ok = [&](const TRef &r, int dt) {
             size_t bytes = (size_t)V * dtype_size(dt);
@@ -183,13 +220,15 @@ struct Lowerer {
             return (reinterpret_cast<uintptr_t>(r.ptr) % al) == 0;
         };
         a.flat = (same && dense) ? 1 : 0;
-        bool vec_ok = ptr_ok(a.out, out.dtype) && (!has_in || ptr_ok(a.in0, idt)) && (!binary || ptr_ok(a.in1, idt));
+        bool vec_ok = ptr_ok(a.out, out.dtype) && (!has_in || a.in0.stride[3] == 0 || ptr_ok(a.in0, idt)) &&
+                      (!binary || a.in1.stride[3] == 0 || ptr_ok(a.in1, idt));
         if (a.flat) {
             vec_ok = vec_ok && (nelem % V == 0);
         } else {
             vec_ok = vec_ok && (osh[3] % V == 0);
             auto strides_ok = [&](const TRef &r) {
                 if (r.stride[3] != 0 && r.stride[3] != 1) return false;
+                if (r.stride[3] == 0) return true;  // broadcast along W: read as one scalar per unit
                 for (int i = 0; i < 3; ++i)
                     if (r.stride[i] % V) return false;
                 return true;
@@ -374,6 +413,10 @@ struct Lowerer {
             push(s, "Matmul(simt) " + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" + std::to_string(K));
             return;
         }
+        // Skinny problems (few rows of activations against a large weight matrix, the
+        // decode case) are run swapped: the weights become the 128-row A operand that fills
+        // the shared-memory ring, the activations the narrow B operand.
+        const bool swapped = full && !ta && M <= 64;
         Stage s = new_stage(SK_GEMM, proc);
         GemmArgs &g = s.gm;
         g.C = pc;
@@ -385,14 +428,49 @@ struct Lowerer {
         g.a_bc = ash[1] > 1; g.a_bn = ash[0] > 1; g.b_bc = bsh[1] > 1; g.b_bn = bsh[0] > 1;
         g.a_mn_major = ta ? 1 : 0;   // A stored [K, M]: M is the inner dim
         g.b_mn_major = tb ? 0 : 1;   // B stored [K, N]: N is the inner dim
+        if (swapped) {
+            std::swap(g.M, g.N);
+            std::swap(g.a_bc, g.b_bc);
+            std::swap(g.a_bn, g.b_bn);
+            g.a_mn_major = tb ? 0 : 1;  // the weights in the A role
+            g.b_mn_major = 0;           // the activations [M, K] in the B role
+            g.out_transposed = 1;
+        }
         g.dtype = A.dtype;
         g.act = act < 0 ? ACT_NONE : act;
         g.c_vec = (aligned16(pc) && ldc % 8 == 0 && g.c_stride_c % 8 == 0 && g.c_stride_n % 8 == 0) ? 1 : 0;
         const int tile_m = prog.pair_mode ? 256 : 128;
         g.tile_m = tile_m;
         const int64_t P = prog.pair_mode ? proc.count() / 2 : proc.count();
-        const int64_t tiles_m = (M + tile_m - 1) / tile_m;
-        if (full) {
+        const int64_t tiles_m = ((swapped ? N : M) + tile_m - 1) / tile_m;
+        if (swapped) {
+            g.tile_n = (int32_t)((M + 15) / 16 * 16);
+            g.plan_tiles = 0;
+            g.tiles_m = (int32_t)tiles_m;
+            g.tiles_n = 1;
+            g.raster_group = (int32_t)tiles_m;
+            g.n_units = (int32_t)(bn * bc * tiles_m);
+            // Split K when the tiles alone cannot keep every CTA (pair) streaming weights: pick the
+            // split with the least makespan in k-blocks. Partials go to scratch and a second stage
+            // sums them in a fixed order (deterministic).
+            const int64_t kblocks = (K + 63) / 64, tiles = g.n_units;
+            int best_s = 1;
+            double best = 1e30;
+            for (int sp = 1; sp <= 32 && sp * 2 <= kblocks; ++sp) {
+                const int64_t kper = (kblocks + sp - 1) / sp;
+                const int64_t eff = (kblocks + kper - 1) / kper;
+                const int64_t waves = (tiles * eff + P - 1) / P;
+                const double cost = (double)waves * kper + 0.5 * eff;
+                if (cost < best - 1e-9) { best = cost; best_s = (int)eff; }
+            }
+            if (best_s > 1 && env.workspace) {
+                g.splits = best_s;
+                g.n_units = (int32_t)(tiles * best_s);
+                const size_t bytes = (size_t)best_s * bn * bc * M * N * sizeof(float);
+                g.ws = reinterpret_cast<float *>(env.workspace + prog.workspace_bytes);
+                prog.workspace_bytes += (bytes + 255) / 256 * 256;
+            }
+        } else if (full) {
             // tile_n: with many waves of tiles the widest tile is the most efficient; with few,
             // pick the width whose makespan (waves x tile width, plus a fixed cost per tile) is least,
             // so that skinny and small problems spread evenly over the CTAs.
@@ -460,17 +538,47 @@ struct Lowerer {
             env.encode_tmap(out, sp);
         };
         // 1-D operands ([K] vectors) are viewed as one row / one column
-        std::vector<int64_t> ash2 = ash, bsh2 = bsh;
-        mk(A, ash2, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
-        // K-major B: one box holds the rows (output columns) this CTA stages — all of the tile, or half in a pair
-        mk(B, bsh2, bst, pb, 64, g.b_mn_major ? 64 : (uint32_t)(prog.pair_mode ? g.tile_n / 2 : g.tile_n), &g.tmB);
+        // K-major B role: one box holds the rows this CTA stages — all of the tile, or half in a pair
+        const uint32_t b_rows = (uint32_t)(prog.pair_mode ? g.tile_n / 2 : g.tile_n);
+        if (!swapped) {
+            mk(A, ash, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
+            mk(B, bsh, bst, pb, 64, g.b_mn_major ? 64 : b_rows, &g.tmB);
+        } else {
+            mk(B, bsh, bst, pb, 64, g.a_mn_major ? 64 : 128, &g.tmA);  // weights
+            mk(A, ash, ast, pa, 64, b_rows, &g.tmB);                    // activations
+        }
+        // ring: 16 KiB A block + this CTA's B block per stage, as many stages as fit in 192 KiB (at most 12)
+        g.stage_b_bytes = (int32_t)(g.b_mn_major ? ((b_rows + 63) / 64) * 64 * 128 : b_rows * 128);
+        g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / (16 * 1024 + g.stage_b_bytes));
         // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
-        g.c_tma = (g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
+        g.c_tma = (!swapped && g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
         if (g.c_tma) mk(C, csh, cst, pc, 32, 32, &g.tmC, 64);
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
-                    (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K"));
+                    (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K") + (swapped ? " swapped" : "") +
+                    " stages=" + std::to_string(g.stages) + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
+        if (g.splits > 1) {
+            // the activation and the rounding belong to the sum, not to the partials
+            GemmArgs &gg = prog.stages.back().gm;
+            const int act_final = gg.act;
+            gg.act = ACT_NONE;
+            emit_sync(proc);
+            Stage r = new_stage(SK_SPLITK_REDUCE, proc);
+            SplitKReduceArgs &a = r.sr;
+            a.C = pc;
+            a.bias = nullptr;
+            a.ws = gg.ws;
+            a.ldc = ldc;
+            a.c_stride_c = cst[2] * cst[3];
+            a.c_stride_n = cst[1] * cst[2] * cst[3];
+            a.M = (int32_t)M; a.N = (int32_t)N;
+            a.batch_c = (int32_t)bc; a.batch_n = (int32_t)bn;
+            a.splits = gg.splits;
+            a.dtype = A.dtype;
+            a.act = act_final;
+            push(r, "  split-K sum " + op.name + " splits=" + std::to_string(a.splits));
+        }
     }
 
     // ---- transpose / embedding ---------------------------------------------------------

@@ -148,6 +148,7 @@ struct LowerEnv {
     TmapEncoder encode_tmap;
     int num_sm = 148;
     bool allow_pair = true;  // let matmul tiles span CTA pairs (tcgen05 cta_group::2) when the plan permits
+    char *workspace = nullptr;  // scratch for split-K partials (sized by a first lowering pass: Program::workspace_bytes)
 };
 
 struct Program {
@@ -158,6 +159,7 @@ struct Program {
     int syncs_per_iter[kMaxSyncGroups] = {};
     int peersyncs_per_iter = 0;
     int oneshots_per_iter = 0;
+    size_t workspace_bytes = 0;  // scratch the program needs beyond the arena (split-K partials)
     bool pair_mode = false;  // launch clusters of 2 CTAs; matmul tiles are 256 x tile_n per pair
     std::string dump() const;
 };

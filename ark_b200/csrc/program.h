@@ -36,6 +36,7 @@ enum StageKind : int32_t {
     SK_ALLREDUCE = 11, // data phase of the in-kernel all_reduce
     SK_GEMM_SIMT = 12, // CUDA-core matmul for shapes the TMA path cannot take
     SK_SIGNAL = 13,    // raise a channel flag on a peer (after the put's data is complete)
+    SK_SPLITK_REDUCE = 14,  // sum the fp32 partials of a split-K matmul, add bias, activate, round, store
 };
 
 enum EwiseOp : int32_t {
@@ -119,6 +120,20 @@ struct GemmArgs {
     int32_t ptm, ptn, p_tiles_h, p_tiles_w, sub_m, sub_n, task_b, task_s;
     int32_t n_units;
     int32_t tile_m;                  // 128 (one CTA per tile) or 256 (CTA pair per tile)
+    int32_t stages, stage_b_bytes;   // ring depth and bytes of the B block of one stage (A block: 16 KiB)
+    int32_t out_transposed;          // 1: operands are swapped (A = weights, B = activations); D[n][m] is stored to C[m][n]
+    int32_t splits;                  // > 1: K is cut into `splits` ranges; unit = tile * splits + range, fp32 partials go to `ws`
+    float *ws;                       // split-K partials, layout [splits][batch][rows of C][cols of C]
+};
+
+// Second half of a split-K matmul: C = act(sum_s ws[s] + bias), one rounding.
+struct SplitKReduceArgs {
+    void *C;
+    const void *bias;
+    const float *ws;
+    int64_t ldc, c_stride_c, c_stride_n;
+    int32_t M, N, batch_c, batch_n;
+    int32_t splits, dtype, act, pad;
 };
 
 struct GemvArgs {
@@ -207,6 +222,7 @@ struct alignas(128) Stage {
         RowOpArgs ro;
         GemmArgs gm;
         GemvArgs gv;
+        SplitKReduceArgs sr;
         GemmSimtArgs gs;
         TransposeArgs tp;
         EmbedArgs em;

@@ -1,0 +1,100 @@
+"""Llama-2-shaped decoder layers, tensor-parallel (Megatron split), built from the
+engine's operators. Shapes follow examples/llama/model.py of the reference
+(RMSNorm :79-99, Column/RowParallelLinear :102-216, FeedForward :316-333,
+Attention :336-444): weights are stored [out_features, in_features]; QKV and
+W1/W3 are split by output features, Wo and W2 by input features, and the two
+partial outputs per layer are summed over the ranks.
+
+Differences from the reference example, all inside one rank's graph:
+RMSNorm and softmax are single row kernels, SiLU runs in the W1 epilogue, the
+two all_reduces are single in-kernel collectives, and a decode step reads a
+K/V cache (the reference example has none).
+"""
+import math
+
+from . import ops
+from .planner import PlannerContext
+
+
+class LlamaConfig:
+    def __init__(self, dim=4096, n_heads=32, n_kv_heads=None, head_dim=128, ffn_dim=11008, norm_eps=1e-5, rope_theta=10000.0):
+        self.dim, self.n_heads, self.head_dim = dim, n_heads, head_dim
+        self.n_kv_heads = n_kv_heads or n_heads
+        self.ffn_dim, self.norm_eps, self.rope_theta = ffn_dim, norm_eps, rope_theta
+
+
+LLAMA2_7B = dict(dim=4096, n_heads=32, n_kv_heads=32, ffn_dim=11008)
+LLAMA2_70B = dict(dim=8192, n_heads=64, n_kv_heads=8, ffn_dim=28672)
+
+
+def layer_weights(cfg, dtype, world_size, prefix=""):
+    """Creates this rank's weight tensors of one layer. Returns a dict name -> Tensor."""
+    p = world_size
+    hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
+    if cfg.ffn_dim % p or cfg.n_heads % p:
+        raise ValueError("heads and ffn_dim must be divisible by the world size")
+    f = cfg.ffn_dim // p
+    t = ops.tensor
+    return {
+        "attn_norm": t([cfg.dim], dtype, name=prefix + "attn_norm"),
+        "wq": t([hl * hd, cfg.dim], dtype, name=prefix + "wq"),
+        "wk": t([kvl * hd, cfg.dim], dtype, name=prefix + "wk"),
+        "wv": t([kvl * hd, cfg.dim], dtype, name=prefix + "wv"),
+        "wo": t([cfg.dim, hl * hd], dtype, name=prefix + "wo"),
+        "ffn_norm": t([cfg.dim], dtype, name=prefix + "ffn_norm"),
+        "w1": t([f, cfg.dim], dtype, name=prefix + "w1"),
+        "w3": t([f, cfg.dim], dtype, name=prefix + "w3"),
+        "w2": t([cfg.dim, f], dtype, name=prefix + "w2"),
+    }
+
+
+def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None):
+    """One layer on `x` [batch*seq, dim].
+
+    Prefill: `mask` [1, 1, seq, seq] (additive, -inf above the diagonal) and `rope` [1, seq, 1, head_dim]
+    (interleaved cos/sin pairs, examples/llama/model_test.py:379-384). Decode (seq == 1): `k_cache`/`v_cache`
+    [batch, kv_heads_local, t_kv, head_dim] hold the keys/values attended to; `rope` is [1, 1, 1, head_dim].
+    Returns the layer output [batch*seq, dim]."""
+    p = world_size
+    hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
+    bt = batch * seq
+    h, x = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps), x
+    q = ops.matmul(h, w["wq"], transpose_other=True)   # [bt, hl*hd]
+    q = ops.reshape(q, [batch, seq, hl, hd])
+    if rope is not None:
+        q = ops.rope(q, rope)
+    q = ops.transpose(q, [0, 2, 1, 3])                 # [b, hl, seq, hd]
+    if k_cache is None:
+        k = ops.matmul(h, w["wk"], transpose_other=True)
+        v = ops.matmul(h, w["wv"], transpose_other=True)
+        k = ops.reshape(k, [batch, seq, kvl, hd])
+        if rope is not None:
+            k = ops.rope(k, rope)
+        k = ops.transpose(k, [0, 2, 1, 3])             # [b, kvl, seq, hd]
+        v = ops.transpose(ops.reshape(v, [batch, seq, kvl, hd]), [0, 2, 1, 3])
+    else:
+        k, v = k_cache, v_cache
+    scale = 1.0 / math.sqrt(hd)
+    if kvl == hl or kvl == 1:
+        scores = ops.matmul(q, k, transpose_other=True)     # [b, hl, seq, t_kv]; C broadcasts when kvl == 1
+        if mask is not None:
+            scores = ops.add(ops.mul(scores, scale), mask)
+            probs = ops.softmax(scores)
+        else:
+            probs = ops.softmax(scores, scale=scale)
+        o = ops.matmul(probs, v)                            # [b, hl, seq, hd]
+    else:
+        raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")
+    o = ops.reshape(ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
+    attn = ops.matmul(o, w["wo"], transpose_other=True)     # partial [bt, dim]
+    if p > 1:
+        attn = ops.all_reduce(attn, rank, p, output=attn)
+    h2, x1 = ops.rmsnorm(attn, w["ffn_norm"], eps=cfg.norm_eps, residual=x)
+    with PlannerContext(sync=False):                        # SiLU in the W1 epilogue
+        gate = ops.silu(ops.matmul(h2, w["w1"], transpose_other=True))
+    up = ops.matmul(h2, w["w3"], transpose_other=True)
+    g = ops.mul(gate, up)
+    down = ops.matmul(g, w["w2"], transpose_other=True)     # partial [bt, dim]
+    if p > 1:
+        down = ops.all_reduce(down, rank, p, output=down)
+    return ops.add(x1, down)

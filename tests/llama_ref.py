@@ -1,0 +1,81 @@
+"""CPU composition of one tensor-parallel Llama decoder layer from the oracle's
+per-op functions, in the op order of ark_b200/llama.py (which follows
+examples/llama/model.py of the reference). Storage type roundings happen where
+the engine materialises a tensor; fused kernels keep fp32 inside (rmsnorm,
+softmax, matmul + SiLU)."""
+import math
+
+import numpy as np
+
+from oracle import oracle as O
+
+
+def rope_table(seq, head_dim, theta=10000.0, start=0):
+    """Interleaved (cos, sin) pairs per position (examples/llama/generator.py:20-27,
+    model_test.py:379-384), shape [1, seq, 1, head_dim] in fp32."""
+    freqs = 1.0 / (theta ** (np.arange(0, head_dim, 2)[: head_dim // 2].astype(np.float32) / head_dim))
+    t = np.arange(start, start + seq, dtype=np.float32)
+    ang = np.outer(t, freqs)
+    tab = np.stack([np.cos(ang), np.sin(ang)], axis=-1).reshape(seq, head_dim)
+    return tab.reshape(1, seq, 1, head_dim).astype(np.float32)
+
+
+def causal_mask(seq, dt):
+    m = np.triu(np.full((seq, seq), -np.inf, np.float32), k=1)
+    m = np.where(np.isinf(m), np.float32(-60000.0 if dt == "fp16" else -1e30), m)
+    return m.reshape(1, 1, seq, seq)
+
+
+def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_caches=None):
+    """Full layer over all ranks: ws is a list (one dict of numpy weights per rank);
+    returns the layer output (identical on all ranks)."""
+    p = len(ws)
+    hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
+    bt = batch * seq
+    f32 = lambda a: O.to_f32(a, dt)
+    st = lambda a: O.to_storage(a, dt)
+    scale = 1.0 / math.sqrt(hd)
+    attn_parts = []
+    for r in range(p):
+        w = ws[r]
+        h = O.rmsnorm(x, w["attn_norm"], dt, cfg.norm_eps)
+        q = O.matmul(h, w["wq"], dt, trans_b=True).reshape(batch, seq, hl, hd)
+        if rope is not None:
+            q = O.rope(q, np.ascontiguousarray(np.broadcast_to(rope, q.shape)), dt)
+        q = np.ascontiguousarray(q.transpose(0, 2, 1, 3))
+        if k_caches is None:
+            k = O.matmul(h, w["wk"], dt, trans_b=True).reshape(batch, seq, kvl, hd)
+            v = O.matmul(h, w["wv"], dt, trans_b=True).reshape(batch, seq, kvl, hd)
+            if rope is not None:
+                k = O.rope(k, np.ascontiguousarray(np.broadcast_to(rope, k.shape)), dt)
+            k = np.ascontiguousarray(k.transpose(0, 2, 1, 3))
+            v = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
+        else:
+            k, v = k_caches[r], v_caches[r]
+        scores = O.matmul(q, k, dt, trans_b=True)
+        if mask is not None:
+            scores = O.scalar("mul", scores, scale, dt)
+            scores = O.binary("add", scores, mask, dt)
+            probs = O.softmax(scores, dt)
+        else:
+            # the engine's softmax multiplies by the scale in fp32 before the max/exp
+            sf = f32(scores) * np.float32(scale)
+            e = np.exp(sf - sf.max(-1, keepdims=True))
+            probs = st(e / e.sum(-1, keepdims=True))
+        o = O.matmul(probs, v, dt)
+        o = np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(bt, hl * hd)
+        attn_parts.append(O.matmul(o, w["wo"], dt, trans_b=True))
+    attn = O.all_reduce(attn_parts, dt) if p > 1 else attn_parts[0]
+    x1 = O.binary("add", attn, x, dt)
+    down_parts = []
+    for r in range(p):
+        w = ws[r]
+        h2 = O.rmsnorm(x1, w["ffn_norm"], dt, cfg.norm_eps)
+        # SiLU runs on the fp32 accumulator in the epilogue: recompute the gate in fp32
+        a32 = f32(h2).astype(np.float32) @ f32(w["w1"]).astype(np.float32).T
+        gate = st(a32 / (1.0 + np.exp(-a32)))
+        up = O.matmul(h2, w["w3"], dt, trans_b=True)
+        g = O.binary("mul", gate, up, dt)
+        down_parts.append(O.matmul(g, w["w2"], dt, trans_b=True))
+    down = O.all_reduce(down_parts, dt) if p > 1 else down_parts[0]
+    return O.binary("add", x1, down, dt)

@@ -1,0 +1,77 @@
+"""GPU parity of Llama-shaped decoder layers (prefill with causal mask and RoPE,
+decode against a K/V cache) against the per-op oracle composition, one GPU."""
+import numpy as np
+import pytest
+
+import ark_b200 as ark
+from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+from oracle import oracle as O
+from tests.ark_util import NAME, execute
+from tests.llama_ref import causal_mask, layer, rope_table
+
+pytestmark = pytest.mark.gpu
+
+
+def make_weights(cfg, dt, world, rng):
+    hl, kvl, hd, f = cfg.n_heads // world, max(1, cfg.n_kv_heads // world), cfg.head_dim, cfg.ffn_dim // world
+    shapes = {"attn_norm": (cfg.dim,), "wq": (hl * hd, cfg.dim), "wk": (kvl * hd, cfg.dim), "wv": (kvl * hd, cfg.dim),
+              "wo": (cfg.dim, hl * hd), "ffn_norm": (cfg.dim,), "w1": (f, cfg.dim), "w3": (f, cfg.dim), "w2": (cfg.dim, f)}
+    out = {}
+    for k, sh in shapes.items():
+        if "norm" in k:
+            out[k] = O.to_storage(rng.normal(1.0, 0.05, sh).astype(np.float32), dt)
+        else:
+            out[k] = O.to_storage(rng.normal(0.0, 0.02, sh).astype(np.float32), dt)
+    return out
+
+
+def check(got, want, dt):
+    g, w = O.to_f32(got, dt), O.to_f32(want, dt)
+    err = np.abs(g - w)
+    rel = err / np.maximum(np.abs(w), 1e-2)
+    assert float(err.mean()) <= 2e-3 or float(rel.max()) <= 1e-2, (float(err.mean()), float(rel.max()))
+    assert float(err.max()) <= (0.05 if dt == "fp16" else 0.25), float(err.max())
+
+
+@pytest.mark.parametrize("dt,heads,kv", [("fp16", 4, 4), ("bf16", 8, 1)])
+def test_prefill_layer(dt, heads, kv):
+    cfg = LlamaConfig(dim=512, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
+    batch, seq = 2, 128
+    rng = np.random.default_rng(51)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), dt)
+    mask = O.to_storage(causal_mask(seq, dt), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx = ark.tensor([batch * seq, cfg.dim], NAME[dt])
+    tr, tm = ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt]), ark.tensor([1, 1, seq, seq], NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
+    feeds = {tx: x, tr: rope, tm: mask}
+    feeds.update({tw[k]: w[k] for k in w})
+    (got,) = execute([ty], feeds, loop_mode=True)
+    want = layer(x, [w], cfg, batch, seq, dt, rope=rope, mask=mask)
+    check(got, want, dt)
+
+
+@pytest.mark.parametrize("dt,heads,kv,batch", [("fp16", 4, 4, 1), ("bf16", 8, 1, 16)])
+def test_decode_layer_with_kv_cache(dt, heads, kv, batch):
+    cfg = LlamaConfig(dim=512, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
+    t_kv = 256
+    rng = np.random.default_rng(52)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(1, cfg.head_dim, start=t_kv), dt)
+    kc = O.to_storage(rng.normal(0, 1, (batch, kv, t_kv, cfg.head_dim)).astype(np.float32), dt)
+    vc = O.to_storage(rng.normal(0, 1, (batch, kv, t_kv, cfg.head_dim)).astype(np.float32), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx = ark.tensor([batch, cfg.dim], NAME[dt])
+    tr = ark.tensor([1, 1, 1, cfg.head_dim], NAME[dt])
+    tk, tv = ark.tensor(list(kc.shape), NAME[dt]), ark.tensor(list(vc.shape), NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, 1, 0, 1, rope=tr, k_cache=tk, v_cache=tv)
+    feeds = {tx: x, tr: rope, tk: kc, tv: vc}
+    feeds.update({tw[k]: w[k] for k in w if k not in ("wk", "wv")})  # K/V come from the cache
+    (got,) = execute([ty], feeds, loop_mode=True)
+    want = layer(x, [w], cfg, batch, 1, dt, rope=rope, k_caches=[kc], v_caches=[vc])
+    check(got, want, dt)
