@@ -15,6 +15,11 @@ for f in loop_kernel dev_ewise dev_reduce dev_gemm dev_comm; do
     pids+=($!)
   fi
 done
+# stand-alone CUDA translation units (no relocatable device code)
+for f in noalloc_gemv; do
+  $NVCC $ARCH ${ARKB_DEFS:-} -lineinfo -O3 -std=c++17 -Xcompiler -fPIC -I"$HERE/../../include" -c "$HERE/$f.cu" -o "$OUT/obj/$f.o" > "$OUT/obj/$f.log" 2>&1 &
+  pids+=($!)
+done
 HOSTSRC=""
 for f in "$HERE"/*.cpp; do [ -f "$f" ] && HOSTSRC="$HOSTSRC $f"; done
 for f in $HOSTSRC; do

@@ -30,6 +30,10 @@ arkb::Executor *ex(arkb_executor *e) {
 }
 }  // namespace
 
+namespace arkb {
+void set_last_error(const std::string &msg) { g_last_error = msg; }
+}  // namespace arkb
+
 extern "C" {
 
 const char *arkb_last_error(void) { return g_last_error.c_str(); }

@@ -58,6 +58,7 @@ def lib():
         L.arkb_executor_stream.argtypes = [vp, ctypes.POINTER(vp)]
         L.arkb_executor_program_dump.argtypes = [vp, ctypes.POINTER(cp)]
         L.arkb_executor_set_wait_limit.argtypes = [vp, ctypes.c_uint64]
+        L.arkb_matvec_splitk_static.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
         _lib = L
     return _lib
 
@@ -92,6 +93,15 @@ def plan_dump(plan_str):
     buf = ctypes.create_string_buffer(need.value)
     _check(lib().arkb_plan_dump(str(plan_str).encode(), buf, need.value, ctypes.byref(need)))
     return buf.value.decode()
+
+
+def matvec_splitk_static(x_ptr, w_ptr, y_ptr, m, n, k, dtype, stream=0):
+    """y[m,n] = x[m,k] . w[n,k]^T on device pointers without any allocation (scratch is a fixed 4 MiB
+    array inside the library). dtype: "fp16" or "bf16". Raises InvalidUsageError when the problem's
+    partial sums do not fit the fixed scratch. Calls sharing a device must not overlap on the GPU."""
+    code = {"fp16": 1, "bf16": 2}[dtype]
+    _check(lib().arkb_matvec_splitk_static(ctypes.c_void_p(x_ptr), ctypes.c_void_p(w_ptr), ctypes.c_void_p(y_ptr), int(m),
+                                           int(n), int(k), code, ctypes.c_void_p(stream or None)))
 
 
 def torch_allgather(group=None):

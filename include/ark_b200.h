@@ -132,6 +132,21 @@ arkb_status arkb_executor_program_dump(arkb_executor *e, const char **text);
  * comm::wait (ark/include/kernels/comm.h:197-206), which its ops leave at -1. */
 arkb_status arkb_executor_set_wait_limit(arkb_executor *e, uint64_t nanoseconds);
 
+/* y[m, n] = x[m, k] . w[n, k]^T for 1 <= m <= 16 (dtype 1 = fp16, 2 = bf16; fp32 accumulation), the
+ * split-K form of the engine's skinny Matmul, for callers that cannot allocate device memory at the
+ * point of the call (inside a stream capture, in a pre-allocated real-time loop, inside a host whose
+ * memory pool they do not own). It has no counterpart in the reference. It allocates nothing: the
+ * fp32 partial sums live in a 4 MiB array that is part of the library image (every GPU that loads
+ * the library holds it until the process exits). x, w and y are device pointers (x and w 16-byte
+ * aligned), k a multiple of 8; `stream` is a cudaStream_t or NULL. A call whose partials
+ * (k-ranges * m * n * 4 bytes; the k-range count is chosen by the library, up to 64) exceed 4 MiB
+ * returns ARKB_INVALID_USAGE. All calls on a device share the array: it needs no clearing (each call
+ * overwrites what it reads), but calls that overlap in time on the GPU race on it — order them on
+ * one stream or with events. The first call on each device resolves the array's device address;
+ * make that call before any stream capture begins. */
+arkb_status arkb_matvec_splitk_static(const void *x, const void *w, void *y, int m, int n, int k, int dtype,
+                                      void *stream);
+
 #ifdef __cplusplus
 }
 #endif
