@@ -225,7 +225,7 @@ void Executor::fill_params(LaunchParams &P, int iters) const {
 
 void Executor::launch_kernel(int iters) {
     // barrier counters restart at every launch; iter_total and the status persist
-    CUDA_CHECK(cudaMemsetAsync(state_, 0, sizeof(unsigned long long) * kMaxSyncGroups, stream_));
+    CUDA_CHECK(cudaMemsetAsync(state_, 0, sizeof(unsigned long long) * (kMaxSyncGroups + 1), stream_));  // barrier[] and run_seq
     LaunchParams P;
     fill_params(P, iters);
     CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_));

@@ -91,30 +91,49 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
     DeviceState *st = P.state;
     const int whole = kMaxSyncGroups - 1;  // barrier counter reserved for the run protocol
     unsigned long long whole_k = 0;        // whole-grid barriers passed since launch
+    unsigned long long run_seq = 0;        // run requests seen since launch
     unsigned long long iter_local = 0;
     unsigned long long iter_no = st->iter_total;  // stable: only advanced after the last barrier of a run
 
     for (;;) {
         int iters = P.iters;
         if (P.loop_mode) {
-            if (blockIdx.x == 0 && threadIdx.x == 0) {
+            // CTA 0 polls the host's run flag and publishes each request (sequence number +
+            // iteration count) in device memory; the other CTAs poll that word. Waiting for work
+            // is not a failure: it is bounded by the idle limit, not by the wait limit.
+            ++run_seq;
+            if (threadIdx.x == 0) {
                 const unsigned long long t0 = globaltimer();
-                int v;
-                for (;;) {
-                    v = *P.run_flag;
-                    if (v != 0) break;
-                    if (globaltimer() - t0 > P.idle_limit_ns) {
-                        v = -2;  // idle for too long: leave, the host relaunches on the next run
-                        break;
+                if (blockIdx.x == 0) {
+                    int v;
+                    for (;;) {
+                        v = *P.run_flag;
+                        if (v != 0) break;
+                        if (globaltimer() - t0 > P.idle_limit_ns) {
+                            v = -2;  // idle for too long: leave, the host relaunches on the next run
+                            break;
+                        }
+                        __nanosleep(200);
                     }
-                    __nanosleep(200);
+                    st->run_iters = v;
+                    __threadfence();
+                    st_release_gpu(&st->run_seq, run_seq);
+                    ctl.run_iters = v;
+                } else {
+                    int v = -2;
+                    for (;;) {
+                        if (ld_acquire_gpu(&st->run_seq) >= run_seq) {
+                            v = *reinterpret_cast<volatile int32_t *>(&st->run_iters);
+                            break;
+                        }
+                        if (globaltimer() - t0 > P.idle_limit_ns + P.spin_limit) break;
+                        __nanosleep(500);
+                    }
+                    ctl.run_iters = v;
                 }
-                st->run_iters = v;
-                __threadfence();
             }
-            ++whole_k;
-            if (!grid_barrier(&st->barrier[whole], whole_k * gridDim.x, P.spin_limit, &ctl, st, -1)) break;
-            iters = *reinterpret_cast<volatile int32_t *>(&st->run_iters);
+            __syncthreads();
+            iters = ctl.run_iters;
             if (iters < 0) {
                 if (iters == -2 && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(&st->status, ST_OK, ST_IDLE_EXIT);
                 break;

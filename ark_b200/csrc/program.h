@@ -247,6 +247,7 @@ constexpr int kChannels = 64;  // send/recv flag channels per rank pair
 
 struct DeviceState {
     unsigned long long barrier[kMaxSyncGroups];  // monotonic arrive counters (host zeroes them at launch)
+    unsigned long long run_seq;                  // run requests published by CTA 0 since launch (zeroed at launch)
     unsigned long long iter_total;               // iterations completed over the executor's life (never reset)
     int32_t status;                              // StatusCode (first failure wins)
     int32_t status_stage;                        // stage index where it happened

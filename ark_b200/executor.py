@@ -105,7 +105,9 @@ def matvec_splitk_static(x_ptr, w_ptr, y_ptr, m, n, k, dtype, stream=0):
 
 
 def torch_allgather(group=None):
-    """Bootstrap callback over torch.distributed (any backend): gathers raw bytes from all ranks."""
+    """Bootstrap callback over torch.distributed (any backend): gathers raw bytes from all ranks.
+    Pass a gloo group when the callback can be invoked (Executor.barrier) while a loop kernel is
+    resident: the kernel keeps every SM busy, so an NCCL kernel would wait until it leaves."""
     import torch
     import torch.distributed as dist
 

@@ -165,7 +165,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         from ark_b200.executor import torch_allgather
-        allgather = torch_allgather()
+        # host-side rendezvous goes over gloo: while a loop kernel is resident it owns every SM,
+        # so an NCCL kernel issued for a barrier could not start
+        host_group = dist.new_group(backend="gloo")
+        allgather = torch_allgather(host_group)
     tokens = args.tokens
     flops = 4.0 * tokens * D_MODEL * D_FF
     warm = max(args.warmup, 3)
@@ -183,7 +186,7 @@ def main():
 
     def barrier():
         if world > 1:
-            torch.distributed.barrier()
+            torch.distributed.barrier(group=host_group)
         torch.cuda.synchronize()
 
     # ---- device-resident timing: one launch runs all K iterations of the stage program ----
@@ -241,7 +244,7 @@ def main():
     for _ in range(warm):
         e2e_step()
     if world > 1:
-        torch.distributed.barrier()
+        torch.distributed.barrier(group=host_group)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         e2e_step()

@@ -37,7 +37,8 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ag = torch_allgather()
+    host_group = dist.new_group(backend="gloo")  # host-side rendezvous without GPU kernels
+    ag = torch_allgather(host_group)
     size = args.min_bytes
     while size <= args.max_bytes:
         n = size // 2
@@ -56,7 +57,7 @@ def main():
         ex.wait()
         iters = args.iters if size <= (64 << 20) else max(3, args.iters // 4)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        dist.barrier()
+        dist.barrier(group=host_group)
         torch.cuda.synchronize()
         e0.record(stream)
         ex.run(iters)

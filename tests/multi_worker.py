@@ -22,7 +22,9 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ag = torch_allgather()
+    # host-side rendezvous over gloo: a resident loop kernel owns every SM, so NCCL kernels could not start
+    host_group = dist.new_group(backend="gloo")
+    ag = torch_allgather(host_group)
 
     def run(outputs, feeds, iters=1, loop_mode=True):
         plan = ark.Planner(local).plan()
@@ -99,6 +101,31 @@ def main():
     want = O.all_reduce(parts, "fp16")
     err = np.abs(got.astype(np.float32) - want.astype(np.float32))
     assert err.mean() <= 2e-3 and err.max() <= 5e-2, (err.mean(), err.max())
+
+    # ---- one tensor-parallel Llama-shaped decoder layer (prefill), against the per-op oracle composition ----
+    from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+    from tests.llama_ref import causal_mask, layer, rope_table
+    from tests.test_gpu_llama import make_weights
+    cfg = LlamaConfig(dim=512, n_heads=8, n_kv_heads=8, ffn_dim=1024 * world)
+    batch, seq = 1, 64
+    rng = np.random.default_rng(77)
+    ws = [make_weights(cfg, "fp16", world, rng) for _ in range(world)]
+    for r in range(1, world):  # the norm weights are replicated
+        ws[r]["attn_norm"], ws[r]["ffn_norm"] = ws[0]["attn_norm"], ws[0]["ffn_norm"]
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), "fp16")
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), "fp16")
+    mask = O.to_storage(causal_mask(seq, "fp16"), "fp16")
+    fresh()
+    tw = layer_weights(cfg, ark.fp16, world)
+    tx = ark.tensor([batch * seq, cfg.dim], ark.fp16)
+    tr, tm = ark.tensor([1, seq, 1, cfg.head_dim], ark.fp16), ark.tensor([1, 1, seq, seq], ark.fp16)
+    ty = decoder_layer(tx, tw, cfg, batch, seq, rank, world, rope=tr, mask=tm)
+    feeds = {tx: x, tr: rope, tm: mask}
+    feeds.update({tw[k]: ws[rank][k] for k in tw})
+    (got,) = run([ty], feeds)
+    want = layer(x, ws, cfg, batch, seq, "fp16", rope=rope, mask=mask)
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("llama layer", err.mean(), err.max())
 
     dist.barrier()
     dist.destroy_process_group()
