@@ -102,6 +102,11 @@ def cpu_sample(rows, threads_note=True):
     """Times the oracle (CPU port of the reference host baselines) on `rows` rows of X
     through the full-width FFN. Returns (TFLOP/s, seconds)."""
     from oracle import oracle as O
+    try:  # launchers set OMP_NUM_THREADS=1; the CPU baseline uses every host core
+        import ctypes
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(os.cpu_count() or 1)
+    except OSError:
+        pass
     x, w1, w2 = synth(0, 1)
     xs = np.ascontiguousarray(x[:rows])
     t0 = time.perf_counter()
@@ -201,9 +206,9 @@ def main():
     ex.wait()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
-    barrier()
     if rank == 0:
-        sampler.start()
+        sampler.start()  # before the barrier: every rank must enter the timed region together
+    barrier()
     t_b = time.perf_counter()
     e0.record(stream)
     ex.run(args.steps)
