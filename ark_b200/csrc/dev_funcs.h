@@ -8,7 +8,8 @@ namespace arkb {
 struct GemmPipe;
 __device__ void run_ewise(const EwiseArgs &a, int p, int P);
 __device__ void run_reduce(const ReduceArgs &a, int p, int P);
-__device__ void run_rowop(const RowOpArgs &a, int p, int P);
+__device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
+                          unsigned long long wait_limit);
 __device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem);
 __device__ void run_embed(const EmbedArgs &a, int p, int P);
 __device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,

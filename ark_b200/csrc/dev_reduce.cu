@@ -13,6 +13,7 @@
 #include <type_traits>
 
 #include "dev_common.cuh"
+#include "dev_gemm.cuh"  // mbarrier and bulk-copy helpers
 #include "dev_funcs.h"
 
 namespace arkb {
@@ -355,18 +356,176 @@ __device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
     }
 }
 
+// Streaming variant: every active warp owns one or more row buffers in shared memory. Lane 0
+// fetches whole rows with bulk asynchronous copies (completion on an mbarrier), the warp
+// computes the statistics and the result in place and lane 0 hands the buffer to a bulk
+// store, then refills it. With all 16 warps streaming, an SM keeps ~100 KB of loads
+// outstanding — what the HBM bandwidth-delay product asks for — without spending
+// registers on it. (More warps beat deeper per-warp buffering here: measured.)
+constexpr int kRowStageMaxBufs = 4;
+struct RowStageBars {
+    unsigned long long bar[(kThreads / 32) * kRowStageMaxBufs];
+};
+
+__device__ __forceinline__ void bulk_load_row(void *smem_dst, const void *gsrc, uint32_t bytes, void *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_store_row(void *gdst, const void *smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 template <typename T>
-__device__ __forceinline__ void rowop_dispatch(const RowOpArgs &a, int p, int P) {
+__device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
+                             unsigned long long wait_limit) {
+    constexpr int V = 16 / sizeof(T);
+    __shared__ RowStageBars bars;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int W = a.staged_warps, NB = a.staged_bufs;
+    if (warp >= W) return;
+    const int64_t cols = a.cols, nv = cols / V;
+    const uint32_t row_bytes = (uint32_t)(cols * sizeof(T));
+    const uint32_t buf_bytes = (row_bytes + 127) & ~127u;
+    char *mybuf = smem + (size_t)warp * NB * buf_bytes;
+    unsigned long long *mybar = &bars.bar[warp * kRowStageMaxBufs];
+    const int op = a.op;
+    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    const float inv_cols = 1.0f / (float)cols, eps = a.eps;
+    const T *wgt = reinterpret_cast<const T *>(a.weight);
+    const T *in = reinterpret_cast<const T *>(a.in);
+    T *out = reinterpret_cast<T *>(a.out);
+    const int64_t in_ld = a.in_ld, out_ld = a.out_ld;
+    const int64_t first = (int64_t)p * W + warp, step = (int64_t)P * W;
+    const int64_t mine = first < a.rows ? (a.rows - first + step - 1) / step : 0;
+    if (lane == 0) {
+        for (int b = 0; b < NB; ++b) mbar_init(&mybar[b], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        for (int64_t i = 0; i < mine && i < NB; ++i) {
+            mbar_expect_tx(&mybar[i], row_bytes);
+            bulk_load_row(mybuf + i * buf_bytes, in + (first + i * step) * in_ld, row_bytes, &mybar[i]);
+        }
+    }
+    __syncwarp();
+    for (int64_t i = 0; i < mine; ++i) {
+        const int b = (int)(i % NB);
+        bool ok = mbar_wait(&mybar[b], (uint32_t)((i / NB) & 1), wait_limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) {
+                ctl->abort = 1;
+                report(st, ST_MBAR_TIMEOUT, stage_idx);
+            }
+            return;
+        }
+        T *row = reinterpret_cast<T *>(mybuf + b * buf_bytes);
+        float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
+        for (int64_t v = lane; v < nv; v += 32) {
+            const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+            const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+            for (int k = 0; k < V; ++k) {
+                const float x = to_f32(e[k]) * scale;
+                s1 += x;
+                s2 += x * x;
+                mx = fmaxf(mx, x);
+            }
+        }
+        float mul = 1.0f, sub = 0.0f;
+        if (op == RO_RMSNORM) {
+            mul = 1.0f / sqrtf(warp_sum(s2) * inv_cols + eps);
+        } else if (op == RO_LAYERNORM) {
+            const float mean = warp_sum(s1) * inv_cols;
+            float var = 0.0f;
+            for (int64_t v = lane; v < nv; v += 32) {
+                const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+                const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+                for (int k = 0; k < V; ++k) var += (to_f32(e[k]) - mean) * (to_f32(e[k]) - mean);
+            }
+            mul = 1.0f / sqrtf(warp_sum(var) * inv_cols + eps);
+            sub = mean;
+        } else {
+            mx = warp_max(mx);
+            float se = 0.0f;
+            for (int64_t v = lane; v < nv; v += 32) {
+                const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+                const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    se += (sizeof(T) == 2 ? __expf(to_f32(e[k]) * scale - mx) : expf(to_f32(e[k]) * scale - mx));
+            }
+            mul = 1.0f / warp_sum(se);
+        }
+        for (int64_t v = lane; v < nv; v += 32) {
+            const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+            const T *e = reinterpret_cast<const T *>(&q);
+            float f[V];
+            if (op == RO_SOFTMAX) {
+#pragma unroll
+                for (int k = 0; k < V; ++k)
+                    f[k] = (sizeof(T) == 2 ? __expf(to_f32(e[k]) * scale - mx) : expf(to_f32(e[k]) * scale - mx)) * mul;
+            } else {
+#pragma unroll
+                for (int k = 0; k < V; ++k) f[k] = (to_f32(e[k]) - sub) * mul;
+                if (wgt) {
+                    float g[V];
+                    load_vec_cached<T, V>(wgt + v * V, g);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) f[k] *= g[k];
+                }
+            }
+            store_vec<T, V>(row + v * V, f);  // in place, in shared memory
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            bulk_store_row(out + (first + i * step) * out_ld, row, row_bytes);
+            // refill a buffer whose store has finished reading it: with several buffers per warp the one
+            // stored an iteration ago (this iteration's store stays in flight), with a single buffer this one
+            if (NB == 1) {
+                if (i + 1 < mine) {
+                    tma_store_wait_read<0>();
+                    mbar_expect_tx(&mybar[0], row_bytes);
+                    bulk_load_row(mybuf, in + (first + (i + 1) * step) * in_ld, row_bytes, &mybar[0]);
+                }
+            } else if (i >= 1 && (i - 1) + NB < mine) {
+                tma_store_wait_read<1>();
+                const int pb = (int)((i - 1) % NB);
+                mbar_expect_tx(&mybar[pb], row_bytes);
+                bulk_load_row(mybuf + pb * buf_bytes, in + (first + (i - 1 + NB) * step) * in_ld, row_bytes, &mybar[pb]);
+            }
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        tma_store_wait<0>();  // results are in global memory before the stage ends
+        // the barriers are re-created by the next row stage: retire them
+        for (int b = 0; b < NB; ++b) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(&mybar[b])) : "memory");
+    }
+    __syncwarp();
+}
+
+template <typename T>
+__device__ __forceinline__ void rowop_dispatch(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st,
+                                               int stage_idx, unsigned long long wait_limit) {
     const int G = a.warps_per_row;
-    if (G > 0) rowop_regs<T>(a, p, P, G);
+    if (a.staged_warps > 0) rowop_staged<T>(a, p, P, smem, ctl, st, stage_idx, wait_limit);
+    else if (G > 0) rowop_regs<T>(a, p, P, G);
     else rowop_typed<T>(a, p, P);
 }
 
-__device__ void run_rowop(const RowOpArgs &a, int p, int P) {
+__device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
+                          unsigned long long wait_limit) {
     switch (a.dtype) {
-        case DT_F32: rowop_dispatch<float>(a, p, P); break;
-        case DT_F16: rowop_dispatch<__half>(a, p, P); break;
-        case DT_BF16: rowop_dispatch<__nv_bfloat16>(a, p, P); break;
+        case DT_F32: rowop_dispatch<float>(a, p, P, smem, ctl, st, stage_idx, wait_limit); break;
+        case DT_F16: rowop_dispatch<__half>(a, p, P, smem, ctl, st, stage_idx, wait_limit); break;
+        case DT_BF16: rowop_dispatch<__nv_bfloat16>(a, p, P, smem, ctl, st, stage_idx, wait_limit); break;
         default: break;
     }
 }

@@ -44,7 +44,7 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             }
             case SK_EWISE: run_ewise(S.ew, p, Pn); break;
             case SK_REDUCE: run_reduce(S.rd, p, Pn); break;
-            case SK_ROWOP: run_rowop(S.ro, p, Pn); break;
+            case SK_ROWOP: run_rowop(S.ro, p, Pn, smem, ctl, P.state, s, P.spin_limit); break;
             case SK_GEMM:
                 if constexpr (PAIR) run_gemm_pair(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
                 else run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);

@@ -334,8 +334,23 @@ struct Lowerer {
             while (gw < 16 && nv > (int64_t)32 * gw * 8) gw *= 2;
             a.warps_per_row = nv <= (int64_t)32 * gw * 8 ? gw : 0;
         }
+        // streaming through shared memory (bulk copies): rows of 1 KiB .. 48 KiB, no residual form, enough rows
+        // to give every warp several; 16 warps first, then up to 3 row buffers per warp, within 192 KiB
+        {
+            const int64_t row_bytes = a.cols * (int64_t)dtype_size(in.dtype);
+            const int64_t buf = (row_bytes + 127) / 128 * 128;
+            const char *e = getenv("ARKB_ROW_STAGED");
+            const bool want = e ? atoi(e) != 0 : true;
+            if (want && !a.residual && row_bytes >= 1024 && buf <= 96 * 1024 && a.rows >= 4 * proc.count()) {
+                // all row buffers that fit are kept in flight; warps first (they do the arithmetic), then depth
+                const int64_t total = (192 * 1024) / buf;
+                a.staged_bufs = (int32_t)std::max<int64_t>(1, std::min<int64_t>(3, total / 16));
+                a.staged_warps = (int32_t)std::min<int64_t>(16, total / a.staged_bufs);
+            }
+        }
         push(s, op.type + " " + op.name + " rows=" + std::to_string(a.rows) + " cols=" + std::to_string(a.cols) +
-                    " warps/row=" + std::to_string(a.warps_per_row));
+                    " warps/row=" + std::to_string(a.warps_per_row) +
+                    (a.staged_warps ? " staged(" + std::to_string(a.staged_warps) + " warps x " + std::to_string(a.staged_bufs) + " rows)" : ""));
     }
 
     // ---- matmul --------------------------------------------------------------------

@@ -88,6 +88,9 @@ struct RowOpArgs {
     float eps;
     float scale;           // softmax: logits are multiplied by this first
     int32_t warps_per_row; // 1,2,4,8,16: the row is held in registers by that many warps; 0: two-pass fallback
+    int32_t staged_warps;  // > 0: rows are streamed through shared memory with bulk copies by this many warps,
+                           // each with `staged_bufs` row buffers (takes precedence over warps_per_row)
+    int32_t staged_bufs;
     int32_t pad;
 };
 
