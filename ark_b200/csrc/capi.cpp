@@ -158,4 +158,14 @@ arkb_status arkb_executor_set_wait_limit(arkb_executor *e, uint64_t nanoseconds)
     return guard([&] { ex(e)->set_spin_limit(nanoseconds); });
 }
 
+arkb_status arkb_executor_stage_times(arkb_executor *e, int enable, uint64_t *out, size_t capacity, size_t *written,
+                                      int *n_stages, int *grid) {
+    return guard([&] {
+        arkb::Executor *x = ex(e);
+        if (enable >= 0) x->enable_stage_times(enable != 0);
+        const size_t w = x->read_stage_times(reinterpret_cast<unsigned long long *>(out), capacity, n_stages, grid);
+        if (written) *written = w;
+    });
+}
+
 }  // extern "C"

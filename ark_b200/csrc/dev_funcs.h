@@ -12,11 +12,13 @@ __device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *
                           unsigned long long wait_limit);
 __device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem);
 __device__ void run_embed(const EmbedArgs &a, int p, int P);
-__device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
-                         int stage_idx, unsigned long long spin_limit);
-__device__ void run_gemm_pair(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
-                              int stage_idx, unsigned long long spin_limit);
+// `g` may be a copy of the stage record in shared memory; `gmaps` is the record in global memory (tensor maps are read there)
+__device__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+                         DeviceState *st, int stage_idx, unsigned long long spin_limit);
+__device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+                              DeviceState *st, int stage_idx, unsigned long long spin_limit);
 __device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
+__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P);
 __device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no);

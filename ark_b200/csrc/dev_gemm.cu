@@ -222,10 +222,13 @@ __device__ void gemm_epilogue_tile_partial(const GemmLocal &g, const TileCoord &
 //   `empty` slot and publish `acc_full` in both CTAs; the epilogue warps of
 //   both CTAs arrive on the leader's `acc_empty`.
 template <bool PAIR>
-__device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
-                           int stage_idx, unsigned long long lim) {
+__device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+                           DeviceState *st, int stage_idx, unsigned long long lim) {
     const int STAGES = g.stages;
-    const int stage_bytes = kGemmABytes + g.stage_b_bytes;
+    // a ring slot holds G consecutive k-blocks of both operands: [G blocks of A][G blocks of B]
+    const int G = g.kgroup > 1 ? g.kgroup : 1;
+    const int blk_b_bytes = g.stage_b_bytes;
+    const int stage_bytes = G * (kGemmABytes + blk_b_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     GemmLocal L;
     L.C = g.C; L.bias = g.bias; L.ldc = g.ldc; L.c_stride_c = g.c_stride_c; L.c_stride_n = g.c_stride_n;
@@ -235,7 +238,8 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
     L.a_mn_major = g.a_mn_major; L.b_mn_major = g.b_mn_major;
     L.a_bc = g.a_bc; L.a_bn = g.a_bn; L.b_bc = g.b_bc; L.b_bn = g.b_bn;
     const int n_units = g.n_units;
-    const CUtensorMap *tmA = &g.tmA, *tmB = &g.tmB, *tmC = &g.tmC;
+    // the TMA unit reads tensor maps from global memory: `gmaps` is the stage record there, `g` a copy that may sit in shared memory
+    const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
     char *epi_stage = smem + kGemmPipeBytes;
     unsigned int epi_blk = 0;
     const int kblocks = (L.K + kGemmBK - 1) / kGemmBK;
@@ -250,13 +254,13 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
     const int n_half = PAIR ? L.tile_n / 2 : L.tile_n;  // B columns staged by this CTA
     // split-K: unit = tile * splits + range; a unit runs k-blocks [kb_lo, kb_hi) of its tile
     const int splits = L.splits > 1 ? L.splits : 1;
-    const int kper = (kblocks + splits - 1) / splits;
+    const int kper = g.kper > 0 ? g.kper : (kblocks + splits - 1) / splits;
     int my_tiles = 0;
-    unsigned int my_kblocks = 0;
+    unsigned int my_slots = 0;  // ring slots this CTA fills in this stage
     for (int u = up; u < n_units; u += UP) {
         ++my_tiles;
         const int lo = (u % splits) * kper;
-        my_kblocks += (unsigned int)(min(kblocks, lo + kper) - lo);
+        my_slots += (unsigned int)((min(kblocks, lo + kper) - lo + G - 1) / G);
     }
     const uint32_t tmem_base = ctl->tmem_base;
 
@@ -268,7 +272,8 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
             const int mn_major = is_a ? L.a_mn_major : L.b_mn_major;
             const int span = is_a ? kGemmTileM : n_half;              // rows (K-major) or columns (MN-major) staged
             const int chunks = mn_major ? (span + 63) / 64 : 1;       // 64-wide MN chunks
-            const uint32_t bytes = mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2;
+            // a slot always receives G whole k-blocks (those past the end of K arrive as zeros)
+            const uint32_t bytes = (uint32_t)G * (mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2);
             const CUtensorMap *tm = is_a ? tmA : tmB;
             const int has_c = is_a ? L.a_bc : L.b_bc, has_n = is_a ? L.a_bn : L.b_bn;
             int s = 0;
@@ -278,31 +283,34 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
                 const int mn0 = is_a ? tc.m0 + crank * kGemmTileM : tc.n0 + crank * n_half;
                 const int bc = has_c ? tc.bc : 0, bn = has_n ? tc.bn : 0;
                 const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
-                for (int k = kb_lo; k < kb_hi; ++k, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+                for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
                     const uint32_t par = (((base_par >> s) ^ wrap) & 1) ^ 1;
                     if (!mbar_wait(&pp->empty[s], par, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
-                    char *dst = smem + s * stage_bytes + (is_a ? 0 : kGemmABytes);
+                    char *dst = smem + s * stage_bytes + (is_a ? 0 : G * kGemmABytes);
+                    const int chunk_stride = G * 64 * kGemmBK * 2;  // MN-major: G k-blocks of one 64-wide chunk are contiguous
                     if constexpr (!PAIR) {
                         mbar_expect_tx(&pp->full[s], bytes);
                         if (!mn_major) {
-                            tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
+                            if (G == 1) tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
+                            else tma_load_5d(dst, tm, &pp->full[s], 0, mn0, k, bc, bn);
                         } else {
                             for (int c = 0; c < chunks; ++c)
-                                tma_load_4d(dst + c * 64 * kGemmBK * 2, tm, &pp->full[s], mn0 + c * 64, k * kGemmBK, bc, bn);
+                                tma_load_4d(dst + c * chunk_stride, tm, &pp->full[s], mn0 + c * 64, k * kGemmBK, bc, bn);
                         }
                     } else {
                         // both CTAs' copies are credited to the leader's barrier
                         const uint32_t full_leader = mapa_u32(smem_u32(&pp->full[s]), 0);
                         if (crank == 0) mbar_expect_tx(&pp->full[s], 2 * bytes);
                         if (!mn_major) {
-                            tma_load_4d_pair(dst, tm, full_leader, k * kGemmBK, mn0, bc, bn);
+                            if (G == 1) tma_load_4d_pair(dst, tm, full_leader, k * kGemmBK, mn0, bc, bn);
+                            else tma_load_5d_pair(dst, tm, full_leader, 0, mn0, k, bc, bn);
                         } else {
                             for (int c = 0; c < chunks; ++c)
-                                tma_load_4d_pair(dst + c * 64 * kGemmBK * 2, tm, full_leader, mn0 + c * 64, k * kGemmBK, bc, bn);
+                                tma_load_4d_pair(dst + c * chunk_stride, tm, full_leader, mn0 + c * 64, k * kGemmBK, bc, bn);
                         }
                     }
                 }
@@ -314,7 +322,10 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
             // per-MMA (K=16) advance of the descriptor start address, in 16-byte units
             const uint32_t a_adv = L.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
             const uint32_t b_adv = L.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
-            const uint32_t chunk_bytes = 64 * kGemmBK * 2;  // one 64-wide MN chunk
+            const uint32_t blk_mn_bytes = 64 * kGemmBK * 2;        // one k-block of a 64-wide MN chunk
+            const uint32_t chunk_bytes = (uint32_t)G * blk_mn_bytes;  // distance between the chunks of one k-block
+            const uint32_t a_blk = L.a_mn_major ? blk_mn_bytes : (uint32_t)kGemmABytes;   // k-block to k-block inside a slot
+            const uint32_t b_blk = L.b_mn_major ? blk_mn_bytes : (uint32_t)blk_b_bytes;
             unsigned int t = t0;
             int s = 0;
             uint32_t wrap = 0;
@@ -328,22 +339,38 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
                 }
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * 256;
-                for (int k = kb_lo; k < kb_hi; ++k, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+                for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
                     if (!mbar_wait(&pp->full[s], ((base_par >> s) ^ wrap) & 1, lim)) {
                         ctl->abort = 1;
                         report(st, ST_MBAR_TIMEOUT, stage_idx);
                         goto done;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * stage_bytes);
-                    const uint32_t sb = sa + kGemmABytes;
-                    const uint64_t da = L.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
-                    const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
+                    const uint32_t sa0 = smem_u32(smem + s * stage_bytes);
+                    if (G == 1) {
+                        const uint32_t sb = sa0 + kGemmABytes;
+                        const uint64_t da = L.a_mn_major ? umma_desc(sa0, chunk_bytes, 1024) : umma_desc(sa0, 16, 1024);
+                        const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-                        const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
-                        if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
-                        else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                        for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                            const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
+                            if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                            else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                        }
+                    } else {
+                        const uint32_t sb0 = sa0 + G * kGemmABytes;
+                        const int nblk = min(G, kb_hi - k);
+                        for (int j = 0; j < nblk; ++j) {
+                            const uint32_t sa = sa0 + j * a_blk, sb = sb0 + j * b_blk;
+                            const uint64_t da = L.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
+                            const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
+#pragma unroll
+                            for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                                const uint32_t accum = (k + j > kb_lo || kk > 0) ? 1u : 0u;
+                                if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                                else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                            }
+                        }
                     }
                     // free the shared-memory slot once these MMAs have read it
                     if constexpr (PAIR) {
@@ -406,7 +433,7 @@ __device__ void run_gemm_t(const GemmArgs &g, int p, int P, char *smem, GemmPipe
 done:
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int total = my_kblocks;
+        const unsigned int total = my_slots;
         for (int s = 0; s < STAGES; ++s)
             if (total > (unsigned int)s) pp->use[s] += (total - s + STAGES - 1) / STAGES;
         pp->tile_count = t0 + (unsigned int)my_tiles;
@@ -416,13 +443,13 @@ done:
     __syncthreads();
 }
 
-__device__ void run_gemm(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
-                         int stage_idx, unsigned long long spin_limit) {
-    run_gemm_t<false>(g, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+__device__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+                         DeviceState *st, int stage_idx, unsigned long long spin_limit) {
+    run_gemm_t<false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
-__device__ void run_gemm_pair(const GemmArgs &g, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl, DeviceState *st,
-                              int stage_idx, unsigned long long spin_limit) {
-    run_gemm_t<true>(g, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+__device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+                              DeviceState *st, int stage_idx, unsigned long long spin_limit) {
+    run_gemm_t<true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
 
 // Sums the split-K partials (fixed order: deterministic), adds the optional bias,

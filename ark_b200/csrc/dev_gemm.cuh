@@ -39,6 +39,7 @@ constexpr int kGemmPipeBytes = 4 * (kGemmABytes + 256 * kGemmBK * 2);  // 192 Ki
 constexpr int kEpiBlockBytes = 32 * 64;
 constexpr int kEpiStageBytes = 4 * 2 * kEpiBlockBytes;                  // 16 KiB
 constexpr int kGemmSmemBytes = kGemmPipeBytes + kEpiStageBytes;
+static_assert(kGemmSmemBytes >= kSwappedRingBytes, "ring of the swapped form must fit the kernel's shared memory");
 constexpr int kTmemCols = 512;
 constexpr int kEpiWarps = 4, kProducerWarp = 4, kMmaWarp = 5, kProducerWarpB = 6;  // warp 4 loads A, warp 6 loads B
 
@@ -89,6 +90,14 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *t
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void *smem_dst, const CUtensorMap *tm, void *bar, int c0, int c1, int c2,
+                                            int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 
@@ -198,6 +207,13 @@ __device__ __forceinline__ void tma_load_4d_pair(void *smem_dst, const CUtensorM
     asm volatile(
         "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_5d_pair(void *smem_dst, const CUtensorMap *tm, uint32_t bar_cluster_addr,
+                                                 int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(tm), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
 }
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {

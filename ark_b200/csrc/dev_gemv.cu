@@ -1,0 +1,261 @@
+// Weight-streaming matmul for one or two activation rows: y[M, N] = x[M, K] . W.
+// The reference runs these shapes through the same tiled GEMM as everything
+// else (ark/include/kernels/matmul.h:36-115); at one or two rows that work is
+// a read of W at HBM speed and nothing else, so this stage is built around the
+// read: every lane keeps four to eight 16-byte loads of W in flight (64 KiB and more per SM),
+// the activations sit in shared memory as fp32, products are accumulated in
+// fp32 on the CUDA cores and rounded once. The tensor cores are left out on
+// purpose: with W in the 128-row operand of tcgen05.mma an SM consumes at most
+// 32 bytes of W per clock and the accumulate-commit-reload chain of a ring slot
+// sits on the critical path; measured, that form stays below 65% of HBM peak.
+//
+// Two layouts of W:
+//   [N, K] (K contiguous): a warp owns whole rows of W inside the CTA's
+//       k-range; lanes stride the row in 16-byte vectors; one shuffle
+//       reduction per row and activation row.
+//   [K, N] (N contiguous): a warp owns 256 output columns and a k-range; a lane
+//       owns 8 columns and adds up the rows of the range.
+// When K is split into ranges (splits > 1) the fp32 partials go to
+// ws[range][m][n] and the split-K sum stage that follows adds them in range
+// order, applies the activation and rounds (deterministic).
+#include "dev_common.cuh"
+#include "dev_funcs.h"
+
+namespace arkb {
+
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
+    const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
+}
+
+// Copies x[0..M)[k0 .. k0+kr) into shared memory as fp32, laid out for the way gemv_nk reads it: a
+// lane reads VC consecutive 8-element vectors (vector vi = g * VC + c); for each (row m, c, half h of
+// the vector) the values of all g are consecutive float4, so lanes with consecutive g touch
+// consecutive 16-byte words (no bank conflicts). Index: ((m * VC + c) * 2 + h) * ng + g.
+template <typename T, int VC>
+__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int ng, int k0) {
+    const T *x = reinterpret_cast<const T *>(a.x);
+    for (int i = threadIdx.x; i < a.M * nv; i += blockDim.x) {
+        const int m = i / nv, v = i % nv;
+        const uint4 q = *reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k0 + v * 8);
+        float f[8];
+        unpack8<T>(q, f);
+        const int g = v / VC, c = v % VC;
+        xs[((size_t)(m * VC + c) * 2 + 0) * ng + g] = make_float4(f[0], f[1], f[2], f[3]);
+        xs[((size_t)(m * VC + c) * 2 + 1) * ng + g] = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void emit(const GemvArgs &a, int split, int m, int n, float v) {
+    if (a.splits > 1) a.ws[((int64_t)split * a.M + m) * a.N + n] = v;
+    else reinterpret_cast<T *>(a.out)[(int64_t)m * a.ldo + n] = from_f32<T>(apply_act_fast(a.act, v));
+}
+
+// ---- W stored [N, K] ---------------------------------------------------------------
+// A warp walks RW rows of W together; per step a lane loads VC consecutive 16-byte vectors of each
+// row (RW * VC <= 8 loads), so a warp reads VC * 512 contiguous bytes of each row and the
+// activations of a step are read from shared memory once for all RW rows. Two register buffers
+// alternate: the loads of step t+1 are issued before step t is consumed, across row groups too.
+template <typename T, int M, int RW, int VC>
+__device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs) {
+    const int cps = a.ctas_per_split;
+    const int split = p / cps, q = p % cps;
+    if (split >= a.splits) return;
+    const int k0 = split * a.kper;
+    const int kr = min(a.K, k0 + a.kper) - k0;
+    const int nv = kr / 8;
+    const int ng = (nv + VC - 1) / VC;  // groups of VC vectors per row
+    stage_x<T, VC>(a, xs, nv, ng, k0);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    const int row_lo = (int)((int64_t)q * a.N / cps), row_hi = (int)((int64_t)(q + 1) * a.N / cps);
+    const int steps = (ng + 31) / 32;  // per row group
+    const T *w = reinterpret_cast<const T *>(a.w) + k0;
+    const int64_t ldw = a.ldw;
+    const int rows_m = a.M;
+
+    struct Cursor {
+        int r0, j;
+    };
+    auto valid = [&](const Cursor &c) { return c.r0 < row_hi; };
+    auto advance = [&](Cursor &c) {
+        if (++c.j == steps) {
+            c.j = 0;
+            c.r0 += nwarps * RW;
+        }
+    };
+    auto issue = [&](uint4 (&buf)[RW][VC], const Cursor &c) {
+        const int g = lane + 32 * c.j;
+#pragma unroll
+        for (int r = 0; r < RW; ++r)
+#pragma unroll
+            for (int v = 0; v < VC; ++v) {
+                const int vi = g * VC + v;
+                if (c.r0 + r < row_hi && vi < nv) buf[r][v] = ldg16_stream(w + (int64_t)(c.r0 + r) * ldw + vi * 8);
+                else buf[r][v] = make_uint4(0, 0, 0, 0);
+            }
+    };
+    float acc[RW][M];
+#pragma unroll
+    for (int r = 0; r < RW; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    auto consume = [&](uint4 (&buf)[RW][VC], const Cursor &c) {
+        const int g = lane + 32 * c.j;
+#pragma unroll
+        for (int v = 0; v < VC; ++v) {
+            if (g * VC + v < nv) {
+                float f[RW][8];
+#pragma unroll
+                for (int r = 0; r < RW; ++r) unpack8<T>(buf[r][v], f[r]);
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    if (m < rows_m) {
+                        const float4 x0 = xs[((size_t)(m * VC + v) * 2 + 0) * ng + g], x1 = xs[((size_t)(m * VC + v) * 2 + 1) * ng + g];
+#pragma unroll
+                        for (int r = 0; r < RW; ++r)
+                            acc[r][m] += f[r][0] * x0.x + f[r][1] * x0.y + f[r][2] * x0.z + f[r][3] * x0.w + f[r][4] * x1.x +
+                                         f[r][5] * x1.y + f[r][6] * x1.z + f[r][7] * x1.w;
+                    }
+                }
+            }
+        }
+        if (c.j == steps - 1) {  // the rows of this group are complete
+#pragma unroll
+            for (int r = 0; r < RW; ++r)
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const float sum = warp_sum(acc[r][m]);
+                    if (lane == 0 && m < rows_m && c.r0 + r < row_hi) emit<T>(a, split, m, c.r0 + r, sum);
+                    acc[r][m] = 0.0f;
+                }
+        }
+    };
+    Cursor ld{row_lo + warp * RW, 0}, cp = ld;
+    uint4 qa[RW][VC], qb[RW][VC];
+    if (valid(ld)) {
+        issue(qa, ld);
+        advance(ld);
+    }
+    while (valid(cp)) {
+        if (valid(ld)) {
+            issue(qb, ld);
+            advance(ld);
+        }
+        consume(qa, cp);
+        advance(cp);
+        if (!valid(cp)) break;
+        if (valid(ld)) {
+            issue(qa, ld);
+            advance(ld);
+        }
+        consume(qb, cp);
+        advance(cp);
+    }
+}
+
+// ---- W stored [K, N] ---------------------------------------------------------------
+// Item = (block of 256 columns, k-range), one warp per item: a lane owns 8 columns, walks the rows
+// of the range U at a time (two register buffers alternating as above) and writes its sums itself,
+// so warps never wait for one another. All of x sits in shared memory as 16-bit values.
+template <typename T, int M, int U>
+__device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nwarps = blockDim.x >> 5;
+    const int rows_m = a.M;
+    const int64_t ldw = a.ldw;
+    const int K = a.K;
+    {
+        const T *x = reinterpret_cast<const T *>(a.x);
+        for (int i = threadIdx.x; i < rows_m * K; i += blockDim.x) {
+            const int m = i / K, k = i % K;
+            xs[(size_t)m * K + k] = x[(int64_t)m * a.ldx + k];
+        }
+    }
+    __syncthreads();
+    const int items = a.nblocks * a.splits;
+    const T *w = reinterpret_cast<const T *>(a.w);
+    for (int it = p * nwarps + warp; it < items; it += P * nwarps) {
+        const int split = it / a.nblocks, nb = it % a.nblocks;
+        const int k0 = split * a.kper;
+        const int kr = min(K, k0 + a.kper) - k0;
+        const int col = nb * 256 + lane * 8;
+        if (col >= a.N) continue;  // N is a multiple of 8
+        float acc[M][8];
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[m][j] = 0.0f;
+        const T *wc = w + (int64_t)k0 * ldw + col;
+        const T *xk = xs + k0;
+        auto issue = [&](uint4 (&buf)[U], int kb) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) buf[u] = kb + u < kr ? ldg16_stream(wc + (int64_t)(kb + u) * ldw) : make_uint4(0, 0, 0, 0);
+        };
+        auto consume = [&](uint4 (&buf)[U], int kb) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = kb + u;
+                if (k < kr) {
+                    float f[8];
+                    unpack8<T>(buf[u], f);
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        if (m < rows_m) {
+                            const float xv = to_f32(xk[(size_t)m * K + k]);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) acc[m][j] += xv * f[j];
+                        }
+                    }
+                }
+            }
+        };
+        uint4 qa[U], qb[U];
+        int kb = 0;
+        issue(qa, kb);
+        while (kb < kr) {
+            if (kb + U < kr) issue(qb, kb + U);
+            consume(qa, kb);
+            kb += U;
+            if (kb >= kr) break;
+            if (kb + U < kr) issue(qa, kb + U);
+            consume(qb, kb);
+            kb += U;
+        }
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            if (m < rows_m) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) emit<T>(a, split, m, col + j, acc[m][j]);
+            }
+        }
+    }
+}
+
+template <typename T>
+__device__ void gemv_typed(const GemvArgs &a, int p, int P, char *smem) {
+    if (a.w_is_nk) {
+        float4 *xs = reinterpret_cast<float4 *>(smem);
+        if (a.M == 1) gemv_nk<T, 1, kGemvRowsM1, 1>(a, p, P, xs);
+        else gemv_nk<T, 2, kGemvRowsM2, 1>(a, p, P, xs);
+    } else {
+        T *xs = reinterpret_cast<T *>(smem);
+        if (a.M == 1) gemv_kn<T, 1, 8>(a, p, P, xs);
+        else gemv_kn<T, 2, 4>(a, p, P, xs);
+    }
+}
+
+}  // namespace
+
+__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem) {
+    if (a.dtype == DT_BF16) gemv_typed<__nv_bfloat16>(a, p, P, smem);
+    else gemv_typed<__half>(a, p, P, smem);
+}
+
+}  // namespace arkb

@@ -41,15 +41,15 @@ static EncodeTiledFn get_encode_fn() {
 }
 
 static void encode_tmap_cuda(CUtensorMap *out, const TmapSpec &sp) {
-    cuuint64_t dims[4] = {sp.dims[0], sp.dims[1], sp.dims[2], sp.dims[3]};
-    cuuint64_t strides[3] = {sp.strides_bytes[0], sp.strides_bytes[1], sp.strides_bytes[2]};
-    cuuint32_t box[4] = {sp.box[0], sp.box[1], sp.box[2], sp.box[3]};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint64_t dims[5] = {sp.dims[0], sp.dims[1], sp.dims[2], sp.dims[3], sp.dims[4]};
+    cuuint64_t strides[4] = {sp.strides_bytes[0], sp.strides_bytes[1], sp.strides_bytes[2], sp.strides_bytes[3]};
+    cuuint32_t box[5] = {sp.box[0], sp.box[1], sp.box[2], sp.box[3], sp.box[4]};
+    cuuint32_t estr[5] = {1, 1, 1, 1, 1};
     // strides of size-1 dims still have to be valid (multiple of 16, non-zero)
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < sp.rank - 1; ++i)
         if (strides[i] == 0 || strides[i] % 16) strides[i] = ((strides[i] + 15) / 16 + (strides[i] == 0)) * 16;
     CUtensorMapDataType dt = sp.dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUresult r = get_encode_fn()(out, dt, 4, const_cast<void *>(sp.base), dims, strides, box, estr,
+    CUresult r = get_encode_fn()(out, dt, (cuuint32_t)sp.rank, const_cast<void *>(sp.base), dims, strides, box, estr,
                                  CU_TENSOR_MAP_INTERLEAVE_NONE,
                                  sp.swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -60,9 +60,9 @@ static void encode_tmap_cuda(CUtensorMap *out, const TmapSpec &sp) {
 static void encode_tmap_check(CUtensorMap *out, const TmapSpec &sp) {
     std::memset(out, 0, sizeof(*out));
     if (reinterpret_cast<uintptr_t>(sp.base) % 16) throw Error(E_INTERNAL, "tensor map base not 16-byte aligned");
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < sp.rank - 1; ++i)
         if (sp.dims[i + 1] > 1 && sp.strides_bytes[i] % 16) throw Error(E_INTERNAL, "tensor map stride not a multiple of 16");
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < sp.rank; ++i)
         if (sp.box[i] == 0 || sp.box[i] > 256) throw Error(E_INTERNAL, "tensor map box dimension out of range");
 }
 
@@ -221,6 +221,30 @@ void Executor::fill_params(LaunchParams &P, int iters) const {
     }
     P.spin_limit = spin_limit_ ? spin_limit_ : kDefaultSpinLimit;
     P.idle_limit_ns = kDefaultIdleNs;
+    P.stage_times = stage_times_on_ ? stage_times_ : nullptr;
+}
+
+void Executor::enable_stage_times(bool on) {
+    if (kernel_live_) throw Error(E_USAGE, "stage times are switched before launch");
+    if (on && !compiled_) throw Error(E_USAGE, "Need to compile first.");
+    if (on && !stage_times_ && !program_.stages.empty()) {
+        const size_t bytes = program_.stages.size() * (size_t)program_.grid * 2 * sizeof(unsigned long long);
+        CUDA_CHECK(cudaSetDevice(device_id_));
+        CUDA_CHECK(cudaMalloc(&stage_times_, bytes));
+        CUDA_CHECK(cudaMemset(stage_times_, 0, bytes));
+    }
+    stage_times_on_ = on && stage_times_;
+}
+
+size_t Executor::read_stage_times(unsigned long long *out, size_t capacity, int *n_stages, int *grid) {
+    if (n_stages) *n_stages = (int)program_.stages.size();
+    if (grid) *grid = program_.grid;
+    if (!stage_times_on_ || !out) return 0;
+    if (kernel_live_ && pending_) throw Error(E_USAGE, "wait() before reading stage times");
+    const size_t words = std::min(capacity, program_.stages.size() * (size_t)program_.grid * 2);
+    CUDA_CHECK(cudaMemcpyAsync(out, stage_times_, words * sizeof(unsigned long long), cudaMemcpyDeviceToHost, copy_stream_));
+    CUDA_CHECK(cudaStreamSynchronize(copy_stream_));
+    return words;
 }
 
 void Executor::launch_kernel(int iters) {
@@ -362,6 +386,8 @@ void Executor::destroy() {
     if (stages_dev_) cudaFree(stages_dev_);
     if (workspace_) cudaFree(workspace_);
     workspace_ = nullptr;
+    if (stage_times_) cudaFree(stage_times_);
+    stage_times_ = nullptr;
     if (arena_) cudaFree(arena_);
     if (comm_) cudaFree(comm_);
     if (state_) cudaFree(state_);

@@ -40,6 +40,9 @@ class Executor {
     void *stream() const { return stream_; }
     const Program &program() const { return program_; }
     void set_spin_limit(unsigned long long v) { spin_limit_ = v; }
+    void enable_stage_times(bool on);
+    // copies the [n_stages][grid][2] time stamps of the last iteration; returns the number of words written
+    size_t read_stage_times(unsigned long long *out, size_t capacity, int *n_stages, int *grid);
     std::string dump_text;
 
    private:
@@ -61,6 +64,8 @@ class Executor {
     bool own_stream_ = false;
     cudaEvent_t ev_start_ = nullptr, ev_stop_ = nullptr;
     void *workspace_ = nullptr;  // split-K partials
+    unsigned long long *stage_times_ = nullptr;  // per-stage, per-CTA time stamps (diagnostic, off by default)
+    bool stage_times_on_ = false;
     void *arena_ = nullptr, *comm_ = nullptr, *state_ = nullptr, *stages_dev_ = nullptr;
     size_t arena_bytes_ = 0, comm_bytes_ = 0;
     int32_t *host_flags_ = nullptr;          // [0] run flag, [1] status mirror (mapped host memory)

@@ -24,16 +24,41 @@ __device__ __forceinline__ bool in_range(const Stage &S, int cta, int &p, int &P
 // One pass over the stage list. iter_local counts iterations since this
 // launch (barrier phases); iter_no is the 1-based iteration number over the
 // executor's life (cross-rank epochs and channel flags).
+// Stage records are read through a two-slot cache in shared memory: while a CTA works on stage s the
+// record of stage s+1 (of stage 0 after the last one) is copied asynchronously into the other slot, so
+// the global-memory latency of fetching a record is off the path between two stages.
+struct StageCache {
+    Stage slot[2];
+};
+
+__device__ __forceinline__ void stage_fetch(StageCache *sc, int slot, const Stage *src) {
+    constexpr int kWords = sizeof(Stage) / 16;
+    static_assert(sizeof(Stage) % 16 == 0 && kWords <= kThreads, "stage record is copied 16 bytes per thread");
+    if (threadIdx.x < kWords) {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(reinterpret_cast<char *>(&sc->slot[slot]) + threadIdx.x * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(reinterpret_cast<const char *>(src) + threadIdx.x * 16)
+                     : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void stage_fetch_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <bool PAIR>
-__device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, GemmPipe *pipe, CtaCtl *ctl,
-                                         unsigned long long iter_local, unsigned long long iter_no) {
+__device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, GemmPipe *pipe, CtaCtl *ctl, StageCache *sc,
+                                         int &cur, unsigned long long iter_local, unsigned long long iter_no) {
     const int cta = blockIdx.x;
     for (int s = 0; s < P.n_stages; ++s) {
-        const Stage &S = P.stages[s];
+        stage_fetch_wait();
+        __syncthreads();  // the record of stage s has landed; every thread is done with stage s-1
+        // `cur` (the slot holding stage s) is the same in every thread: all threads of a CTA walk the same stages
+        const Stage &S = sc->slot[cur];
+        stage_fetch(sc, cur ^ 1, &P.stages[s + 1 == P.n_stages ? 0 : s + 1]);
+        cur ^= 1;
         int p = 0, Pn = 1;
         if (!in_range(S, cta, p, Pn)) continue;
-        __syncthreads();
         if (ctl->abort) return;
+        unsigned long long *stamp = P.stage_times ? P.stage_times + ((size_t)s * gridDim.x + cta) * 2 : nullptr;
+        if (stamp && threadIdx.x == 0) stamp[0] = globaltimer();
         switch (S.kind) {
             case SK_SYNC: {
                 const unsigned long long k = iter_local * (unsigned long long)P.syncs_per_iter[S.sync_group] + S.sync_ord;
@@ -46,9 +71,10 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             case SK_REDUCE: run_reduce(S.rd, p, Pn); break;
             case SK_ROWOP: run_rowop(S.ro, p, Pn, smem, ctl, P.state, s, P.spin_limit); break;
             case SK_GEMM:
-                if constexpr (PAIR) run_gemm_pair(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
-                else run_gemm(S.gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
+                if constexpr (PAIR) run_gemm_pair(S.gm, &P.stages[s].gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
+                else run_gemm(S.gm, &P.stages[s].gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
                 break;
+            case SK_GEMV: run_gemv(S.gv, p, Pn, smem); break;
             case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
             case SK_SPLITK_REDUCE: run_splitk_reduce(S.sr, p, Pn); break;
             case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;
@@ -63,6 +89,10 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             case SK_ALLREDUCE: run_allreduce(P, S.ar, p, Pn, iter_no); break;
             default: break;
         }
+        if (stamp) {
+            __syncthreads();
+            if (threadIdx.x == 0) stamp[1] = globaltimer();
+        }
     }
 }
 
@@ -71,6 +101,7 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
     extern __shared__ __align__(1024) char dyn_smem[];
     __shared__ CtaCtl ctl;
     __shared__ GemmPipe pipe;
+    __shared__ StageCache stage_cache;
     // dynamic shared memory base rounded up to 1 KiB (128-byte swizzle atoms)
     char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(dyn_smem) + 1023) & ~(uintptr_t)1023);
 
@@ -87,6 +118,9 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
     __syncthreads();
     if constexpr (PAIR) cluster_sync_all();  // the partner's barriers are initialised before anything signals them
     tc_fence_after();
+
+    int cache_slot = 0;
+    if (P.n_stages > 0) stage_fetch(&stage_cache, 0, &P.stages[0]);
 
     DeviceState *st = P.state;
     const int whole = kMaxSyncGroups - 1;  // barrier counter reserved for the run protocol
@@ -142,7 +176,7 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
         if (blockIdx.x == 0 && threadIdx.x == 0) st->t_begin = globaltimer();
         bool ok = true;
         for (int i = 0; i < iters && ok; ++i) {
-            run_body<PAIR>(P, smem, &pipe, &ctl, iter_local, iter_no + 1);
+            run_body<PAIR>(P, smem, &pipe, &ctl, &stage_cache, cache_slot, iter_local, iter_no + 1);
             ++whole_k;
             ok = grid_barrier(&st->barrier[whole], whole_k * gridDim.x, P.spin_limit, &ctl, st, -2);
             ++iter_local;
@@ -157,6 +191,7 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
         if (!ok || !P.loop_mode) break;
     }
 
+    stage_fetch_wait();
     __syncthreads();
     if (ctl.abort && threadIdx.x == 0) {
         // give bulk copies still in flight time to land before the CTA's shared memory goes away

@@ -428,6 +428,103 @@ struct Lowerer {
             push(s, "Matmul(simt) " + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" + std::to_string(K));
             return;
         }
+        // One or two rows of activations against an unbatched weight matrix: the work is a read of the weights at
+        // HBM speed; it runs on the CUDA cores with the activations in shared memory. (From three rows on the
+        // multiply-adds outweigh the read and the swapped tensor-core form below is faster.)
+        {
+            const char *e = getenv("ARKB_GEMV");
+            const bool want = e ? atoi(e) != 0 : true;
+            const int64_t P = proc.count();
+            const bool shapes_ok = full && !ta && M <= kGemvMaxM && bn * bc == 1 && (tb ? K % 8 == 0 && K >= 512 : N % 8 == 0 && N >= 256 && M * K * 2 <= 160 * 1024) &&
+                                   lda % 8 == 0 && N * K >= 65536;
+            if (want && shapes_ok) {
+                Stage s = new_stage(SK_GEMV, proc);
+                GemvArgs &g = s.gv;
+                g.out = pc; g.x = pa; g.w = pb;
+                g.ldx = lda; g.ldw = ldb; g.ldo = ldc;
+                g.M = (int32_t)M; g.N = (int32_t)N; g.K = (int32_t)K;
+                g.w_is_nk = tb ? 1 : 0;
+                g.dtype = A.dtype;
+                g.act = act < 0 ? ACT_NONE : act;
+                if (tb) {
+                    // CTAs = k-ranges x row blocks; a warp walks whole groups of RW rows, so the time of the stage is
+                    // (groups per warp, rounded up) x (length of a k-range). Pick the number of k-ranges with the
+                    // least such time; more than one range costs a barrier and a pass over the partials.
+                    const int64_t RW = M == 1 ? kGemvRowsM1 : kGemvRowsM2, warps = kThreads / 32;
+                    auto kper_of = [&](int64_t sp) { return ((K + sp - 1) / sp + 255) / 256 * 256; };
+                    // time in steps (a step = 256 elements of K for RW rows) scaled to microseconds by the HBM rate
+                    const double step_us = 256.0 * RW * es * (double)(P * warps) / 6.5e6;
+                    int64_t splits = 0;
+                    double best = 1e30;
+                    for (int64_t sp = 1; sp <= std::min<int64_t>(P, 32); ++sp) {
+                        const int64_t kp = kper_of(sp), eff = (K + kp - 1) / kp;
+                        if (eff != sp) continue;
+                        if (M * kp * 4 > 160 * 1024) continue;
+                        if (kp < 1024 && sp > 1) break;
+                        const int64_t cps = P / eff;
+                        const int64_t rows_cta = (N + cps - 1) / cps;
+                        const int64_t rounds = ((rows_cta + RW - 1) / RW + warps - 1) / warps;
+                        const double t = (double)rounds * ((double)kp / 256.0 + 0.5) * step_us + (eff > 1 ? 6.0 : 0.0);
+                        if (t < best - 1e-9) { best = t; splits = eff; }
+                    }
+                    if (!splits) throw Error(E_INTERNAL, "gemv: k-range does not fit");
+                    const int64_t kper = kper_of(splits);
+                    g.kper = (int32_t)kper;
+                    g.splits = (int32_t)splits;
+                    g.ctas_per_split = (int32_t)(P / splits);
+                } else {
+                    // items = column blocks x k-ranges, one warp each, dealt round-robin over all warps: enough
+                    // k-ranges to give every warp an item, and the count whose last wave is fullest
+                    const int64_t nblocks = (N + 255) / 256, W = P * (kThreads / 32);
+                    int64_t best_sp = 1;
+                    double best = -1;
+                    for (int64_t sp = 1; sp <= 256; ++sp) {
+                        const int64_t kper = (K + sp - 1) / sp;
+                        if (kper < 64 && sp > 1) break;
+                        const int64_t items = nblocks * ((K + kper - 1) / kper);
+                        const double eff = (double)items / (double)(((items + W - 1) / W) * W);
+                        if (eff > best + 0.03) { best = eff; best_sp = sp; }
+                    }
+                    const int64_t kper = (K + best_sp - 1) / best_sp;
+                    g.kper = (int32_t)kper;
+                    g.splits = (int32_t)((K + kper - 1) / kper);
+                    g.nblocks = (int32_t)nblocks;
+                }
+                if (g.splits > 1) {
+                    if (!env.workspace) {
+                        g.splits = 1;  // no scratch in this pass (plan checks): shape of the stage list is all that matters
+                    } else {
+                        const size_t bytes = (size_t)g.splits * M * N * sizeof(float);
+                        g.ws = reinterpret_cast<float *>(env.workspace + prog.workspace_bytes);
+                        prog.workspace_bytes += (bytes + 255) / 256 * 256;
+                    }
+                }
+                const int act_final = g.act;
+                if (g.splits > 1) g.act = ACT_NONE;
+                const GemvArgs gv = g;
+                push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
+                            std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
+                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) : ""));
+                if (gv.splits > 1) {
+                    emit_sync(proc);
+                    Stage r = new_stage(SK_SPLITK_REDUCE, proc);
+                    SplitKReduceArgs &a = r.sr;
+                    a.C = pc;
+                    a.bias = nullptr;
+                    a.ws = gv.ws;
+                    a.ldc = ldc;
+                    a.c_stride_c = cst[2] * cst[3];
+                    a.c_stride_n = cst[1] * cst[2] * cst[3];
+                    a.M = (int32_t)M; a.N = (int32_t)N;
+                    a.batch_c = 1; a.batch_n = 1;
+                    a.splits = gv.splits;
+                    a.dtype = A.dtype;
+                    a.act = act_final;
+                    push(r, "  split-K sum " + op.name + " splits=" + std::to_string(a.splits));
+                }
+                return;
+            }
+        }
         // Skinny problems (few rows of activations against a large weight matrix, the
         // decode case) are run swapped: the weights become the 128-row A operand that fills
         // the shared-memory ring, the activations the narrow B operand.
@@ -465,19 +562,34 @@ struct Lowerer {
             g.tiles_n = 1;
             g.raster_group = (int32_t)tiles_m;
             g.n_units = (int32_t)(bn * bc * tiles_m);
+            // One bulk tensor copy per operand brings `kgroup` k-blocks into a ring slot: a producer thread that
+            // issues one 16 KiB copy at a time tops out near 5.2 TB/s over all SMs, 32 KiB copies reach 6.3.
+            // Needs whole k-blocks (K % 64 == 0) and at least 4 slots in shared memory.
+            {
+                const int64_t b_rows_k = prog.pair_mode ? g.tile_n / 2 : g.tile_n;
+                const int64_t per_block = 16 * 1024 + b_rows_k * 128;
+                int G = 1;
+                if (K % 64 == 0) {
+                    if (kSwappedRingBytes / (2 * per_block) >= 4) G = 2;
+                }
+                if (const char *e = getenv("ARKB_KGROUP")) G = std::max(1, std::min(G, atoi(e)));
+                g.kgroup = G;
+            }
             // Split K when the tiles alone cannot keep every CTA (pair) streaming weights: pick the
             // split with the least makespan in k-blocks. Partials go to scratch and a second stage
             // sums them in a fixed order (deterministic).
             const int64_t kblocks = (K + 63) / 64, tiles = g.n_units;
             int best_s = 1;
+            int64_t best_kper = kblocks;
             double best = 1e30;
             for (int sp = 1; sp <= 32 && sp * 2 <= kblocks; ++sp) {
-                const int64_t kper = (kblocks + sp - 1) / sp;
+                const int64_t kper = ((kblocks + sp - 1) / sp + g.kgroup - 1) / g.kgroup * g.kgroup;
                 const int64_t eff = (kblocks + kper - 1) / kper;
                 const int64_t waves = (tiles * eff + P - 1) / P;
                 const double cost = (double)waves * kper + 0.5 * eff;
-                if (cost < best - 1e-9) { best = cost; best_s = (int)eff; }
+                if (cost < best - 1e-9) { best = cost; best_s = (int)eff; best_kper = kper; }
             }
+            if (best_s > 1 && env.workspace) g.kper = (int32_t)best_kper;
             if (best_s > 1 && env.workspace) {
                 g.splits = best_s;
                 g.n_units = (int32_t)(tiles * best_s);
@@ -536,12 +648,29 @@ struct Lowerer {
             g.n_units = (int32_t)(tg.task_range.count() * g.sub_m * g.sub_n);
         }
         // tensor maps: dims {inner, rows, C, N}
+        // group > 1 (K-major operands only): the K axis is cut into 64-element blocks that become a dimension
+        // of their own, {64, rows, K/64, C, N}, so that one box {64, rows, group} covers `group` k-blocks
         auto mk = [&](const TensorDesc &T, const std::vector<int64_t> &sh, const std::vector<int64_t> &st, char *base,
-                      uint32_t box_inner, uint32_t box_rows, CUtensorMap *out, int swizzle = 128) {
+                      uint32_t box_inner, uint32_t box_rows, CUtensorMap *out, int swizzle = 128, int group = 1) {
             TmapSpec sp;
             sp.swizzle_bytes = swizzle;
             sp.base = base;
             sp.dtype = T.dtype;
+            if (group > 1) {
+                sp.rank = 5;
+                sp.dims[0] = 64;
+                sp.dims[1] = (uint64_t)sh[2];
+                sp.dims[2] = (uint64_t)(sh[3] / 64);
+                sp.dims[3] = (uint64_t)sh[1];
+                sp.dims[4] = (uint64_t)sh[0];
+                sp.strides_bytes[0] = (uint64_t)st[3] * es;
+                sp.strides_bytes[1] = 128;
+                sp.strides_bytes[2] = (uint64_t)st[2] * st[3] * es;
+                sp.strides_bytes[3] = (uint64_t)st[1] * st[2] * st[3] * es;
+                sp.box[0] = 64; sp.box[1] = box_rows; sp.box[2] = (uint32_t)group; sp.box[3] = 1; sp.box[4] = 1;
+                env.encode_tmap(out, sp);
+                return;
+            }
             sp.dims[0] = (uint64_t)sh[3];
             sp.dims[1] = (uint64_t)sh[2];
             sp.dims[2] = (uint64_t)sh[1];
@@ -559,12 +688,15 @@ struct Lowerer {
             mk(A, ash, ast, pa, 64, g.a_mn_major ? 64 : 128, &g.tmA);
             mk(B, bsh, bst, pb, 64, g.b_mn_major ? 64 : b_rows, &g.tmB);
         } else {
-            mk(B, bsh, bst, pb, 64, g.a_mn_major ? 64 : 128, &g.tmA);  // weights
-            mk(A, ash, ast, pa, 64, b_rows, &g.tmB);                    // activations
+            const int G = g.kgroup > 1 ? g.kgroup : 1;
+            if (g.a_mn_major) mk(B, bsh, bst, pb, 64, 64 * G, &g.tmA);   // weights [K, N]: G k-blocks of a 64-wide chunk per box
+            else mk(B, bsh, bst, pb, 64, 128, &g.tmA, 128, G);           // weights [N, K]
+            mk(A, ash, ast, pa, 64, b_rows, &g.tmB, 128, G);             // activations
         }
         // ring: 16 KiB A block + this CTA's B block per stage, as many stages as fit in 192 KiB (at most 12)
         g.stage_b_bytes = (int32_t)(g.b_mn_major ? ((b_rows + 63) / 64) * 64 * 128 : b_rows * 128);
-        g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / (16 * 1024 + g.stage_b_bytes));
+        if (swapped && g.kgroup > 1) g.stages = (int32_t)std::min<int64_t>(12, kSwappedRingBytes / (g.kgroup * (16 * 1024 + g.stage_b_bytes)));
+        else g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / (16 * 1024 + g.stage_b_bytes));
         // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
         g.c_tma = (!swapped && g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
         if (g.c_tma) mk(C, csh, cst, pc, 32, 32, &g.tmC, 64);
@@ -572,7 +704,7 @@ struct Lowerer {
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
                     (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K") + (swapped ? " swapped" : "") +
-                    " stages=" + std::to_string(g.stages) + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
+                    " stages=" + std::to_string(g.stages) + (g.kgroup > 1 ? "x" + std::to_string(g.kgroup) + "kb" : "") + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
         if (g.splits > 1) {
             // the activation and the rounding belong to the sum, not to the partials
             GemmArgs &gg = prog.stages.back().gm;

@@ -133,9 +133,10 @@ void resolve_remote(const Plan &plan, Layout &lay, const std::vector<std::vector
 struct TmapSpec {
     const void *base;
     int dtype;
-    uint64_t dims[4];
-    uint64_t strides_bytes[3];  // strides of dims 1..3
-    uint32_t box[4];
+    int rank = 4;               // 4, or 5 for the k-block-grouped view {64, rows, K/64, C, N}
+    uint64_t dims[5] = {1, 1, 1, 1, 1};
+    uint64_t strides_bytes[4] = {0, 0, 0, 0};  // strides of dims 1..rank-1
+    uint32_t box[5] = {1, 1, 1, 1, 1};
     int swizzle_bytes = 128;  // 128 or 64
 };
 // Encodes a 128-byte-swizzled tiled tensor map; throws on failure.

@@ -94,9 +94,15 @@ struct RowOpArgs {
     int32_t pad;
 };
 
+// Shared memory the loop kernel offers a matmul stage for operand ring slots when its epilogue needs no staging
+// area (the swapped and split-K forms); stages with a TMA-store epilogue use the first 192 KiB only.
+constexpr int kSwappedRingBytes = 208 * 1024;
+
 struct GemmArgs {
     CUtensorMap tmA;  // dims {inner, rows, C, N}; box {64, 128 or 64, 1, 1}, 128-byte swizzle
     CUtensorMap tmB;  // dims {inner, rows, C, N}; box {64, tile_n or 64, 1, 1}
+                      // kgroup > 1, K-major operand: dims {64, rows, K/64, C, N}, box {64, rows, kgroup, 1, 1}
+                      // kgroup > 1, MN-major operand: the 4-d map with box {64, 64 * kgroup, 1, 1}
     CUtensorMap tmC;  // output, dims {N, M, C, N}; box {32, 32, 1, 1}, 64-byte swizzle (used when c_tma)
     void *C;
     const void *bias;     // optional tensor added in the epilogue (same layout as C)
@@ -111,7 +117,7 @@ struct GemmArgs {
     int32_t tile_n;                  // UMMA N (multiple of 16, <= 256)
     int32_t c_vec;                   // 1: C rows allow 16-byte stores
     int32_t c_tma;                   // 1: the epilogue stages 32x32 blocks in shared memory and stores them with TMA
-    int32_t pad1;
+    int32_t kgroup;                  // k-blocks brought by one ring slot (1, 2 or 4): one bulk tensor copy per operand per slot
     // Unit enumeration. plan_tiles == 0: units are this engine's own tiles
     // (128 x tile_n) over the whole output, rasterised in groups of
     // `raster_group` m-tiles. plan_tiles == 1: units follow the plan's task ids
@@ -126,6 +132,8 @@ struct GemmArgs {
     int32_t stages, stage_b_bytes;   // ring depth and bytes of the B block of one stage (A block: 16 KiB)
     int32_t out_transposed;          // 1: operands are swapped (A = weights, B = activations); D[n][m] is stored to C[m][n]
     int32_t splits;                  // > 1: K is cut into `splits` ranges; unit = tile * splits + range, fp32 partials go to `ws`
+    int32_t kper;                    // k-blocks per range (a multiple of kgroup); 0: ceil(k-blocks / splits)
+    int32_t pad2;
     float *ws;                       // split-K partials, layout [splits][batch][rows of C][cols of C]
 };
 
@@ -140,15 +148,24 @@ struct SplitKReduceArgs {
 };
 
 struct GemvArgs {
-    // y[m, n] = sum_k x[m,k] * W, m <= 16; W is [N,K] (K-major) or [K,N].
-    void *out;
-    const void *x;
-    const void *w;
+    // y[M, N] = x[M, K] . W with M <= kGemvMaxM on the CUDA cores; W is [N, K] (w_is_nk) or [K, N]
+    void *out;        // y, row pitch ldo (written when splits == 1)
+    const void *x;    // activations, row pitch ldx
+    const void *w;    // weights, row pitch ldw
+    float *ws;        // splits > 1: fp32 partials [splits][M][N]
     int64_t ldx, ldw, ldo;
     int32_t M, N, K;
-    int32_t w_is_nk;  // 1: W stored [N,K]
+    int32_t w_is_nk;
     int32_t dtype, act;
+    int32_t splits;          // k-ranges
+    int32_t kper;            // elements of K per range ([N, K]: a multiple of 8)
+    int32_t ctas_per_split;  // [N, K]: CTAs that share a k-range and split the rows of W
+    int32_t nblocks;         // [K, N]: blocks of 256 output columns
+    int32_t pad[2];
 };
+// rows of W a warp walks together in the [N, K] form (M = 1 and M = 2): the lowering balances whole groups over the warps
+constexpr int kGemvRowsM1 = 8, kGemvRowsM2 = 4;
+constexpr int kGemvMaxM = 2;
 
 struct GemmSimtArgs {
     void *C;
@@ -283,6 +300,7 @@ struct LaunchParams {
     char *comm[kMaxPeers];        // comm allocation of every rank as mapped here (own included)
     unsigned long long spin_limit;     // nanoseconds a device-side wait may last before it gives up
     unsigned long long idle_limit_ns;  // loop mode: return after this long without a run request
+    unsigned long long *stage_times;   // optional [n_stages][grid][2]: when each CTA entered / left each stage of the last iteration (ns)
 };
 
 }  // namespace arkb

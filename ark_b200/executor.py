@@ -58,6 +58,8 @@ def lib():
         L.arkb_executor_stream.argtypes = [vp, ctypes.POINTER(vp)]
         L.arkb_executor_program_dump.argtypes = [vp, ctypes.POINTER(cp)]
         L.arkb_executor_set_wait_limit.argtypes = [vp, ctypes.c_uint64]
+        L.arkb_executor_stage_times.argtypes = [vp, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
+                                                ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         L.arkb_matvec_splitk_static.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
         _lib = L
     return _lib
@@ -198,6 +200,19 @@ class Executor:
     def set_wait_limit(self, nanoseconds):
         """Bound of every device-side wait; a wait that runs out makes wait() raise GpuError."""
         _check(lib().arkb_executor_set_wait_limit(self._h, int(nanoseconds)))
+
+    def enable_stage_times(self, on=True):
+        """Diagnostic (after compile, before launch): every CTA records when it enters and leaves each stage."""
+        _check(lib().arkb_executor_stage_times(self._h, 1 if on else 0, None, 0, None, None, None))
+
+    def stage_times(self):
+        """Time stamps of the last finished iteration as an int64 array [n_stages, grid, 2] (GPU nanosecond
+        timer; zeros for CTAs outside a stage's processor range). Call after wait()."""
+        ns, grid, w = ctypes.c_int(), ctypes.c_int(), ctypes.c_size_t()
+        _check(lib().arkb_executor_stage_times(self._h, -1, None, 0, None, ctypes.byref(ns), ctypes.byref(grid)))
+        out = np.zeros((ns.value, grid.value, 2), np.uint64)
+        _check(lib().arkb_executor_stage_times(self._h, -1, ctypes.c_void_p(out.ctypes.data), out.size, ctypes.byref(w), None, None))
+        return out.astype(np.int64)
 
     @staticmethod
     def _tjson(tensor):

@@ -124,6 +124,14 @@ def main():
     case("softmax_fp16_65536x2048", rows("softmax", 65536, 2048, ark.fp16, 2))
     case("layernorm_fp16_32768x4096", rows("layernorm", 32768, 4096, ark.fp16, 2))
 
+    # ---- fixed cost of a stage: 16 dependent tiny operators (time / 16 = one stage + one grid barrier) ----
+    def chain16():
+        t = ark.tensor([148, 2048], ark.fp16)
+        for _ in range(16):
+            t = ark.relu(t)
+        return 16 * 2 * 148 * 2048 * 2, 0
+    case("chain16_relu_148x2048", chain16)
+
     # ---- weight-streaming matmuls (decode shapes): bytes = weights ----
     def gemv(m, n, k, dt, es, nk=True):
         def b():

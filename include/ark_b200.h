@@ -131,6 +131,14 @@ arkb_status arkb_executor_program_dump(arkb_executor *e, const char **text);
  * launch. Stands in for the MaxSpinCount template argument of the reference's
  * comm::wait (ark/include/kernels/comm.h:197-206), which its ops leave at -1. */
 arkb_status arkb_executor_set_wait_limit(arkb_executor *e, uint64_t nanoseconds);
+/* Diagnostic: per-stage, per-CTA time stamps. enable = 1 / 0 switches the recording on / off (after
+ * compile, before launch; -1 leaves it as it is). When it is on, every CTA notes the GPU's nanosecond
+ * timer on entering and leaving each stage; `out` receives the stamps of the last finished iteration
+ * as [n_stages][grid][2] words (at most `capacity`), `written` how many. Call after wait(). Stands in
+ * for reading the reference's per-kernel timings out of a profiler; off by default (it adds a CTA-wide
+ * barrier after every stage). */
+arkb_status arkb_executor_stage_times(arkb_executor *e, int enable, uint64_t *out, size_t capacity, size_t *written,
+                                      int *n_stages, int *grid);
 
 /* y[m, n] = x[m, k] . w[n, k]^T for 1 <= m <= 16 (dtype 1 = fp16, 2 = bf16; fp32 accumulation), the
  * split-K form of the engine's skinny Matmul, for callers that cannot allocate device memory at the

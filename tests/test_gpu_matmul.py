@@ -119,3 +119,30 @@ def test_matmul_partial_task_range_follows_plan_tiles():
     plan["NumProcessors"] = 4
     (got,) = execute([out], {t_a: a, t_b: b}, plan=ark.Plan(plan))
     assert_matmul_close(got, O.matmul(a, b, "fp16"), "fp16", "partial ranges")
+
+
+# ---- few activation rows against a weight matrix: the CUDA-core weight-streaming stage ----
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("tb", [True, False])
+@pytest.mark.parametrize("mnk", [(1, 4096, 4096), (1, 1000, 520), (2, 2048, 1024), (3, 264, 3072), (4, 8192, 2048),
+                                 (5, 1536, 1288), (8, 4096, 8192), (8, 512, 512), (1, 256, 16384)])
+def test_matmul_few_rows_stream_weights(dt, tb, mnk):
+    m, n, k = mnk
+    got, want = run_mm((m, k), (n, k) if tb else (k, n), dt, tb=tb, seed=37)
+    assert_matmul_close(got, want, dt, f"gemv {mnk} tb={tb}")
+
+
+@pytest.mark.parametrize("tb", [True, False])
+def test_matmul_few_rows_fused_activation(tb):
+    got, want = run_mm((2, 2048), (4096, 2048) if tb else (2048, 4096), "fp16", tb=tb, seed=38, fuse="gelu")
+    assert_matmul_close(got, want, "fp16", "gemv + gelu")
+
+
+def test_matmul_few_rows_uses_the_streaming_stage():
+    ark.init()
+    x, w = ark.tensor([1, 4096], ark.fp16), ark.tensor([4096, 4096], ark.fp16)
+    ark.matmul(x, w, transpose_other=True)
+    ex = ark.Executor(0, 0, "gemv", str(ark.Planner(0).plan()), loop_mode=False)
+    ex.compile()
+    assert "Matmul(gemv)" in ex.program_dump()
+    ex.destroy()
