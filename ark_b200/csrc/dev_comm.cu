@@ -50,9 +50,11 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
         }
         return;
     }
-    // two-shot: this rank owns vectors [lo, hi)
+    // two-shot and slots: this rank owns vectors [lo, hi). Two-shot reads the partial of every rank from that
+    // rank's tensor; slots (algo 2) finds them in its own staging slots, where the peers' matmul epilogues put them.
     const int64_t per = (nv + R - 1) / R;
     const int64_t lo = per * me, hi = min(nv, lo + per);
+    const bool slots = a.algo == 2;
     for (int64_t i = lo + tid; i < hi; i += nth) {
         float acc[V];
 #pragma unroll
@@ -60,7 +62,9 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
         uint4 raw[kMaxPeers];
 #pragma unroll
         for (int q = 0; q < kMaxPeers; ++q)
-            if (q < R) raw[q] = reinterpret_cast<const uint4 *>(P.arena[q] + a.buf_off[q])[i];
+            if (q < R)
+                raw[q] = slots ? reinterpret_cast<const uint4 *>(P.arena[me] + a.stage_off + q * a.stage_bytes)[i - lo]
+                               : reinterpret_cast<const uint4 *>(P.arena[q] + a.buf_off[q])[i];
 #pragma unroll
         for (int q = 0; q < kMaxPeers; ++q)
             if (q < R) {

@@ -47,6 +47,7 @@ struct GemmLocal {
     float *ws;
     int64_t splits_stride;  // elements between the partials of consecutive k-ranges
     int a_mn_major, b_mn_major, a_bc, a_bn, b_bc, b_bn;
+    int peer_rows;
 };
 
 template <typename T>
@@ -101,7 +102,7 @@ __device__ __forceinline__ void gemm_store_row(const GemmLocal &g, T *crow, cons
 // store of block i. Rows and columns outside the tensor are clipped by TMA.
 template <typename T>
 __device__ void gemm_epilogue_tile_tma(const GemmLocal &g, const CUtensorMap *tmC, const TileCoord &tc, uint32_t tmem_acc,
-                                       int warp, int lane, char *stage, unsigned int &blk) {
+                                       int warp, int lane, char *stage, unsigned int &blk, int row_shift = 0) {
     const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
     const int ncols_tile = min(g.tile_n, g.N - tc.n0);
     const int row0 = tc.m0 + warp * 32;
@@ -123,7 +124,7 @@ __device__ void gemm_epilogue_tile_tma(const GemmLocal &g, const CUtensorMap *tm
             *reinterpret_cast<uint4 *>(buf + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = o.q[j];
         fence_async_smem();
         __syncwarp();
-        if (lane == 0) tma_store_4d(tmC, buf, tc.n0 + c, row0, tc.bc, tc.bn);
+        if (lane == 0) tma_store_4d(tmC, buf, tc.n0 + c, row0 - row_shift, tc.bc, tc.bn);
         ++blk;
     }
 }
@@ -237,6 +238,7 @@ __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int 
     L.splits_stride = (int64_t)g.batch_c * g.batch_n * g.M * g.N;
     L.a_mn_major = g.a_mn_major; L.b_mn_major = g.b_mn_major;
     L.a_bc = g.a_bc; L.a_bn = g.a_bn; L.b_bc = g.b_bc; L.b_bn = g.b_bn;
+    L.peer_rows = g.peer_rows;
     const int n_units = g.n_units;
     // the TMA unit reads tensor maps from global memory: `gmaps` is the stage record there, `g` a copy that may sit in shared memory
     const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
@@ -413,6 +415,13 @@ __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int 
             } else if (L.out_transposed) {
                 if (L.dtype == DT_BF16) gemm_epilogue_tile_swapped<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
                 else gemm_epilogue_tile_swapped<__half>(L, tc, tmem_acc, warp, lane);
+            } else if (L.peer_rows > 0) {
+                // fused all_reduce: the tile goes to the rank that sums these rows (tiles never straddle two owners)
+                const int owner = tc.m0 / L.peer_rows;
+                const CUtensorMap *tm = &gmaps->tmPeer[owner];
+                if (L.dtype == DT_BF16)
+                    gemm_epilogue_tile_tma<__nv_bfloat16>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, owner * L.peer_rows);
+                else gemm_epilogue_tile_tma<__half>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, owner * L.peer_rows);
             } else if (L.c_tma) {
                 if (L.dtype == DT_BF16) gemm_epilogue_tile_tma<__nv_bfloat16>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
                 else gemm_epilogue_tile_tma<__half>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
@@ -428,7 +437,10 @@ __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int 
             }
         }
         // the stage's output must be in global memory before the CTA reaches the next barrier
-        if (lane == 0) tma_store_wait<0>();
+        if (lane == 0) {
+            tma_store_wait<0>();
+            if (L.peer_rows > 0) __threadfence_system();  // tiles stored into peer memory: ordered before the peer barrier that follows
+        }
     }
 done:
     __syncthreads();

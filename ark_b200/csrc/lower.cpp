@@ -380,7 +380,8 @@ struct Lowerer {
         return n;
     }
 
-    void lower_matmul(const OpDesc &op, const Range &proc, const TaskGroup &tg, int act, const TensorDesc *act_out) {
+    void lower_matmul(const OpDesc &op, const Range &proc, const TaskGroup &tg, int act, const TensorDesc *act_out,
+                      const OpDesc *fuse_ar = nullptr) {
         const TensorDesc &A = op.reads.at(0), &B = op.reads.at(1);
         const TensorDesc &C = act_out ? *act_out : op.results.at(0);
         const bool ta = op.arg_bool("TransposeInput");
@@ -700,10 +701,35 @@ struct Lowerer {
         // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
         g.c_tma = (!swapped && g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
         if (g.c_tma) mk(C, csh, cst, pc, 32, 32, &g.tmC, 64);
+        if (fuse_ar) {
+            // Fused all_reduce: tiles go to the staging slots on the rank that sums their rows.
+            const int R = env.nranks;
+            if (!full || swapped || !g.c_tma || g.act != ACT_NONE || M % ((int64_t)R * tile_m) != 0)
+                throw Error(E_UNSUPPORTED, "Matmul fused with AllReduce (one task) needs the full task range, TMA-aligned operands and "
+                                           "M a multiple of 256 x world size");
+            auto it = lay.coll_stage_offsets.find((int)fuse_ar->arg_int("Tag"));
+            if (it == lay.coll_stage_offsets.end() || (int)it->second.size() != R)
+                throw Error(E_PLAN, "fused AllReduce: staging slots were not published by every rank");
+            g.peer_rows = (int32_t)(M / R);
+            const uint64_t slot_bytes = (uint64_t)g.peer_rows * N * es;
+            for (int r = 0; r < R; ++r) {
+                TmapSpec sp;
+                sp.swizzle_bytes = 64;
+                sp.base = env.arena[r] + it->second[r] + (uint64_t)env.rank * slot_bytes;
+                sp.dtype = C.dtype;
+                sp.dims[0] = (uint64_t)N; sp.dims[1] = (uint64_t)g.peer_rows; sp.dims[2] = 1; sp.dims[3] = 1;
+                sp.strides_bytes[0] = (uint64_t)N * es;
+                sp.strides_bytes[1] = slot_bytes;
+                sp.strides_bytes[2] = slot_bytes;
+                sp.box[0] = 32; sp.box[1] = 32; sp.box[2] = 1; sp.box[3] = 1;
+                env.encode_tmap(&g.tmPeer[r], sp);
+            }
+        }
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
                     (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K") + (swapped ? " swapped" : "") +
+                    (g.peer_rows ? " tiles->peer slots" : "") +
                     " stages=" + std::to_string(g.stages) + (g.kgroup > 1 ? "x" + std::to_string(g.kgroup) + "kb" : "") + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
         if (g.splits > 1) {
             // the activation and the rounding belong to the sum, not to the partials
@@ -824,7 +850,8 @@ struct Lowerer {
         emit_sync(proc);
     }
 
-    void lower_all_reduce(const OpDesc &op, const Range &proc) {
+    // fused: the partials already sit in this rank's staging slots (put there by every rank's Matmul epilogue)
+    void lower_all_reduce(const OpDesc &op, const Range &proc, bool fused = false) {
         if (env.nranks == 1) return;
         const TensorDesc &t = op.results.at(0);
         if (!t.dense()) throw Error(E_UNSUPPORTED, "AllReduce: dense tensors only");
@@ -846,6 +873,22 @@ struct Lowerer {
         a.nelem = n;
         a.dtype = t.dtype;
         std::string algo = op.config.is_object() && op.config.contains("Algo") ? op.config.at("Algo").as_string() : "auto";
+        if (fused) {
+            auto st = lay.coll_stage_offsets.find(tag);
+            if (st == lay.coll_stage_offsets.end()) throw Error(E_PLAN, "fused AllReduce: no staging slots");
+            if (n % ((int64_t)V * env.nranks)) throw Error(E_UNSUPPORTED, "fused AllReduce: size must split evenly over the ranks");
+            a.algo = 2;
+            a.stage_off = st->second[env.rank];
+            a.stage_bytes = bytes / env.nranks;
+            emit_sync(proc);
+            emit_peersync(proc, "partial tiles pushed");
+            emit_sync(proc);
+            push(s, "AllReduce " + op.name + " sum of staging slots + all-gather bytes=" + std::to_string(bytes));
+            emit_sync(proc);
+            emit_peersync(proc, "all_reduce outputs stored");
+            emit_sync(proc);
+            return;
+        }
         const size_t slot = lay.comm_stage_bytes / kMaxPeers;
         const bool one = (algo == "oneshot") || (algo == "auto" && bytes <= 256 * 1024);
         if (one && bytes > slot) throw Error(E_PLAN, "AllReduce: tensor exceeds the one-shot staging area");
@@ -900,6 +943,14 @@ struct Lowerer {
             if (op.is_virtual) continue;
             // Matmul followed by a unary activation on its result, merged into one task
             // by the planner (Sync=false): run the activation in the GEMM epilogue.
+            if (op.type == "Matmul" && fused_allreduce(plan, ti, i)) {
+                if (!first) emit_sync(proc);
+                lower_matmul(op, proc, tg, -1, nullptr, &ti.ops[i + 1]);
+                lower_all_reduce(ti.ops[i + 1], proc, true);
+                first = false;
+                ++i;
+                continue;
+            }
             if (op.type == "Matmul" && i + 1 < ti.ops.size()) {
                 const OpDesc &nx = ti.ops[i + 1];
                 const int act = act_code(nx.type);

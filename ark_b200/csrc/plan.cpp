@@ -225,6 +225,19 @@ const TaskInfo &Plan::task(int64_t id) const {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+bool fused_allreduce(const Plan &plan, const TaskInfo &ti, size_t i) {
+    if (plan.world_size < 2 || plan.world_size > kMaxPeers || i + 1 >= ti.ops.size()) return false;
+    const OpDesc &mm = ti.ops[i], &ar = ti.ops[i + 1];
+    if (mm.type != "Matmul" || ar.type != "AllReduce" || mm.results.empty() || ar.results.empty() || ar.reads.empty()) return false;
+    const TensorDesc &c = mm.results[0];
+    if (ar.reads[0].id != c.id || ar.results[0].buffer_id != c.buffer_id) return false;
+    if (c.dtype != DT_F16 && c.dtype != DT_BF16) return false;
+    if (!c.dense()) return false;
+    auto sh = c.shape4();
+    if (sh[0] != 1 || sh[1] != 1) return false;
+    return sh[2] % (256 * (int64_t)plan.world_size) == 0 && sh[3] % 32 == 0;
+}
+
 Layout plan_layout(const Plan &plan) {
     Layout lay;
     auto visit = [&](const TensorDesc &t) {
@@ -271,6 +284,15 @@ Layout plan_layout(const Plan &plan) {
                 const BufferInfo &b = lay.buffers.at(t.buffer_id);
                 lay.published.push_back({2, -1, (int)op.arg_int("Tag"), 0, b.offset + (uint64_t)org * dtype_size(t.dtype)});
             }
+    // staging slots of fused Matmul + AllReduce pairs: one slot per rank, together the size of the tensor
+    for (auto &ti : plan.task_infos)
+        for (size_t i = 0; i < ti.ops.size(); ++i)
+            if (fused_allreduce(plan, ti, i)) {
+                const TensorDesc &t = ti.ops[i].results[0];
+                off = align_up(off, 1024);
+                lay.published.push_back({3, -1, (int)ti.ops[i + 1].arg_int("Tag"), 0, off});
+                off = align_up(off + (size_t)t.nelems() * dtype_size(t.dtype), kArenaAlign);
+            }
     lay.arena_bytes = std::max<size_t>(off, kArenaAlign);
     // one-shot staging: kMaxPeers slots of the largest small all_reduce, capped
     const size_t kOneShotMax = 512 * 1024;
@@ -306,8 +328,8 @@ void resolve_remote(const Plan &plan, Layout &lay, const std::vector<std::vector
     }
     for (size_t r = 0; r < records.size(); ++r)
         for (auto &rec : records[r])
-            if (rec.kind == 2) {
-                auto &v = lay.coll_offsets[rec.tag];
+            if (rec.kind == 2 || rec.kind == 3) {
+                auto &v = rec.kind == 2 ? lay.coll_offsets[rec.tag] : lay.coll_stage_offsets[rec.tag];
                 v.resize(records.size(), 0);
                 v[r] = rec.offset;
             }

@@ -102,7 +102,7 @@ struct BufferInfo {
 };
 
 // One record a rank publishes so peers can resolve their remote buffers:
-// kind 0 = send tag, 1 = recv tag, 2 = collective tag.
+// kind 0 = send tag, 1 = recv tag, 2 = collective tag, 3 = staging slots of a fused collective.
 struct TagRecord {
     int32_t kind, peer, tag, pad;
     uint64_t offset;
@@ -115,9 +115,16 @@ struct Layout {
     std::vector<TagRecord> published;  // this rank's records
     // collective tag -> arena offset on every rank
     std::map<int, std::vector<uint64_t>> coll_offsets;
+    // collective tag -> arena offset, on every rank, of the staging slots of an all_reduce fused into the Matmul before it
+    std::map<int, std::vector<uint64_t>> coll_stage_offsets;
 };
 
 constexpr size_t kArenaAlign = 256;  // buffer alignment inside the arena
+
+// True when ops[i] of `ti` is a Matmul and ops[i+1] the AllReduce (same task, i.e. planned with Sync=false) that sums
+// the Matmul's result in place, in a shape the engine fuses: the Matmul's epilogue stores its tiles into staging
+// slots on the rank that sums them. Needs a dense [M, N] fp16/bf16 result with M a multiple of 256 * world size.
+bool fused_allreduce(const Plan &plan, const TaskInfo &ti, size_t i);
 
 // Walks the plan, sizes every buffer and bump-allocates the local ones.
 // Counterpart of Executor::Impl::init_buffers (ark/api/executor.cpp:300-408),

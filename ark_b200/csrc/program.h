@@ -104,6 +104,10 @@ struct GemmArgs {
                       // kgroup > 1, K-major operand: dims {64, rows, K/64, C, N}, box {64, rows, kgroup, 1, 1}
                       // kgroup > 1, MN-major operand: the 4-d map with box {64, 64 * kgroup, 1, 1}
     CUtensorMap tmC;  // output, dims {N, M, C, N}; box {32, 32, 1, 1}, 64-byte swizzle (used when c_tma)
+    // Matmul fused with the all_reduce that follows it: the epilogue stores each tile of the partial product
+    // straight into the staging slot this rank owns on the rank that will sum those rows (peer memory).
+    // tmPeer[r]: dims {N, peer_rows}, rank r's slot for this rank; rows [r * peer_rows, (r+1) * peer_rows) go there.
+    CUtensorMap tmPeer[kMaxPeers];
     void *C;
     const void *bias;     // optional tensor added in the epilogue (same layout as C)
     int64_t ldc;
@@ -135,6 +139,8 @@ struct GemmArgs {
     int32_t kper;                    // k-blocks per range (a multiple of kgroup); 0: ceil(k-blocks / splits)
     int32_t pad2;
     float *ws;                       // split-K partials, layout [splits][batch][rows of C][cols of C]
+    int32_t peer_rows;               // > 0: fused all_reduce, rows of C each rank sums (M / ranks)
+    int32_t pad3;
 };
 
 // Second half of a split-K matmul: C = act(sum_s ws[s] + bias), one rounding.
@@ -226,7 +232,8 @@ struct AllReduceArgs {
     int32_t algo, phase;
     int32_t ord, per_iter;    // one-shot: ordinal among the one-shot all_reduces of an iteration, and their count
                               // (consecutive invocations alternate between two staging buffers)
-    uint64_t stage_bytes;     // one-shot: bytes of one staging buffer (nranks slots)
+    uint64_t stage_bytes;     // one-shot: bytes of one staging buffer (nranks slots); slots: bytes of one slot
+    uint64_t stage_off;       // slots (algo 2): arena offset of this rank's staging slots, filled by the peers' matmul epilogues
 };
 
 struct alignas(128) Stage {

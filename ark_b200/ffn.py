@@ -6,7 +6,8 @@ from . import ops
 from .planner import PlannerContext
 
 
-def build_ffn(tokens, d_model, d_ff, dtype, rank=0, world_size=1, act="gelu", fuse_act=True, weights_nk=False):
+def build_ffn(tokens, d_model, d_ff, dtype, rank=0, world_size=1, act="gelu", fuse_act=True, weights_nk=False,
+              fuse_all_reduce=True):
     """Adds the block to the global model. Returns (x, w1_shard, w2_shard, out).
     w1_shard is [d_model, d_ff / world_size], w2_shard is [d_ff / world_size, d_model]."""
     if d_ff % world_size:
@@ -22,6 +23,13 @@ def build_ffn(tokens, d_model, d_ff, dtype, rank=0, world_size=1, act="gelu", fu
             h = actf(ops.matmul(x, w1, transpose_other=weights_nk))
     else:
         h = actf(ops.matmul(x, w1, transpose_other=weights_nk))
+    if world_size > 1 and fuse_all_reduce:
+        # one task: the W2 matmul's epilogue stores its tiles on the rank that sums them (needs tokens to be a
+        # multiple of 256 x world size; otherwise the two run one after the other as below)
+        with PlannerContext(sync=False):
+            y = ops.matmul(h, w2, transpose_other=weights_nk)
+            y = ops.all_reduce(y, rank, world_size, output=y)
+        return x, w1, w2, y
     y = ops.matmul(h, w2, transpose_other=weights_nk)
     if world_size > 1:
         y = ops.all_reduce(y, rank, world_size, output=y)

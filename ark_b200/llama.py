@@ -86,15 +86,17 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     else:
         raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")
     o = ops.reshape(ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
-    attn = ops.matmul(o, w["wo"], transpose_other=True)     # partial [bt, dim]
-    if p > 1:
-        attn = ops.all_reduce(attn, rank, p, output=attn)
+    with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
+        attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
+        if p > 1:
+            attn = ops.all_reduce(attn, rank, p, output=attn)
     h2, x1 = ops.rmsnorm(attn, w["ffn_norm"], eps=cfg.norm_eps, residual=x)
     with PlannerContext(sync=False):                        # SiLU in the W1 epilogue
         gate = ops.silu(ops.matmul(h2, w["w1"], transpose_other=True))
     up = ops.matmul(h2, w["w3"], transpose_other=True)
     g = ops.mul(gate, up)
-    down = ops.matmul(g, w["w2"], transpose_other=True)     # partial [bt, dim]
-    if p > 1:
-        down = ops.all_reduce(down, rank, p, output=down)
+    with PlannerContext(sync=False):
+        down = ops.matmul(g, w["w2"], transpose_other=True)  # partial [bt, dim]
+        if p > 1:
+            down = ops.all_reduce(down, rank, p, output=down)
     return ops.add(x1, down)

@@ -151,6 +151,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ark_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-fused-all-reduce", action="store_true",
+                    help="run the W2 matmul and the all_reduce as separate stages (two-shot) instead of fusing them")
     ap.add_argument("--no-e2e", action="store_true", help="skip the loop-mode end-to-end leg (profiler captures)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="reduced size for profiler captures only")
     ap.add_argument("--procs", type=int, default=0, help="experiment: plan for this many SMs instead of all")
@@ -182,7 +184,8 @@ def main():
     ark.set_rank(rank)
     ark.set_world_size(world)
     from ark_b200.ffn import build_ffn
-    tx, t1, t2, ty = build_ffn(tokens, D_MODEL, D_FF, ark.fp16, rank, world, act="gelu", weights_nk=args.weights_nk)
+    tx, t1, t2, ty = build_ffn(tokens, D_MODEL, D_FF, ark.fp16, rank, world, act="gelu", weights_nk=args.weights_nk,
+                               fuse_all_reduce=not args.no_fused_all_reduce)
     plan = ark.Planner(local, num_sm=args.procs or None).plan()
     x, w1, w2 = synth(rank, world)
     x = x[:tokens]

@@ -153,6 +153,23 @@ def test_multi_rank_plan_lowering_all_reduce_and_send_recv():
     ark.set_world_size(1)
 
 
+def test_matmul_and_all_reduce_of_one_task_are_fused():
+    """Planned as one task (Sync=false), a Matmul and the AllReduce of its result become: tiles stored into the summing
+    rank's staging slots by the epilogue, then one sum-and-gather stage; otherwise matmul, then the two-shot collective."""
+    from ark_b200.ffn import build_ffn
+    for tokens, fused in ((1024, True), (256, False)):
+        ark.init()
+        ark.set_rank(1)
+        ark.set_world_size(2)
+        build_ffn(tokens, 512, 2048, ark.fp16, 1, 2)
+        text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+        assert ("tiles->peer slots" in text) == fused and ("sum of staging slots" in text) == fused
+        assert ("two-shot" in text or "one-shot" in text) == (not fused)
+        assert "peer barrier" in text
+    ark.set_rank(0)
+    ark.set_world_size(1)
+
+
 def test_naive_all_reduce_composition_matches_reference_structure():
     """Model::all_reduce of the reference: world_size-1 rounds of send/send_done/recv/add (ops_all_reduce.cpp:8-37)."""
     ark.init()
