@@ -147,10 +147,25 @@ __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
     const int64_t nv = cols / V;  // host guarantees cols % V == 0 and 16-byte aligned rows
     const T *wgt = reinterpret_cast<const T *>(a.weight);
     const int op = a.op;
-    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    const T *mask = reinterpret_cast<const T *>(a.mask);
+    const float scale = (op == RO_SOFTMAX && !mask) ? a.scale : 1.0f;
     for (int64_t row = (int64_t)p * WPC + warp; row < a.rows; row += (int64_t)P * WPC) {
         const T *src = reinterpret_cast<const T *>(a.in) + row * a.in_ld;
         T *dst = reinterpret_cast<T *>(a.out) + row * a.out_ld;
+        if (mask) {
+            // masked softmax: the logits x * scale + mask are formed first, rounded to the storage type, in the output row
+            const T *mk = mask + (row % a.mask_rows) * a.mask_ld;
+            for (int64_t v = lane; v < nv; v += 32) {
+                float f[V], g[V];
+                load_vec<T, V>(src + v * V, f);
+                load_vec_cached<T, V>(mk + v * V, g);
+#pragma unroll
+                for (int i = 0; i < V; ++i) f[i] = f[i] * a.scale + g[i];
+                store_vec<T, V>(dst + v * V, f);
+            }
+            __syncwarp();
+            src = dst;
+        }
         if (a.residual) {
             // x := x + residual, rounded to the storage type and kept (res_out) for the next block
             const T *res = reinterpret_cast<const T *>(a.residual) + row * a.in_ld;
@@ -249,7 +264,10 @@ __device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
     const int li = wig * 32 + lane, lstride = 32 * G;
     const int64_t cols = a.cols, nv = cols / V;
     const int op = a.op;
-    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    const T *mask = reinterpret_cast<const T *>(a.mask);
+    const float scale = (op == RO_SOFTMAX && !mask) ? a.scale : 1.0f;
+    const float pre_scale = a.scale;
+    const int64_t mask_ld = a.mask_ld, mask_rows = a.mask_rows;
     const T *wgt = reinterpret_cast<const T *>(a.weight);
     const int64_t in_ld = a.in_ld, out_ld = a.out_ld, rows = a.rows;
     const float eps = a.eps, inv_cols = 1.0f / (float)cols;
@@ -285,6 +303,19 @@ __device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
 #pragma unroll
                     for (int i = 0; i < V; ++i) e[i] = from_f32<T>(to_f32(e[i]) + to_f32(ge[i]));
                     *reinterpret_cast<uint4 *>(ro + (int64_t)(li + j * lstride) * V) = rx[j];
+                }
+        }
+        if (mask) {
+            // masked softmax: logits x * scale + mask, rounded to the storage type, replace the row in registers
+            const T *mk = mask + (row % mask_rows) * mask_ld;
+#pragma unroll
+            for (int j = 0; j < MAXV; ++j)
+                if (li + j * lstride < nv) {
+                    const uint4 g4 = *reinterpret_cast<const uint4 *>(mk + (int64_t)(li + j * lstride) * V);
+                    T *e = reinterpret_cast<T *>(&rx[j]);
+                    const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) e[i] = from_f32<T>(to_f32(e[i]) * pre_scale + to_f32(ge[i]));
                 }
         }
         float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
@@ -394,7 +425,9 @@ __device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCt
     char *mybuf = smem + (size_t)warp * NB * buf_bytes;
     unsigned long long *mybar = &bars.bar[warp * kRowStageMaxBufs];
     const int op = a.op;
-    const float scale = (op == RO_SOFTMAX) ? a.scale : 1.0f;
+    const T *mask = reinterpret_cast<const T *>(a.mask);
+    const float scale = (op == RO_SOFTMAX && !mask) ? a.scale : 1.0f;
+    const float pre_scale = a.scale;
     const float inv_cols = 1.0f / (float)cols, eps = a.eps;
     const T *wgt = reinterpret_cast<const T *>(a.weight);
     const T *in = reinterpret_cast<const T *>(a.in);
@@ -424,6 +457,20 @@ __device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCt
             return;
         }
         T *row = reinterpret_cast<T *>(mybuf + b * buf_bytes);
+        if (mask) {
+            // masked softmax: logits x * scale + mask, rounded to the storage type, replace the row in shared memory
+            const T *mk = mask + ((first + i * step) % a.mask_rows) * a.mask_ld;
+            for (int64_t v = lane; v < nv; v += 32) {
+                uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+                const uint4 g4 = *reinterpret_cast<const uint4 *>(mk + v * V);
+                T *e = reinterpret_cast<T *>(&q);
+                const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                for (int k = 0; k < V; ++k) e[k] = from_f32<T>(to_f32(e[k]) * pre_scale + to_f32(ge[k]));
+                *reinterpret_cast<uint4 *>(row + v * V) = q;
+            }
+            __syncwarp();
+        }
         float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
         for (int64_t v = lane; v < nv; v += 32) {
             const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);

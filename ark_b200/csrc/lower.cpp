@@ -321,9 +321,22 @@ struct Lowerer {
             a.residual = tensor_ptr(op.reads[ri]);
             a.res_out = tensor_ptr(op.results[1]);
         }
+        if (a.op == RO_SOFTMAX && op.has_arg("Mask") && op.arg_bool("Mask")) {
+            // additive mask [.., R, cols] broadcast over the leading dims: row r of the input uses mask row r % R
+            if (op.reads.size() <= ri) throw Error(E_MODEL, "Softmax: mask tensor missing");
+            const TensorDesc &mk = op.reads[ri++];
+            auto ms = mk.shape4();
+            auto mst = mk.strides4();
+            if (mk.dtype != in.dtype || ms[3] != a.cols || ms[0] != 1 || ms[1] != 1 || sh[2] % ms[2] != 0 || (ms[2] != sh[2] && ms[2] != 1))
+                throw Error(E_UNSUPPORTED, "Softmax: the mask must be [1, 1, rows or 1, cols] of the input's type");
+            a.mask = tensor_ptr(mk);
+            a.mask_ld = mst[3];
+            a.mask_rows = (int32_t)ms[2];
+        }
         const int V = (int)(16 / dtype_size(in.dtype));
         bool ok = (a.cols % V == 0) && aligned16(a.in) && aligned16(a.out) && (a.in_ld % V == 0) && (a.out_ld % V == 0);
         if (a.weight) ok = ok && aligned16(a.weight);
+        if (a.mask) ok = ok && aligned16(a.mask) && (a.mask_ld % V == 0);
         if (a.residual) ok = ok && aligned16(a.residual) && aligned16(a.res_out);
         if (!ok) throw Error(E_UNSUPPORTED, op.type + ": rows must be 16-byte aligned and a multiple of 16 bytes long");
         if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16)) throw Error(E_UNSUPPORTED, op.type + ": floating-point only");
@@ -700,6 +713,10 @@ struct Lowerer {
         else g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / (16 * 1024 + g.stage_b_bytes));
         // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
         g.c_tma = (!swapped && g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
+        // The TMA-store epilogue (32x32 blocks through shared memory) keeps the accumulator hand-over short, which pays
+        // when the main loop is long; its store rate is low (~0.45 TB/s over all SMs against ~1.4 TB/s for direct
+        // stores), so tiles with a short K loop store directly. A fused all_reduce needs the TMA form.
+        if (K < 8192 && !fuse_ar) g.c_tma = 0;
         if (g.c_tma) mk(C, csh, cst, pc, 32, 32, &g.tmC, 64);
         if (fuse_ar) {
             // Fused all_reduce: tiles go to the staging slots on the rank that sums their rows.

@@ -91,7 +91,9 @@ struct RowOpArgs {
     int32_t staged_warps;  // > 0: rows are streamed through shared memory with bulk copies by this many warps,
                            // each with `staged_bufs` row buffers (takes precedence over warps_per_row)
     int32_t staged_bufs;
-    int32_t pad;
+    int32_t mask_rows;     // softmax: logits := logits * scale + mask[row % mask_rows] first (rounded to the storage type)
+    const void *mask;      // optional additive mask, mask_rows x cols, row pitch mask_ld
+    int64_t mask_ld;
 };
 
 // Shared memory the loop kernel offers a matmul stage for operand ring slots when its epilogue needs no staging

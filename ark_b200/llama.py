@@ -6,7 +6,8 @@ W1/W3 are split by output features, Wo and W2 by input features, and the two
 partial outputs per layer are summed over the ranks.
 
 Differences from the reference example, all inside one rank's graph:
-RMSNorm and softmax are single row kernels, SiLU runs in the W1 epilogue, the
+RMSNorm and softmax (with the score scale and the causal mask folded in) are
+single row kernels, SiLU runs in the W1 epilogue, the
 two all_reduces are single in-kernel collectives, and a decode step reads a
 K/V cache (the reference example has none).
 """
@@ -77,11 +78,7 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     scale = 1.0 / math.sqrt(hd)
     if kvl == hl or kvl == 1:
         scores = ops.matmul(q, k, transpose_other=True)     # [b, hl, seq, t_kv]; C broadcasts when kvl == 1
-        if mask is not None:
-            scores = ops.add(ops.mul(scores, scale), mask)
-            probs = ops.softmax(scores)
-        else:
-            probs = ops.softmax(scores, scale=scale)
+        probs = ops.softmax(scores, scale=scale, mask=mask)  # scale, causal mask and softmax in one pass over the scores
         o = ops.matmul(probs, v)                            # [b, hl, seq, hd]
     else:
         raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")

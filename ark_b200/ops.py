@@ -334,15 +334,20 @@ def embedding(input, weight, output=None, name="embedding"):
 
 
 # ---- compositions / fused rows ----------------------------------------------------------------
-def softmax(input, output=None, name="softmax", fused=True, scale=1.0):
-    """Softmax over the last axis. The reference composes five ops
-    (python/ark/ops.py:491-500); `fused=True` runs one row kernel instead."""
+def softmax(input, output=None, name="softmax", fused=True, scale=1.0, mask=None):
+    """Softmax over the last axis of `input * scale + mask`. The reference composes five ops
+    (python/ark/ops.py:491-500) after a separate scale and mask add; `fused=True` runs one row
+    kernel instead. `mask` is additive, shaped [1, 1, rows, cols] or [1, 1, 1, cols]; the masked
+    logits are rounded to the storage type before the softmax, like the separate ops would."""
     if fused:
         out = _out_like(input.shape, input.dtype, output)
         res = _result_of(out)
-        _m().add_op("Softmax", name, [input], [out], [res], {"Scale": float(scale)})
+        reads = [input] if mask is None else [input, mask]
+        _m().add_op("Softmax", name, reads, [out], [res], {"Scale": float(scale), "Mask": mask is not None})
         return res
     x = input if scale == 1.0 else mul(input, float(scale))
+    if mask is not None:
+        x = add(x, mask)
     mx = reduce_max(x, axis=-1)
     e = exp(sub(x, mx))
     s = reduce_sum(e, axis=-1)

@@ -67,6 +67,28 @@ def test_rmsnorm_softmax_layernorm(dt, rows, cols):
     assert_close(g3, O.layernorm(x, dt), dt, rtol=tol, atol=tol, what="layernorm")
 
 
+@pytest.mark.parametrize("dt", ["fp16", "bf16", "fp32"])
+@pytest.mark.parametrize("shape,mrows", [((2, 3, 64, 512), 64), ((1, 4, 1024, 1024), 1024), ((1, 2, 8, 20000), 8), ((1, 1, 40, 256), 1)])
+def test_softmax_with_scale_and_additive_mask(dt, shape, mrows):
+    """One row kernel for softmax(x * scale + mask): each variant of the kernel (rows in registers, rows streamed
+    through shared memory, two-pass) against the oracle's scalar-mul, add, softmax with their per-op rounding."""
+    rng = np.random.default_rng(26)
+    cols = shape[-1]
+    x = O.to_storage(rng.normal(0, 3, shape).astype(np.float32), dt)
+    m = np.where(rng.random((1, 1, mrows, cols)) < 0.3, -np.inf, 0.0).astype(np.float32)
+    m[..., 0] = 0.0  # no fully masked row
+    mk = O.to_storage(m, dt)
+    scale = 0.125
+    ark.init()
+    t, tm = ark.tensor(list(shape), NAME[dt]), ark.tensor([1, 1, mrows, cols], NAME[dt])
+    out = ark.softmax(t, scale=scale, mask=tm)
+    (got,) = execute([out], {t: x, tm: mk})
+    logits = O.binary("add", O.scalar("mul", x, scale, dt), np.broadcast_to(mk, shape).copy(), dt)
+    want = O.softmax(logits, dt)
+    tol = {"fp32": 2e-5, "fp16": 2e-3, "bf16": 1.6e-2}[dt]
+    assert_close(got, want, dt, rtol=tol, atol=1e-7 if dt == "fp32" else 1e-5, what="masked softmax")
+
+
 def test_fused_rows_match_the_reference_compositions():
     """softmax/layernorm as the reference composes them (python/ark/ops.py:491-513) vs the fused kernels."""
     rng = np.random.default_rng(24)
