@@ -32,21 +32,19 @@ __device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
     for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
 }
 
-// Copies x[0..M)[k0 .. k0+kr) into shared memory as fp32, laid out for the way gemv_nk reads it: a
-// lane reads VC consecutive 8-element vectors (vector vi = g * VC + c); for each (row m, c, half h of
-// the vector) the values of all g are consecutive float4, so lanes with consecutive g touch
-// consecutive 16-byte words (no bank conflicts). Index: ((m * VC + c) * 2 + h) * ng + g.
-template <typename T, int VC>
-__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int ng, int k0) {
+// Copies x[0..M)[k0 .. k0+kr) into shared memory as fp32. The 8 values of vector v of row m are kept as two
+// float4 in separate planes, xs[(m * 2 + h) * nv + v], so that lanes reading consecutive vectors touch
+// consecutive 16-byte words (no bank conflicts).
+template <typename T>
+__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int k0) {
     const T *x = reinterpret_cast<const T *>(a.x);
     for (int i = threadIdx.x; i < a.M * nv; i += blockDim.x) {
         const int m = i / nv, v = i % nv;
         const uint4 q = *reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k0 + v * 8);
         float f[8];
         unpack8<T>(q, f);
-        const int g = v / VC, c = v % VC;
-        xs[((size_t)(m * VC + c) * 2 + 0) * ng + g] = make_float4(f[0], f[1], f[2], f[3]);
-        xs[((size_t)(m * VC + c) * 2 + 1) * ng + g] = make_float4(f[4], f[5], f[6], f[7]);
+        xs[((size_t)m * 2 + 0) * nv + v] = make_float4(f[0], f[1], f[2], f[3]);
+        xs[((size_t)m * 2 + 1) * nv + v] = make_float4(f[4], f[5], f[6], f[7]);
     }
 }
 
@@ -57,9 +55,10 @@ __device__ __forceinline__ void emit(const GemvArgs &a, int split, int m, int n,
 }
 
 // ---- W stored [N, K] ---------------------------------------------------------------
-// A warp walks RW rows of W together; per step a lane loads VC consecutive 16-byte vectors of each
-// row (RW * VC <= 8 loads), so a warp reads VC * 512 contiguous bytes of each row and the
-// activations of a step are read from shared memory once for all RW rows. Two register buffers
+// A warp walks RW rows of W together; per step a lane loads VC 16-byte vectors of each row, 32
+// vectors apart (every load instruction covers 512 contiguous bytes; RW * VC = 8 loads per step).
+// The activations of a step are read from shared memory once for all RW rows: many rows per warp
+// when the matrix has rows to spare, few rows and more vectors per row when it has not. Two register buffers
 // alternate: the loads of step t+1 are issued before step t is consumed, across row groups too.
 template <typename T, int M, int RW, int VC>
 __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs) {
@@ -69,13 +68,12 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
     const int k0 = split * a.kper;
     const int kr = min(a.K, k0 + a.kper) - k0;
     const int nv = kr / 8;
-    const int ng = (nv + VC - 1) / VC;  // groups of VC vectors per row
-    stage_x<T, VC>(a, xs, nv, ng, k0);
+    stage_x<T>(a, xs, nv, k0);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int row_lo = (int)((int64_t)q * a.N / cps), row_hi = (int)((int64_t)(q + 1) * a.N / cps);
-    const int steps = (ng + 31) / 32;  // per row group
+    const int steps = (nv + 32 * VC - 1) / (32 * VC);  // per row group
     const T *w = reinterpret_cast<const T *>(a.w) + k0;
     const int64_t ldw = a.ldw;
     const int rows_m = a.M;
@@ -91,12 +89,11 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
         }
     };
     auto issue = [&](uint4 (&buf)[RW][VC], const Cursor &c) {
-        const int g = lane + 32 * c.j;
 #pragma unroll
         for (int r = 0; r < RW; ++r)
 #pragma unroll
             for (int v = 0; v < VC; ++v) {
-                const int vi = g * VC + v;
+                const int vi = lane + 32 * (c.j * VC + v);
                 if (c.r0 + r < row_hi && vi < nv) buf[r][v] = ldg16_stream(w + (int64_t)(c.r0 + r) * ldw + vi * 8);
                 else buf[r][v] = make_uint4(0, 0, 0, 0);
             }
@@ -107,17 +104,17 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
     auto consume = [&](uint4 (&buf)[RW][VC], const Cursor &c) {
-        const int g = lane + 32 * c.j;
 #pragma unroll
         for (int v = 0; v < VC; ++v) {
-            if (g * VC + v < nv) {
+            const int vi = lane + 32 * (c.j * VC + v);
+            if (vi < nv) {
                 float f[RW][8];
 #pragma unroll
                 for (int r = 0; r < RW; ++r) unpack8<T>(buf[r][v], f[r]);
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     if (m < rows_m) {
-                        const float4 x0 = xs[((size_t)(m * VC + v) * 2 + 0) * ng + g], x1 = xs[((size_t)(m * VC + v) * 2 + 1) * ng + g];
+                        const float4 x0 = xs[((size_t)m * 2 + 0) * nv + vi], x1 = xs[((size_t)m * 2 + 1) * nv + vi];
 #pragma unroll
                         for (int r = 0; r < RW; ++r)
                             acc[r][m] += f[r][0] * x0.x + f[r][1] * x0.y + f[r][2] * x0.z + f[r][3] * x0.w + f[r][4] * x1.x +
@@ -242,8 +239,20 @@ template <typename T>
 __device__ void gemv_typed(const GemvArgs &a, int p, int P, char *smem) {
     if (a.w_is_nk) {
         float4 *xs = reinterpret_cast<float4 *>(smem);
-        if (a.M == 1) gemv_nk<T, 1, kGemvRowsM1, 1>(a, p, P, xs);
-        else gemv_nk<T, 2, kGemvRowsM2, 1>(a, p, P, xs);
+        if (a.M == 1) {
+            switch (a.rows_together) {
+                case 8: gemv_nk<T, 1, 8, 1>(a, p, P, xs); break;
+                case 4: gemv_nk<T, 1, 4, 2>(a, p, P, xs); break;
+                case 2: gemv_nk<T, 1, 2, 4>(a, p, P, xs); break;
+                default: gemv_nk<T, 1, 1, 8>(a, p, P, xs); break;
+            }
+        } else {
+            switch (a.rows_together) {
+                case 4: gemv_nk<T, 2, 4, 1>(a, p, P, xs); break;
+                case 2: gemv_nk<T, 2, 2, 2>(a, p, P, xs); break;
+                default: gemv_nk<T, 2, 1, 4>(a, p, P, xs); break;
+            }
+        }
     } else {
         T *xs = reinterpret_cast<T *>(smem);
         if (a.M == 1) gemv_kn<T, 1, 8>(a, p, P, xs);

@@ -462,26 +462,32 @@ struct Lowerer {
                 g.act = act < 0 ? ACT_NONE : act;
                 if (tb) {
                     // CTAs = k-ranges x row blocks; a warp walks whole groups of RW rows, so the time of the stage is
-                    // (groups per warp, rounded up) x (length of a k-range). Pick the number of k-ranges with the
-                    // least such time; more than one range costs a barrier and a pass over the partials.
-                    const int64_t RW = M == 1 ? kGemvRowsM1 : kGemvRowsM2, warps = kThreads / 32;
+                    // (groups per warp, rounded up) x (steps per group). Pick the rows per group and the number of
+                    // k-ranges with the least such time: fewer rows per group when there are not enough rows to go
+                    // round (the activations are then re-read from shared memory more often), more than one k-range
+                    // only when it pays for the barrier and the pass over the partials it adds.
+                    const int64_t warps = kThreads / 32, loads = M == 1 ? 8 : 4;  // 16-byte loads per lane and step
                     auto kper_of = [&](int64_t sp) { return ((K + sp - 1) / sp + 255) / 256 * 256; };
-                    // time in steps (a step = 256 elements of K for RW rows) scaled to microseconds by the HBM rate
-                    const double step_us = 256.0 * RW * es * (double)(P * warps) / 6.5e6;
-                    int64_t splits = 0;
+                    const double step_us = 256.0 * loads * es * (double)(P * warps) / 6.5e6;
+                    int64_t splits = 0, best_rw = loads;
                     double best = 1e30;
-                    for (int64_t sp = 1; sp <= std::min<int64_t>(P, 32); ++sp) {
-                        const int64_t kp = kper_of(sp), eff = (K + kp - 1) / kp;
-                        if (eff != sp) continue;
-                        if (M * kp * 4 > 160 * 1024) continue;
-                        if (kp < 1024 && sp > 1) break;
-                        const int64_t cps = P / eff;
-                        const int64_t rows_cta = (N + cps - 1) / cps;
-                        const int64_t rounds = ((rows_cta + RW - 1) / RW + warps - 1) / warps;
-                        const double t = (double)rounds * ((double)kp / 256.0 + 0.5) * step_us + (eff > 1 ? 6.0 : 0.0);
-                        if (t < best - 1e-9) { best = t; splits = eff; }
+                    for (int64_t RW = loads; RW >= 1; RW /= 2) {
+                        const int64_t VC = loads / RW;
+                        for (int64_t sp = 1; sp <= std::min<int64_t>(P, 32); ++sp) {
+                            const int64_t kp = kper_of(sp), eff = (K + kp - 1) / kp;
+                            if (eff != sp) continue;
+                            if (M * kp * 4 > 160 * 1024) continue;
+                            if (kp < 1024 && sp > 1) break;
+                            const int64_t cps = P / eff;
+                            const int64_t rows_cta = (N + cps - 1) / cps;
+                            const int64_t rounds = ((rows_cta + RW - 1) / RW + warps - 1) / warps;
+                            const double steps = (double)((kp + 256 * VC - 1) / (256 * VC));
+                            const double t = (double)rounds * (steps + 1.5) * step_us * (1.0 + 0.03 * (double)(VC - 1)) +
+                                             (eff > 1 ? 7.0 : 0.0);
+                            if (t < best - 1e-9) { best = t; splits = eff; best_rw = RW; }
+                        }
                     }
-                    if (!splits) throw Error(E_INTERNAL, "gemv: k-range does not fit");
+                    g.rows_together = (int32_t)best_rw;
                     const int64_t kper = kper_of(splits);
                     g.kper = (int32_t)kper;
                     g.splits = (int32_t)splits;
@@ -518,7 +524,7 @@ struct Lowerer {
                 const GemvArgs gv = g;
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
-                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) : ""));
+                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : ""));
                 if (gv.splits > 1) {
                     emit_sync(proc);
                     Stage r = new_stage(SK_SPLITK_REDUCE, proc);

@@ -169,10 +169,9 @@ struct GemvArgs {
     int32_t kper;            // elements of K per range ([N, K]: a multiple of 8)
     int32_t ctas_per_split;  // [N, K]: CTAs that share a k-range and split the rows of W
     int32_t nblocks;         // [K, N]: blocks of 256 output columns
-    int32_t pad[2];
+    int32_t rows_together;   // [N, K]: rows of W a warp walks together (8, 4, 2 or 1 for M = 1; 4, 2 or 1 for M = 2)
+    int32_t pad;
 };
-// rows of W a warp walks together in the [N, K] form (M = 1 and M = 2): the lowering balances whole groups over the warps
-constexpr int kGemvRowsM1 = 8, kGemvRowsM2 = 4;
 constexpr int kGemvMaxM = 2;
 
 struct GemmSimtArgs {

@@ -64,7 +64,8 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     q = ops.reshape(q, [batch, seq, hl, hd])
     if rope is not None:
         q = ops.rope(q, rope)
-    q = ops.transpose(q, [0, 2, 1, 3])                 # [b, hl, seq, hd]
+    # [b, hl, seq, hd]; with one token per sequence the two layouts are the same memory
+    q = ops.reshape(q, [batch, hl, 1, hd]) if seq == 1 else ops.transpose(q, [0, 2, 1, 3])
     if k_cache is None:
         k = ops.matmul(h, w["wk"], transpose_other=True)
         v = ops.matmul(h, w["wv"], transpose_other=True)
@@ -82,7 +83,7 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
         o = ops.matmul(probs, v)                            # [b, hl, seq, hd]
     else:
         raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")
-    o = ops.reshape(ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
+    o = ops.reshape(o if seq == 1 else ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
     with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
         attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
         if p > 1:
