@@ -7,7 +7,7 @@
 namespace arkb {
 struct GemmPipe;
 __device__ void run_ewise(const EwiseArgs &a, int p, int P);
-__device__ void run_reduce(const ReduceArgs &a, int p, int P);
+__device__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem);
 __device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
                           unsigned long long wait_limit);
 __device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem);
@@ -19,6 +19,7 @@ __device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, i
                               DeviceState *st, int stage_idx, unsigned long long spin_limit);
 __device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
 __device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem);
+__device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P);
 __device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no);

@@ -32,17 +32,90 @@ __device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
     for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
 }
 
-// Copies x[0..M)[k0 .. k0+kr) into shared memory as fp32. The 8 values of vector v of row m are kept as two
-// float4 in separate planes, xs[(m * 2 + h) * nv + v], so that lanes reading consecutive vectors touch
-// consecutive 16-byte words (no bank conflicts).
+// Sum over the CTA of one float per thread (all threads call it; `scratch` holds one float per warp).
+__device__ __forceinline__ float cta_sum(float v, float *scratch) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = 0.0f;
+    for (int i = 0; i < nw; ++i) r += scratch[i];
+    return r;
+}
+
+// The activations as this stage consumes them: the raw x, or the operator folded in before it
+// (GP_MUL: x * other; GP_RMSNORM: (x [+ residual]) * rstd * weight), rounded to the storage type like
+// the separate operator would have stored them. `rstd` is per activation row (GP_RMSNORM only).
 template <typename T>
-__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int k0) {
+__device__ __forceinline__ void load_x8(const GemvArgs &a, int m, int k, float rstd, float (&f)[8]) {
     const T *x = reinterpret_cast<const T *>(a.x);
+    unpack8<T>(*reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k), f);
+    if (a.pro == GP_MUL) {
+        float g[8];
+        unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.pro_a) + (int64_t)m * a.ldx + k), g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] * g[i]));
+    } else if (a.pro == GP_RMSNORM) {
+        if (a.pro_b) {
+            float g[8];
+            unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.pro_b) + (int64_t)m * a.ldx + k), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] + g[i]));
+        }
+        if (a.pro_a) {
+            float g[8];
+            unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.pro_a) + k), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] * rstd * g[i]));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] * rstd));
+        }
+    }
+}
+
+// 1 / rms of every activation row over the WHOLE of K (GP_RMSNORM), into rstd[0..M). With a residual, CTA 0
+// also stores x + residual (the value the norm is taken of) for the operators that follow.
+template <typename T>
+__device__ __forceinline__ void row_rstd(const GemvArgs &a, int p, float *rstd, float *scratch) {
+    const T *x = reinterpret_cast<const T *>(a.x);
+    const T *r = reinterpret_cast<const T *>(a.pro_b);
+    T *ro = reinterpret_cast<T *>(a.pro_out);
+    for (int m = 0; m < a.M; ++m) {
+        float ss = 0.0f;
+        for (int k = threadIdx.x * 8; k < a.K; k += blockDim.x * 8) {
+            float f[8];
+            unpack8<T>(*reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k), f);
+            if (r) {
+                float g[8];
+                unpack8<T>(*reinterpret_cast<const uint4 *>(r + (int64_t)m * a.ldx + k), g);
+                union { uint4 q; T e[8]; } o;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    o.e[i] = from_f32<T>(f[i] + g[i]);
+                    f[i] = to_f32(o.e[i]);
+                }
+                if (ro && p == 0) *reinterpret_cast<uint4 *>(ro + (int64_t)m * a.ldx + k) = o.q;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+        }
+        ss = cta_sum(ss, scratch);
+        if (threadIdx.x == 0) rstd[m] = 1.0f / sqrtf(ss / (float)a.K + a.pro_eps);
+    }
+    __syncthreads();
+}
+
+// Copies the activations [0..M)[k0 .. k0+kr) into shared memory as fp32. The 8 values of vector v of row m are
+// kept as two float4 in separate planes, xs[(m * 2 + h) * nv + v], so that lanes reading consecutive vectors
+// touch consecutive 16-byte words (no bank conflicts).
+template <typename T>
+__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int k0, const float *rstd) {
     for (int i = threadIdx.x; i < a.M * nv; i += blockDim.x) {
         const int m = i / nv, v = i % nv;
-        const uint4 q = *reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k0 + v * 8);
         float f[8];
-        unpack8<T>(q, f);
+        load_x8<T>(a, m, k0 + v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
         xs[((size_t)m * 2 + 0) * nv + v] = make_float4(f[0], f[1], f[2], f[3]);
         xs[((size_t)m * 2 + 1) * nv + v] = make_float4(f[4], f[5], f[6], f[7]);
     }
@@ -50,8 +123,13 @@ __device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, i
 
 template <typename T>
 __device__ __forceinline__ void emit(const GemvArgs &a, int split, int m, int n, float v) {
-    if (a.splits > 1) a.ws[((int64_t)split * a.M + m) * a.N + n] = v;
-    else reinterpret_cast<T *>(a.out)[(int64_t)m * a.ldo + n] = from_f32<T>(apply_act_fast(a.act, v));
+    if (a.splits > 1) {
+        a.ws[((int64_t)split * a.M + m) * a.N + n] = v;
+    } else {
+        v = apply_act_fast(a.act, v);
+        if (a.residual) v = to_f32(from_f32<T>(v)) + to_f32(reinterpret_cast<const T *>(a.residual)[(int64_t)m * a.ldo + n]);
+        reinterpret_cast<T *>(a.out)[(int64_t)m * a.ldo + n] = from_f32<T>(v);
+    }
 }
 
 // ---- W stored [N, K] ---------------------------------------------------------------
@@ -68,7 +146,9 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
     const int k0 = split * a.kper;
     const int kr = min(a.K, k0 + a.kper) - k0;
     const int nv = kr / 8;
-    stage_x<T>(a, xs, nv, k0);
+    float *rstd = reinterpret_cast<float *>(xs + (size_t)a.M * 2 * nv);  // [M], then one float per warp of scratch
+    if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
+    stage_x<T>(a, xs, nv, k0, rstd);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
@@ -169,10 +249,17 @@ __device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs) {
     const int64_t ldw = a.ldw;
     const int K = a.K;
     {
-        const T *x = reinterpret_cast<const T *>(a.x);
-        for (int i = threadIdx.x; i < rows_m * K; i += blockDim.x) {
-            const int m = i / K, k = i % K;
-            xs[(size_t)m * K + k] = x[(int64_t)m * a.ldx + k];
+        float *rstd = reinterpret_cast<float *>(xs + (size_t)rows_m * K);  // [M], then one float per warp of scratch (K is a multiple of 8)
+        if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
+        const int nvk = K / 8;
+        for (int i = threadIdx.x; i < rows_m * nvk; i += blockDim.x) {
+            const int m = i / nvk, v = i % nvk;
+            float f[8];
+            load_x8<T>(a, m, v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
+            union { uint4 q; T e[8]; } o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o.e[e] = from_f32<T>(f[e]);
+            *reinterpret_cast<uint4 *>(xs + (size_t)m * K + v * 8) = o.q;
         }
     }
     __syncthreads();

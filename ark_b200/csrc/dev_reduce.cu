@@ -27,47 +27,115 @@ __device__ void reduce_last_axis(const ReduceArgs &a, int p, int P) {
     const int64_t rows = (int64_t)a.in.shape[0] * C * H;
     const T *in = reinterpret_cast<const T *>(a.in.ptr);
     T *out = reinterpret_cast<T *>(a.out.ptr);
+    const int op = a.op;
+    const int64_t nv = W / V;
+    if constexpr (V * sizeof(T) == 16) {
+        // A warp walks its rows in steps of U 16-byte vectors per lane. Two register buffers alternate: the loads
+        // of step t+1 are issued before step t is consumed, across row boundaries too, so the row-end shuffle
+        // reduction never leaves the memory pipe empty.
+        constexpr int U = 8;
+        const int steps = (int)((nv + 32 * U - 1) / (32 * U));
+        const int64_t row_step = (int64_t)P * WPC;
+        struct Cursor {
+            int64_t row;
+            int j;
+        };
+        auto valid = [&](const Cursor &c) { return c.row < rows; };
+        auto advance = [&](Cursor &c) {
+            if (++c.j == steps) {
+                c.j = 0;
+                c.row += row_step;
+            }
+        };
+        auto row_ptr = [&](int64_t row, int64_t &n, int64_t &c, int64_t &h) -> const T * {
+            h = row % H;
+            const int64_t r = row / H;
+            c = r % C;
+            n = r / C;
+            return in + tref_off(a.in, n, c, h, 0);
+        };
+        auto issue = [&](uint4 (&buf)[U], const Cursor &cu) {
+            int64_t n, c, h;
+            const T *src = row_ptr(cu.row, n, c, h);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t v = lane + 32 * ((int64_t)cu.j * U + u);
+                if (v < nv) buf[u] = ldg16_stream(src + v * V);
+            }
+        };
+        float acc = (op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        auto consume = [&](uint4 (&buf)[U], const Cursor &cu) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t v = lane + 32 * ((int64_t)cu.j * U + u);
+                if (v < nv) {
+                    const T *e = reinterpret_cast<const T *>(&buf[u]);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc = (op == RD_MAX) ? fmaxf(acc, to_f32(e[i])) : acc + to_f32(e[i]);
+                }
+            }
+            if (cu.j == steps - 1) {  // the row is complete
+                int64_t n, c, h;
+                const T *src = row_ptr(cu.row, n, c, h);
+                for (int64_t w = nv * V + lane; w < W; w += 32) {
+                    const float x = to_f32(src[w]);
+                    acc = (op == RD_MAX) ? fmaxf(acc, x) : acc + x;
+                }
+                acc = (op == RD_MAX) ? warp_max(acc) : warp_sum(acc);
+                if (op == RD_MEAN) acc /= (float)W;
+                if (lane == 0) out[tref_off(a.out, n, c, h, 0)] = from_f32<T>(acc);
+                acc = (op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+            }
+        };
+        if (steps == 0) {  // rows shorter than one vector: scalar path below handles them
+        } else {
+            Cursor ld{(int64_t)p * WPC + warp, 0}, cp = ld;
+            uint4 qa[U], qb[U];
+            if (valid(ld)) {
+                issue(qa, ld);
+                advance(ld);
+            }
+            while (valid(cp)) {
+                if (valid(ld)) {
+                    issue(qb, ld);
+                    advance(ld);
+                }
+                consume(qa, cp);
+                advance(cp);
+                if (!valid(cp)) break;
+                if (valid(ld)) {
+                    issue(qa, ld);
+                    advance(ld);
+                }
+                consume(qb, cp);
+                advance(cp);
+            }
+            return;
+        }
+    }
     for (int64_t row = (int64_t)p * WPC + warp; row < rows; row += (int64_t)P * WPC) {
         int64_t h = row % H, r = row / H;
         int64_t c = r % C, n = r / C;
         const T *src = in + tref_off(a.in, n, c, h, 0);
-        float acc = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
-        const int64_t nv = W / V;
-        constexpr int U = 8;
-        if constexpr (V * sizeof(T) == 16) {
-            for (int64_t v0 = lane; v0 < nv; v0 += 32 * U) {
-                uint4 rx[U];
+        float acc = (op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        for (int64_t v0 = lane; v0 < nv; v0 += 32) {
+            float x[V];
+            load_vec<T, V>(src + v0 * V, x);
 #pragma unroll
-                for (int j = 0; j < U; ++j)
-                    if (v0 + j * 32 < nv) rx[j] = ldg16_stream(src + (v0 + j * 32) * V);
-#pragma unroll
-                for (int j = 0; j < U; ++j)
-                    if (v0 + j * 32 < nv) {
-                        const T *e = reinterpret_cast<const T *>(&rx[j]);
-#pragma unroll
-                        for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, to_f32(e[i])) : acc + to_f32(e[i]);
-                    }
-            }
-        } else {
-            for (int64_t v0 = lane; v0 < nv; v0 += 32) {
-                float x[V];
-                load_vec<T, V>(src + v0 * V, x);
-#pragma unroll
-                for (int i = 0; i < V; ++i) acc = (a.op == RD_MAX) ? fmaxf(acc, x[i]) : acc + x[i];
-            }
+            for (int i = 0; i < V; ++i) acc = (op == RD_MAX) ? fmaxf(acc, x[i]) : acc + x[i];
         }
         for (int64_t w = nv * V + lane; w < W; w += 32) {
             float x = to_f32(src[w]);
-            acc = (a.op == RD_MAX) ? fmaxf(acc, x) : acc + x;
+            acc = (op == RD_MAX) ? fmaxf(acc, x) : acc + x;
         }
-        acc = (a.op == RD_MAX) ? warp_max(acc) : warp_sum(acc);
-        if (a.op == RD_MEAN) acc /= (float)W;
+        acc = (op == RD_MAX) ? warp_max(acc) : warp_sum(acc);
+        if (op == RD_MEAN) acc /= (float)W;
         if (lane == 0) out[tref_off(a.out, n, c, h, 0)] = from_f32<T>(acc);
     }
 }
 
 template <typename T, int V>
-__device__ void reduce_other_axis(const ReduceArgs &a, int p, int P) {
+__device__ void reduce_other_axis(const ReduceArgs &a, int p, int P, float *red) {
     const int ax = a.axis;
     int32_t osh[4] = {a.in.shape[0], a.in.shape[1], a.in.shape[2], a.in.shape[3]};
     const int64_t len = osh[ax];
@@ -77,58 +145,90 @@ __device__ void reduce_other_axis(const ReduceArgs &a, int p, int P) {
     const T *in = reinterpret_cast<const T *>(a.in.ptr);
     T *out = reinterpret_cast<T *>(a.out.ptr);
     const int64_t astr = a.in.stride[ax];
-    for (int64_t u = (int64_t)p * kThreads + threadIdx.x; u < units; u += (int64_t)P * kThreads) {
+    const int op = a.op;
+    // With fewer output vectors than threads, S threads of a CTA share one output vector: each walks 1/S of the
+    // reduced axis and the partial results are added through shared memory (segment order: deterministic).
+    int S = 1;
+    while (S < 16 && units * S * 2 <= (int64_t)P * kThreads && len / (S * 2) >= 16) S *= 2;
+    const int UPB = kThreads / S;  // output vectors per CTA pass
+    const int ul = threadIdx.x % UPB, seg = threadIdx.x / UPB;
+    const int64_t k_lo = len * seg / S, k_hi = len * (seg + 1) / S;
+    for (int64_t ub = (int64_t)p * UPB; ub < units; ub += (int64_t)P * UPB) {
+        const int64_t u = ub + ul;
+        const bool live = u < units;
         int64_t wv = u % WV, r = u / WV;
         int64_t h = r % osh[2];
         r /= osh[2];
         int64_t c = r % osh[1], n = r / osh[1];
-        const T *src = in + tref_off(a.in, n, c, h, wv * V);
         float acc[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
-        constexpr int U = 8;  // independent loads in flight along the reduced axis
-        int64_t k = 0;
-        for (; k + U <= len; k += U) {
-            float x[U][V];
+        for (int i = 0; i < V; ++i) acc[i] = (op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        if (live) {
+            const T *src = in + tref_off(a.in, n, c, h, wv * V);
+            constexpr int U = 8;  // independent loads in flight along the reduced axis
+            int64_t k = k_lo;
+            for (; k + U <= k_hi; k += U) {
+                float x[U][V];
 #pragma unroll
-            for (int j = 0; j < U; ++j) load_vec<T, V>(src + (k + j) * astr, x[j]);
+                for (int j = 0; j < U; ++j) load_vec<T, V>(src + (k + j) * astr, x[j]);
 #pragma unroll
-            for (int j = 0; j < U; ++j) {
+                for (int j = 0; j < U; ++j) {
 #pragma unroll
-                for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? fmaxf(acc[i], x[j][i]) : acc[i] + x[j][i];
+                    for (int i = 0; i < V; ++i) acc[i] = (op == RD_MAX) ? fmaxf(acc[i], x[j][i]) : acc[i] + x[j][i];
+                }
+            }
+            for (; k < k_hi; ++k) {
+                float x[V];
+                load_vec<T, V>(src + k * astr, x);
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] = (op == RD_MAX) ? fmaxf(acc[i], x[i]) : acc[i] + x[i];
             }
         }
-        for (; k < len; ++k) {
-            float x[V];
-            load_vec<T, V>(src + k * astr, x);
+        if (S > 1) {
+            __syncthreads();  // the previous pass no longer reads `red`
+            if (seg > 0) {
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] = (a.op == RD_MAX) ? fmaxf(acc[i], x[i]) : acc[i] + x[i];
-        }
-        if (a.op == RD_MEAN) {
+                for (int i = 0; i < V; ++i) red[((size_t)seg * UPB + ul) * V + i] = acc[i];
+            }
+            __syncthreads();
+            if (seg == 0) {
+                for (int sg = 1; sg < S; ++sg) {
 #pragma unroll
-            for (int i = 0; i < V; ++i) acc[i] /= (float)len;
+                    for (int i = 0; i < V; ++i) {
+                        const float x = red[((size_t)sg * UPB + ul) * V + i];
+                        acc[i] = (op == RD_MAX) ? fmaxf(acc[i], x) : acc[i] + x;
+                    }
+                }
+            }
         }
-        store_vec<T, V>(out + tref_off(a.out, n, c, h, wv * V), acc);
+        if (live && seg == 0) {
+            if (op == RD_MEAN) {
+#pragma unroll
+                for (int i = 0; i < V; ++i) acc[i] /= (float)len;
+            }
+            store_vec<T, V>(out + tref_off(a.out, n, c, h, wv * V), acc);
+        }
     }
 }
 
 template <typename T>
-__device__ __forceinline__ void reduce_typed(const ReduceArgs &a, int p, int P) {
+__device__ __forceinline__ void reduce_typed(const ReduceArgs &a, int p, int P, float *red) {
     constexpr int V = 16 / sizeof(T);
     if (a.axis == 3) {
         if (a.vec > 1) reduce_last_axis<T, V>(a, p, P);
         else reduce_last_axis<T, 1>(a, p, P);
     } else {
-        if (a.vec > 1) reduce_other_axis<T, V>(a, p, P);
-        else reduce_other_axis<T, 1>(a, p, P);
+        if (a.vec > 1) reduce_other_axis<T, V>(a, p, P, red);
+        else reduce_other_axis<T, 1>(a, p, P, red);
     }
 }
 
-__device__ void run_reduce(const ReduceArgs &a, int p, int P) {
+__device__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem) {
+    float *red = reinterpret_cast<float *>(smem);  // kThreads x 8 floats at most
     switch (a.in.dtype) {
-        case DT_F32: reduce_typed<float>(a, p, P); break;
-        case DT_F16: reduce_typed<__half>(a, p, P); break;
-        case DT_BF16: reduce_typed<__nv_bfloat16>(a, p, P); break;
+        case DT_F32: reduce_typed<float>(a, p, P, red); break;
+        case DT_F16: reduce_typed<__half>(a, p, P, red); break;
+        case DT_BF16: reduce_typed<__nv_bfloat16>(a, p, P, red); break;
         default: break;
     }
 }

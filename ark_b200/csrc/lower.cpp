@@ -393,8 +393,48 @@ struct Lowerer {
         return n;
     }
 
+    // Operators of the same task folded into a weight-streaming matmul (SK_GEMV): a prologue applied to the
+    // activations while they are staged, and a residual added to the result.
+    struct GemvFuse {
+        int pro = GP_NONE;
+        const TensorDesc *x = nullptr;        // what the prologue reads (takes the place of the matmul's first operand)
+        const TensorDesc *pro_a = nullptr;    // rmsnorm weight / second factor of the mul
+        const TensorDesc *pro_b = nullptr;    // rmsnorm residual
+        const TensorDesc *pro_out = nullptr;  // where x + residual is kept
+        float eps = 1e-5f;
+        const TensorDesc *residual = nullptr; // added to the matmul's result
+        const TensorDesc *out = nullptr;      // result tensor of the last folded operator
+    };
+
+    static bool gemv_wanted() {
+        const char *e = getenv("ARKB_GEMV");
+        return e ? atoi(e) != 0 : true;
+    }
+    // shapes the weight-streaming stage takes (the same test decides inside lower_matmul)
+    static bool gemv_shape_ok(bool full, bool ta, bool tb, int64_t M, int64_t N, int64_t K, int64_t batches, int64_t lda) {
+        return full && !ta && M <= kGemvMaxM && batches == 1 && K % 8 == 0 &&
+               (tb ? K >= 512 : N % 8 == 0 && N >= 256 && M * K * 2 <= 160 * 1024) && lda % 8 == 0 && N * K >= 65536;
+    }
+    bool matmul_is_gemv(const OpDesc &op, const TaskGroup &tg) const {
+        if (op.type != "Matmul" || op.reads.size() < 2 || op.results.empty()) return false;
+        const TensorDesc &A = op.reads[0], &B = op.reads[1], &C = op.results[0];
+        if (A.dtype != B.dtype || (A.dtype != DT_F16 && A.dtype != DT_BF16)) return false;
+        const bool ta = op.arg_bool("TransposeInput");
+        const bool tb = B.shape.size() == 1 ? true : op.arg_bool("TransposeOther");
+        auto ash = A.shape4(), bsh = B.shape4(), csh = C.shape4();
+        int64_t M = A.shape.size() == 1 ? 1 : ash[2], K = ash[3];
+        if (ta) std::swap(M, K);
+        int64_t N = bsh[3];
+        if (tb) N = bsh[2];
+        const size_t es = dtype_size(A.dtype);
+        auto ast = A.strides4(), bst = B.strides4();
+        const bool aligned = aligned16(tensor_ptr(A)) && aligned16(tensor_ptr(B)) && (ast[3] * es) % 16 == 0 && (bst[3] * es) % 16 == 0;
+        return gemv_wanted() && aligned && env.encode_tmap &&
+               gemv_shape_ok(full_range(tg.task_range, num_tasks(op)), ta, tb, M, N, K, csh[0] * csh[1], ast[3]);
+    }
+
     void lower_matmul(const OpDesc &op, const Range &proc, const TaskGroup &tg, int act, const TensorDesc *act_out,
-                      const OpDesc *fuse_ar = nullptr) {
+                      const OpDesc *fuse_ar = nullptr, const GemvFuse *gf = nullptr) {
         const TensorDesc &A = op.reads.at(0), &B = op.reads.at(1);
         const TensorDesc &C = act_out ? *act_out : op.results.at(0);
         const bool ta = op.arg_bool("TransposeInput");
@@ -446,15 +486,32 @@ struct Lowerer {
         // HBM speed; it runs on the CUDA cores with the activations in shared memory. (From three rows on the
         // multiply-adds outweigh the read and the swapped tensor-core form below is faster.)
         {
-            const char *e = getenv("ARKB_GEMV");
-            const bool want = e ? atoi(e) != 0 : true;
             const int64_t P = proc.count();
-            const bool shapes_ok = full && !ta && M <= kGemvMaxM && bn * bc == 1 && (tb ? K % 8 == 0 && K >= 512 : N % 8 == 0 && N >= 256 && M * K * 2 <= 160 * 1024) &&
-                                   lda % 8 == 0 && N * K >= 65536;
-            if (want && shapes_ok) {
+            const bool shapes_ok = gemv_shape_ok(full, ta, tb, M, N, K, bn * bc, lda);
+            if (gf && !(gemv_wanted() && shapes_ok)) throw Error(E_INTERNAL, "operators were folded into a matmul that is not weight-streaming");
+            if (gemv_wanted() && shapes_ok) {
                 Stage s = new_stage(SK_GEMV, proc);
                 GemvArgs &g = s.gv;
                 g.out = pc; g.x = pa; g.w = pb;
+                if (gf) {
+                    // the prologue's input stands in for the first operand; every folded operand shares its row pitch
+                    auto same_rows = [&](const TensorDesc *t) { return !t || (t->strides4()[3] == gf->x->strides4()[3] && aligned16(tensor_ptr(*t))); };
+                    if (gf->x) {
+                        if (gf->x->strides4()[3] != lda || lda % 8 || !aligned16(tensor_ptr(*gf->x)) || !same_rows(gf->pro_b) || !same_rows(gf->pro_out) ||
+                            (gf->pro == GP_MUL && !same_rows(gf->pro_a)))
+                            throw Error(E_UNSUPPORTED, "folded operands of a weight-streaming matmul must share one 16-byte aligned row pitch");
+                        g.x = tensor_ptr(*gf->x);
+                    }
+                    g.pro = gf->pro;
+                    g.pro_a = gf->pro_a ? tensor_ptr(*gf->pro_a) : nullptr;
+                    g.pro_b = gf->pro_b ? tensor_ptr(*gf->pro_b) : nullptr;
+                    g.pro_out = gf->pro_out ? tensor_ptr(*gf->pro_out) : nullptr;
+                    g.pro_eps = gf->eps;
+                    if (gf->residual) {
+                        if (gf->residual->strides4()[3] != ldc) throw Error(E_UNSUPPORTED, "residual of a weight-streaming matmul must have the result's row pitch");
+                        g.residual = tensor_ptr(*gf->residual);
+                    }
+                }
                 g.ldx = lda; g.ldw = ldb; g.ldo = ldc;
                 g.M = (int32_t)M; g.N = (int32_t)N; g.K = (int32_t)K;
                 g.w_is_nk = tb ? 1 : 0;
@@ -521,16 +578,19 @@ struct Lowerer {
                 }
                 const int act_final = g.act;
                 if (g.splits > 1) g.act = ACT_NONE;
+                if (g.residual && act_final != ACT_NONE) throw Error(E_INTERNAL, "residual and activation folded into one matmul");
                 const GemvArgs gv = g;
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
-                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : ""));
+                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : "") +
+                            (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : "") + (gv.residual ? " +residual" : "") +
+                            (gv.act ? " act=" + std::to_string(gv.act) : ""));
                 if (gv.splits > 1) {
                     emit_sync(proc);
                     Stage r = new_stage(SK_SPLITK_REDUCE, proc);
                     SplitKReduceArgs &a = r.sr;
                     a.C = pc;
-                    a.bias = nullptr;
+                    a.bias = gv.residual;  // a folded residual is added by the sum stage
                     a.ws = gv.ws;
                     a.ldc = ldc;
                     a.c_stride_c = cst[2] * cst[3];
@@ -777,6 +837,50 @@ struct Lowerer {
         }
     }
 
+    // ---- decode attention -------------------------------------------------------------
+    void lower_decode_attention(const OpDesc &op, const Range &proc) {
+        const TensorDesc &q = op.reads.at(0), &k = op.reads.at(1), &v = op.reads.at(2), &o = op.results.at(0);
+        auto qs = q.shape4(), ks = k.shape4(), vs = v.shape4(), os = o.shape4();
+        auto qst = q.strides4(), kst = k.strides4(), vst = v.strides4(), ost = o.strides4();
+        const int64_t B = qs[0], Hq = qs[1], Hkv = ks[1], T = ks[2], D = qs[3];
+        if (q.dtype != k.dtype || q.dtype != v.dtype || q.dtype != o.dtype || (q.dtype != DT_F16 && q.dtype != DT_BF16))
+            throw Error(E_UNSUPPORTED, "DecodeAttention: fp16 or bf16 operands of one type");
+        if (D != 128 || qs[2] != 1 || ks[3] != D || vs[3] != D || ks[0] != B || vs[0] != B || vs[1] != Hkv || vs[2] != T || os != qs)
+            throw Error(E_UNSUPPORTED, "DecodeAttention: q [B, Hq, 1, 128], k and v [B, Hkv, T, 128]");
+        const int64_t G = Hkv > 0 ? Hq / Hkv : 0;
+        if (Hkv <= 0 || Hq % Hkv || !(G == 1 || G == 2 || G == 4 || G == 8))
+            throw Error(E_UNSUPPORTED, "DecodeAttention: 1, 2, 4 or 8 query heads per K/V head");
+        Stage s = new_stage(SK_DECODE_ATTN, proc);
+        DecodeAttnArgs &a = s.da;
+        a.out = tensor_ptr(o); a.q = tensor_ptr(q); a.k = tensor_ptr(k); a.v = tensor_ptr(v);
+        a.q_stride_h = qst[2] * qst[3]; a.q_stride_b = qst[1] * qst[2] * qst[3];
+        a.o_stride_h = ost[2] * ost[3]; a.o_stride_b = ost[1] * ost[2] * ost[3];
+        a.k_ld = kst[3]; a.k_stride_h = kst[2] * kst[3]; a.k_stride_b = kst[1] * kst[2] * kst[3];
+        a.v_ld = vst[3]; a.v_stride_h = vst[2] * vst[3]; a.v_stride_b = vst[1] * vst[2] * vst[3];
+        if (!aligned16(a.q) || !aligned16(a.k) || !aligned16(a.v) || a.k_ld % 8 || a.v_ld % 8 || a.q_stride_h % 8 || a.q_stride_b % 8 ||
+            a.k_stride_h % 8 || a.k_stride_b % 8 || a.v_stride_h % 8 || a.v_stride_b % 8)
+            throw Error(E_UNSUPPORTED, "DecodeAttention: rows must be 16-byte aligned");
+        a.B = (int32_t)B; a.Hq = (int32_t)Hq; a.Hkv = (int32_t)Hkv; a.T = (int32_t)T;
+        a.dtype = q.dtype;
+        a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
+        // chunks of the cache: about two work items per CTA, at least 128 and at most 2048 keys each
+        const int64_t P = proc.count();
+        int64_t chunks = std::max<int64_t>(1, std::min<int64_t>((2 * P + B * Hkv - 1) / (B * Hkv), (T + 127) / 128));
+        int64_t chunk_len = std::min<int64_t>(2048, ((T + chunks - 1) / chunks + 31) / 32 * 32);
+        chunks = (T + chunk_len - 1) / chunk_len;
+        a.chunks = (int32_t)chunks; a.chunk_len = (int32_t)chunk_len;
+        const size_t bytes = (size_t)B * Hkv * chunks * G * (128 + 2) * sizeof(float);
+        a.ws = env.workspace ? reinterpret_cast<float *>(env.workspace + prog.workspace_bytes) : nullptr;
+        prog.workspace_bytes += (bytes + 255) / 256 * 256;
+        a.phase = 0;
+        push(s, "DecodeAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
+                    " keys=" + std::to_string(T) + " chunks=" + std::to_string(chunks) + " x " + std::to_string(chunk_len));
+        emit_sync(proc);
+        Stage m = s;
+        m.da.phase = 1;
+        push(m, "  merge of the chunks " + op.name);
+    }
+
     // ---- transpose / embedding ---------------------------------------------------------
     void lower_transpose(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
         if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Transpose: partial TaskRange");
@@ -949,6 +1053,7 @@ struct Lowerer {
         if (t == "Matmul") return lower_matmul(op, proc, tg, -1, nullptr);
         if (t == "Transpose") return lower_transpose(op, proc, tg);
         if (t == "Embedding") return lower_embedding(op, proc, tg);
+        if (t == "DecodeAttention") return lower_decode_attention(op, proc);
         if (t == "RMSNorm" || t == "LayerNorm" || t == "Softmax") return lower_rowop(op, proc);
         if (t == "Send") return lower_send(op, proc);
         if (t == "Recv") return lower_recv(op, proc);
@@ -966,6 +1071,75 @@ struct Lowerer {
             if (op.is_virtual) continue;
             // Matmul followed by a unary activation on its result, merged into one task
             // by the planner (Sync=false): run the activation in the GEMM epilogue.
+            // [RMSNorm | Mul] Matmul [activation] [Add]: one weight-streaming stage when the Matmul is one
+            {
+                GemvFuse gf;
+                size_t mm = i;
+                auto sole_input_of = [&](const OpDesc &prod, const OpDesc &cons) {
+                    return !prod.results.empty() && !cons.reads.empty() && cons.reads[0].id == prod.results[0].id &&
+                           other_readers(prod.results[0].buffer_id, &cons) == 0;
+                };
+                if (i + 1 < ti.ops.size() && ti.ops[i + 1].type == "Matmul" && sole_input_of(op, ti.ops[i + 1]) &&
+                    matmul_is_gemv(ti.ops[i + 1], tg)) {
+                    const TensorDesc &mx = ti.ops[i + 1].reads[0];
+                    if (op.type == "RMSNorm" && op.reads[0].shape4() == mx.shape4() && op.reads[0].dtype == mx.dtype) {
+                        const bool res = op.has_arg("Residual") && op.arg_bool("Residual");
+                        size_t ri = 1;
+                        gf.pro = GP_RMSNORM;
+                        gf.x = &op.reads[0];
+                        if (op.reads.size() > ri && op.reads[ri].nelems() == mx.shape4()[3]) gf.pro_a = &op.reads[ri++];
+                        if (res && op.reads.size() > ri && op.results.size() >= 2) {
+                            gf.pro_b = &op.reads[ri];
+                            gf.pro_out = &op.results[1];
+                        }
+                        gf.eps = op.has_arg("Eps") ? (float)op.arg_float("Eps") : 1e-5f;
+                        if (!res || gf.pro_b) mm = i + 1;
+                    } else if (op.type == "Mul" && op.reads.size() == 2 && op.reads[0].shape4() == mx.shape4() &&
+                               op.reads[1].shape4() == mx.shape4() && op.reads[0].dtype == mx.dtype && op.reads[1].dtype == mx.dtype) {
+                        gf.pro = GP_MUL;
+                        gf.x = &op.reads[0];
+                        gf.pro_a = &op.reads[1];
+                        mm = i + 1;
+                    }
+                    if (mm == i) gf = GemvFuse();
+                }
+                if (ti.ops[mm].type == "Matmul" && matmul_is_gemv(ti.ops[mm], tg)) {
+                    const OpDesc &m = ti.ops[mm];
+                    size_t last = mm;
+                    int act = -1;
+                    const TensorDesc *res_out = nullptr;
+                    if (last + 1 < ti.ops.size()) {
+                        const OpDesc &nx = ti.ops[last + 1];
+                        const int ac = act_code(nx.type);
+                        if (ac > 0 && nx.reads.size() == 1 && sole_input_of(m, nx) && nx.reads[0].shape == nx.results.at(0).shape &&
+                            nx.results[0].dtype == m.results[0].dtype) {
+                            act = ac;
+                            res_out = &nx.results[0];
+                            ++last;
+                        }
+                    }
+                    if (act < 0 && last + 1 < ti.ops.size()) {
+                        const OpDesc &nx = ti.ops[last + 1];
+                        if (nx.type == "Add" && nx.reads.size() == 2 && !nx.results.empty() && nx.results[0].dtype == m.results[0].dtype &&
+                            nx.reads[0].shape4() == m.results[0].shape4() && nx.reads[1].shape4() == m.results[0].shape4() &&
+                            nx.results[0].shape4() == m.results[0].shape4() && other_readers(m.results[0].buffer_id, &nx) == 0) {
+                            const bool first_is_mm = nx.reads[0].id == m.results[0].id, second_is_mm = nx.reads[1].id == m.results[0].id;
+                            if (first_is_mm != second_is_mm) {
+                                gf.residual = first_is_mm ? &nx.reads[1] : &nx.reads[0];
+                                res_out = &nx.results[0];
+                                ++last;
+                            }
+                        }
+                    }
+                    if (gf.pro != GP_NONE || gf.residual) {
+                        if (!first) emit_sync(proc);
+                        lower_matmul(m, proc, tg, act, res_out, nullptr, &gf);
+                        first = false;
+                        i = last;
+                        continue;
+                    }
+                }
+            }
             if (op.type == "Matmul" && fused_allreduce(plan, ti, i)) {
                 if (!first) emit_sync(proc);
                 lower_matmul(op, proc, tg, -1, nullptr, &ti.ops[i + 1]);

@@ -37,6 +37,7 @@ enum StageKind : int32_t {
     SK_GEMM_SIMT = 12, // CUDA-core matmul for shapes the TMA path cannot take
     SK_SIGNAL = 13,    // raise a channel flag on a peer (after the put's data is complete)
     SK_SPLITK_REDUCE = 14,  // sum the fp32 partials of a split-K matmul, add bias, activate, round, store
+    SK_DECODE_ATTN = 15,    // one query row per head against a K/V cache: scores, softmax and output in one pass over the cache
 };
 
 enum EwiseOp : int32_t {
@@ -170,9 +171,32 @@ struct GemvArgs {
     int32_t ctas_per_split;  // [N, K]: CTAs that share a k-range and split the rows of W
     int32_t nblocks;         // [K, N]: blocks of 256 output columns
     int32_t rows_together;   // [N, K]: rows of W a warp walks together (8, 4, 2 or 1 for M = 1; 4, 2 or 1 for M = 2)
+    // Operators of the same task folded into this stage (each CTA applies the prologue to the activations while
+    // it stages them, so the producer needs no stage and no barrier of its own):
+    int32_t pro;             // GP_NONE; GP_RMSNORM: x := rmsnorm(x [+ pro_b]) * pro_a; GP_MUL: x := x * pro_a
+    const void *pro_a;       // GP_RMSNORM: weight [K] (may be null); GP_MUL: second operand [M, K], row pitch ldx
+    const void *pro_b;       // GP_RMSNORM: optional residual [M, K] added first (row pitch ldx)
+    void *pro_out;           // GP_RMSNORM with residual: x + residual is also stored here (by CTA 0), row pitch ldx
+    float pro_eps;
+    int32_t pad;
+    const void *residual;    // epilogue: y := act(x . W) + residual [M, N] (row pitch ldo); with k-ranges the sum stage adds it
+};
+enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2 };
+constexpr int kGemvMaxM = 2;
+
+// softmax(scale * q . K^T) . V for one query row per head (decode); phase 0: per cache chunk, phase 1: merge the chunks
+struct DecodeAttnArgs {
+    void *out;                 // [B, Hq, 1, 128]
+    const void *q, *k, *v;     // q [B, Hq, 1, 128]; k, v [B, Hkv, T, 128]
+    float *ws;                 // per (b, kv head, chunk): G x (128 outputs + maximum + sum), fp32
+    int64_t q_stride_b, q_stride_h, o_stride_b, o_stride_h;          // elements
+    int64_t k_stride_b, k_stride_h, k_ld, v_stride_b, v_stride_h, v_ld;
+    int32_t B, Hq, Hkv, T;
+    int32_t chunks, chunk_len;  // the cache is cut into `chunks` pieces of chunk_len keys (a multiple of 32)
+    int32_t dtype, phase;
+    float scale;
     int32_t pad;
 };
-constexpr int kGemvMaxM = 2;
 
 struct GemmSimtArgs {
     void *C;
@@ -250,6 +274,7 @@ struct alignas(128) Stage {
         RowOpArgs ro;
         GemmArgs gm;
         GemvArgs gv;
+        DecodeAttnArgs da;
         SplitKReduceArgs sr;
         GemmSimtArgs gs;
         TransposeArgs tp;

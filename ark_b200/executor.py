@@ -58,8 +58,9 @@ def lib():
         L.arkb_executor_stream.argtypes = [vp, ctypes.POINTER(vp)]
         L.arkb_executor_program_dump.argtypes = [vp, ctypes.POINTER(cp)]
         L.arkb_executor_set_wait_limit.argtypes = [vp, ctypes.c_uint64]
-        L.arkb_executor_stage_times.argtypes = [vp, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
-                                                ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+        if hasattr(L, "arkb_executor_stage_times"):  # absent from older builds of the library
+            L.arkb_executor_stage_times.argtypes = [vp, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
+                                                    ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         L.arkb_matvec_splitk_static.argtypes = [vp, vp, vp, ci, ci, ci, ci, vp]
         _lib = L
     return _lib

@@ -59,8 +59,13 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     p = world_size
     hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
     bt = batch * seq
-    h, x = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps), x
-    q = ops.matmul(h, w["wq"], transpose_other=True)   # [bt, hl*hd]
+    # Decode: the small operators around each weight matrix are planned into the matmul's task (Sync=false); with one
+    # or two rows of activations the engine folds them into the weight-streaming stage (norm and gate*up while the
+    # activations are staged, the residual add on the way out) and otherwise runs them one after the other.
+    decode = seq == 1 and k_cache is not None
+    with PlannerContext(sync=False):
+        h = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps)
+        q = ops.matmul(h, w["wq"], transpose_other=True)   # [bt, hl*hd]
     q = ops.reshape(q, [batch, seq, hl, hd])
     if rope is not None:
         q = ops.rope(q, rope)
@@ -77,13 +82,35 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     else:
         k, v = k_cache, v_cache
     scale = 1.0 / math.sqrt(hd)
-    if kvl == hl or kvl == 1:
+    if seq == 1 and k_cache is not None and hd == 128 and hl % kvl == 0 and hl // kvl in (1, 2, 4, 8):
+        o = ops.decode_attention(q, k, v, scale)            # one pass over the cache: scores, softmax, output
+    elif kvl == hl or kvl == 1:
         scores = ops.matmul(q, k, transpose_other=True)     # [b, hl, seq, t_kv]; C broadcasts when kvl == 1
         probs = ops.softmax(scores, scale=scale, mask=mask)  # scale, causal mask and softmax in one pass over the scores
         o = ops.matmul(probs, v)                            # [b, hl, seq, hd]
     else:
         raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")
     o = ops.reshape(o if seq == 1 else ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
+    if decode:
+        with PlannerContext(sync=False):
+            attn = ops.matmul(o, w["wo"], transpose_other=True)
+            if p > 1:
+                attn = ops.all_reduce(attn, rank, p, output=attn)
+            else:
+                x1 = ops.add(attn, x)
+        if p > 1:
+            x1 = ops.add(attn, x)
+        with PlannerContext(sync=False):                    # the norm is recomputed per consumer: it costs one row
+            gate = ops.silu(ops.matmul(ops.rmsnorm(x1, w["ffn_norm"], eps=cfg.norm_eps), w["w1"], transpose_other=True))
+        with PlannerContext(sync=False):
+            up = ops.matmul(ops.rmsnorm(x1, w["ffn_norm"], eps=cfg.norm_eps), w["w3"], transpose_other=True)
+        with PlannerContext(sync=False):
+            down = ops.matmul(ops.mul(gate, up), w["w2"], transpose_other=True)
+            if p > 1:
+                down = ops.all_reduce(down, rank, p, output=down)
+            else:
+                return ops.add(down, x1)
+        return ops.add(x1, down)
     with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
         attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
         if p > 1:

@@ -354,6 +354,19 @@ def softmax(input, output=None, name="softmax", fused=True, scale=1.0, mask=None
     return div(e, s, output)
 
 
+def decode_attention(q, k_cache, v_cache, scale=1.0, output=None, name="decode_attention"):
+    """softmax(scale * q . K^T) . V for ONE query row per head against a K/V cache: q [B, Hq, 1, 128],
+    k_cache and v_cache [B, Hkv, T, 128] with Hq / Hkv in {1, 2, 4, 8} (grouped-query attention).
+    Engine extension: the reference example builds it from two matmuls, a scale and a softmax
+    (examples/llama/model.py:336-444); here the cache is read once."""
+    if len(q.shape) != 4 or q.shape[2] != 1 or len(k_cache.shape) != 4 or list(k_cache.shape) != list(v_cache.shape):
+        raise ModelError("decode_attention: q [B, Hq, 1, D], k_cache and v_cache [B, Hkv, T, D]")
+    out = _out_like(q.shape, q.dtype, output)
+    res = _result_of(out)
+    _m().add_op("DecodeAttention", name, [q, k_cache, v_cache], [out], [res], {"Scale": float(scale)})
+    return res
+
+
 def layernorm(input, eps=1e-5, output=None, name="layernorm", fused=True):
     """Layer normalisation over the last axis (python/ark/ops.py:503-513 composes six ops)."""
     if fused:

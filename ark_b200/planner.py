@@ -124,6 +124,9 @@ def default_config(op, num_sm=DEFAULT_NUM_SM):
     if t in ("RMSNorm", "LayerNorm", "Softmax"):
         sh = _dims4(op.reads[0].shape)
         return {"NumWarps": 1, "SramBytes": 0, "NumTasks": sh[0] * sh[1] * sh[2]}
+    if t == "DecodeAttention":
+        sh = _dims4(op.results[0].shape)
+        return {"NumWarps": 16, "SramBytes": 0, "NumTasks": sh[0] * sh[1]}
     if t == "Embedding":
         sh = _dims4(op.results[0].shape)
         return {"NumWarps": 1, "SramBytes": 0, "NumTasks": sh[0] * sh[1] * sh[2]}
@@ -205,6 +208,10 @@ class Planner:
                 ti["NumWarps"] = max(ti["NumWarps"], num_warps)
                 ti["SramBytes"] = max(ti["SramBytes"], sram)
                 ti["Ops"].append(op_json)
+                # the task's range covers the op with the most tasks (the reference keeps the first op's count,
+                # ark/api/planner.cpp:229-231, which only suits ops with equal task counts)
+                tgrp = processor_groups[-1]["ResourceGroups"][0]["TaskGroups"][0]
+                tgrp["TaskRange"] = [0, max(tgrp["TaskRange"][1], num_tasks)]
             else:
                 tid = next_task_id if first else next_task_id + 1
                 next_task_id = tid

@@ -67,6 +67,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--stage-times", action="store_true",
+                    help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
     args = ap.parse_args()
     import torch
     import ark_b200 as ark
@@ -129,6 +131,27 @@ def main():
     if mask is not None:
         m = np.triu(np.full((seq, seq), -np.inf, np.float32), 1).reshape(1, 1, seq, seq)
         ex.tensor_from_numpy(mask, to_storage(m, dt))
+    if args.stage_times:
+        ex.enable_stage_times(True)
+        ex.launch()
+        ex.barrier()
+        ex.run(3)
+        ex.wait()
+        t = ex.stage_times()
+        notes = ex.program_dump().splitlines()[1:]
+        if rank == 0:
+            t0 = t[t > 0].min()
+            print(f"stages of {nlayers} layer(s), {args.phase}: first entry -> last exit over the CTAs, microseconds")
+            for si in range(t.shape[0]):
+                m = t[si, :, 0] > 0
+                if not m.any():
+                    continue
+                b, e = (t[si, m, 0].min() - t0) / 1e3, (t[si, m, 1].max() - t0) / 1e3
+                print(f"{si:4d} {b:9.1f} -> {e:9.1f}  {e - b:8.1f}  {notes[si] if si < len(notes) else ''}")
+        ex.barrier()
+        ex.stop()
+        ex.destroy()
+        return
     stream = torch.cuda.ExternalStream(ex.stream())
     ex.launch()
     ex.barrier()

@@ -75,3 +75,28 @@ def test_decode_layer_with_kv_cache(dt, heads, kv, batch):
     (got,) = execute([ty], feeds, loop_mode=True)
     want = layer(x, [w], cfg, batch, 1, dt, rope=rope, k_caches=[kc], v_caches=[vc])
     check(got, want, dt)
+
+
+@pytest.mark.parametrize("dt,b,hq,hkv,t", [("fp16", 1, 4, 4, 2048), ("bf16", 16, 8, 1, 1000), ("fp16", 3, 8, 2, 333),
+                                           ("bf16", 2, 4, 2, 4096), ("fp16", 1, 32, 32, 40)])
+def test_decode_attention_against_float64(dt, b, hq, hkv, t):
+    """One query row per head against a K/V cache, grouped-query heads, cache lengths that do not divide into chunks."""
+    rng = np.random.default_rng(53)
+    q = O.to_storage(rng.normal(0, 1, (b, hq, 1, 128)).astype(np.float32), dt)
+    k = O.to_storage(rng.normal(0, 1, (b, hkv, t, 128)).astype(np.float32), dt)
+    v = O.to_storage(rng.normal(0, 1, (b, hkv, t, 128)).astype(np.float32), dt)
+    scale = 1.0 / np.sqrt(128.0)
+    ark.init()
+    tq, tk, tv = ark.tensor(list(q.shape), NAME[dt]), ark.tensor(list(k.shape), NAME[dt]), ark.tensor(list(v.shape), NAME[dt])
+    out = ark.decode_attention(tq, tk, tv, scale)
+    (got,) = execute([out], {tq: q, tk: k, tv: v}, loop_mode=True)
+    g = hq // hkv
+    qf, kf, vf = (O.to_f32(x, dt).astype(np.float64) for x in (q, k, v))
+    kf, vf = np.repeat(kf, g, axis=1), np.repeat(vf, g, axis=1)
+    s = np.einsum("bhqd,bhtd->bhqt", qf, kf) * scale
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bhqt,bhtd->bhqd", p, vf)
+    err = np.abs(O.to_f32(got, dt).astype(np.float64) - want)
+    tol = 2e-3 if dt == "fp16" else 1.6e-2   # one rounding of outputs of magnitude <= ~1
+    assert float(err.max()) <= tol, float(err.max())

@@ -146,3 +146,47 @@ def test_matmul_few_rows_uses_the_streaming_stage():
     ex.compile()
     assert "Matmul(gemv)" in ex.program_dump()
     ex.destroy()
+
+
+# ---- operators of the same task folded into the weight-streaming stage ----
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("tb", [True, False])
+@pytest.mark.parametrize("m", [1, 2])
+def test_rmsnorm_folded_into_weight_streaming_matmul(dt, tb, m):
+    n, k = 2048, 4096
+    rng = np.random.default_rng(41)
+    x, r = rand(rng, (m, k), dt), rand(rng, (m, k), dt)
+    g = O.to_storage(rng.normal(1, 0.1, (k,)).astype(np.float32), dt)
+    w = O.to_storage(rng.normal(0, 0.02, (n, k) if tb else (k, n)).astype(np.float32), dt)
+    ark.init()
+    tx, tr, tg, tw = (ark.tensor(list(a.shape), NAME[dt]) for a in (x, r, g, w))
+    with ark.PlannerContext(sync=False):
+        y1 = ark.matmul(ark.rmsnorm(tx, tg, eps=1e-5), tw, transpose_other=tb)
+    with ark.PlannerContext(sync=False):
+        h, xr = ark.rmsnorm(tx, tg, eps=1e-5, residual=tr)
+        y2 = ark.matmul(h, tw, transpose_other=tb)
+    plan = ark.Planner(0).plan()
+    assert ark.plan_dump(str(plan)).count("<-rmsnorm") == 2
+    g1, g2, gxr = execute([y1, y2, xr], {tx: x, tr: r, tg: g, tw: w})
+    assert_matmul_close(g1, O.matmul(O.rmsnorm(x, g, dt, 1e-5), w, dt, False, tb), dt, "rmsnorm -> gemv")
+    xs = O.binary("add", x, r, dt)
+    assert np.array_equal(gxr.view(np.uint16), xs.view(np.uint16)), "x + residual kept for later"
+    assert_matmul_close(g2, O.matmul(O.rmsnorm(xs, g, dt, 1e-5), w, dt, False, tb), dt, "rmsnorm(residual) -> gemv")
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("tb", [True, False])
+def test_mul_and_residual_add_folded_into_weight_streaming_matmul(dt, tb):
+    m, n, k = 1, 4096, 2048
+    rng = np.random.default_rng(42)
+    a, b, res = rand(rng, (m, k), dt), rand(rng, (m, k), dt), rand(rng, (m, n), dt)
+    w = O.to_storage(rng.normal(0, 0.02, (n, k) if tb else (k, n)).astype(np.float32), dt)
+    ark.init()
+    ta_, tb_, tres, tw = (ark.tensor(list(t.shape), NAME[dt]) for t in (a, b, res, w))
+    with ark.PlannerContext(sync=False):
+        y = ark.add(ark.matmul(ark.mul(ta_, tb_), tw, transpose_other=tb), tres)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert "<-mul" in text and "+residual" in text and "Add" not in text
+    (got,) = execute([y], {ta_: a, tb_: b, tres: res, tw: w})
+    want = O.binary("add", O.matmul(O.binary("mul", a, b, dt), w, dt, False, tb), res, dt)
+    assert_matmul_close(got, want, dt, "mul -> gemv -> add")

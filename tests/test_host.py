@@ -170,6 +170,29 @@ def test_matmul_and_all_reduce_of_one_task_are_fused():
     ark.set_world_size(1)
 
 
+def test_decode_layer_folds_small_operators_into_the_weight_streaming_matmuls():
+    """One token per sequence: norm, gate*up and the residual adds ride in the matmul stages (planned as one task
+    each), attention is one stage plus its merge; a prefill layer keeps them as stages of their own."""
+    from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+    cfg = LlamaConfig(dim=4096, n_heads=32, n_kv_heads=32, ffn_dim=11008)
+    ark.init()
+    x, rope = ark.tensor([1, 4096], ark.fp16), ark.tensor([1, 1, 1, 128], ark.fp16)
+    w = layer_weights(cfg, ark.fp16, 1)
+    kc, vc = ark.tensor([1, 32, 2048, 128], ark.fp16), ark.tensor([1, 32, 2048, 128], ark.fp16)
+    decoder_layer(x, w, cfg, 1, 1, 0, 1, rope=rope, k_cache=kc, v_cache=vc)
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    assert text.count("Matmul(gemv)") == 5 and text.count("<-rmsnorm") == 3 and text.count("+residual") == 2
+    assert "<-mul" in text and "DecodeAttention" in text
+    assert "RMSNorm" not in text and " Add " not in text and " Mul " not in text
+    ark.init()
+    x, rope = ark.tensor([256, 4096], ark.fp16), ark.tensor([1, 256, 1, 128], ark.fp16)
+    mask = ark.tensor([1, 1, 256, 256], ark.fp16)
+    w = layer_weights(cfg, ark.fp16, 1)
+    decoder_layer(x, w, cfg, 1, 256, 0, 1, rope=rope, mask=mask)
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    assert "Matmul(gemv)" not in text and text.count("RMSNorm") == 2 and "Softmax" in text
+
+
 def test_naive_all_reduce_composition_matches_reference_structure():
     """Model::all_reduce of the reference: world_size-1 rounds of send/send_done/recv/add (ops_all_reduce.cpp:8-37)."""
     ark.init()
