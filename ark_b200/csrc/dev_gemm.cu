@@ -222,16 +222,272 @@ __device__ void gemm_epilogue_tile_partial(const GemmLocal &g, const TileCoord &
 //   credited to the leader's `full` barrier; the leader's commits release the
 //   `empty` slot and publish `acc_full` in both CTAs; the epilogue warps of
 //   both CTAs arrive on the leader's `acc_empty`.
+// Everything the warp roles of one matmul stage share. Built by every thread at the start of the stage; the roles
+// are separate functions (own register allocation: the threads that issue the copies and the MMAs are the critical
+// path of large matmuls, and spills or extra instructions there cost several per cent).
+struct GemmRun {
+    GemmLocal L;
+    const GemmArgs *g;      // the stage record (a copy in shared memory)
+    const GemmArgs *gmaps;  // the stage record in global memory: the TMA unit reads tensor maps there
+    char *smem;
+    GemmPipe *pp;
+    CtaCtl *ctl;
+    DeviceState *st;
+    unsigned long long lim;
+    int stage_idx;
+    int STAGES, G, blk_b_bytes, stage_bytes;  // a ring slot holds G consecutive k-blocks of both operands: [G blocks of A][G blocks of B]
+    int n_units, kblocks, crank, up, UP, n_half, splits, kper;
+    uint32_t base_par, tmem_base;
+    unsigned int t0;
+};
+
+// GROUPED == false compiles the loops for one k-block per ring slot (G is the constant 1).
+// Producer: one lane of warp 4 (operand A) and one of warp 6 (operand B). Returns false when a wait ran out.
+template <bool PAIR, bool GROUPED>
+__device__ __noinline__ bool gemm_produce(const GemmRun &R, int warp) {
+    const GemmLocal &L = R.L;
+    const GemmArgs &g = *R.g;
+    const GemmArgs *gmaps = R.gmaps;
+    char *smem = R.smem;
+    GemmPipe *pp = R.pp;
+    CtaCtl *ctl = R.ctl;
+    DeviceState *st = R.st;
+    const int stage_idx = R.stage_idx;
+    const unsigned long long lim = R.lim;
+    const int STAGES = R.STAGES, G = GROUPED ? R.G : 1, blk_b_bytes = R.blk_b_bytes, stage_bytes = R.stage_bytes;
+    const int n_units = R.n_units, kblocks = R.kblocks, crank = R.crank, up = R.up, UP = R.UP, n_half = R.n_half;
+    const int splits = R.splits, kper = R.kper;
+    const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
+    const unsigned int t0 = R.t0;
+    const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
+    (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
+    (void)stage_bytes; (void)n_units; (void)kblocks; (void)crank; (void)up; (void)UP; (void)n_half; (void)splits; (void)kper;
+    (void)base_par; (void)tmem_base; (void)t0; (void)tmA; (void)tmB; (void)tmC;
+
+    const bool is_a = warp == kProducerWarp;
+    const int mn_major = is_a ? L.a_mn_major : L.b_mn_major;
+    const int span = is_a ? kGemmTileM : n_half;              // rows (K-major) or columns (MN-major) staged
+    const int chunks = mn_major ? (span + 63) / 64 : 1;       // 64-wide MN chunks
+    // a slot always receives G whole k-blocks (those past the end of K arrive as zeros)
+    const uint32_t bytes = (uint32_t)G * (mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2);
+    const CUtensorMap *tm = is_a ? tmA : tmB;
+    const int has_c = is_a ? L.a_bc : L.b_bc, has_n = is_a ? L.a_bn : L.b_bn;
+    int s = 0;
+    uint32_t wrap = 0;
+    for (int u = up; u < n_units; u += UP) {
+        const TileCoord tc = gemm_unit(g, u / splits);
+        const int mn0 = is_a ? tc.m0 + crank * kGemmTileM : tc.n0 + crank * n_half;
+        const int bc = has_c ? tc.bc : 0, bn = has_n ? tc.bn : 0;
+        const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
+        for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+            const uint32_t par = (((base_par >> s) ^ wrap) & 1) ^ 1;
+            if (!mbar_wait(&pp->empty[s], par, lim)) {
+                ctl->abort = 1;
+                report(st, ST_MBAR_TIMEOUT, stage_idx);
+                return false;
+            }
+            char *dst = smem + s * stage_bytes + (is_a ? 0 : G * kGemmABytes);
+            const int chunk_stride = G * 64 * kGemmBK * 2;  // MN-major: G k-blocks of one 64-wide chunk are contiguous
+            if constexpr (!PAIR) {
+                mbar_expect_tx(&pp->full[s], bytes);
+                if (!mn_major) {
+                    if (G == 1) tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
+                    else tma_load_5d(dst, tm, &pp->full[s], 0, mn0, k, bc, bn);
+                } else {
+                    for (int c = 0; c < chunks; ++c)
+                        tma_load_4d(dst + c * chunk_stride, tm, &pp->full[s], mn0 + c * 64, k * kGemmBK, bc, bn);
+                }
+            } else {
+                // both CTAs' copies are credited to the leader's barrier
+                const uint32_t full_leader = mapa_u32(smem_u32(&pp->full[s]), 0);
+                if (crank == 0) mbar_expect_tx(&pp->full[s], 2 * bytes);
+                if (!mn_major) {
+                    if (G == 1) tma_load_4d_pair(dst, tm, full_leader, k * kGemmBK, mn0, bc, bn);
+                    else tma_load_5d_pair(dst, tm, full_leader, 0, mn0, k, bc, bn);
+                } else {
+                    for (int c = 0; c < chunks; ++c)
+                        tma_load_4d_pair(dst + c * chunk_stride, tm, full_leader, mn0 + c * 64, k * kGemmBK, bc, bn);
+                }
+            }
+        }
+    }
+    return true;
+}
+
+// MMA issue: one lane of warp 5 of the leader CTA.
+template <bool PAIR, bool GROUPED>
+__device__ __noinline__ bool gemm_issue(const GemmRun &R) {
+    const GemmLocal &L = R.L;
+    const GemmArgs &g = *R.g;
+    const GemmArgs *gmaps = R.gmaps;
+    char *smem = R.smem;
+    GemmPipe *pp = R.pp;
+    CtaCtl *ctl = R.ctl;
+    DeviceState *st = R.st;
+    const int stage_idx = R.stage_idx;
+    const unsigned long long lim = R.lim;
+    const int STAGES = R.STAGES, G = GROUPED ? R.G : 1, blk_b_bytes = R.blk_b_bytes, stage_bytes = R.stage_bytes;
+    const int n_units = R.n_units, kblocks = R.kblocks, crank = R.crank, up = R.up, UP = R.UP, n_half = R.n_half;
+    const int splits = R.splits, kper = R.kper;
+    const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
+    const unsigned int t0 = R.t0;
+    const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
+    (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
+    (void)stage_bytes; (void)n_units; (void)kblocks; (void)crank; (void)up; (void)UP; (void)n_half; (void)splits; (void)kper;
+    (void)base_par; (void)tmem_base; (void)t0; (void)tmA; (void)tmB; (void)tmC;
+
+    const uint32_t idesc = umma_idesc(L.dtype == DT_BF16, L.a_mn_major, L.b_mn_major, L.tile_n, PAIR ? 256 : 128);
+    // per-MMA (K=16) advance of the descriptor start address, in 16-byte units
+    const uint32_t a_adv = L.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
+    const uint32_t b_adv = L.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
+    const uint32_t blk_mn_bytes = 64 * kGemmBK * 2;        // one k-block of a 64-wide MN chunk
+    const uint32_t chunk_bytes = (uint32_t)G * blk_mn_bytes;  // distance between the chunks of one k-block
+    const uint32_t a_blk = L.a_mn_major ? blk_mn_bytes : (uint32_t)kGemmABytes;   // k-block to k-block inside a slot
+    const uint32_t b_blk = L.b_mn_major ? blk_mn_bytes : (uint32_t)blk_b_bytes;
+    unsigned int t = t0;
+    int s = 0;
+    uint32_t wrap = 0;
+    for (int u = up; u < n_units; u += UP, ++t) {
+        const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
+        const int acc = t & 1;
+        if (!mbar_wait(&pp->acc_empty[acc], ((t >> 1) & 1) ^ 1, lim)) {
+            ctl->abort = 1;
+            report(st, ST_MBAR_TIMEOUT, stage_idx);
+            return false;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * 256;
+        for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
+            if (!mbar_wait(&pp->full[s], ((base_par >> s) ^ wrap) & 1, lim)) {
+                ctl->abort = 1;
+                report(st, ST_MBAR_TIMEOUT, stage_idx);
+                return false;
+            }
+            tc_fence_after();
+            const uint32_t sa0 = smem_u32(smem + s * stage_bytes);
+            if (G == 1) {
+                const uint32_t sb = sa0 + kGemmABytes;
+                const uint64_t da = L.a_mn_major ? umma_desc(sa0, chunk_bytes, 1024) : umma_desc(sa0, 16, 1024);
+                const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
+#pragma unroll
+                for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                    const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
+                    if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                    else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                }
+            } else {
+                const uint32_t sb0 = sa0 + G * kGemmABytes;
+                const int nblk = min(G, kb_hi - k);
+                for (int j = 0; j < nblk; ++j) {
+                    const uint32_t sa = sa0 + j * a_blk, sb = sb0 + j * b_blk;
+                    const uint64_t da = L.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
+                    const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
+#pragma unroll
+                    for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                        const uint32_t accum = (k + j > kb_lo || kk > 0) ? 1u : 0u;
+                        if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                        else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                    }
+                }
+            }
+            // free the shared-memory slot once these MMAs have read it
+            if constexpr (PAIR) {
+                const uint32_t e = smem_u32(&pp->empty[s]);
+                umma_commit_pair(mapa_u32(e, 0));
+                umma_commit_pair(mapa_u32(e, 1));
+            } else {
+                umma_commit(&pp->empty[s]);
+            }
+        }
+        if constexpr (PAIR) {  // accumulator complete, in both CTAs
+            const uint32_t f = smem_u32(&pp->acc_full[acc]);
+            umma_commit_pair(mapa_u32(f, 0));
+            umma_commit_pair(mapa_u32(f, 1));
+        } else {
+            umma_commit(&pp->acc_full[acc]);
+        }
+    }
+    return true;
+}
+
+// Epilogue: warps 0-3, each on its 32-lane quarter of the accumulator.
 template <bool PAIR>
+__device__ __noinline__ bool gemm_drain(const GemmRun &R, int warp, int lane) {
+    constexpr bool GROUPED = true;
+    const GemmLocal &L = R.L;
+    const GemmArgs &g = *R.g;
+    const GemmArgs *gmaps = R.gmaps;
+    char *smem = R.smem;
+    GemmPipe *pp = R.pp;
+    CtaCtl *ctl = R.ctl;
+    DeviceState *st = R.st;
+    const int stage_idx = R.stage_idx;
+    const unsigned long long lim = R.lim;
+    const int STAGES = R.STAGES, G = GROUPED ? R.G : 1, blk_b_bytes = R.blk_b_bytes, stage_bytes = R.stage_bytes;
+    const int n_units = R.n_units, kblocks = R.kblocks, crank = R.crank, up = R.up, UP = R.UP, n_half = R.n_half;
+    const int splits = R.splits, kper = R.kper;
+    const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
+    const unsigned int t0 = R.t0;
+    const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
+    (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
+    (void)stage_bytes; (void)n_units; (void)kblocks; (void)crank; (void)up; (void)UP; (void)n_half; (void)splits; (void)kper;
+    (void)base_par; (void)tmem_base; (void)t0; (void)tmA; (void)tmB; (void)tmC;
+    char *epi_stage = smem + kGemmPipeBytes;
+    unsigned int epi_blk = 0;
+    unsigned int t = t0;
+    for (int u = up; u < n_units; u += UP, ++t) {
+        TileCoord tc = gemm_unit(g, u / splits);
+        tc.m0 += crank * kGemmTileM;
+        const int split = u % splits;
+        const int acc = t & 1;
+        bool ok = mbar_wait(&pp->acc_full[acc], (t >> 1) & 1, lim);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            if (lane == 0) {
+                ctl->abort = 1;
+                report(st, ST_MBAR_TIMEOUT, stage_idx);
+            }
+            return false;
+        }
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * 256;
+        if (L.splits > 1) {
+            gemm_epilogue_tile_partial(L, tc, split, tmem_acc, warp, lane);
+        } else if (L.out_transposed) {
+            if (L.dtype == DT_BF16) gemm_epilogue_tile_swapped<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
+            else gemm_epilogue_tile_swapped<__half>(L, tc, tmem_acc, warp, lane);
+        } else if (L.c_tma) {
+            // fused all_reduce: the tile goes to the rank that sums these rows (tiles never straddle two owners)
+            const int owner = L.peer_rows > 0 ? tc.m0 / L.peer_rows : 0;
+            const CUtensorMap *tm = L.peer_rows > 0 ? &gmaps->tmPeer[owner] : tmC;
+            const int shift = owner * L.peer_rows;
+            if (L.dtype == DT_BF16) gemm_epilogue_tile_tma<__nv_bfloat16>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, shift);
+            else gemm_epilogue_tile_tma<__half>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, shift);
+        } else {
+            if (L.dtype == DT_BF16) gemm_epilogue_tile<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
+            else gemm_epilogue_tile<__half>(L, tc, tmem_acc, warp, lane);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+            if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&pp->acc_empty[acc]), 0));
+            else mbar_arrive(&pp->acc_empty[acc]);
+        }
+    }
+    // the stage's output must be in global memory before the CTA reaches the next barrier
+    if (lane == 0) {
+        tma_store_wait<0>();
+        if (L.peer_rows > 0) __threadfence_system();  // tiles stored into peer memory: ordered before the peer barrier that follows
+    }
+    return true;
+}
+
+template <bool PAIR, bool GROUPED>
 __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                            DeviceState *st, int stage_idx, unsigned long long lim) {
-    const int STAGES = g.stages;
-    // a ring slot holds G consecutive k-blocks of both operands: [G blocks of A][G blocks of B]
-    const int G = g.kgroup > 1 ? g.kgroup : 1;
-    const int blk_b_bytes = g.stage_b_bytes;
-    const int stage_bytes = G * (kGemmABytes + blk_b_bytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    GemmLocal L;
+    GemmRun R;
+    GemmLocal &L = R.L;
     L.C = g.C; L.bias = g.bias; L.ldc = g.ldc; L.c_stride_c = g.c_stride_c; L.c_stride_n = g.c_stride_n;
     L.M = g.M; L.N = g.N; L.K = g.K; L.tile_n = g.tile_n; L.act = g.act; L.c_vec = g.c_vec; L.c_tma = g.c_tma;
     L.dtype = g.dtype; L.out_transposed = g.out_transposed; L.splits = g.splits; L.ws = g.ws; L.batch_c = g.batch_c;
@@ -239,216 +495,47 @@ __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int 
     L.a_mn_major = g.a_mn_major; L.b_mn_major = g.b_mn_major;
     L.a_bc = g.a_bc; L.a_bn = g.a_bn; L.b_bc = g.b_bc; L.b_bn = g.b_bn;
     L.peer_rows = g.peer_rows;
-    const int n_units = g.n_units;
-    // the TMA unit reads tensor maps from global memory: `gmaps` is the stage record there, `g` a copy that may sit in shared memory
-    const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
-    char *epi_stage = smem + kGemmPipeBytes;
-    unsigned int epi_blk = 0;
-    const int kblocks = (L.K + kGemmBK - 1) / kGemmBK;
-    const unsigned int t0 = pp->tile_count;
+    R.g = &g; R.gmaps = gmaps; R.smem = smem; R.pp = pp; R.ctl = ctl; R.st = st; R.lim = lim; R.stage_idx = stage_idx;
+    R.STAGES = g.stages;
+    R.G = GROUPED ? g.kgroup : 1;
+    R.blk_b_bytes = g.stage_b_bytes;
+    R.stage_bytes = R.G * (kGemmABytes + R.blk_b_bytes);
+    R.n_units = g.n_units;
+    R.kblocks = (L.K + kGemmBK - 1) / kGemmBK;
+    R.t0 = pp->tile_count;
     // phase bit of every ring slot at the start of this stage; inside the loops the slot index
     // and a wrap bit are stepped by hand (no division on the MMA-issuing thread's critical path)
-    uint32_t base_par = 0;
-    for (int s = 0; s < STAGES; ++s) base_par |= (pp->use[s] & 1u) << s;
-    const int crank = PAIR ? (p & 1) : 0;          // rank inside the CTA pair
-    const int up = PAIR ? (p >> 1) : p;             // which tile walker this CTA belongs to
-    const int UP = PAIR ? (P >> 1) : P;
-    const int n_half = PAIR ? L.tile_n / 2 : L.tile_n;  // B columns staged by this CTA
+    R.base_par = 0;
+    for (int s = 0; s < R.STAGES; ++s) R.base_par |= (pp->use[s] & 1u) << s;
+    R.crank = PAIR ? (p & 1) : 0;          // rank inside the CTA pair
+    R.up = PAIR ? (p >> 1) : p;             // which tile walker this CTA belongs to
+    R.UP = PAIR ? (P >> 1) : P;
+    R.n_half = PAIR ? L.tile_n / 2 : L.tile_n;  // B columns staged by this CTA
     // split-K: unit = tile * splits + range; a unit runs k-blocks [kb_lo, kb_hi) of its tile
-    const int splits = L.splits > 1 ? L.splits : 1;
-    const int kper = g.kper > 0 ? g.kper : (kblocks + splits - 1) / splits;
+    R.splits = L.splits > 1 ? L.splits : 1;
+    R.kper = g.kper > 0 ? g.kper : (R.kblocks + R.splits - 1) / R.splits;
     int my_tiles = 0;
     unsigned int my_slots = 0;  // ring slots this CTA fills in this stage
-    for (int u = up; u < n_units; u += UP) {
+    for (int u = R.up; u < R.n_units; u += R.UP) {
         ++my_tiles;
-        const int lo = (u % splits) * kper;
-        my_slots += (unsigned int)((min(kblocks, lo + kper) - lo + G - 1) / G);
+        const int lo = (u % R.splits) * R.kper;
+        my_slots += (unsigned int)((min(R.kblocks, lo + R.kper) - lo + R.G - 1) / R.G);
     }
-    const uint32_t tmem_base = ctl->tmem_base;
+    R.tmem_base = ctl->tmem_base;
 
     if (warp == kProducerWarp || warp == kProducerWarpB) {
-        // Two producer warps, one per operand: a thread can hand a bulk tensor copy to the
-        // TMA unit only every few hundred cycles, so A and B are issued from different warps.
-        if (lane == 0) {
-            const bool is_a = warp == kProducerWarp;
-            const int mn_major = is_a ? L.a_mn_major : L.b_mn_major;
-            const int span = is_a ? kGemmTileM : n_half;              // rows (K-major) or columns (MN-major) staged
-            const int chunks = mn_major ? (span + 63) / 64 : 1;       // 64-wide MN chunks
-            // a slot always receives G whole k-blocks (those past the end of K arrive as zeros)
-            const uint32_t bytes = (uint32_t)G * (mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2);
-            const CUtensorMap *tm = is_a ? tmA : tmB;
-            const int has_c = is_a ? L.a_bc : L.b_bc, has_n = is_a ? L.a_bn : L.b_bn;
-            int s = 0;
-            uint32_t wrap = 0;
-            for (int u = up; u < n_units; u += UP) {
-                const TileCoord tc = gemm_unit(g, u / splits);
-                const int mn0 = is_a ? tc.m0 + crank * kGemmTileM : tc.n0 + crank * n_half;
-                const int bc = has_c ? tc.bc : 0, bn = has_n ? tc.bn : 0;
-                const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
-                for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
-                    const uint32_t par = (((base_par >> s) ^ wrap) & 1) ^ 1;
-                    if (!mbar_wait(&pp->empty[s], par, lim)) {
-                        ctl->abort = 1;
-                        report(st, ST_MBAR_TIMEOUT, stage_idx);
-                        goto done;
-                    }
-                    char *dst = smem + s * stage_bytes + (is_a ? 0 : G * kGemmABytes);
-                    const int chunk_stride = G * 64 * kGemmBK * 2;  // MN-major: G k-blocks of one 64-wide chunk are contiguous
-                    if constexpr (!PAIR) {
-                        mbar_expect_tx(&pp->full[s], bytes);
-                        if (!mn_major) {
-                            if (G == 1) tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
-                            else tma_load_5d(dst, tm, &pp->full[s], 0, mn0, k, bc, bn);
-                        } else {
-                            for (int c = 0; c < chunks; ++c)
-                                tma_load_4d(dst + c * chunk_stride, tm, &pp->full[s], mn0 + c * 64, k * kGemmBK, bc, bn);
-                        }
-                    } else {
-                        // both CTAs' copies are credited to the leader's barrier
-                        const uint32_t full_leader = mapa_u32(smem_u32(&pp->full[s]), 0);
-                        if (crank == 0) mbar_expect_tx(&pp->full[s], 2 * bytes);
-                        if (!mn_major) {
-                            if (G == 1) tma_load_4d_pair(dst, tm, full_leader, k * kGemmBK, mn0, bc, bn);
-                            else tma_load_5d_pair(dst, tm, full_leader, 0, mn0, k, bc, bn);
-                        } else {
-                            for (int c = 0; c < chunks; ++c)
-                                tma_load_4d_pair(dst + c * chunk_stride, tm, full_leader, mn0 + c * 64, k * kGemmBK, bc, bn);
-                        }
-                    }
-                }
-            }
-        }
+        if (lane == 0) gemm_produce<PAIR, GROUPED>(R, warp);
     } else if (warp == kMmaWarp) {
-        if (lane == 0 && crank == 0) {
-            const uint32_t idesc = umma_idesc(L.dtype == DT_BF16, L.a_mn_major, L.b_mn_major, L.tile_n, PAIR ? 256 : 128);
-            // per-MMA (K=16) advance of the descriptor start address, in 16-byte units
-            const uint32_t a_adv = L.a_mn_major ? (16 * 128) >> 4 : 32 >> 4;
-            const uint32_t b_adv = L.b_mn_major ? (16 * 128) >> 4 : 32 >> 4;
-            const uint32_t blk_mn_bytes = 64 * kGemmBK * 2;        // one k-block of a 64-wide MN chunk
-            const uint32_t chunk_bytes = (uint32_t)G * blk_mn_bytes;  // distance between the chunks of one k-block
-            const uint32_t a_blk = L.a_mn_major ? blk_mn_bytes : (uint32_t)kGemmABytes;   // k-block to k-block inside a slot
-            const uint32_t b_blk = L.b_mn_major ? blk_mn_bytes : (uint32_t)blk_b_bytes;
-            unsigned int t = t0;
-            int s = 0;
-            uint32_t wrap = 0;
-            for (int u = up; u < n_units; u += UP, ++t) {
-                const int kb_lo = (u % splits) * kper, kb_hi = min(kblocks, kb_lo + kper);
-                const int acc = t & 1;
-                if (!mbar_wait(&pp->acc_empty[acc], ((t >> 1) & 1) ^ 1, lim)) {
-                    ctl->abort = 1;
-                    report(st, ST_MBAR_TIMEOUT, stage_idx);
-                    goto done;
-                }
-                tc_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * 256;
-                for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
-                    if (!mbar_wait(&pp->full[s], ((base_par >> s) ^ wrap) & 1, lim)) {
-                        ctl->abort = 1;
-                        report(st, ST_MBAR_TIMEOUT, stage_idx);
-                        goto done;
-                    }
-                    tc_fence_after();
-                    const uint32_t sa0 = smem_u32(smem + s * stage_bytes);
-                    if (G == 1) {
-                        const uint32_t sb = sa0 + kGemmABytes;
-                        const uint64_t da = L.a_mn_major ? umma_desc(sa0, chunk_bytes, 1024) : umma_desc(sa0, 16, 1024);
-                        const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
-#pragma unroll
-                        for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-                            const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
-                            if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
-                            else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
-                        }
-                    } else {
-                        const uint32_t sb0 = sa0 + G * kGemmABytes;
-                        const int nblk = min(G, kb_hi - k);
-                        for (int j = 0; j < nblk; ++j) {
-                            const uint32_t sa = sa0 + j * a_blk, sb = sb0 + j * b_blk;
-                            const uint64_t da = L.a_mn_major ? umma_desc(sa, chunk_bytes, 1024) : umma_desc(sa, 16, 1024);
-                            const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
-#pragma unroll
-                            for (int kk = 0; kk < kGemmBK / 16; ++kk) {
-                                const uint32_t accum = (k + j > kb_lo || kk > 0) ? 1u : 0u;
-                                if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
-                                else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
-                            }
-                        }
-                    }
-                    // free the shared-memory slot once these MMAs have read it
-                    if constexpr (PAIR) {
-                        const uint32_t e = smem_u32(&pp->empty[s]);
-                        umma_commit_pair(mapa_u32(e, 0));
-                        umma_commit_pair(mapa_u32(e, 1));
-                    } else {
-                        umma_commit(&pp->empty[s]);
-                    }
-                }
-                if constexpr (PAIR) {  // accumulator complete, in both CTAs
-                    const uint32_t f = smem_u32(&pp->acc_full[acc]);
-                    umma_commit_pair(mapa_u32(f, 0));
-                    umma_commit_pair(mapa_u32(f, 1));
-                } else {
-                    umma_commit(&pp->acc_full[acc]);
-                }
-            }
-        }
+        if (lane == 0 && R.crank == 0) gemm_issue<PAIR, GROUPED>(R);
     } else if (warp < kEpiWarps) {
-        unsigned int t = t0;
-        for (int u = up; u < n_units; u += UP, ++t) {
-            TileCoord tc = gemm_unit(g, u / splits);
-            tc.m0 += crank * kGemmTileM;
-            const int split = u % splits;
-            const int acc = t & 1;
-            bool ok = mbar_wait(&pp->acc_full[acc], (t >> 1) & 1, lim);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                if (lane == 0) {
-                    ctl->abort = 1;
-                    report(st, ST_MBAR_TIMEOUT, stage_idx);
-                }
-                goto done;
-            }
-            tc_fence_after();
-            const uint32_t tmem_acc = tmem_base + acc * 256;
-            if (L.splits > 1) {
-                gemm_epilogue_tile_partial(L, tc, split, tmem_acc, warp, lane);
-            } else if (L.out_transposed) {
-                if (L.dtype == DT_BF16) gemm_epilogue_tile_swapped<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
-                else gemm_epilogue_tile_swapped<__half>(L, tc, tmem_acc, warp, lane);
-            } else if (L.peer_rows > 0) {
-                // fused all_reduce: the tile goes to the rank that sums these rows (tiles never straddle two owners)
-                const int owner = tc.m0 / L.peer_rows;
-                const CUtensorMap *tm = &gmaps->tmPeer[owner];
-                if (L.dtype == DT_BF16)
-                    gemm_epilogue_tile_tma<__nv_bfloat16>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, owner * L.peer_rows);
-                else gemm_epilogue_tile_tma<__half>(L, tm, tc, tmem_acc, warp, lane, epi_stage, epi_blk, owner * L.peer_rows);
-            } else if (L.c_tma) {
-                if (L.dtype == DT_BF16) gemm_epilogue_tile_tma<__nv_bfloat16>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
-                else gemm_epilogue_tile_tma<__half>(L, tmC, tc, tmem_acc, warp, lane, epi_stage, epi_blk);
-            } else {
-                if (L.dtype == DT_BF16) gemm_epilogue_tile<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
-                else gemm_epilogue_tile<__half>(L, tc, tmem_acc, warp, lane);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if constexpr (PAIR) mbar_arrive_cluster(mapa_u32(smem_u32(&pp->acc_empty[acc]), 0));
-                else mbar_arrive(&pp->acc_empty[acc]);
-            }
-        }
-        // the stage's output must be in global memory before the CTA reaches the next barrier
-        if (lane == 0) {
-            tma_store_wait<0>();
-            if (L.peer_rows > 0) __threadfence_system();  // tiles stored into peer memory: ordered before the peer barrier that follows
-        }
+        gemm_drain<PAIR>(R, warp, lane);
     }
-done:
     __syncthreads();
     if (threadIdx.x == 0) {
         const unsigned int total = my_slots;
-        for (int s = 0; s < STAGES; ++s)
-            if (total > (unsigned int)s) pp->use[s] += (total - s + STAGES - 1) / STAGES;
-        pp->tile_count = t0 + (unsigned int)my_tiles;
+        for (int s = 0; s < R.STAGES; ++s)
+            if (total > (unsigned int)s) pp->use[s] += (total - s + R.STAGES - 1) / R.STAGES;
+        pp->tile_count = R.t0 + (unsigned int)my_tiles;
     }
     // the partner may still read this CTA's shared memory / signal its barriers
     if constexpr (PAIR) cluster_sync_all();
@@ -457,11 +544,13 @@ done:
 
 __device__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                          DeviceState *st, int stage_idx, unsigned long long spin_limit) {
-    run_gemm_t<false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+    if (g.kgroup > 1) run_gemm_t<false, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+    else run_gemm_t<false, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
 __device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                               DeviceState *st, int stage_idx, unsigned long long spin_limit) {
-    run_gemm_t<true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+    if (g.kgroup > 1) run_gemm_t<true, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
+    else run_gemm_t<true, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
 
 // Sums the split-K partials (fixed order: deterministic), adds the optional bias,

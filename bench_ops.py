@@ -53,11 +53,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="")
+    ap.add_argument("--mib", type=int, default=256,
+                    help="size of the tensors of the HBM-bound cases in MiB (256: the per-iteration barrier is ~10 %% of the time; "
+                         "1024 shows the streaming rate)")
     args = ap.parse_args()
     import torch
     import ark_b200 as ark
     pk, which = peaks()
     MB = 1 << 20
+    SC = max(1, args.mib // 256)  # row-count multiplier of the HBM-bound cases
     cases = []
 
     def case(name, fn):
@@ -67,7 +71,7 @@ def main():
     # ---- HBM-bound stages: tensors of 256 MiB so that nothing fits in L2 ----
     def ew_unary(op, dt, es):
         def b():
-            n = 256 * MB // es
+            n = args.mib * MB // es
             t = ark.tensor([n // 8192, 8192], dt)
             getattr(ark, op)(t)
             return 2 * n * es, 0
@@ -75,7 +79,7 @@ def main():
 
     def ew_binary(op, dt, es):
         def b():
-            n = 256 * MB // es
+            n = args.mib * MB // es
             a, c = ark.tensor([n // 8192, 8192], dt), ark.tensor([n // 8192, 8192], dt)
             getattr(ark, op)(a, c)
             return 3 * n * es, 0
@@ -87,9 +91,9 @@ def main():
     case("mul_bf16", ew_binary("mul", ark.bf16, 2))
 
     def add_bcast():
-        a, c = ark.tensor([16384, 8192], ark.fp16), ark.tensor([1, 8192], ark.fp16)
+        a, c = ark.tensor([16384 * SC, 8192], ark.fp16), ark.tensor([1, 8192], ark.fp16)
         ark.add(a, c)
-        return 2 * 16384 * 8192 * 2, 0
+        return 2 * 16384 * SC * 8192 * 2, 0
     case("add_broadcast_row_fp16", add_bcast)
 
     def reduce_last(rows, cols, dt, es):
@@ -98,13 +102,13 @@ def main():
             ark.reduce_sum(t, axis=-1)
             return rows * cols * es, 0
         return b
-    case("reduce_sum_w_fp16_32768x4096", reduce_last(32768, 4096, ark.fp16, 2))
-    case("reduce_sum_w_fp32_16384x4096", reduce_last(16384, 4096, ark.fp32, 4))
+    case("reduce_sum_w_fp16_32768x4096", reduce_last(32768 * SC, 4096, ark.fp16, 2))
+    case("reduce_sum_w_fp32_16384x4096", reduce_last(16384 * SC, 4096, ark.fp32, 4))
 
     def reduce_h():
-        t = ark.tensor([64, 1024, 2048], ark.fp16)
+        t = ark.tensor([64 * SC, 1024, 2048], ark.fp16)
         ark.reduce_sum(t, axis=1)
-        return 64 * 1024 * 2048 * 2, 0
+        return 64 * SC * 1024 * 2048 * 2, 0
     case("reduce_sum_h_fp16", reduce_h)
 
     def rows(opname, r, c, dt, es):
@@ -119,10 +123,10 @@ def main():
                 ark.layernorm(t)
             return 2 * r * c * es, 0
         return b
-    case("rmsnorm_fp16_32768x4096", rows("rmsnorm", 32768, 4096, ark.fp16, 2))
-    case("rmsnorm_bf16_16384x8192", rows("rmsnorm", 16384, 8192, ark.bf16, 2))
-    case("softmax_fp16_65536x2048", rows("softmax", 65536, 2048, ark.fp16, 2))
-    case("layernorm_fp16_32768x4096", rows("layernorm", 32768, 4096, ark.fp16, 2))
+    case("rmsnorm_fp16_32768x4096", rows("rmsnorm", 32768 * SC, 4096, ark.fp16, 2))
+    case("rmsnorm_bf16_16384x8192", rows("rmsnorm", 16384 * SC, 8192, ark.bf16, 2))
+    case("softmax_fp16_65536x2048", rows("softmax", 65536 * SC, 2048, ark.fp16, 2))
+    case("layernorm_fp16_32768x4096", rows("layernorm", 32768 * SC, 4096, ark.fp16, 2))
 
     # ---- fixed cost of a stage: 16 dependent tiny operators (time / 16 = one stage + one grid barrier) ----
     def chain16():
@@ -143,6 +147,8 @@ def main():
     case("gemv_m1_fp16_28672x8192", gemv(1, 28672, 8192, ark.fp16, 2))
     case("gemv_m16_bf16_28672x8192", gemv(16, 28672, 8192, ark.bf16, 2))
     case("gemv_m1_fp16_4096x4096", gemv(1, 4096, 4096, ark.fp16, 2))
+    case("gemv_m1_fp16_65536x8192", gemv(1, 65536, 8192, ark.fp16, 2))
+    case("gemv_m2_bf16_32768x8192", gemv(2, 32768, 8192, ark.bf16, 2))
     case("gemv_m1_fp16_kn_8192x28672", gemv(1, 28672, 8192, ark.fp16, 2, nk=False))
 
     # ---- tensor-core matmuls ----
