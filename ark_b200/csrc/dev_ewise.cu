@@ -180,57 +180,6 @@ __device__ void ewise_walk(const EwiseArgs &a, int p, int P) {
     const int64_t s03 = a.in0.stride[3], s13 = a.in1.stride[3];
     // an operand with a broadcast dimension is re-read many times: keep it in L1
     const bool bc0 = !(s02 && s03), bc1 = !(s12 && s13);
-    // Up to three collapsed dimensions, every operand with a W extent (row / plane broadcasts: bias adds, rope
-    // tables): 32-bit index arithmetic recomputed where it is needed, so that eight packed 16-byte loads per
-    // operand are in flight per thread like in the flat path.
-    if constexpr (V * sizeof(TI) == 16) {
-        if (a.out.shape[0] == 1 && n_units <= 0xffffffffll && (!rd0 || s03) && (!bin || s13)) {
-            // strides are in elements, 0 along a broadcast dimension
-            const int64_t so1 = a.out.stride[1], s01 = a.in0.stride[1], s11 = a.in1.stride[1];
-            auto where = [&](uint32_t uu, int64_t &oo, int64_t &o0, int64_t &o1) {
-                const uint32_t row = uu / WV;
-                const int64_t w = (int64_t)(uu - row * WV) * V;
-                const uint32_t c = row / H, h = row - c * H;
-                oo = c * so1 + h * so2 + w;
-                o0 = c * s01 + h * s02 + w;
-                o1 = c * s11 + h * s12 + w;
-            };
-            constexpr int U8 = 8;
-            // an operand with a broadcast dimension is re-read many times: it goes through L1, the others stream
-            const bool bcast0 = rd0 && ((C > 1 && !s01) || (H > 1 && !s02));
-            const bool bcast1 = bin && ((C > 1 && !s11) || (H > 1 && !s12));
-            for (int64_t u0 = tid; u0 < n_units; u0 += nth * U8) {
-                uint4 rx[U8], ry[U8];
-#pragma unroll
-                for (int k = 0; k < U8; ++k) {
-                    const int64_t u = u0 + k * nth;
-                    if (u >= n_units) continue;
-                    int64_t oo, o0, o1;
-                    where((uint32_t)u, oo, o0, o1);
-                    if (rd0) rx[k] = bcast0 ? *reinterpret_cast<const uint4 *>(in0 + o0) : ldg16_stream(in0 + o0);
-                    if (bin) ry[k] = bcast1 ? *reinterpret_cast<const uint4 *>(in1 + o1) : ldg16_stream(in1 + o1);
-                }
-#pragma unroll
-                for (int k = 0; k < U8; ++k) {
-                    const int64_t u = u0 + k * nth;
-                    if (u >= n_units) continue;
-                    int64_t oo, o0, o1;
-                    where((uint32_t)u, oo, o0, o1);
-                    float x[V], y[V], r[V];
-                    const TI *ex = reinterpret_cast<const TI *>(&rx[k]);
-                    const TI *ey = reinterpret_cast<const TI *>(&ry[k]);
-#pragma unroll
-                    for (int i = 0; i < V; ++i) {
-                        x[i] = to_f32(ex[i]);
-                        y[i] = to_f32(ey[i]);
-                    }
-                    ewise_math<V, sizeof(TO) == 2>(op, scalar, x, y, r);
-                    store_vec<TO, V>(out + oo, r);
-                }
-            }
-            return;
-        }
-    }
     constexpr int U = 4;
     for (int64_t u0 = tid; u0 < n_units; u0 += nth * U) {
         int64_t oo[U], o0[U], o1[U];
