@@ -34,7 +34,8 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
                     reinterpret_cast<uint4 *>(P.comm[q] + base + me * slot_bytes)[i] = v;
             }
         } else {
-            T *dst = reinterpret_cast<T *>(P.arena[me] + a.buf_off[me]);
+            T *dst = a.sum_out ? reinterpret_cast<T *>(a.sum_out) : reinterpret_cast<T *>(P.arena[me] + a.buf_off[me]);
+            const T *res = reinterpret_cast<const T *>(a.residual);
             for (int64_t i = tid; i < nv; i += nth) {
                 float acc[V];
 #pragma unroll
@@ -44,6 +45,12 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
                     load_vec<T, V>(reinterpret_cast<const T *>(P.comm[me] + base + q * slot_bytes) + i * V, x);
 #pragma unroll
                     for (int k = 0; k < V; ++k) acc[k] += x[k];
+                }
+                if (res) {  // the sum is rounded where the all_reduce would have stored it, then the residual is added
+                    float r[V];
+                    load_vec<T, V>(res + i * V, r);
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[k] = to_f32(from_f32<T>(acc[k])) + r[k];
                 }
                 store_vec<T, V>(dst + i * V, acc);
             }

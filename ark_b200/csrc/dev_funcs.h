@@ -18,7 +18,7 @@ __device__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P,
 __device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                               DeviceState *st, int stage_idx, unsigned long long spin_limit);
 __device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
-__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem);
+__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no);
 __device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P);

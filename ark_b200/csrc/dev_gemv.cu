@@ -18,6 +18,7 @@
 // When K is split into ranges (splits > 1) the fp32 partials go to
 // ws[range][m][n] and the split-K sum stage that follows adds them in range
 // order, applies the activation and rounds (deterministic).
+#include "dev_comm.cuh"
 #include "dev_common.cuh"
 #include "dev_funcs.h"
 
@@ -121,14 +122,33 @@ __device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, i
     }
 }
 
+// Where a folded one-shot all_reduce wants the result: slot [rank] of every rank's staging buffer (dense [M, N]).
+struct PushTo {
+    char *slot[kMaxPeers];  // this rank's slot on every rank, null when nothing is pushed
+    int nranks;
+};
+__device__ __forceinline__ PushTo push_targets(const GemvArgs &a, const LaunchParams &P, unsigned long long iter_no) {
+    PushTo t;
+    t.nranks = 0;
+    if (a.push_ord > 0) {
+        const uint64_t par = (iter_no * (unsigned long long)a.push_per_iter + (unsigned long long)(a.push_ord - 1)) & 1;
+        const uint64_t base = kCommDataOff + par * a.push_stage_bytes + (uint64_t)P.rank * (a.push_stage_bytes / kMaxPeers);
+        t.nranks = P.nranks;
+        for (int q = 0; q < kMaxPeers; ++q) t.slot[q] = q < P.nranks ? P.comm[q] + base : nullptr;
+    }
+    return t;
+}
+
 template <typename T>
-__device__ __forceinline__ void emit(const GemvArgs &a, int split, int m, int n, float v) {
+__device__ __forceinline__ void emit(const GemvArgs &a, const PushTo &push, int split, int m, int n, float v) {
     if (a.splits > 1) {
         a.ws[((int64_t)split * a.M + m) * a.N + n] = v;
     } else {
         v = apply_act_fast(a.act, v);
         if (a.residual) v = to_f32(from_f32<T>(v)) + to_f32(reinterpret_cast<const T *>(a.residual)[(int64_t)m * a.ldo + n]);
-        reinterpret_cast<T *>(a.out)[(int64_t)m * a.ldo + n] = from_f32<T>(v);
+        const T r = from_f32<T>(v);
+        reinterpret_cast<T *>(a.out)[(int64_t)m * a.ldo + n] = r;
+        for (int q = 0; q < push.nranks; ++q) reinterpret_cast<T *>(push.slot[q])[(int64_t)m * a.N + n] = r;
     }
 }
 
@@ -139,7 +159,7 @@ __device__ __forceinline__ void emit(const GemvArgs &a, int split, int m, int n,
 // when the matrix has rows to spare, few rows and more vectors per row when it has not. Two register buffers
 // alternate: the loads of step t+1 are issued before step t is consumed, across row groups too.
 template <typename T, int M, int RW, int VC>
-__device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs) {
+__device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs, const PushTo &push) {
     const int cps = a.ctas_per_split;
     const int split = p / cps, q = p % cps;
     if (split >= a.splits) return;
@@ -209,7 +229,7 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     const float sum = warp_sum(acc[r][m]);
-                    if (lane == 0 && m < rows_m && c.r0 + r < row_hi) emit<T>(a, split, m, c.r0 + r, sum);
+                    if (lane == 0 && m < rows_m && c.r0 + r < row_hi) emit<T>(a, push, split, m, c.r0 + r, sum);
                     acc[r][m] = 0.0f;
                 }
         }
@@ -242,7 +262,7 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
 // of the range U at a time (two register buffers alternating as above) and writes its sums itself,
 // so warps never wait for one another. All of x sits in shared memory as 16-bit values.
 template <typename T, int M, int U>
-__device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs) {
+__device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs, const PushTo &push) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int rows_m = a.M;
@@ -316,42 +336,43 @@ __device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs) {
         for (int m = 0; m < M; ++m) {
             if (m < rows_m) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) emit<T>(a, split, m, col + j, acc[m][j]);
+                for (int j = 0; j < 8; ++j) emit<T>(a, push, split, m, col + j, acc[m][j]);
             }
         }
     }
 }
 
 template <typename T>
-__device__ void gemv_typed(const GemvArgs &a, int p, int P, char *smem) {
+__device__ void gemv_typed(const GemvArgs &a, int p, int P, char *smem, const PushTo &push) {
     if (a.w_is_nk) {
         float4 *xs = reinterpret_cast<float4 *>(smem);
         if (a.M == 1) {
             switch (a.rows_together) {
-                case 8: gemv_nk<T, 1, 8, 1>(a, p, P, xs); break;
-                case 4: gemv_nk<T, 1, 4, 2>(a, p, P, xs); break;
-                case 2: gemv_nk<T, 1, 2, 4>(a, p, P, xs); break;
-                default: gemv_nk<T, 1, 1, 8>(a, p, P, xs); break;
+                case 8: gemv_nk<T, 1, 8, 1>(a, p, P, xs, push); break;
+                case 4: gemv_nk<T, 1, 4, 2>(a, p, P, xs, push); break;
+                case 2: gemv_nk<T, 1, 2, 4>(a, p, P, xs, push); break;
+                default: gemv_nk<T, 1, 1, 8>(a, p, P, xs, push); break;
             }
         } else {
             switch (a.rows_together) {
-                case 4: gemv_nk<T, 2, 4, 1>(a, p, P, xs); break;
-                case 2: gemv_nk<T, 2, 2, 2>(a, p, P, xs); break;
-                default: gemv_nk<T, 2, 1, 4>(a, p, P, xs); break;
+                case 4: gemv_nk<T, 2, 4, 1>(a, p, P, xs, push); break;
+                case 2: gemv_nk<T, 2, 2, 2>(a, p, P, xs, push); break;
+                default: gemv_nk<T, 2, 1, 4>(a, p, P, xs, push); break;
             }
         }
     } else {
         T *xs = reinterpret_cast<T *>(smem);
-        if (a.M == 1) gemv_kn<T, 1, 8>(a, p, P, xs);
-        else gemv_kn<T, 2, 4>(a, p, P, xs);
+        if (a.M == 1) gemv_kn<T, 1, 8>(a, p, P, xs, push);
+        else gemv_kn<T, 2, 4>(a, p, P, xs, push);
     }
 }
 
 }  // namespace
 
-__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem) {
-    if (a.dtype == DT_BF16) gemv_typed<__nv_bfloat16>(a, p, P, smem);
-    else gemv_typed<__half>(a, p, P, smem);
+__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no) {
+    const PushTo push = push_targets(a, LP, iter_no);
+    if (a.dtype == DT_BF16) gemv_typed<__nv_bfloat16>(a, p, P, smem, push);
+    else gemv_typed<__half>(a, p, P, smem, push);
 }
 
 }  // namespace arkb

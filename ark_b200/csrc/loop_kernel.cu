@@ -74,7 +74,7 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
                 if constexpr (PAIR) run_gemm_pair(S.gm, &P.stages[s].gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
                 else run_gemm(S.gm, &P.stages[s].gm, p, Pn, smem, pipe, ctl, P.state, s, P.spin_limit);
                 break;
-            case SK_GEMV: run_gemv(S.gv, p, Pn, smem); break;
+            case SK_GEMV: run_gemv(S.gv, p, Pn, smem, P, iter_no); break;
             case SK_DECODE_ATTN: run_decode_attn(S.da, p, Pn, smem); break;
             case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
             case SK_SPLITK_REDUCE: run_splitk_reduce(S.sr, p, Pn); break;

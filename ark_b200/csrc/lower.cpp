@@ -404,7 +404,39 @@ struct Lowerer {
         float eps = 1e-5f;
         const TensorDesc *residual = nullptr; // added to the matmul's result
         const TensorDesc *out = nullptr;      // result tensor of the last folded operator
+        int push_ord = -1;                    // >= 0: ordinal of the one-shot all_reduce whose push this matmul does
     };
+    bool gemv_pushed = false;  // set by lower_matmul when the push of a one-shot all_reduce was folded in
+
+    // an AllReduce the engine runs one-shot (every rank pushes its tensor into every rank's staging slots)
+    bool all_reduce_is_one_shot(const OpDesc &op) const {
+        if (op.type != "AllReduce" || op.results.empty() || env.nranks < 2) return false;
+        const TensorDesc &t = op.results[0];
+        const size_t bytes = (size_t)t.nelems() * dtype_size(t.dtype);
+        const std::string algo = op.config.is_object() && op.config.contains("Algo") ? op.config.at("Algo").as_string() : "auto";
+        return t.dense() && ((algo == "oneshot") || (algo == "auto" && bytes <= 256 * 1024)) && bytes <= lay.comm_stage_bytes / kMaxPeers;
+    }
+
+    // ops[j] is a one-shot AllReduce and ops[j+1] the Add of its sum with a dense tensor of the same shape: the Add
+    const OpDesc *add_after_all_reduce(const TaskInfo &ti, size_t j) const {
+        if (j + 1 >= ti.ops.size() || !all_reduce_is_one_shot(ti.ops[j])) return nullptr;
+        const OpDesc &ar = ti.ops[j], &nx = ti.ops[j + 1];
+        if (nx.type != "Add" || nx.reads.size() != 2 || nx.results.empty()) return nullptr;
+        const TensorDesc &t = ar.results[0];
+        const bool first = nx.reads[0].id == t.id, second = nx.reads[1].id == t.id;
+        if (first == second) return nullptr;
+        const TensorDesc &other = first ? nx.reads[1] : nx.reads[0];
+        if (!other.dense() || !nx.results[0].dense() || other.shape4() != t.shape4() || nx.results[0].shape4() != t.shape4() ||
+            other.dtype != t.dtype || nx.results[0].dtype != t.dtype)
+            return nullptr;
+        for (auto &tk : plan.task_infos)  // the bare sum must not be used elsewhere
+            for (auto &o : tk.ops) {
+                if (&o == &nx || &o == &ar) continue;
+                for (auto &rd : o.reads)
+                    if (rd.buffer_id == t.buffer_id) return nullptr;
+            }
+        return &nx;
+    }
 
     static bool gemv_wanted() {
         const char *e = getenv("ARKB_GEMV");
@@ -579,11 +611,18 @@ struct Lowerer {
                 const int act_final = g.act;
                 if (g.splits > 1) g.act = ACT_NONE;
                 if (g.residual && act_final != ACT_NONE) throw Error(E_INTERNAL, "residual and activation folded into one matmul");
+                gemv_pushed = false;
+                if (gf && gf->push_ord >= 0 && g.splits == 1 && ldc == N) {
+                    g.push_ord = gf->push_ord + 1;
+                    g.push_stage_bytes = lay.comm_stage_bytes;
+                    gemv_pushed = true;
+                }
                 const GemvArgs gv = g;
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
                             std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : "") +
                             (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : "") + (gv.residual ? " +residual" : "") +
+                            (gv.push_ord ? " ->all_reduce slots" : "") +
                             (gv.act ? " act=" + std::to_string(gv.act) : ""));
                 if (gv.splits > 1) {
                     emit_sync(proc);
@@ -978,7 +1017,9 @@ struct Lowerer {
     }
 
     // fused: the partials already sit in this rank's staging slots (put there by every rank's Matmul epilogue)
-    void lower_all_reduce(const OpDesc &op, const Range &proc, bool fused = false) {
+    // pushed: the matmul before it (same task) has already stored its result into every rank's staging slot
+    // add: the Add of the same task that consumes the sum (one-shot only): folded into the reduce phase
+    void lower_all_reduce(const OpDesc &op, const Range &proc, bool fused = false, bool pushed = false, const OpDesc *add = nullptr) {
         if (env.nranks == 1) return;
         const TensorDesc &t = op.results.at(0);
         if (!t.dense()) throw Error(E_UNSUPPORTED, "AllReduce: dense tensors only");
@@ -1024,13 +1065,19 @@ struct Lowerer {
             a.stage_bytes = lay.comm_stage_bytes;
             a.ord = oneshot_ord++;
             a.phase = 0;
-            push(s, "AllReduce " + op.name + " one-shot push bytes=" + std::to_string(bytes));
+            if (!pushed) push(s, "AllReduce " + op.name + " one-shot push bytes=" + std::to_string(bytes));
             emit_sync(proc);
             emit_peersync(proc, "all_reduce data pushed");
             emit_sync(proc);
             Stage s2 = s;
             s2.ar.phase = 1;
-            push(s2, "AllReduce " + op.name + " one-shot reduce");
+            if (add) {
+                const TensorDesc &other = add->reads[0].id == t.id ? add->reads[1] : add->reads[0];
+                s2.ar.residual = tensor_ptr(other);
+                s2.ar.sum_out = tensor_ptr(add->results.at(0));
+                if (!aligned16(s2.ar.residual) || !aligned16(s2.ar.sum_out)) throw Error(E_UNSUPPORTED, "AllReduce + Add: operands must be 16-byte aligned");
+            }
+            push(s2, "AllReduce " + op.name + " one-shot reduce" + (add ? " +residual" : ""));
         } else {
             a.algo = 1;
             emit_sync(proc);
@@ -1131,11 +1178,26 @@ struct Lowerer {
                             }
                         }
                     }
-                    if (gf.pro != GP_NONE || gf.residual) {
+                    // Matmul -> one-shot AllReduce of its result (in place): the matmul stores into the staging slots itself
+                    const OpDesc *ar = nullptr;
+                    if (act < 0 && !gf.residual && last + 1 < ti.ops.size()) {
+                        const OpDesc &nx = ti.ops[last + 1];
+                        if (all_reduce_is_one_shot(nx) && !nx.reads.empty() && nx.reads[0].id == m.results[0].id &&
+                            nx.results[0].buffer_id == m.results[0].buffer_id) {
+                            ar = &nx;
+                            gf.push_ord = oneshot_ord;
+                        }
+                    }
+                    if (gf.pro != GP_NONE || gf.residual || ar) {
                         if (!first) emit_sync(proc);
                         lower_matmul(m, proc, tg, act, res_out, nullptr, &gf);
                         first = false;
                         i = last;
+                        if (ar) {
+                            const OpDesc *add = add_after_all_reduce(ti, i + 1);
+                            lower_all_reduce(*ar, proc, false, gemv_pushed, add);
+                            i += add ? 2 : 1;
+                        }
                         continue;
                     }
                 }
@@ -1156,6 +1218,15 @@ struct Lowerer {
                     (other_readers(op.results[0].buffer_id, &nx) == 0 || nx.results[0].buffer_id == op.results[0].buffer_id)) {
                     if (!first) emit_sync(proc);
                     lower_matmul(op, proc, tg, act, &nx.results[0]);
+                    first = false;
+                    ++i;
+                    continue;
+                }
+            }
+            if (op.type == "AllReduce") {
+                if (const OpDesc *add = add_after_all_reduce(ti, i)) {
+                    if (!first) emit_sync(proc);
+                    lower_all_reduce(op, proc, false, false, add);
                     first = false;
                     ++i;
                     continue;
@@ -1260,8 +1331,10 @@ struct Lowerer {
         }
         prog.n_sync_groups = (int)sync_ids.size();
         prog.oneshots_per_iter = oneshot_ord;
-        for (auto &s : prog.stages)
+        for (auto &s : prog.stages) {
             if (s.kind == SK_ALLREDUCE && s.ar.algo == 0) s.ar.per_iter = oneshot_ord;
+            if (s.kind == SK_GEMV && s.gv.push_ord > 0) s.gv.push_per_iter = oneshot_ord;
+        }
     }
 };
 

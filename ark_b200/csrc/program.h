@@ -180,6 +180,10 @@ struct GemvArgs {
     float pro_eps;
     int32_t pad;
     const void *residual;    // epilogue: y := act(x . W) + residual [M, N] (row pitch ldo); with k-ranges the sum stage adds it
+    // The one-shot all_reduce that follows in the same task: the result is also stored into slot [rank] of every rank's
+    // staging buffer (the all_reduce's own push stage and its barrier are then left out). push_ord = its ordinal + 1, 0: none.
+    int32_t push_ord, push_per_iter;
+    uint64_t push_stage_bytes;
 };
 enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2 };
 constexpr int kGemvMaxM = 2;
@@ -259,6 +263,10 @@ struct AllReduceArgs {
                               // (consecutive invocations alternate between two staging buffers)
     uint64_t stage_bytes;     // one-shot: bytes of one staging buffer (nranks slots); slots: bytes of one slot
     uint64_t stage_off;       // slots (algo 2): arena offset of this rank's staging slots, filled by the peers' matmul epilogues
+    // one-shot: the Add that consumes the sum in the same task, folded into the reduce phase:
+    // out := round(sum) + residual, stored to `sum_out` instead of the all_reduce's own tensor
+    const void *residual;
+    void *sum_out;
 };
 
 struct alignas(128) Stage {

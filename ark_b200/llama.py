@@ -92,13 +92,10 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
         raise ValueError("grouped-query attention needs 1 or n_heads KV heads per rank")
     o = ops.reshape(o if seq == 1 else ops.transpose(o, [0, 2, 1, 3]), [bt, hl * hd])
     if decode:
-        with PlannerContext(sync=False):
+        with PlannerContext(sync=False):                    # matmul [-> all_reduce] -> residual add: one task
             attn = ops.matmul(o, w["wo"], transpose_other=True)
             if p > 1:
                 attn = ops.all_reduce(attn, rank, p, output=attn)
-            else:
-                x1 = ops.add(attn, x)
-        if p > 1:
             x1 = ops.add(attn, x)
         with PlannerContext(sync=False):                    # the norm is recomputed per consumer: it costs one row
             gate = ops.silu(ops.matmul(ops.rmsnorm(x1, w["ffn_norm"], eps=cfg.norm_eps), w["w1"], transpose_other=True))
@@ -108,9 +105,7 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
             down = ops.matmul(ops.mul(gate, up), w["w2"], transpose_other=True)
             if p > 1:
                 down = ops.all_reduce(down, rank, p, output=down)
-            else:
-                return ops.add(down, x1)
-        return ops.add(x1, down)
+            return ops.add(down, x1)
     with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
         attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
         if p > 1:

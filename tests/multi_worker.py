@@ -133,6 +133,34 @@ def main():
     err = np.abs(got.astype(np.float32) - want.astype(np.float32))
     assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("llama layer", err.mean(), err.max())
 
+    # ---- the same layer, one token against a K/V cache (decode): the one-shot all_reduces ride on the weight-streaming
+    # matmuls (result stored straight into every rank's staging slots) and the residual adds on their sum stages ----
+    # 4 heads per rank so that every weight matrix keeps >= 512 columns per rank at any world size
+    cfg = LlamaConfig(dim=512 * world, n_heads=4 * world, n_kv_heads=4 * world, ffn_dim=1024 * world)
+    t_kv, hd = 256, cfg.head_dim
+    hl = cfg.n_heads // world
+    rng = np.random.default_rng(78)
+    ws = [make_weights(cfg, "fp16", world, rng) for _ in range(world)]
+    for r in range(1, world):
+        ws[r]["attn_norm"], ws[r]["ffn_norm"] = ws[0]["attn_norm"], ws[0]["ffn_norm"]
+    xd = O.to_storage(rng.normal(0, 1, (1, cfg.dim)).astype(np.float32), "fp16")
+    rope1 = O.to_storage(rope_table(1, hd, start=t_kv), "fp16")
+    kcs = [O.to_storage(rng.normal(0, 1, (1, hl, t_kv, hd)).astype(np.float32), "fp16") for _ in range(world)]
+    vcs = [O.to_storage(rng.normal(0, 1, (1, hl, t_kv, hd)).astype(np.float32), "fp16") for _ in range(world)]
+    fresh()
+    tw = layer_weights(cfg, ark.fp16, world)
+    tx, tr = ark.tensor([1, cfg.dim], ark.fp16), ark.tensor([1, 1, 1, hd], ark.fp16)
+    tk, tv = ark.tensor([1, hl, t_kv, hd], ark.fp16), ark.tensor([1, hl, t_kv, hd], ark.fp16)
+    ty = decoder_layer(tx, tw, cfg, 1, 1, rank, world, rope=tr, k_cache=tk, v_cache=tv)
+    text = ark.plan_dump(str(ark.Planner(local).plan()))
+    assert text.count("->all_reduce slots") == 2 and text.count("one-shot reduce +residual") == 2, text
+    feeds = {tx: xd, tr: rope1, tk: kcs[rank], tv: vcs[rank]}
+    feeds.update({tw[k]: ws[rank][k] for k in tw if k not in ("wk", "wv")})
+    (got,) = run([ty], feeds, iters=3)
+    want = layer(xd, ws, cfg, 1, 1, "fp16", rope=rope1, k_caches=kcs, v_caches=vcs)
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("llama decode layer", err.mean(), err.max())
+
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: multi-GPU checks passed")
