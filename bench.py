@@ -237,40 +237,72 @@ def main():
         return
     hx = torch.from_numpy(x.copy()).pin_memory()
     hy = torch.empty((tokens, D_MODEL), dtype=torch.float16).pin_memory()
-    ex2 = ark.Executor(local, 0, "bench_e2e", str(plan), loop_mode=True, allgather=allgather)
-    ex2.compile()
-    ex2.tensor_from_numpy(t1, w1)
-    ex2.tensor_from_numpy(t2, w2)
-    ex2.launch()
     nby = hx.numel() * 2
-
-    # End to end through the Executor API, host buffers in pinned memory: every step copies its X to the device and
-    # reads a result Y back. PCIe is full duplex, so the read of step i's Y and the write of step i+1's X are issued
-    # together (two host threads, one stream each; tensor_read / tensor_write block like the reference's). Every
-    # step's X write and Y read are inside the timed region.
     from concurrent.futures import ThreadPoolExecutor
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
     pool = ThreadPoolExecutor(2)
+    # End to end through the Executor API, host buffers in pinned memory: every step copies its X to the device and
+    # reads its Y back (tensor_write / tensor_read block like the reference's), all inside the timed region.
+    if world == 1:
+        # Two executors over the same plan (each with its own arena, weights loaded once) take the steps in turn from
+        # two host threads: while one computes, the other's result goes back and its next input comes in.
+        exs, hys, streams = [], [hy, torch.empty_like(hy).pin_memory()], [torch.cuda.Stream(), torch.cuda.Stream()]
+        for i in range(2):
+            e = ark.Executor(local, 0, f"bench_e2e{i}", str(plan), loop_mode=False)
+            e.compile()
+            e.tensor_from_numpy(t1, w1)
+            e.tensor_from_numpy(t2, w2)
+            e.launch()
+            exs.append(e)
 
-    def e2e_steps(n):
-        ex2.tensor_write(tx, hx.data_ptr(), nby, s_in.cuda_stream)
-        for i in range(n):
-            ex2.run(1)
-            ex2.wait()
-            rd = pool.submit(ex2.tensor_read, ty, hy.data_ptr(), nby, s_out.cuda_stream)
-            if i + 1 < n:
-                wr = pool.submit(ex2.tensor_write, tx, hx.data_ptr(), nby, s_in.cuda_stream)
-                wr.result()
-            rd.result()
+        def lane(i, n):
+            for _ in range(n):
+                exs[i].tensor_write(tx, hx.data_ptr(), nby, streams[i].cuda_stream)
+                exs[i].run(1)
+                exs[i].wait()
+                exs[i].tensor_read(ty, hys[i].data_ptr(), nby, streams[i].cuda_stream)
+
+        def e2e_steps(n):
+            jobs = [pool.submit(lane, 0, (n + 1) // 2), pool.submit(lane, 1, n // 2)]
+            for j in jobs:
+                j.result()
+
+        def e2e_close():
+            for e in exs:
+                e.stop()
+                e.destroy()
+    else:
+        # Tensor-parallel: one executor per rank (two would let the ranks pair up different kernels at the in-kernel
+        # barriers). PCIe is full duplex, so the read of step i's Y and the write of step i+1's X are issued together
+        # (two host threads, one stream each).
+        ex2 = ark.Executor(local, 0, "bench_e2e", str(plan), loop_mode=True, allgather=allgather)
+        ex2.compile()
+        ex2.tensor_from_numpy(t1, w1)
+        ex2.tensor_from_numpy(t2, w2)
+        ex2.launch()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+
+        def e2e_steps(n):
+            ex2.tensor_write(tx, hx.data_ptr(), nby, s_in.cuda_stream)
+            for i in range(n):
+                ex2.run(1)
+                ex2.wait()
+                rd = pool.submit(ex2.tensor_read, ty, hy.data_ptr(), nby, s_out.cuda_stream)
+                if i + 1 < n:
+                    wr = pool.submit(ex2.tensor_write, tx, hx.data_ptr(), nby, s_in.cuda_stream)
+                    wr.result()
+                rd.result()
+
+        def e2e_close():
+            ex2.stop()
+            ex2.destroy()
     e2e_steps(warm)
     if world > 1:
         torch.distributed.barrier(group=host_group)
     t0 = time.perf_counter()
     e2e_steps(args.steps)
     e2e_s = time.perf_counter() - t0
-    ex2.stop()
     checksum = float(hy.float().abs().mean())
-    ex2.destroy()
+    e2e_close()
     ex.destroy()
 
     if world > 1:
