@@ -193,6 +193,25 @@ def test_decode_layer_folds_small_operators_into_the_weight_streaming_matmuls():
     assert "Matmul(gemv)" not in text and text.count("RMSNorm") == 2 and "Softmax" in text
 
 
+def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
+    """With several ranks the small all_reduces of a decode layer take their input straight from the weight-streaming
+    matmul (no push stage) and add the residual in their sum stage."""
+    from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+    cfg = LlamaConfig(dim=4096, n_heads=32, n_kv_heads=32, ffn_dim=11008)
+    ark.init()
+    ark.set_rank(1)
+    ark.set_world_size(8)
+    x, rope = ark.tensor([1, 4096], ark.fp16), ark.tensor([1, 1, 1, 128], ark.fp16)
+    w = layer_weights(cfg, ark.fp16, 8)
+    kc, vc = ark.tensor([1, 4, 2048, 128], ark.fp16), ark.tensor([1, 4, 2048, 128], ark.fp16)
+    decoder_layer(x, w, cfg, 1, 1, 1, 8, rope=rope, k_cache=kc, v_cache=vc)
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    ark.set_rank(0)
+    ark.set_world_size(1)
+    assert text.count("->all_reduce slots") == 2 and text.count("one-shot reduce +residual") == 2
+    assert "one-shot push" not in text and " Add " not in text and text.count("peer barrier") == 2
+
+
 def test_naive_all_reduce_composition_matches_reference_structure():
     """Model::all_reduce of the reference: world_size-1 rounds of send/send_done/recv/add (ops_all_reduce.cpp:8-37)."""
     ark.init()
