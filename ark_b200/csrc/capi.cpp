@@ -158,6 +158,10 @@ arkb_status arkb_executor_set_wait_limit(arkb_executor *e, uint64_t nanoseconds)
     return guard([&] { ex(e)->set_spin_limit(nanoseconds); });
 }
 
+arkb_status arkb_executor_set_idle_limit(arkb_executor *e, uint64_t nanoseconds) {
+    return guard([&] { ex(e)->set_idle_limit(nanoseconds); });
+}
+
 arkb_status arkb_executor_stage_times(arkb_executor *e, int enable, uint64_t *out, size_t capacity, size_t *written,
                                       int *n_stages, int *grid) {
     return guard([&] {

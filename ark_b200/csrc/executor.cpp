@@ -7,7 +7,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
 #include <thread>
@@ -116,15 +118,17 @@ void Executor::init_memory() {
     CUDA_CHECK(cudaMemset(comm_, 0, comm_bytes_));
     CUDA_CHECK(cudaMalloc(&state_, sizeof(DeviceState)));
     CUDA_CHECK(cudaMemset(state_, 0, sizeof(DeviceState)));
-    CUDA_CHECK(cudaHostAlloc(&host_flags_, 2 * sizeof(int32_t), cudaHostAllocMapped));
+    CUDA_CHECK(cudaHostAlloc(&host_flags_, 4 * sizeof(int32_t), cudaHostAllocMapped));
     host_flags_[0] = 0;  // run flag
     host_flags_[1] = 0;  // status mirror
+    host_flags_[2] = host_flags_[3] = 0;  // iterations finished (64 bits)
     int32_t *dflags = nullptr;
     CUDA_CHECK(cudaHostGetDevicePointer(&dflags, host_flags_, 0));
     dev_flags_ = dflags;
     DeviceState init;
     std::memset(&init, 0, sizeof(init));
     init.host_status = dflags + 1;
+    init.host_iters = reinterpret_cast<volatile unsigned long long *>(dflags + 2);
     CUDA_CHECK(cudaMemcpy(state_, &init, sizeof(init), cudaMemcpyHostToDevice));
     for (int r = 0; r < kMaxPeers; ++r) peer_arena_[r] = peer_comm_[r] = nullptr;
     peer_arena_[me] = reinterpret_cast<char *>(arena_);
@@ -220,7 +224,8 @@ void Executor::fill_params(LaunchParams &P, int iters) const {
         P.comm[r] = peer_comm_[r];
     }
     P.spin_limit = spin_limit_ ? spin_limit_ : kDefaultSpinLimit;
-    P.idle_limit_ns = kDefaultIdleNs;
+    // serialised launches: the kernel serves the request that is already posted and leaves at once
+    P.idle_limit_ns = blocking_launch_ ? 0 : (idle_limit_ ? idle_limit_ : kDefaultIdleNs);
     P.stage_times = stage_times_on_ ? stage_times_ : nullptr;
 }
 
@@ -256,16 +261,63 @@ void Executor::launch_kernel(int iters) {
     ++n_launches_;
 }
 
+bool Executor::stream_idle() {
+    const cudaError_t q = cudaStreamQuery(stream_);
+    if (q == cudaSuccess) return true;
+    if (q != cudaErrorNotReady) throw Error(E_GPU, std::string("loop kernel failed: ") + cudaGetErrorString(q));
+    return false;
+}
+
+// Finds out whether kernel launches return before the kernel ends. An empty loop kernel that leaves after 2 ms
+// without work is launched: with ordinary launches it is still running when the call returns (it is then told to
+// leave through the run flag); with serialised launches (CUDA_LAUNCH_BLOCKING=1, a profiler attached) it has
+// already ended, and a resident kernel that waits for the host could never be served by it.
+void Executor::probe_blocking_launch() {
+    if (probed_) return;
+    probed_ = true;
+    host_flags_[0] = 0;
+    CUDA_CHECK(cudaMemsetAsync(state_, 0, sizeof(unsigned long long) * (kMaxSyncGroups + 1), stream_));
+    LaunchParams P;
+    fill_params(P, 0);
+    P.n_stages = 0;
+    P.loop_mode = 1;
+    P.idle_limit_ns = 2ull * 1000000;
+    P.stage_times = nullptr;
+    CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_));
+    blocking_launch_ = stream_idle();
+    if (!blocking_launch_) {
+        *reinterpret_cast<volatile int32_t *>(&host_flags_[0]) = -1;
+        CUDA_CHECK(cudaStreamSynchronize(stream_));
+    }
+    host_flags_[0] = 0;
+    host_flags_[1] = 0;
+    CUDA_CHECK(cudaMemsetAsync(reinterpret_cast<char *>(state_) + offsetof(DeviceState, status), 0, sizeof(int32_t), stream_));
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+}
+
+// Starts the resident kernel again after it left (idle exit). A posted run request stays posted: the new kernel
+// finds it in the run flag.
+void Executor::relaunch_loop_kernel() {
+    CUDA_CHECK(cudaStreamSynchronize(stream_));
+    host_flags_[1] = 0;
+    CUDA_CHECK(cudaMemsetAsync(reinterpret_cast<char *>(state_) + offsetof(DeviceState, status), 0, sizeof(int32_t), stream_));
+    launch_kernel(0);
+    kernel_live_ = !blocking_launch_;
+}
+
 void Executor::launch() {
     if (!compiled_) throw Error(E_USAGE, "Need to compile first before launch.");
     if (launched_) return;  // the reference ignores a second launch with a warning (api/executor_test.cpp:149-155)
     CUDA_CHECK(cudaSetDevice(device_id_));
     elapsed_ms_ = -1;
+    if (loop_mode_) probe_blocking_launch();
     CUDA_CHECK(cudaEventRecord(ev_start_, stream_));
     if (loop_mode_) {
         host_flags_[0] = 0;
-        launch_kernel(0);
-        kernel_live_ = true;
+        if (!blocking_launch_) {
+            launch_kernel(0);
+            kernel_live_ = true;
+        }
     }
     launched_ = true;
     stopped_ = false;
@@ -275,6 +327,7 @@ void Executor::check_status() {
     const int32_t st = *reinterpret_cast<volatile int32_t *>(&host_flags_[1]);
     if (st != ST_OK && st != ST_IDLE_EXIT) {
         arkb_status_snapshot snap = status();
+        iters_expected_ = snap.iterations;  // what did run; later requests count from here
         throw Error(E_GPU, "loop kernel gave up: status " + std::to_string(snap.code) + " at stage " +
                                std::to_string(snap.stage) + " (CTA " + std::to_string(snap.cta) + ")");
     }
@@ -285,26 +338,25 @@ void Executor::run(int iter) {
     if (iter <= 0) return;
     CUDA_CHECK(cudaSetDevice(device_id_));
     if (loop_mode_) {
-        volatile int32_t *flag = host_flags_;
-        // previous request must have been consumed (ark/api/executor.cpp:698-704)
-        while (*flag > 0) {
-            if (cudaStreamQuery(stream_) != cudaErrorNotReady) break;
-        }
+        // the previous request must have been consumed (ark/api/executor.cpp:698-704)
+        if (pending_) wait(-1);
         check_status();
-        if (!kernel_live_ || cudaStreamQuery(stream_) != cudaErrorNotReady) {
-            // the kernel left after a long idle period: bring it back
-            CUDA_CHECK(cudaStreamSynchronize(stream_));
-            host_flags_[1] = 0;
-            CUDA_CHECK(cudaMemsetAsync(reinterpret_cast<char *>(state_) + offsetof(DeviceState, status), 0, sizeof(int32_t), stream_));
-            *flag = 0;
-            launch_kernel(0);
-            kernel_live_ = true;
-        }
+        volatile int32_t *flag = host_flags_;
+        // The request is posted before anything else: a kernel started from here on finds it, and a resident
+        // kernel that leaves (idle exit) at this very moment is noticed by wait(), which starts it again.
+        iters_expected_ += (unsigned long long)iter;
+        pending_ = true;
         *flag = iter;
+        if (blocking_launch_) {
+            relaunch_loop_kernel();  // returns when the request is done and the kernel has left again
+        } else if (!kernel_live_ || stream_idle()) {
+            relaunch_loop_kernel();
+        }
     } else {
+        iters_expected_ += (unsigned long long)iter;
+        pending_ = true;
         launch_kernel(iter);
     }
-    pending_ = true;
 }
 
 void Executor::wait(int64_t max_spin_count) {
@@ -313,29 +365,39 @@ void Executor::wait(int64_t max_spin_count) {
     if (loop_mode_) {
         volatile int32_t *flag = host_flags_;
         int64_t spins = 0;
+        int relaunches = 0;
+        const int64_t every = max_spin_count >= 0 ? std::max<int64_t>(max_spin_count, 1) : 0x100000;
         while (*flag > 0) {
-            if (max_spin_count >= 0 && ++spins > max_spin_count) {
-                spins = 0;
-                cudaError_t q = cudaStreamQuery(stream_);
-                if (q == cudaSuccess) {  // kernel ended (abort path): stop waiting
-                    kernel_live_ = false;
-                    break;
-                }
-                if (q != cudaErrorNotReady) throw Error(E_GPU, std::string("loop kernel failed: ") + cudaGetErrorString(q));
-            } else if (max_spin_count < 0 && (++spins & 0xFFFFF) == 0) {
-                cudaError_t q = cudaStreamQuery(stream_);
-                if (q == cudaSuccess) {
-                    kernel_live_ = false;
-                    break;
-                }
-                if (q != cudaErrorNotReady) throw Error(E_GPU, std::string("loop kernel failed: ") + cudaGetErrorString(q));
+            if (++spins < every) continue;
+            spins = 0;
+            if (!stream_idle()) continue;
+            if (*flag <= 0) break;  // finished between the two looks
+            // The kernel is gone and the request is still posted. Either a bounded wait gave up (the status says
+            // so), or the kernel left for lack of work just before the request arrived: start it again, twice at most.
+            kernel_live_ = false;
+            const int32_t st = *reinterpret_cast<volatile int32_t *>(&host_flags_[1]);
+            if (st != ST_OK && st != ST_IDLE_EXIT) break;
+            if (relaunches++ >= 2) {
+                *flag = 0;
+                pending_ = false;
+                iters_expected_ = *reinterpret_cast<volatile unsigned long long *>(&host_flags_[2]);
+                throw Error(E_GPU, "run request was not picked up by the loop kernel (relaunched twice)");
             }
+            relaunch_loop_kernel();
         }
     } else {
         CUDA_CHECK(cudaStreamSynchronize(stream_));
     }
     pending_ = false;
+    if (*reinterpret_cast<volatile int32_t *>(&host_flags_[0]) > 0) host_flags_[0] = 0;  // abort path: withdraw the request
     check_status();
+    // never report success for iterations that did not run
+    const unsigned long long done = *reinterpret_cast<volatile unsigned long long *>(&host_flags_[2]);
+    if (done != iters_expected_) {
+        const unsigned long long want = iters_expected_;
+        iters_expected_ = done;
+        throw Error(E_GPU, "loop kernel finished " + std::to_string(done) + " iterations, " + std::to_string(want) + " were requested");
+    }
 }
 
 float Executor::stop(int64_t max_spin_count) {
@@ -348,12 +410,13 @@ float Executor::stop(int64_t max_spin_count) {
         err = e.what();
     }
     if (loop_mode_ && kernel_live_) {
-        host_flags_[0] = -1;
+        *reinterpret_cast<volatile int32_t *>(&host_flags_[0]) = -1;
     }
     CUDA_CHECK(cudaEventRecord(ev_stop_, stream_));
     CUDA_CHECK(cudaStreamSynchronize(stream_));
     kernel_live_ = false;
     host_flags_[0] = 0;
+    if (host_flags_[1] == ST_IDLE_EXIT) host_flags_[1] = 0;
     CUDA_CHECK(cudaEventElapsedTime(&elapsed_ms_, ev_start_, ev_stop_));
     stopped_ = true;
     launched_ = false;

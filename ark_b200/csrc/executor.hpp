@@ -40,6 +40,7 @@ class Executor {
     void *stream() const { return stream_; }
     const Program &program() const { return program_; }
     void set_spin_limit(unsigned long long v) { spin_limit_ = v; }
+    void set_idle_limit(unsigned long long v) { idle_limit_ = v; }
     void enable_stage_times(bool on);
     // copies the [n_stages][grid][2] time stamps of the last iteration; returns the number of words written
     size_t read_stage_times(unsigned long long *out, size_t capacity, int *n_stages, int *grid);
@@ -49,7 +50,10 @@ class Executor {
     void init_memory();
     void fill_params(LaunchParams &P, int iters) const;
     void launch_kernel(int iters);
+    void relaunch_loop_kernel();
+    void probe_blocking_launch();
     void check_status();
+    bool stream_idle();
     char *tensor_base(const TensorDesc &t) const;
 
     int device_id_;
@@ -68,14 +72,18 @@ class Executor {
     bool stage_times_on_ = false;
     void *arena_ = nullptr, *comm_ = nullptr, *state_ = nullptr, *stages_dev_ = nullptr;
     size_t arena_bytes_ = 0, comm_bytes_ = 0;
-    int32_t *host_flags_ = nullptr;          // [0] run flag, [1] status mirror (mapped host memory)
+    int32_t *host_flags_ = nullptr;          // [0] run flag, [1] status mirror, [2..3] 64-bit count of finished iterations (mapped host memory)
     volatile int32_t *dev_flags_ = nullptr;  // device view of host_flags_
     char *peer_arena_[kMaxPeers], *peer_comm_[kMaxPeers];
     bool compiled_ = false, launched_ = false, stopped_ = false, destroyed_ = false, pending_ = false;
     bool kernel_live_ = false;
     float elapsed_ms_ = -1;
     int n_launches_ = 0;
-    unsigned long long spin_limit_ = 0;
+    unsigned long long spin_limit_ = 0, idle_limit_ = 0;
+    // Kernel launches that only return when the kernel has ended (CUDA_LAUNCH_BLOCKING, a profiler): a resident
+    // loop kernel cannot be kept, so every run request gets a launch of its own that leaves when the request is done.
+    bool blocking_launch_ = false, probed_ = false;
+    unsigned long long iters_expected_ = 0;  // iterations requested over the executor's life
 };
 
 void plan_check(const std::string &plan_json, int *n_stages, size_t *arena_bytes, int *n_processors);

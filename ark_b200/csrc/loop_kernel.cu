@@ -9,6 +9,8 @@
 #include "dev_gemm.cuh"
 #include "loop_kernel.h"
 
+#include <cstring>
+
 namespace arkb {
 
 __device__ __forceinline__ bool in_range(const Stage &S, int cta, int &p, int &Pn) {
@@ -170,7 +172,8 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
             __syncthreads();
             iters = ctl.run_iters;
             if (iters < 0) {
-                if (iters == -2 && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(&st->status, ST_OK, ST_IDLE_EXIT);
+                // (an idle limit of 0 means one launch per request: leaving is then the normal end, not worth a note)
+                if (iters == -2 && P.idle_limit_ns != 0 && blockIdx.x == 0 && threadIdx.x == 0) atomicCAS(&st->status, ST_OK, ST_IDLE_EXIT);
                 break;
             }
         }
@@ -186,6 +189,7 @@ __device__ __forceinline__ void loop_main(const LaunchParams &P) {
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             st->t_end = globaltimer();
             st->iter_total = iter_no;
+            if (st->host_iters) *st->host_iters = iter_no;  // the host checks this count against what it asked for
             __threadfence_system();
             if (P.loop_mode) *P.run_flag = 0;
         }
@@ -232,9 +236,28 @@ cudaError_t loop_kernel_prepare() {
                                 (int)loop_kernel_smem_bytes());
 }
 
+// The grid barriers need every CTA resident at once, so the launch is cooperative: it is refused
+// (cudaErrorCooperativeLaunchTooLarge) or queued behind other work instead of deadlocking when the grid
+// does not fit beside what already runs on the device.
 cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream) {
-    if (P.pair_mode) arkb_loop_kernel_pair<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
-    else arkb_loop_kernel<<<grid, kThreads, loop_kernel_smem_bytes(), stream>>>(P);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = loop_kernel_smem_bytes();
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = P.pair_mode ? cudaLaunchKernelEx(&cfg, arkb_loop_kernel_pair, P) : cudaLaunchKernelEx(&cfg, arkb_loop_kernel, P);
+    if (e == cudaErrorNotSupported || e == cudaErrorInvalidValue) {
+        // a driver that cannot combine the attribute with this kernel: plain launch (the caller keeps the grid <= #SMs)
+        (void)cudaGetLastError();
+        cfg.numAttrs = 0;
+        e = P.pair_mode ? cudaLaunchKernelEx(&cfg, arkb_loop_kernel_pair, P) : cudaLaunchKernelEx(&cfg, arkb_loop_kernel, P);
+    }
+    return e;
 }
 }  // namespace arkb

@@ -1195,6 +1195,9 @@ struct Lowerer {
                         i = last;
                         if (ar) {
                             const OpDesc *add = add_after_all_reduce(ti, i + 1);
+                            // push not folded (K was split, or the result has a row pitch): the push stage reads what the
+                            // matmul / its sum stage wrote with another split over the CTAs, so it waits for all of them
+                            if (!gemv_pushed) emit_sync(proc);
                             lower_all_reduce(*ar, proc, false, gemv_pushed, add);
                             i += add ? 2 : 1;
                         }

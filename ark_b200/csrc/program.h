@@ -316,6 +316,7 @@ struct DeviceState {
     int32_t run_iters;                           // iterations requested by the current run (broadcast)
     unsigned long long t_begin, t_end;           // %globaltimer stamps around the last run
     volatile int32_t *host_status;               // host-mapped mirror of `status`
+    volatile unsigned long long *host_iters;     // host-mapped mirror of `iter_total`, written before the run flag is cleared
 };
 
 // Per-rank communication block, mapped into every peer. It sits at the start

@@ -58,6 +58,7 @@ def lib():
         L.arkb_executor_stream.argtypes = [vp, ctypes.POINTER(vp)]
         L.arkb_executor_program_dump.argtypes = [vp, ctypes.POINTER(cp)]
         L.arkb_executor_set_wait_limit.argtypes = [vp, ctypes.c_uint64]
+        L.arkb_executor_set_idle_limit.argtypes = [vp, ctypes.c_uint64]
         if hasattr(L, "arkb_executor_stage_times"):  # absent from older builds of the library
             L.arkb_executor_stage_times.argtypes = [vp, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t),
                                                     ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
@@ -201,6 +202,10 @@ class Executor:
     def set_wait_limit(self, nanoseconds):
         """Bound of every device-side wait; a wait that runs out makes wait() raise GpuError."""
         _check(lib().arkb_executor_set_wait_limit(self._h, int(nanoseconds)))
+
+    def set_idle_limit(self, nanoseconds):
+        """How long the resident loop kernel stays without a run request before it returns (0: default, 20 s)."""
+        _check(lib().arkb_executor_set_idle_limit(self._h, int(nanoseconds)))
 
     def enable_stage_times(self, on=True):
         """Diagnostic (after compile, before launch): every CTA records when it enters and leaves each stage."""

@@ -94,11 +94,16 @@ arkb_status arkb_executor_create(int device_id, void *stream, const char *name, 
 /* Executor::compile (executor.hpp:46): lowers the plan to the stage program,
  * allocates and zero-fills the arena, maps peers, uploads the program. */
 arkb_status arkb_executor_compile(arkb_executor *e);
-/* Executor::launch (executor.hpp:49): starts the loop kernel (loop mode) and records the start event. */
+/* Executor::launch (executor.hpp:49): starts the loop kernel (loop mode) and records the start event.
+ * When kernel launches only return once the kernel has ended (CUDA_LAUNCH_BLOCKING=1, a profiler
+ * attached; found out with a 2 ms probe launch) no resident kernel is kept: every run() then launches a
+ * kernel that serves that request and leaves. */
 arkb_status arkb_executor_launch(arkb_executor *e);
 /* Executor::run(iter) (executor.hpp:52). */
 arkb_status arkb_executor_run(arkb_executor *e, int iter);
-/* Executor::wait(max_spin_count) (executor.hpp:55); a device-side timeout comes back as ARKB_GPU_ERROR. */
+/* Executor::wait(max_spin_count) (executor.hpp:55); a device-side timeout comes back as ARKB_GPU_ERROR,
+ * and so does a request whose iterations did not all run: the count of finished iterations the kernel
+ * reports is compared with what was asked for, and a request that met no kernel is served by a relaunch. */
 arkb_status arkb_executor_wait(arkb_executor *e, int64_t max_spin_count);
 /* Executor::stop(max_spin_count) (executor.hpp:61): returns milliseconds between launch and stop. */
 arkb_status arkb_executor_stop(arkb_executor *e, int64_t max_spin_count, float *elapsed_msec);
@@ -131,6 +136,12 @@ arkb_status arkb_executor_program_dump(arkb_executor *e, const char **text);
  * launch. Stands in for the MaxSpinCount template argument of the reference's
  * comm::wait (ark/include/kernels/comm.h:197-206), which its ops leave at -1. */
 arkb_status arkb_executor_set_wait_limit(arkb_executor *e, uint64_t nanoseconds);
+/* How long, in nanoseconds, the resident loop kernel stays on the GPU without a run request before it
+ * returns (0 restores the default of 20 s). The next run() starts it again and wait() notices a request
+ * that arrived just as the kernel left, so the limit only trades GPU occupancy against relaunch cost.
+ * Takes effect at the next launch. The reference's loop kernel has no such limit: it spins on the flag
+ * until stop() (ark/include/kernels/kernel_template.in:40-69). */
+arkb_status arkb_executor_set_idle_limit(arkb_executor *e, uint64_t nanoseconds);
 /* Diagnostic: per-stage, per-CTA time stamps. enable = 1 / 0 switches the recording on / off (after
  * compile, before launch; -1 leaves it as it is). When it is on, every CTA notes the GPU's nanosecond
  * timer on entering and leaving each stage; `out` receives the stamps of the last finished iteration

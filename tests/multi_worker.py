@@ -67,6 +67,23 @@ def main():
     (got,) = run([out], {t: np.full(8192, rank + 1, np.float16)}, iters=1)
     assert np.all(got == np.float16(world * (world + 1) / 2)), "closed-form all_reduce"
 
+    # ---- weight-streaming matmul whose K is cut into ranges, then the one-shot all_reduce of the same task: the push
+    # stage follows the sum stage after a barrier (it splits the tensor over the CTAs differently) ----
+    rng = np.random.default_rng(31)
+    xs = [O.to_storage(rng.normal(0, 1, (1, 8192)).astype(np.float32), "fp16") for _ in range(world)]
+    wk = [O.to_storage(rng.normal(0, 0.02, (8192, 1024)).astype(np.float32), "fp16") for _ in range(world)]
+    fresh()
+    tx, tw = ark.tensor([1, 8192], ark.fp16), ark.tensor([8192, 1024], ark.fp16)
+    with ark.PlannerContext(sync=False):
+        ty = ark.matmul(tx, tw)
+        ty = ark.all_reduce(ty, rank, world, output=ty)
+    text = ark.plan_dump(str(ark.Planner(local).plan()))
+    assert "split-K sum" in text and "one-shot push" in text, text
+    (got,) = run([ty], {tx: xs[rank], tw: wk[rank]}, iters=3)
+    want = O.all_reduce([O.matmul(xs[r], wk[r], "fp16") for r in range(world)], "fp16")
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert err.max() <= 1e-2 * max(1.0, float(np.abs(want.astype(np.float32)).max())), ("split-K matmul + all_reduce", err.max())
+
     # ---- send / recv ring: every rank sends its tensor to rank+1 ----
     fresh()
     src = ark.tensor([4, 1024], ark.fp16)

@@ -1,5 +1,5 @@
-"""Multi-GPU parity (needs >= 2 GPUs on the node; skipped otherwise): launches
-tests/multi_worker.py with one process per GPU."""
+"""Multi-rank parity: launches tests/multi_worker.py with one process per GPU (needs >= 2 GPUs on the node; skipped
+otherwise), and the bounded-wait check of tests/timeout_worker.py (two ranks; runs on one GPU too)."""
 import os
 import subprocess
 import sys
@@ -29,3 +29,20 @@ def test_multi_gpu_collectives_and_tp_ffn(world):
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert p.stdout.count("multi-GPU checks passed") == world
+
+
+@pytest.mark.parametrize("same_device", [True, False])
+def test_peer_wait_runs_out_and_reports(same_device):
+    """A Recv whose peer never runs: the wait gives up after 50 ms, wait() raises GpuError with status 3, destroy is
+    clean and the next executor on that GPU passes a parity case."""
+    if not same_device and _ngpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    if _ngpus() < 1:
+        pytest.skip("needs a GPU")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ARKB_SAME_DEVICE="1" if same_device else "0")
+    port = 29650 + int(same_device)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "timeout_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert p.stdout.count("bounded-wait checks passed") == 2

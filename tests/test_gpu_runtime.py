@@ -1,7 +1,13 @@
 """GPU tests of the executor protocol through the C ABI: loop mode, repeated
 runs, error behaviour pinned by the reference's executor tests
-(ark/api/executor_test.cpp:47-59, 149-155, 171-183) and the bounded-wait
-status path."""
+(ark/api/executor_test.cpp:47-59, 149-155, 171-183), the idle exit of the
+resident kernel and serialised kernel launches. (The bounded-wait status path
+is in tests/test_gpu_multi.py: it needs a peer that stays silent.)"""
+import os
+import subprocess
+import sys
+import time
+
 import numpy as np
 import pytest
 
@@ -59,6 +65,74 @@ def test_relaunch_after_stop():
         assert np.all(ex.tensor_to_numpy(o) == expect)
     ex.destroy()
     assert ex.destroyed()
+
+
+def test_idle_exit_is_followed_by_a_relaunch():
+    """The resident kernel leaves after the idle limit; the next request brings it back and every requested
+    iteration runs (the count the kernel reports is checked by wait())."""
+    t, o = build_chain()
+    ex = ark.Executor(0, 0, "t", str(ark.Planner(0).plan()), True)
+    ex.set_wait_limit(3_000_000_000)
+    ex.set_idle_limit(30_000_000)  # 30 ms
+    ex.compile()
+    ex.tensor_from_numpy(t, np.zeros((64, 1024), np.float16))
+    ex.launch()
+    time.sleep(0.3)
+    ex.run(2)
+    ex.wait()
+    time.sleep(0.3)
+    ex.run(1)
+    ex.wait()
+    ex.run(4)  # back to back: the kernel is still there
+    ex.wait()
+    got = ex.tensor_to_numpy(o)
+    ex.stop()
+    st = ex.status()
+    ex.destroy()
+    assert np.all(got == 7.0)
+    assert st["iterations"] == 7 and st["n_launches"] >= 3 and st["code"] in (0, 4)
+
+
+_BLOCKING = r"""
+import sys
+sys.path.insert(0, sys.argv[1])
+import numpy as np
+import __graft_entry__ as g
+import ark_b200 as ark
+g.smoke()  # loop mode: FFN block + rmsnorm against the oracle
+ark.init()
+t = ark.tensor([64, 1024], ark.fp16)
+o = ark.add(t, 1.0, t)
+ex = ark.Executor(0, 0, "t", str(ark.Planner(0).plan()), True)
+ex.set_idle_limit(50_000_000)
+ex.compile()
+ex.tensor_from_numpy(t, np.zeros((64, 1024), np.float16))
+ex.launch()
+ex.run(3); ex.wait()
+ex.run(2); ex.wait()
+got = ex.tensor_to_numpy(o)
+ex.stop()
+st = ex.status()
+ex.destroy()
+assert np.all(got == 5.0), got[0, :4]
+assert st["iterations"] == 5 and st["code"] == 0, st
+print("blocking ok", st["n_launches"])
+"""
+
+
+def test_serialised_launches_give_right_numbers(tmp_path):
+    """With CUDA_LAUNCH_BLOCKING=1 (as under a profiler) a launch only returns when the kernel has ended, so a
+    resident kernel can never see a request posted after its launch: the executor notices and serves every
+    run() with a launch of its own. Right numbers, never a silent success without work."""
+    script = tmp_path / "blocking.py"
+    script.write_text(_BLOCKING)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_LAUNCH_BLOCKING="1")
+    t0 = time.perf_counter()
+    p = subprocess.run([sys.executable, str(script), root], capture_output=True, text=True, timeout=600, env=env)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
+    assert "smoke ok" in p.stdout and "blocking ok" in p.stdout
+    assert time.perf_counter() - t0 < 120
 
 
 def test_usage_errors():

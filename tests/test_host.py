@@ -212,6 +212,23 @@ def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
     assert "one-shot push" not in text and " Add " not in text and text.count("peer barrier") == 2
 
 
+def test_unfolded_one_shot_push_waits_for_the_split_k_sum():
+    """A weight-streaming matmul whose K is cut into ranges cannot store into the all_reduce slots itself: the sum
+    stage writes the result and the push stage, which splits the tensor differently over the CTAs, follows a barrier."""
+    ark.init()
+    ark.set_rank(0)
+    ark.set_world_size(2)
+    x, w = ark.tensor([1, 8192], ark.fp16), ark.tensor([8192, 1024], ark.fp16)  # W:[K,N], K is split
+    with ark.PlannerContext(sync=False):
+        y = ark.matmul(x, w)
+        y = ark.all_reduce(y, 0, 2, output=y)
+    lines = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan())).splitlines()
+    ark.set_world_size(1)
+    idx = {k: next(i for i, l in enumerate(lines) if k in l) for k in ("split-K sum", "one-shot push")}
+    assert idx["one-shot push"] == idx["split-K sum"] + 2 and "sync group" in lines[idx["split-K sum"] + 1]
+    assert "->all_reduce slots" not in "\n".join(lines)
+
+
 def test_naive_all_reduce_composition_matches_reference_structure():
     """Model::all_reduce of the reference: world_size-1 rounds of send/send_done/recv/add (ops_all_reduce.cpp:8-37)."""
     ark.init()
