@@ -542,7 +542,7 @@ void plan_check(const std::string &plan_json, int *n_stages, size_t *arena_bytes
         env.comm[r] = reinterpret_cast<char *>(((uintptr_t)(r + 1) << 40) + ((uintptr_t)1 << 39));
     }
     env.encode_tmap = encode_tmap_check;
-    env.num_sm = 148;
+    env.num_sm = kDefaultNumSm;  // no device to ask
     env.workspace = reinterpret_cast<char *>((uintptr_t)1 << 44);
     // every rank is assumed to publish the same records as this one (SPMD plans)
     std::vector<std::vector<TagRecord>> records(plan.world_size, lay.published);

@@ -22,6 +22,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <string>
 
 #include "ark_b200.h"
@@ -40,7 +41,10 @@ constexpr int kMaxDevices = 64;
 // symbol look-up, never an address to hand to a kernel.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-float *g_scratch_addr[kMaxDevices] = {};  // per-device address of g_static_scratch, filled on first use
+// per-device address of g_static_scratch and SM count, filled on first use (atomics: the first calls on a device
+// may come from several host threads; they all store the same values)
+std::atomic<float *> g_scratch_addr[kMaxDevices];
+std::atomic<int> g_num_sm[kMaxDevices];
 
 __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
 __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -118,16 +122,21 @@ extern "C" arkb_status arkb_matvec_splitk_static(const void *x, const void *w, v
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail(ARKB_GPU_ERROR, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
     if (dev < 0 || dev >= kMaxDevices) return fail(ARKB_UNSUPPORTED, "device ordinal out of range");
-    if (!g_scratch_addr[dev]) {
+    if (!g_scratch_addr[dev].load(std::memory_order_acquire)) {
         // once per device, with that device current: the device address of the static array
         float *p = nullptr;
         e = cudaGetSymbolAddress((void **)&p, g_static_scratch);
         if (e != cudaSuccess || !p) return fail(ARKB_GPU_ERROR, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-        g_scratch_addr[dev] = p;
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms < 1) return fail(ARKB_GPU_ERROR, std::string("cudaDeviceGetAttribute: ") + cudaGetErrorString(e));
+        g_num_sm[dev].store(sms, std::memory_order_relaxed);
+        g_scratch_addr[dev].store(p, std::memory_order_release);
     }
+    const int num_sm = g_num_sm[dev].load(std::memory_order_relaxed);
     // k-ranges: enough warps to fill the GPU, each range a multiple of 256 elements (one 16-byte load per lane)
     int splits = 1;
-    const long long want_warps = 148LL * 32;
+    const long long want_warps = (long long)num_sm * 32;
     while (splits < 64 && (long long)n * splits < want_warps && k / (splits * 2) >= 256) splits *= 2;
     int kper = ((k + splits - 1) / splits + 255) / 256 * 256;
     splits = (k + kper - 1) / kper;
@@ -135,17 +144,17 @@ extern "C" arkb_status arkb_matvec_splitk_static(const void *x, const void *w, v
     if (need > kStaticScratchBytes)
         return fail(ARKB_INVALID_USAGE, "problem needs " + std::to_string(need) + " bytes of scratch, the static array holds " +
                                             std::to_string(kStaticScratchBytes) + " (splits * m * n * 4 must fit)");
-    float *scratch = g_scratch_addr[dev];
+    float *scratch = g_scratch_addr[dev].load(std::memory_order_relaxed);
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const long long items = (long long)n * splits;
-    const int blocks = (int)((items + 7) / 8 < 148 * 8 ? (items + 7) / 8 : 148 * 8);
+    const int blocks = (int)((items + 7) / 8 < num_sm * 8 ? (items + 7) / 8 : num_sm * 8);
     if (dtype == 1)
         matvec_partials<__half, kMaxRows><<<blocks, 256, 0, st>>>((const __half *)x, (const __half *)w, scratch, m, n, k, splits, kper);
     else
         matvec_partials<__nv_bfloat16, kMaxRows><<<blocks, 256, 0, st>>>((const __nv_bfloat16 *)x, (const __nv_bfloat16 *)w, scratch,
                                                                           m, n, k, splits, kper);
     const long long total = (long long)m * n;
-    const int fb = (int)((total + 255) / 256 < 148 * 4 ? (total + 255) / 256 : 148 * 4);
+    const int fb = (int)((total + 255) / 256 < num_sm * 4 ? (total + 255) / 256 : num_sm * 4);
     if (dtype == 1) matvec_finish<__half><<<fb, 256, 0, st>>>(scratch, (__half *)y, m, n, splits);
     else matvec_finish<__nv_bfloat16><<<fb, 256, 0, st>>>(scratch, (__nv_bfloat16 *)y, m, n, splits);
     e = cudaGetLastError();

@@ -149,12 +149,14 @@ struct TmapSpec {
 // Encodes a 128-byte-swizzled tiled tensor map; throws on failure.
 using TmapEncoder = std::function<void(CUtensorMap *out, const TmapSpec &spec)>;
 
+constexpr int kDefaultNumSm = 148;  // SMs of a B200: what plan checks assume on a host with no device to ask
+
 struct LowerEnv {
     int rank = 0, nranks = 1;
     char *arena[kMaxPeers] = {};  // arena base of every rank in this process's address space
     char *comm[kMaxPeers] = {};
     TmapEncoder encode_tmap;
-    int num_sm = 148;
+    int num_sm = kDefaultNumSm;
     bool allow_pair = true;  // let matmul tiles span CTA pairs (tcgen05 cta_group::2) when the plan permits
     char *workspace = nullptr;  // scratch for split-K partials (sized by a first lowering pass: Program::workspace_bytes)
 };

@@ -241,11 +241,14 @@ def test_naive_all_reduce_composition_matches_reference_structure():
     ark.set_world_size(1)
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/examples/tutorial"), reason="reference checkout not present")
+from tests.conftest import reference_dir  # noqa: E402
+
+
+@pytest.mark.skipif(reference_dir() is None, reason="reference checkout not present")
 def test_reference_tutorial_plans_load_unmodified():
     """Plan files written for the reference (CUDA_80, 108 processors) lower as they are."""
     n = 0
-    for f in sorted(glob.glob("/root/reference/examples/tutorial/*.json")):
+    for f in sorted(glob.glob(os.path.join(reference_dir(), "examples", "tutorial", "*.json"))):
         s = open(f).read()
         if '"TaskInfos"' not in s:
             continue

@@ -49,6 +49,27 @@ def test_static_scratch_matvec_matches_engine_twice(dt):
         assert_matmul_close(got, O.matmul(x, w, dt, trans_b=True), dt, f"static-scratch matvec vs oracle, call {call}")
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 1000, 1096), (3, 64, 8), (16, 264, 520)])
+def test_static_scratch_matvec_ragged_k_and_full_rows(m, n, k):
+    """K that is not a multiple of the 256-element lane stride (the tail of the last k-range, a K below one
+    stride) and all 16 accumulator rows, on random data, against the engine and the oracle."""
+    import torch
+    dt = "fp16"
+    rng = np.random.default_rng(73 + m + k)
+    x, w = rand(rng, (m, k), dt, -1.0, 1.0), rand(rng, (n, k), dt, -0.05, 0.05)
+    dx = torch.from_numpy(x.view(np.int16)).cuda().view(torch.float16)
+    dw = torch.from_numpy(w.view(np.int16)).cuda().view(torch.float16)
+    dy = torch.empty((m, n), dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    for call in range(2):
+        dy.zero_()
+        matvec_splitk_static(dx.data_ptr(), dw.data_ptr(), dy.data_ptr(), m, n, k, dt)
+        torch.cuda.synchronize()
+        got = dy.view(torch.int16).cpu().numpy().view(O.NP[dt])
+        assert_matmul_close(got, O.matmul(x, w, dt, trans_b=True), dt, f"static-scratch matvec {m}x{n}x{k} vs oracle, call {call}")
+    assert_matmul_close(got, engine_matmul(x, w, dt), dt, f"static-scratch matvec {m}x{n}x{k} vs engine")
+
+
 def test_static_scratch_rejects_oversized_and_bad_arguments():
     import torch
     x = torch.zeros((16, 512), dtype=torch.float16, device="cuda")
