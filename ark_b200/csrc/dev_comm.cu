@@ -88,6 +88,124 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
     }
 }
 
+// ---- packets ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t packet_flag(uint32_t flag, unsigned long long iter_no) {
+    return (uint32_t)((iter_no & 0xffffffull) << 8) | (flag & 0xffu);  // iter_no >= 1: never 0, the value of untouched memory
+}
+__device__ __forceinline__ void st_packet(void *p, uint32_t d0, uint32_t d1, uint32_t f) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(f), "r"(d1), "r"(f) : "memory");
+}
+// Polls one packet until both flag words carry `f`; false when the wait limit ran out.
+__device__ __forceinline__ bool ld_packet(const void *p, uint32_t f, unsigned long long limit, uint32_t &d0, uint32_t &d1) {
+    unsigned long long spins = 0, t0 = 0;
+    for (;;) {
+        uint32_t a, b, c, d;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "l"(p) : "memory");
+        if (b == f && d == f) {
+            d0 = a;
+            d1 = c;
+            return true;
+        }
+        if ((++spins & 255) == 0) {
+            const unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > limit) return false;
+        }
+        if (spins > 16) __nanosleep(64);
+    }
+}
+
+__device__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage) {
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)Pn * kThreads;
+    const int64_t n = a.payload_bytes / 8;
+    const uint32_t f = packet_flag(a.flag, iter_no);
+    if (!a.get) {
+        const uint2 *src = reinterpret_cast<const uint2 *>(a.src);
+        uint4 *dst = reinterpret_cast<uint4 *>(a.dst);
+        for (int64_t i = tid; i < n; i += nth) {
+            const uint2 v = src[i];
+            st_packet(dst + i, v.x, v.y, f);
+        }
+        return;
+    }
+    const uint4 *src = reinterpret_cast<const uint4 *>(a.src);
+    uint2 *dst = reinterpret_cast<uint2 *>(a.dst);
+    bool ok = true;
+    for (int64_t i = tid; i < n && ok; i += nth) {
+        uint2 v;
+        ok = ld_packet(src + i, f, P.spin_limit, v.x, v.y);
+        if (ok) dst[i] = v;
+    }
+    if (!ok) {
+        ctl->abort = 1;
+        report(P.state, ST_PEER_TIMEOUT, stage);
+    }
+}
+
+template <typename T>
+__device__ void packet_reduce_typed(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
+                                    int stage) {
+    const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)Pn * kThreads;
+    const T *in = reinterpret_cast<const T *>(a.in);
+    T *out = reinterpret_cast<T *>(a.out);
+    if (a.packets) {
+        constexpr int V = 8 / sizeof(T);  // elements in one packet's payload
+        const int64_t n = a.nelem / V;
+        const uint32_t f = packet_flag(a.flag, iter_no);
+        const uint4 *scratch = reinterpret_cast<const uint4 *>(a.scratch);
+        bool ok = true;
+        for (int64_t i = tid; i < n && ok; i += nth) {
+            float acc[V];
+            load_vec<T, V>(in + i * V, acc);
+            for (int q = 0; q < a.npeers && ok; ++q) {
+                union { uint2 u; T e[V]; } v;
+                ok = ld_packet(scratch + (int64_t)q * n + i, f, P.spin_limit, v.u.x, v.u.y);
+#pragma unroll
+                for (int k = 0; k < V; ++k) acc[k] += to_f32(v.e[k]);
+            }
+            if (!ok) break;
+            union { uint2 u; T e[V]; } o;
+#pragma unroll
+            for (int k = 0; k < V; ++k) o.e[k] = from_f32<T>(acc[k]);
+            *reinterpret_cast<uint2 *>(out + i * V) = o.u;
+            for (int q = 0; q < a.npeers; ++q) st_packet(reinterpret_cast<uint4 *>(a.peer_out[q]) + i, o.u.x, o.u.y, f);
+        }
+        if (!ok) {
+            ctl->abort = 1;
+            report(P.state, ST_PEER_TIMEOUT, stage);
+        }
+        return;
+    }
+    constexpr int V = 16 / sizeof(T);
+    const int64_t n = a.nelem / V;
+    const T *scratch = reinterpret_cast<const T *>(a.scratch);
+    for (int64_t i = tid; i < n; i += nth) {
+        float acc[V];
+        load_vec<T, V>(in + i * V, acc);
+        for (int q = 0; q < a.npeers; ++q) {
+            float x[V];
+            load_vec<T, V>(scratch + (int64_t)q * a.nelem + i * V, x);
+#pragma unroll
+            for (int k = 0; k < V; ++k) acc[k] += x[k];
+        }
+        union { uint4 u; T e[V]; } o;
+#pragma unroll
+        for (int k = 0; k < V; ++k) o.e[k] = from_f32<T>(acc[k]);
+        reinterpret_cast<uint4 *>(out)[i] = o.u;
+        for (int q = 0; q < a.npeers; ++q) reinterpret_cast<uint4 *>(a.peer_out[q])[i] = o.u;
+    }
+}
+
+__device__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
+                                  int stage) {
+    switch (a.dtype) {
+        case DT_F32: packet_reduce_typed<float>(P, a, p, Pn, iter_no, ctl, stage); break;
+        case DT_F16: packet_reduce_typed<__half>(P, a, p, Pn, iter_no, ctl, stage); break;
+        case DT_BF16: packet_reduce_typed<__nv_bfloat16>(P, a, p, Pn, iter_no, ctl, stage); break;
+        default: break;
+    }
+}
+
 __device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn,
                                            unsigned long long iter_no) {
     switch (a.dtype) {

@@ -22,5 +22,8 @@ __device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const Laun
 __device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P);
+__device__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage);
+__device__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
+                                  int stage);
 __device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no);
 }  // namespace arkb

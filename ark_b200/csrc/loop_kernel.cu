@@ -90,6 +90,8 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
                     run_peersync(P, (iter_no - 1) * (unsigned long long)P.peersyncs_per_iter + S.ps.ord, ctl, s);
                 break;
             case SK_ALLREDUCE: run_allreduce(P, S.ar, p, Pn, iter_no); break;
+            case SK_PACKET: run_packet(P, S.pk, p, Pn, iter_no, ctl, s); break;
+            case SK_PACKET_REDUCE: run_packet_reduce(P, S.pr, p, Pn, iter_no, ctl, s); break;
             default: break;
         }
         if (stamp) {

@@ -1003,6 +1003,85 @@ struct Lowerer {
         push(s, "Recv " + op.name + " <- rank " + std::to_string(peer) + " ch " + std::to_string(s.wt.channel));
     }
 
+    // ---- packets (SendPacket / RecvPacket / RecvReduceSendPacket) and RecvReduceSend ----------------------
+    // ark/ops/ops_communication.cpp:171-560. Packet tensors are UINT8 views twice the size of their payload.
+    static int64_t dense_bytes(const TensorDesc &t, const char *what) {
+        if (!t.dense()) throw Error(E_UNSUPPORTED, std::string(what) + ": dense tensors only");
+        return t.nelems() * (int64_t)dtype_size(t.dtype);
+    }
+    void check_full(const OpDesc &op, const TaskGroup &tg) const {
+        if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, op.type + ": partial TaskRange is not supported");
+    }
+    uint32_t flag_of(const OpDesc &op) const { return op.has_arg("Flag") ? (uint32_t)op.arg_int("Flag") : 1u; }
+
+    void lower_send_packet(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        check_full(op, tg);
+        const TensorDesc &src = op.reads.at(0), &dst = op.writes.at(0);
+        const int peer = dst.buffer_rank;
+        if (peer < 0 || peer >= env.nranks || peer == env.rank) throw Error(E_MODEL, "SendPacket: invalid remote rank");
+        const int64_t payload = dense_bytes(src, "SendPacket");
+        if (dense_bytes(dst, "SendPacket") != 2 * payload) throw Error(E_MODEL, "SendPacket: the packet tensor must be twice the payload");
+        Stage s = new_stage(SK_PACKET, proc);
+        s.pk.dst = tensor_ptr(dst);
+        s.pk.src = tensor_ptr(src);
+        s.pk.payload_bytes = payload;
+        s.pk.flag = flag_of(op);
+        s.pk.get = 0;
+        if (payload % 8 || !aligned16(s.pk.dst) || (reinterpret_cast<uintptr_t>(s.pk.src) & 7))
+            throw Error(E_UNSUPPORTED, "SendPacket: payload must be a multiple of 8 bytes, 8-byte aligned, the packet buffer 16-byte aligned");
+        push(s, "SendPacket " + op.name + " -> rank " + std::to_string(peer) + " payload=" + std::to_string(payload));
+    }
+
+    void lower_recv_packet(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
+        check_full(op, tg);
+        const TensorDesc &scratch = op.reads.at(1), &out = op.writes.at(0);  // reads[0] only names the sender
+        const int64_t payload = dense_bytes(out, "RecvPacket");
+        if (dense_bytes(scratch, "RecvPacket") != 2 * payload) throw Error(E_MODEL, "RecvPacket: the packet tensor must be twice the payload");
+        Stage s = new_stage(SK_PACKET, proc);
+        s.pk.dst = tensor_ptr(out);
+        s.pk.src = tensor_ptr(scratch);
+        s.pk.payload_bytes = payload;
+        s.pk.flag = flag_of(op);
+        s.pk.get = 1;
+        if (payload % 8 || !aligned16(s.pk.src) || (reinterpret_cast<uintptr_t>(s.pk.dst) & 7))
+            throw Error(E_UNSUPPORTED, "RecvPacket: payload must be a multiple of 8 bytes, 8-byte aligned, the packet buffer 16-byte aligned");
+        push(s, "RecvPacket " + op.name + " <- rank " + std::to_string(op.reads.at(0).buffer_rank) + " payload=" + std::to_string(payload));
+    }
+
+    void lower_recv_reduce_send(const OpDesc &op, const Range &proc, const TaskGroup &tg, bool packets) {
+        check_full(op, tg);
+        const TensorDesc &in = op.reads.at(0), &scratch = op.reads.at(1), &out = op.writes.at(0);
+        const int npeers = (int)op.arg_int("NPeers");
+        if (npeers < 1 || npeers >= kMaxPeers || (int)op.writes.size() != npeers + 1)
+            throw Error(E_MODEL, op.type + ": one output tensor per peer expected");
+        if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16) || out.dtype != in.dtype)
+            throw Error(E_UNSUPPORTED, op.type + ": floating-point tensors of one type");
+        const int64_t bytes = dense_bytes(in, op.type.c_str());
+        if (dense_bytes(out, op.type.c_str()) != bytes) throw Error(E_MODEL, op.type + ": input and output sizes differ");
+        if (dense_bytes(scratch, op.type.c_str()) != bytes * npeers * (packets ? 2 : 1))
+            throw Error(E_MODEL, op.type + ": scratch must hold one shard per peer");
+        Stage s = new_stage(SK_PACKET_REDUCE, proc);
+        PacketReduceArgs &a = s.pr;
+        a.in = tensor_ptr(in);
+        a.out = tensor_ptr(out);
+        a.scratch = tensor_ptr(scratch);
+        a.nelem = in.nelems();
+        a.dtype = in.dtype;
+        a.npeers = npeers;
+        a.packets = packets ? 1 : 0;
+        a.flag = flag_of(op);
+        bool ok = aligned16(a.scratch) && bytes % (packets ? 8 : 16) == 0 &&
+                  (reinterpret_cast<uintptr_t>(a.in) & (packets ? 7 : 15)) == 0 && (reinterpret_cast<uintptr_t>(a.out) & (packets ? 7 : 15)) == 0;
+        for (int q = 0; q < npeers; ++q) {
+            const TensorDesc &po = op.writes[q + 1];
+            if (dense_bytes(po, op.type.c_str()) != bytes * (packets ? 2 : 1)) throw Error(E_MODEL, op.type + ": peer output size mismatch");
+            a.peer_out[q] = tensor_ptr(po);
+            ok = ok && aligned16(a.peer_out[q]);
+        }
+        if (!ok) throw Error(E_UNSUPPORTED, op.type + ": shards must be 16-byte aligned and a multiple of 16 bytes (8 with packets)");
+        push(s, op.type + " " + op.name + " peers=" + std::to_string(npeers) + " bytes=" + std::to_string(bytes) + (packets ? " packets" : ""));
+    }
+
     void emit_peersync(const Range &proc, const std::string &why) {
         Stage s = new_stage(SK_PEERSYNC, proc);
         s.ps.ord = ++prog.peersyncs_per_iter;
@@ -1106,6 +1185,10 @@ struct Lowerer {
         if (t == "Recv") return lower_recv(op, proc);
         if (t == "DeviceSync") return lower_device_sync(op, proc);
         if (t == "AllReduce") return lower_all_reduce(op, proc);
+        if (t == "SendPacket") return lower_send_packet(op, proc, tg);
+        if (t == "RecvPacket") return lower_recv_packet(op, proc, tg);
+        if (t == "RecvReduceSendPacket") return lower_recv_reduce_send(op, proc, tg, true);
+        if (t == "RecvReduceSend") return lower_recv_reduce_send(op, proc, tg, false);
         throw Error(E_UNSUPPORTED, "operator type not supported by this engine: " + t);
     }
 

@@ -323,8 +323,10 @@ void resolve_remote(const Plan &plan, Layout &lay, const std::vector<std::vector
                     found = true;
                 }
         }
-        if (!found) throw Error(E_PLAN, "rank " + std::to_string(r) + " published no buffer matching remote buffer " + std::to_string(b.id));
-        b.resolved = true;
+        // A stand-in no record matches stays without an address, as in the reference (ark/api/executor.cpp:376-392,
+        // 468-500: only tags a peer sent fill in offsets). Plans hold such buffers on purpose: the source tensor of a
+        // RecvPacket, or of a Recv with Wait=false, only names the sender. Using one as an operand is an error then.
+        b.resolved = found;
     }
     for (size_t r = 0; r < records.size(); ++r)
         for (auto &rec : records[r])

@@ -38,6 +38,8 @@ enum StageKind : int32_t {
     SK_SIGNAL = 13,    // raise a channel flag on a peer (after the put's data is complete)
     SK_SPLITK_REDUCE = 14,  // sum the fp32 partials of a split-K matmul, add bias, activate, round, store
     SK_DECODE_ATTN = 15,    // one query row per head against a K/V cache: scores, softmax and output in one pass over the cache
+    SK_PACKET = 16,         // flag-carrying packets: local data -> a peer's packet buffer, or local packet buffer -> local data
+    SK_PACKET_REDUCE = 17,  // own shard + the shards the peers sent (packets or plain) -> local output and every peer's output
 };
 
 enum EwiseOp : int32_t {
@@ -246,6 +248,32 @@ struct PeerSyncArgs {
     int32_t ord;         // 1-based ordinal of this cross-rank barrier within an iteration
     int32_t pad;
 };
+// Packets (the reference's SendPacket / RecvPacket, ark/include/kernels/comm.h:376-396): every 8 bytes of payload
+// travel as one 16-byte store {d0, flag, d1, flag}, so data and "it has arrived" are the same write and the receiver
+// needs neither a signal nor a barrier: it polls the flag words. A packet buffer is twice the size of its payload
+// (as the reference sizes them, ark/ops/ops_communication.cpp:183-187). The flag a plan gives is combined with the
+// iteration number, so packets of an earlier iteration are never taken for new ones.
+struct PacketArgs {
+    void *dst;               // get == 0: the peer's packet buffer; get == 1: local data
+    const void *src;         // get == 0: local data; get == 1: local packet buffer
+    int64_t payload_bytes;   // a multiple of 8
+    uint32_t flag;
+    int32_t get;
+};
+// The reduce step of the reference's two all_reduce compositions (read_reduce_and_write, comm.h:398-428):
+// out = in + sum of the `npeers` shards the peers put into `scratch` (slot q = q-th peer in rank order), stored
+// locally and into every peer's output. packets == 1: scratch slots and peer outputs are packet buffers;
+// packets == 0: plain data (a DeviceSync before and after orders it).
+struct PacketReduceArgs {
+    void *out;
+    const void *in;
+    const void *scratch;
+    void *peer_out[kMaxPeers];
+    int64_t nelem;
+    int32_t dtype, npeers, packets;
+    uint32_t flag;
+};
+
 // Data phase of all_reduce over a dense tensor that sits at the same arena
 // offset on every rank.
 //   algo 0 (one-shot, small): phase 0 pushes the local tensor into slot
@@ -292,6 +320,8 @@ struct alignas(128) Stage {
         PeerSyncArgs ps;
         SignalArgs sg;
         AllReduceArgs ar;
+        PacketArgs pk;
+        PacketReduceArgs pr;
     };
 };
 

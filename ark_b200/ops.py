@@ -438,6 +438,141 @@ def device_sync(input, rank, rank_num, name="device_sync"):
     return res
 
 
+def _nbytes(t):
+    return t.nelems() * t.dtype.nbytes
+
+
+def send_packet(input, remote_rank, tag, flag, output=None, name="send_packet"):
+    """ark::Model::send_packet (ark/ops/ops_communication.cpp:171-197, 612-619): `input` goes to `output`, a UINT8
+    packet tensor on `remote_rank` twice the size of the data (payload and flag words travel together)."""
+    m = _m()
+    if output is None:
+        output = Tensor(m, dt.uint8, Buffer(m, remote_rank), [_nbytes(input) * 2])
+    elif output.buffer.rank != remote_rank:
+        raise ModelError(f"invalid buffer rank: {output.buffer.rank}, expected: {remote_rank}")
+    output.buffer.tag_recv(-1, tag)
+    res = _result_of(output)
+    m.add_op("SendPacket", name, [input], [output], [res], {"Flag": int(flag)})
+    return res
+
+
+def recv_packet(output, remote_rank, tag, flag, scratch=None, name="recv_packet"):
+    """ark::Model::recv_packet (ops_communication.cpp:262-292, 621-628): waits for the packets `remote_rank` wrote into
+    the local packet tensor `scratch` and unpacks them into `output`."""
+    m = _m()
+    if scratch is None:
+        scratch = Tensor(m, dt.uint8, Buffer(m, output.buffer.rank), [_nbytes(output) * 2])
+    elif scratch.buffer.rank not in (-1, output.buffer.rank, m.rank):
+        raise ModelError(f"invalid buffer rank: {scratch.buffer.rank}")
+    sender = Tensor(m, output.dtype, Buffer(m, remote_rank), output.shape)  # names the sender only
+    scratch.buffer.tag_recv(remote_rank, tag)
+    res = _result_of(output)
+    m.add_op("RecvPacket", name, [sender, scratch], [output], [res], {"Flag": int(flag)})
+    return res
+
+
+def _recv_reduce_send(type_, input, remote_ranks, recv_tag, output_tag, flag, output, peer_outputs, scratch, name):
+    m = _m()
+    n = len(remote_ranks)
+    packets = flag is not None
+    if scratch is None:
+        if packets:
+            scratch = Tensor(m, dt.uint8, Buffer(m, m.rank), [_nbytes(input) * 2 * n])
+        else:
+            scratch = Tensor(m, input.dtype, Buffer(m, m.rank), [input.nelems() * n])
+    elif scratch.buffer.rank not in (-1, m.rank):
+        raise ModelError(f"invalid buffer rank: {scratch.buffer.rank}, expected: {m.rank}")
+    if output is None:
+        output = Tensor(m, input.dtype, Buffer(m, m.rank), input.shape, input.strides, input.offsets, input.padded_shape)
+    if not peer_outputs:
+        if packets:
+            peer_outputs = [Tensor(m, dt.uint8, Buffer(m, r), [_nbytes(input) * 2]) for r in remote_ranks]
+        else:
+            peer_outputs = [Tensor(m, input.dtype, Buffer(m, r), input.shape, input.strides, input.offsets, input.padded_shape)
+                            for r in remote_ranks]
+    for r, po in zip(remote_ranks, peer_outputs):
+        scratch.buffer.tag_recv(r, recv_tag)
+        po.buffer.tag_recv(-1, output_tag)
+    res = _result_of(output)
+    args = {"NPeers": n, "Rank": int(m.rank)}
+    if packets:
+        args["Flag"] = int(flag)
+    m.add_op(type_, name, [input, scratch], [output] + list(peer_outputs), [res], args)
+    return res
+
+
+def recv_reduce_send_packet(input, remote_ranks, recv_tag, output_tag, flag, output=None, peer_outputs=None, scratch=None,
+                            name="recv_reduce_send_packet"):
+    """ark::Model::recv_reduce_send_packet (ops_communication.cpp:353-399, 630-661): sums `input` with the packets the
+    peers sent into `scratch`, stores the sum in `output` and sends it, as packets, to every peer's output tensor."""
+    return _recv_reduce_send("RecvReduceSendPacket", input, list(remote_ranks), recv_tag, output_tag, int(flag), output,
+                             peer_outputs, scratch, name)
+
+
+def recv_reduce_send(input, remote_ranks, recv_tag, output_tag, output=None, peer_outputs=None, scratch=None,
+                     name="recv_reduce_send"):
+    """ark::Model::recv_reduce_send (ops_communication.cpp:455-500, 663-692): the same step on plain data; a
+    device_sync before it says that the peers' shards have arrived."""
+    return _recv_reduce_send("RecvReduceSend", input, list(remote_ranks), recv_tag, output_tag, None, output, peer_outputs,
+                             scratch, name)
+
+
+def all_reduce_packet(input, rank, rank_num, flag=1, output=None):
+    """The packet all_reduce the reference composes in its tests (ark/ops/ops_all_reduce_test.cpp:52-118): every rank
+    sends shard i to rank i as packets, reduces its own shard with the n-1 it received and sends the sum to every
+    peer, then unpacks the n-1 sums it receives. Scratch halves alternate with the parity of `flag`."""
+    from .planner import PlannerContext
+    m = _m()
+    tag_send_reduce, tag_output = m.unique_tag(), m.unique_tag()
+    if output is None:
+        output = tensor(input.shape, input.dtype, input.strides, input.offsets, input.padded_shape)
+    peers = [i for i in range(rank_num) if i != rank]
+    flat_in, flat_out = reshape(input, [input.nelems()]), reshape(output, [output.nelems()])
+    per = flat_in.nelems() // rank_num
+    nb = per * flat_in.dtype.nbytes
+    ins, outs = sharding(flat_in, 0, per), sharding(flat_out, 0, per)
+    npeer = rank_num - 1
+    scratch_off = 0 if flag % 2 == 0 else nb * npeer * 2
+    scratch_strides = [nb * 2 * npeer * 2]
+    for i in peers:
+        slot = rank - 1 if i < rank else rank
+        dst = tensor([nb * 2], dt.uint8, scratch_strides, [scratch_off + nb * slot * 2], [nb * 2], i)
+        send_packet(ins[i], i, tag_send_reduce, flag, dst)
+    scratch = tensor([nb * 2 * npeer], dt.uint8, scratch_strides, [scratch_off], [nb * 2 * npeer])
+    out_off = 0 if flag % 2 == 0 else nb * 2
+    peer_outs = [tensor([nb * 2], dt.uint8, [nb * 4], [out_off], [nb * 2], i) for i in peers]
+    deps = [recv_reduce_send_packet(ins[rank], peers, tag_send_reduce, tag_output, flag, outs[rank], peer_outs, scratch)]
+    for i in peers:
+        mine = tensor([nb * 2], dt.uint8, [nb * 4], [out_off], [nb * 2])
+        deps.append(recv_packet(outs[i], i, tag_output, flag, mine))
+    return identity(output, deps)
+
+
+def all_reduce_sm(input, rank, rank_num, output=None):
+    """The plain-data all_reduce of the reference's tests (ark/ops/ops_all_reduce_test.cpp:139-187): put shard i into
+    rank i's scratch, device_sync, recv_reduce_send of the own shard (sum stored into every rank's tensor),
+    device_sync. In place on `input` (as the reference test uses it)."""
+    from .planner import PlannerContext
+    m = _m()
+    send_tag, recv_tag = m.unique_tag(), m.unique_tag()
+    peers = [i for i in range(rank_num) if i != rank]
+    flat_in = reshape(input, [input.nelems()])
+    per = flat_in.nelems() // rank_num
+    npeer = rank_num - 1
+    ins = sharding(flat_in, 0, per)
+    with PlannerContext(config={"ChannelType": "Sm", "Signal": False}):
+        for i in peers:
+            slot = rank - 1 if i < rank else rank
+            dst = tensor([per], flat_in.dtype, [per * npeer], [per * slot], [per], i)
+            send(ins[i], i, send_tag, dst)
+    device_sync(flat_in, rank, rank_num)
+    recv_reduce_send(ins[rank], peers, send_tag, recv_tag, ins[rank])
+    with PlannerContext(config={"ChannelType": "Sm", "Wait": False}):
+        for i in peers:
+            recv(ins[i], i, recv_tag)
+    return device_sync(input, rank, rank_num)
+
+
 def all_reduce(input, rank, world_size, output=None, name="all_reduce", naive=False):
     """Sum over ranks. The reference composes world_size-1 rounds of
     send/send_done/recv/add (ark/ops/ops_all_reduce.cpp:8-37, kept as

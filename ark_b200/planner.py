@@ -121,6 +121,14 @@ def default_config(op, num_sm=DEFAULT_NUM_SM):
         return c
     if t == "AllReduce":
         return {"NumWarps": 16, "SramBytes": 0, "NumTasks": num_sm, "Algo": "auto"}
+    if t in ("SendPacket", "RecvPacket", "RecvReduceSendPacket", "RecvReduceSend"):
+        # ark/ops/ops_communication.cpp:226-246, 332-351, 434-453, 541-557 (1-warp tasks over 1 x 128 / 1 x 512 tiles)
+        sh = _dims4(op.results[0].shape)
+        ty = 512 if t == "SendPacket" else 128
+        c = {"NumWarps": 1, "SramBytes": 0, "Tile": [1, ty], "NumTasks": sh[0] * sh[1] * sh[2] * ((sh[3] + ty - 1) // ty)}
+        if t != "RecvReduceSend":
+            c["PacketType"] = "mscclpp::LL16Packet"
+        return c
     if t in ("RMSNorm", "LayerNorm", "Softmax"):
         sh = _dims4(op.reads[0].shape)
         return {"NumWarps": 1, "SramBytes": 0, "NumTasks": sh[0] * sh[1] * sh[2]}

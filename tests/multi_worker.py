@@ -84,6 +84,61 @@ def main():
     err = np.abs(got.astype(np.float32) - want.astype(np.float32))
     assert err.max() <= 1e-2 * max(1.0, float(np.abs(want.astype(np.float32)).max())), ("split-K matmul + all_reduce", err.max())
 
+    # ---- the reference's two all_reduce compositions (ops_all_reduce_test.cpp:52-187), built with the front end:
+    # packets (SendPacket / RecvReduceSendPacket / RecvPacket) and plain data (Send / DeviceSync / RecvReduceSend) ----
+    for kind, sizes in (("packet", (2048, 8192)), ("sm", (16 * 1024 * world, 256 * 1024 * world))):
+        for n in sizes:
+            for closed_form in (True, False):
+                if closed_form:  # rank r holds r + 1 everywhere: the sum is exact (ops_all_reduce_test.cpp:9-24)
+                    ins = [np.full(n, r + 1, np.float16) for r in range(world)]
+                else:
+                    ins = [O.to_storage(np.random.default_rng(2000 + r).uniform(-1, 1, n).astype(np.float32), "fp16") for r in range(world)]
+                fresh()
+                t = ark.tensor([n], ark.fp16)
+                out = ark.all_reduce_packet(t, rank, world, 1, t) if kind == "packet" else ark.all_reduce_sm(t, rank, world)
+                # 3 iterations in place would sum the sums: run one, then a second executor life is covered by the next case
+                (got,) = run([t], {t: ins[rank]}, iters=1)
+                want = O.all_reduce(ins, "fp16")
+                if closed_form:
+                    assert np.all(got == np.float16(world * (world + 1) / 2)), f"all_reduce_{kind} closed form n={n}"
+                else:  # own shard first, then the peers': same fp32 sums up to the last bit of the rounding
+                    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+                    assert err.max() <= 2.0 ** -9 * max(1.0, float(np.abs(want.astype(np.float32)).max())), (kind, n, err.max())
+    # packets over several iterations of one launch: out of place, so that every iteration sums the same inputs
+    fresh()
+    t = ark.tensor([4096], ark.fp16)
+    o = ark.tensor([4096], ark.fp16)
+    ark.all_reduce_packet(t, rank, world, 1, o)
+    (got,) = run([o], {t: np.full(4096, rank + 1, np.float16)}, iters=5)
+    assert np.all(got == np.float16(world * (world + 1) / 2)), "all_reduce_packet, 5 iterations"
+
+    # ---- the plan files the reference ships for 8 ranks, unmodified (examples/tutorial/allreduce-{sm,packet}) ----
+    if world == 8:
+        import gzip
+        import json
+        with gzip.open(os.path.join(ROOT, "tests", "golden", "ref_allreduce_plans.json.gz"), "rt") as f:
+            plans = json.load(f)
+        for d, nelem in (("allreduce-sm", 8 * 1024 * 1024), ("allreduce-packet", 8192)):
+            text = plans[f"{d}/plan_gpu{rank}.json"]
+            data = json.dumps({"Id": 0, "DataType": "FP16", "Shape": [nelem], "Strides": [nelem], "Offsets": [0],
+                               "PaddedShape": [nelem], "Buffer": {"Id": 0, "Rank": -1, "SendTags": [], "RecvTags": []}})
+            ex = ark.Executor(local, 0, d, text, True, allgather=ag)
+            ex.set_wait_limit(5_000_000_000)
+            ex.compile()
+            x = np.full(nelem, rank + 1, np.float16)
+            ex.tensor_write(data, x.ctypes.data, x.nbytes)
+            ex.barrier()
+            ex.launch()
+            ex.run(1)
+            ex.wait()
+            ex.barrier()  # every rank has finished: the sums the peers stored here have landed
+            got = np.zeros(nelem, np.float16)
+            ex.tensor_read(data, got.ctypes.data, got.nbytes)
+            ex.barrier()
+            ex.stop()
+            ex.destroy()
+            assert np.all(got == np.float16(36.0)), f"reference plan set {d} on rank {rank}: {np.unique(got)[:8]}"
+
     # ---- send / recv ring: every rank sends its tensor to rank+1 ----
     fresh()
     src = ark.tensor([4, 1024], ark.fp16)

@@ -248,14 +248,65 @@ from tests.conftest import reference_dir  # noqa: E402
 def test_reference_tutorial_plans_load_unmodified():
     """Plan files written for the reference (CUDA_80, 108 processors) lower as they are."""
     n = 0
-    for f in sorted(glob.glob(os.path.join(reference_dir(), "examples", "tutorial", "*.json"))):
+    for f in sorted(glob.glob(os.path.join(reference_dir(), "examples", "tutorial", "**", "*.json"), recursive=True)):
         s = open(f).read()
         if '"TaskInfos"' not in s:
             continue
         stages, arena, procs = ark.plan_check(s)
-        assert stages > 0 and procs == 108
+        assert stages > 0 and procs == json.loads(s)["NumProcessors"]
         n += 1
-    assert n >= 4
+    assert n >= 20  # 4 single-GPU tutorial plans + the two 8-rank all_reduce plan sets
+
+
+def ref_allreduce_plans():
+    import gzip
+    with gzip.open(os.path.join(ROOT, "tests", "golden", "ref_allreduce_plans.json.gz"), "rt") as f:
+        return json.load(f)
+
+
+def test_reference_all_reduce_plan_sets_lower_unmodified():
+    """The two 8-rank plan sets the reference ships (written for ROCM_942: 56 and 8 processors, LL8 packets) lower as
+    they are: plain-data shards + DeviceSync + RecvReduceSend, and SendPacket / RecvReduceSendPacket / RecvPacket."""
+    plans = ref_allreduce_plans()
+    assert len(plans) == 16
+    for name, text in plans.items():
+        stages, arena, procs = ark.plan_check(text)
+        dump = ark.plan_dump(text)
+        if name.startswith("allreduce-sm"):
+            assert procs == 56 and dump.count(" Send ") == 7 and "RecvReduceSend recv_reduce_send peers=7" in dump
+            assert "peer barrier #1 (DeviceSync" in dump
+        else:
+            assert procs == 8 and dump.count(") SendPacket") == 7 and dump.count(") RecvPacket") == 7
+            assert "RecvReduceSendPacket recv_reduce_send_packet peers=7 bytes=2048 packets" in dump
+            assert "sync group" not in dump  # senders, reducer and receivers run side by side on their own processors
+
+
+def test_packet_and_plain_all_reduce_compositions_plan_like_the_reference():
+    """ark.all_reduce_packet / ark.all_reduce_sm build the op sequences of ops_all_reduce_test.cpp:52-187."""
+    ark.init()
+    ark.set_rank(2)
+    ark.set_world_size(4)
+    t = ark.tensor([8192], ark.fp16)
+    ark.all_reduce_packet(t, 2, 4, 1, t)
+    types = [o.type for o in ark.Model.get_model().ops if not o.virtual]
+    assert types == ["SendPacket"] * 3 + ["RecvReduceSendPacket"] + ["RecvPacket"] * 3
+    ops = [o for o in ark.Model.get_model().ops if not o.virtual]
+    # flag 1: second half of the double-buffered scratch; rank 2 lands in slot 1 of ranks 0 and 1, slot 2 of rank 3
+    nb = 8192 // 4 * 2
+    assert [o.writes[0].offsets[0] for o in ops[:3]] == [nb * 3 * 2 + nb * 2 * 1, nb * 3 * 2 + nb * 2 * 1, nb * 3 * 2 + nb * 2 * 2]
+    assert ops[3].reads[1].shape == [nb * 2 * 3] and ops[3].reads[1].buffer.recv_tags == [[0, ops[3].reads[1].buffer.recv_tags[0][1]], [1, ops[3].reads[1].buffer.recv_tags[0][1]], [3, ops[3].reads[1].buffer.recv_tags[0][1]]]
+    ark.plan_check(str(ark.Planner(0, num_sm=148).plan()))
+    ark.init()
+    ark.set_rank(2)
+    ark.set_world_size(4)
+    t = ark.tensor([65536], ark.fp16)
+    ark.all_reduce_sm(t, 2, 4)
+    types = [o.type for o in ark.Model.get_model().ops if not o.virtual]
+    assert types == ["Send"] * 3 + ["DeviceSync", "RecvReduceSend"] + ["Recv"] * 3 + ["DeviceSync"]
+    dump = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    assert dump.count("peer barrier") == 2 and "signal" not in dump
+    ark.set_rank(0)
+    ark.set_world_size(1)
 
 
 _GLOO_WORKER = r"""
