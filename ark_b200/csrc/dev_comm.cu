@@ -4,9 +4,10 @@
 namespace arkb {
 
 // Dense byte copy local -> peer by all CTAs of the stage.
-__device__ void run_put(const PutArgs &a, int p, int P) {
+__device__ void run_put(const PutArgs &a, int p, int P, unsigned long long iter_no) {
     const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)P * kThreads;
-    const char *s = reinterpret_cast<const char *>(a.src);
+    const int64_t slot = a.iter_slots > 1 ? (int64_t)((iter_no - 1) % (unsigned long long)a.iter_slots) : 0;
+    const char *s = reinterpret_cast<const char *>(a.src) + slot * a.src_iter_bytes;
     char *d = reinterpret_cast<char *>(a.dst);
     if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d) | (uintptr_t)a.bytes) & 15) == 0) {
         const int64_t n = a.bytes / 16;
@@ -82,6 +83,10 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
         union { uint4 q; T e[V]; } o;
 #pragma unroll
         for (int k = 0; k < V; ++k) o.e[k] = from_f32<T>(acc[k]);
+        if (a.no_gather) {
+            reinterpret_cast<uint4 *>(P.arena[me] + a.buf_off[me])[i] = o.q;
+            continue;
+        }
 #pragma unroll
         for (int q = 0; q < kMaxPeers; ++q)
             if (q < R) reinterpret_cast<uint4 *>(P.arena[q] + a.buf_off[q])[i] = o.q;

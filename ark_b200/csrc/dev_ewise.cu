@@ -259,12 +259,15 @@ __device__ __forceinline__ void ewise_typed(const EwiseArgs &a, int p, int P) {
 }
 
 // Raw copy of integer data (no fp32 round trip): 16 or 1 bytes per access.
-__device__ void ewise_bytes(const EwiseArgs &a, int p, int P, int esize) {
+__device__ void ewise_bytes(const EwiseArgs &a, int p, int P, int esize, unsigned long long iter_no) {
     const int64_t tid = (int64_t)p * kThreads + threadIdx.x;
     const int64_t nth = (int64_t)P * kThreads;
+    const int64_t slot = a.iter_slots > 1 ? (int64_t)((iter_no - 1) % (unsigned long long)a.iter_slots) : 0;
+    const char *in_base = reinterpret_cast<const char *>(a.in0.ptr) + slot * a.in_iter_bytes;
+    char *out_base = reinterpret_cast<char *>(a.out.ptr) + slot * a.out_iter_bytes;
     if (a.flat && a.vec > 1) {
-        const uint4 *s = reinterpret_cast<const uint4 *>(a.in0.ptr);
-        uint4 *d = reinterpret_cast<uint4 *>(a.out.ptr);
+        const uint4 *s = reinterpret_cast<const uint4 *>(in_base);
+        uint4 *d = reinterpret_cast<uint4 *>(out_base);
         const int64_t n = a.n_units;
         constexpr int U = 8;
         for (int64_t u0 = tid; u0 < n; u0 += nth * U) {
@@ -281,8 +284,8 @@ __device__ void ewise_bytes(const EwiseArgs &a, int p, int P, int esize) {
     // generic strided element copy
     const int64_t W = a.out.shape[3], H = a.out.shape[2], C = a.out.shape[1];
     const int64_t total = (int64_t)a.out.shape[0] * C * H * W;
-    const char *s = reinterpret_cast<const char *>(a.in0.ptr);
-    char *d = reinterpret_cast<char *>(a.out.ptr);
+    const char *s = in_base;
+    char *d = out_base;
     for (int64_t i = tid; i < total; i += nth) {
         int64_t w = i % W, r = i / W;
         int64_t h = r % H;
@@ -347,11 +350,11 @@ __device__ void ewise_convert(const EwiseArgs &a, int p, int P) {
     }
 }
 
-__device__ void run_ewise(const EwiseArgs &a, int p, int P) {
+__device__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
     const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
     if (a.op == EW_COPY && idt == a.out.dtype) {
         const int es = (idt == DT_F32 || idt == DT_I32 || idt == DT_U32) ? 4 : (idt == DT_F16 || idt == DT_BF16) ? 2 : 1;
-        ewise_bytes(a, p, P, es);
+        ewise_bytes(a, p, P, es, iter_no);
         return;
     }
     if (a.op == EW_CAST || idt != a.out.dtype) {

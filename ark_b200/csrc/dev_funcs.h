@@ -6,7 +6,7 @@
 
 namespace arkb {
 struct GemmPipe;
-__device__ void run_ewise(const EwiseArgs &a, int p, int P);
+__device__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no);
 __device__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem);
 __device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
                           unsigned long long wait_limit);
@@ -21,7 +21,7 @@ __device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
 __device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no);
 __device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
-__device__ void run_put(const PutArgs &a, int p, int P);
+__device__ void run_put(const PutArgs &a, int p, int P, unsigned long long iter_no);
 __device__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage);
 __device__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
                                   int stage);

@@ -69,7 +69,7 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
                     return;
                 break;
             }
-            case SK_EWISE: run_ewise(S.ew, p, Pn); break;
+            case SK_EWISE: run_ewise(S.ew, p, Pn, iter_no); break;
             case SK_REDUCE: run_reduce(S.rd, p, Pn, smem); break;
             case SK_ROWOP: run_rowop(S.ro, p, Pn, smem, ctl, P.state, s, P.spin_limit); break;
             case SK_GEMM:
@@ -82,7 +82,7 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             case SK_SPLITK_REDUCE: run_splitk_reduce(S.sr, p, Pn); break;
             case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;
             case SK_EMBED: run_embed(S.em, p, Pn); break;
-            case SK_PUT: run_put(S.put, p, Pn); break;
+            case SK_PUT: run_put(S.put, p, Pn, iter_no); break;
             case SK_SIGNAL: if (p == 0) run_signal(P, S.sg, iter_no); break;
             case SK_WAITFLAG: if (p == 0) run_wait(P, S.wt, iter_no, ctl, s); break;
             case SK_PEERSYNC:

@@ -131,6 +131,10 @@ struct Lowerer {
 
     static bool full_range(const Range &tr, int64_t num_tasks) { return tr.b == 0 && tr.s == 1 && tr.e >= num_tasks; }
 
+    static int64_t config_int(const OpDesc &op, const char *key, int64_t dflt) {
+        return op.config.is_object() && op.config.contains(key) ? op.config.at(key).as_int() : dflt;
+    }
+
     int64_t num_tasks(const OpDesc &op) const {
         if (op.config.is_object() && op.config.contains("NumTasks")) return op.config.at("NumTasks").as_int();
         return 1;
@@ -242,6 +246,14 @@ struct Lowerer {
             throw Error(E_UNSUPPORTED, "Rope needs 16-byte aligned rows");
         }
         a.vec = vec_ok ? V : 1;
+        if (int64_t slots = config_int(op, "IterSlots", 1); slots > 1) {
+            // ring of buffers walked by the iteration number (streaming input / output of a resident kernel)
+            if (code != EW_COPY || convert) throw Error(E_UNSUPPORTED, op.type + ": IterSlots is for Copy between tensors of one type");
+            a.iter_slots = (int32_t)slots;
+            a.in_iter_bytes = config_int(op, "InIterStride", 0) * (int64_t)dtype_size(idt);
+            a.out_iter_bytes = config_int(op, "OutIterStride", 0) * (int64_t)dtype_size(out.dtype);
+            if (a.vec > 1 && (a.in_iter_bytes % 16 || a.out_iter_bytes % 16)) a.vec = 1;
+        }
         if (a.flat) a.n_units = nelem / a.vec;
         else a.n_units = osh[0] * osh[1] * osh[2] * ((osh[3] + a.vec - 1) / a.vec);
         push(s, op.type + " " + op.name + " units=" + std::to_string(a.n_units) + " vec=" + std::to_string(a.vec) +
@@ -979,6 +991,8 @@ struct Lowerer {
         s.put.src = tensor_ptr(src);
         s.put.bytes = src.nelems() * (int64_t)dtype_size(src.dtype);
         s.put.peer = peer;
+        s.put.iter_slots = (int32_t)config_int(op, "IterSlots", 1);
+        s.put.src_iter_bytes = config_int(op, "InIterStride", 0) * (int64_t)dtype_size(src.dtype);
         push(s, "Send " + op.name + " -> rank " + std::to_string(peer) + " bytes=" + std::to_string(s.put.bytes));
         const bool signal = !op.config.is_object() || !op.config.contains("Signal") || op.config.at("Signal").as_bool();
         if (signal) {
@@ -1120,6 +1134,10 @@ struct Lowerer {
         a.nelem = n;
         a.dtype = t.dtype;
         std::string algo = op.config.is_object() && op.config.contains("Algo") ? op.config.at("Algo").as_string() : "auto";
+        // Gather = false: every rank keeps only the sum of its own 1/p of the rows (what a host that reads the result
+        // shard by shard needs); only the form fused with the producing Matmul offers it
+        const bool gather = !(op.has_arg("Gather") && !op.arg_bool("Gather"));
+        if (!gather && !fused) throw Error(E_UNSUPPORTED, "AllReduce without gather needs the form fused with the Matmul before it");
         if (fused) {
             auto st = lay.coll_stage_offsets.find(tag);
             if (st == lay.coll_stage_offsets.end()) throw Error(E_PLAN, "fused AllReduce: no staging slots");
@@ -1127,10 +1145,11 @@ struct Lowerer {
             a.algo = 2;
             a.stage_off = st->second[env.rank];
             a.stage_bytes = bytes / env.nranks;
+            a.no_gather = gather ? 0 : 1;
             emit_sync(proc);
             emit_peersync(proc, "partial tiles pushed");
             emit_sync(proc);
-            push(s, "AllReduce " + op.name + " sum of staging slots + all-gather bytes=" + std::to_string(bytes));
+            push(s, "AllReduce " + op.name + (gather ? " sum of staging slots + all-gather bytes=" : " sum of staging slots, own rows only bytes=") + std::to_string(bytes));
             emit_sync(proc);
             emit_peersync(proc, "all_reduce outputs stored");
             emit_sync(proc);

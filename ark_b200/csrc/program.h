@@ -69,6 +69,11 @@ struct EwiseArgs {
     int32_t flat;       // 1: all operands dense and same shape -> 1-D walk
     float scalar;
     int64_t n_units;    // number of vec units
+    // Copy only: a ring of `iter_slots` buffers walked by the iteration number. Iteration i (1-based over the
+    // executor's life) reads in0 + ((i - 1) % iter_slots) * in_iter_bytes and writes out + ... * out_iter_bytes,
+    // so the host can fill or drain the other slots while the iteration runs. iter_slots <= 1: fixed addresses.
+    int32_t iter_slots, pad;
+    int64_t in_iter_bytes, out_iter_bytes;
 };
 
 struct ReduceArgs {
@@ -234,7 +239,9 @@ struct PutArgs {
     void *dst;           // points into the peer's arena mapping
     const void *src;
     int64_t bytes;       // dense copy
-    int32_t peer, pad;
+    int32_t peer;
+    int32_t iter_slots;  // > 1: the source is a ring of buffers walked by the iteration number (see EwiseArgs)
+    int64_t src_iter_bytes;
 };
 struct SignalArgs {
     int32_t peer;        // rank whose comm block gets the flag
@@ -295,6 +302,8 @@ struct AllReduceArgs {
     // out := round(sum) + residual, stored to `sum_out` instead of the all_reduce's own tensor
     const void *residual;
     void *sum_out;
+    int32_t no_gather;        // slots (algo 2): the sum of this rank's rows stays local (a reduce-scatter); the caller reads
+    int32_t pad;              // only those rows, and the closing cross-rank barrier is left out
 };
 
 struct alignas(128) Stage {

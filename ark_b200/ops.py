@@ -573,11 +573,13 @@ def all_reduce_sm(input, rank, rank_num, output=None):
     return device_sync(input, rank, rank_num)
 
 
-def all_reduce(input, rank, world_size, output=None, name="all_reduce", naive=False):
+def all_reduce(input, rank, world_size, output=None, name="all_reduce", naive=False, gather=True):
     """Sum over ranks. The reference composes world_size-1 rounds of
     send/send_done/recv/add (ark/ops/ops_all_reduce.cpp:8-37, kept as
     `naive=True`); by default this is one in-kernel collective on `output`
-    (in place on a copy of `input` when `output` is None)."""
+    (in place on a copy of `input` when `output` is None). `gather=False`
+    (only with a Matmul planned into the same task): rank r keeps the sum of
+    rows [r*M/p, (r+1)*M/p) only, the rest of `output` is undefined."""
     m = _m()
     if output is None:
         output = copy(input)
@@ -603,5 +605,8 @@ def all_reduce(input, rank, world_size, output=None, name="all_reduce", naive=Fa
         return cumulate
     res = output.clone_view()
     tag = m.unique_tag()
-    m.add_op("AllReduce", name, [output], [output], [res], {"Tag": int(tag), "Rank": int(rank), "RankNum": int(world_size)})
+    args = {"Tag": int(tag), "Rank": int(rank), "RankNum": int(world_size)}
+    if not gather:
+        args["Gather"] = False
+    m.add_op("AllReduce", name, [output], [output], [res], args)
     return res

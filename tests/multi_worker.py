@@ -180,6 +180,39 @@ def main():
         results[fused] = got
     assert np.array_equal(results[True].view(np.uint16), results[False].view(np.uint16)), "fused and two-shot sums differ"
 
+    # ---- the same block fed through rings: every rank feeds its tokens/p rows, the ranks exchange them in-kernel, and
+    # the all_reduce keeps each rank's rows of the sum (what bench.py's end-to-end leg runs) ----
+    from ark_b200.ffn import build_ffn_streaming
+    from ark_b200.model import Tensor
+    fresh()
+    rows = tokens // world
+    x_ring, t1, t2, y_ring = build_ffn_streaming(tokens, d, f, ark.fp16, rank, world)
+    mdl = ark.Model.get_model()
+    x_slot = [Tensor(mdl, ark.fp16, x_ring.buffer, [rows, d], [2 * rows, d], [s_ * rows, 0]) for s_ in range(2)]
+    y_slot = [Tensor(mdl, ark.fp16, y_ring.buffer, [rows, d], [2 * rows, d], [s_ * rows, 0]) for s_ in range(2)]
+    x2 = O.to_storage(np.random.default_rng(6).normal(0, 1, (tokens, d)).astype(np.float32), "fp16")
+    ex = ark.Executor(local, 0, "rings", str(ark.Planner(local).plan()), True, allgather=ag)
+    ex.set_wait_limit(5_000_000_000)
+    ex.compile()
+    ex.tensor_from_numpy(t1, np.ascontiguousarray(w1[:, rank * sh:(rank + 1) * sh]))
+    ex.tensor_from_numpy(t2, np.ascontiguousarray(w2[rank * sh:(rank + 1) * sh, :]))
+    ex.tensor_from_numpy(x_slot[0], np.ascontiguousarray(x[rank * rows:(rank + 1) * rows]))
+    ex.tensor_from_numpy(x_slot[1], np.ascontiguousarray(x2[rank * rows:(rank + 1) * rows]))
+    ex.barrier()
+    ex.launch()
+    ex.run(2)
+    ex.wait()
+    got0, got1 = ex.tensor_to_numpy(y_slot[0]), ex.tensor_to_numpy(y_slot[1])
+    ex.barrier()
+    ex.stop()
+    ex.destroy()
+    assert np.array_equal(got0.view(np.uint16), results[True][rank * rows:(rank + 1) * rows].view(np.uint16)), "streamed rows differ from the fused all_reduce"
+    parts2 = [O.matmul(O.matmul(x2, np.ascontiguousarray(w1[:, r * sh:(r + 1) * sh]), "fp16", act="gelu"),
+                       np.ascontiguousarray(w2[r * sh:(r + 1) * sh, :]), "fp16") for r in range(world)]
+    want2 = O.all_reduce(parts2, "fp16")[rank * rows:(rank + 1) * rows]
+    err = np.abs(got1.astype(np.float32) - want2.astype(np.float32))
+    assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("streamed tp ffn, second slot", err.mean(), err.max())
+
     # ---- one tensor-parallel Llama-shaped decoder layer (prefill), against the per-op oracle composition ----
     from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
     from tests.llama_ref import causal_mask, layer, rope_table

@@ -179,3 +179,41 @@ def test_multi_op_plan_ffn_block():
     want = O.matmul(hh, w2, "fp16")
     from tests.ark_util import assert_matmul_close
     assert_matmul_close(got, want, "fp16", "ffn block")
+
+
+def test_streaming_rings_feed_and_drain_a_resident_kernel():
+    """Input and output rings walked by the iteration number: iteration i reads slot (i-1) % 2 and leaves its
+    result in the same slot, so the host can fill / drain the other slot meanwhile (what bench.py's end-to-end leg does)."""
+    from ark_b200.ffn import build_ffn_streaming
+    from ark_b200.model import Tensor
+    from tests.ark_util import assert_matmul_close
+    tokens, d, f = 256, 512, 1024
+    rng = np.random.default_rng(11)
+    w1 = O.to_storage(rng.normal(0, 0.02, (d, f)).astype(np.float32), "fp16")
+    w2 = O.to_storage(rng.normal(0, 0.02, (f, d)).astype(np.float32), "fp16")
+    xs = [O.to_storage(rng.normal(0, 1, (tokens, d)).astype(np.float32), "fp16") for _ in range(3)]
+    ark.init()
+    x_ring, t1, t2, y_ring = build_ffn_streaming(tokens, d, f, ark.fp16)
+    m = ark.Model.get_model()
+    x_slot = [Tensor(m, ark.fp16, x_ring.buffer, [tokens, d], [2 * tokens, d], [s * tokens, 0]) for s in range(2)]
+    y_slot = [Tensor(m, ark.fp16, y_ring.buffer, [tokens, d], [2 * tokens, d], [s * tokens, 0]) for s in range(2)]
+    ex = ark.Executor(0, 0, "rings", str(ark.Planner(0).plan()), True)
+    ex.set_wait_limit(3_000_000_000)
+    ex.compile()
+    ex.tensor_from_numpy(t1, w1)
+    ex.tensor_from_numpy(t2, w2)
+    ex.launch()
+    ex.tensor_from_numpy(x_slot[0], xs[0])
+    ex.tensor_from_numpy(x_slot[1], xs[1])
+    ex.run(2)  # iterations 1 and 2: slots 0 and 1
+    ex.wait()
+    got = [ex.tensor_to_numpy(y_slot[0]), ex.tensor_to_numpy(y_slot[1])]
+    ex.tensor_from_numpy(x_slot[0], xs[2])
+    ex.run(1)  # iteration 3: slot 0 again
+    ex.wait()
+    got.append(ex.tensor_to_numpy(y_slot[0]))
+    ex.stop()
+    ex.destroy()
+    for i in range(3):
+        want = O.matmul(O.matmul(xs[i], w1, "fp16", act="gelu"), w2, "fp16")
+        assert_matmul_close(got[i], want, "fp16", f"streamed batch {i}")
