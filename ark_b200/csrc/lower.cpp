@@ -103,8 +103,33 @@ struct Lowerer {
         s.proc_s = (int32_t)proc.s;
         return s;
     }
+    // ---- what the stage being built touches (see StageAccess) ---------------------------------
+    StageAccess acc;
+    void acc_begin() {
+        acc = StageAccess();
+        acc.opaque = false;
+    }
+    static std::pair<uintptr_t, uintptr_t> span_of(const void *p, size_t bytes) {
+        const uintptr_t b = reinterpret_cast<uintptr_t>(p);
+        return {b, b + bytes};
+    }
+    std::pair<uintptr_t, uintptr_t> span_of(const TensorDesc &t) const {
+        int64_t es[4], org;
+        t.elem_strides(es, org);
+        auto sh = t.shape4();
+        int64_t last = 0;
+        for (int i = 0; i < 4; ++i) last += (sh[i] - 1) * es[i];
+        return span_of(tensor_ptr(t), (size_t)(last + 1) * dtype_size(t.dtype));
+    }
+    void rd(const TensorDesc &t) { acc.reads.push_back(span_of(t)); }
+    void wr(const TensorDesc &t) { acc.writes.push_back(span_of(t)); }
+    void rd_raw(const void *p, size_t bytes) { if (p && bytes) acc.reads.push_back(span_of(p, bytes)); }
+    void wr_raw(const void *p, size_t bytes) { if (p && bytes) acc.writes.push_back(span_of(p, bytes)); }
+
     void push(const Stage &s, const std::string &note) {
         prog.stages.push_back(s);
+        prog.access.push_back(acc);
+        acc = StageAccess();  // opaque until a lowering function says what its stage touches
         std::ostringstream os;
         os << "[" << s.proc_b << "," << s.proc_e << (s.proc_s != 1 ? "," + std::to_string(s.proc_s) : "") << ") " << note;
         prog.notes.push_back(os.str());
@@ -161,6 +186,10 @@ struct Lowerer {
         if ((has_in && op.reads.size() < (binary ? 2u : 1u))) throw Error(E_MODEL, op.type + ": missing operand");
         Stage s = new_stage(SK_EWISE, proc);
         EwiseArgs &a = s.ew;
+        acc_begin();
+        wr(out);
+        if (has_in) rd(op.reads[0]);
+        if (binary) rd(op.reads[1]);
         auto osh = out.shape4();
         a.out = make_ref(out);
         if (has_in) a.in0 = make_ref(op.reads[0], &osh);
@@ -256,6 +285,12 @@ struct Lowerer {
         }
         if (a.flat) a.n_units = nelem / a.vec;
         else a.n_units = osh[0] * osh[1] * osh[2] * ((osh[3] + a.vec - 1) / a.vec);
+        if (a.iter_slots > 1) {
+            acc.opaque = true;  // the ring slots move with the iteration number
+        } else if (a.flat && !convert && code != EW_ROPE) {
+            acc.aligned_units = a.n_units;
+            acc.aligned_unit_bytes = (int)(a.vec * dtype_size(out.dtype));
+        }
         push(s, op.type + " " + op.name + " units=" + std::to_string(a.n_units) + " vec=" + std::to_string(a.vec) +
                     (a.flat ? " flat" : " strided"));
     }
@@ -283,6 +318,9 @@ struct Lowerer {
             throw Error(E_UNSUPPORTED, "reduce: floating-point tensors only");
         Stage s = new_stage(SK_REDUCE, proc);
         ReduceArgs &a = s.rd;
+        acc_begin();
+        rd(in);
+        wr(out);
         a.in = make_ref(in);
         a.out = make_ref(out);
         a.op = op.type == "ReduceSum" ? RD_SUM : op.type == "ReduceMax" ? RD_MAX : RD_MEAN;
@@ -304,6 +342,10 @@ struct Lowerer {
         const TensorDesc &out = op.results.at(0);
         Stage s = new_stage(SK_ROWOP, proc);
         RowOpArgs &a = s.ro;
+        acc_begin();
+        for (auto &t : op.reads) rd(t);
+        for (auto &t : op.results) wr(t);
+        for (auto &t : op.writes) wr(t);
         a.op = op.type == "RMSNorm" ? RO_RMSNORM : op.type == "LayerNorm" ? RO_LAYERNORM : RO_SOFTMAX;
         a.dtype = in.dtype;
         auto sh = in.shape4();
@@ -511,6 +553,8 @@ struct Lowerer {
             if (!full) throw Error(E_UNSUPPORTED, "Matmul: partial TaskRange needs 16-byte aligned fp16/bf16 operands");
             Stage s = new_stage(SK_GEMM_SIMT, proc);
             GemmSimtArgs &g = s.gs;
+            acc_begin();
+            rd(A); rd(B); wr(C);
             g.A = pa; g.B = pb; g.C = pc;
             g.lda = lda; g.ldb = ldb; g.ldc = ldc;
             g.a_stride_c = ash[1] > 1 ? ast[2] * ast[3] : 0;
@@ -630,6 +674,16 @@ struct Lowerer {
                     gemv_pushed = true;
                 }
                 const GemvArgs gv = g;
+                acc_begin();
+                rd(A); rd(B);
+                if (gf) {
+                    for (const TensorDesc *t : {gf->x, gf->pro_a, gf->pro_b, gf->residual})
+                        if (t) rd(*t);
+                    if (gf->pro_out) wr(*gf->pro_out);
+                }
+                if (gv.splits > 1) wr_raw(gv.ws, (size_t)gv.splits * M * N * sizeof(float));
+                else wr(C);
+                if (gv.push_ord) acc.opaque = true;  // also stores into every rank's all_reduce slots
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
                             std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : "") +
@@ -651,6 +705,10 @@ struct Lowerer {
                     a.splits = gv.splits;
                     a.dtype = A.dtype;
                     a.act = act_final;
+                    acc_begin();
+                    rd_raw(gv.ws, (size_t)gv.splits * M * N * sizeof(float));
+                    if (gf && gf->residual) rd(*gf->residual);
+                    wr(C);
                     push(r, "  split-K sum " + op.name + " splits=" + std::to_string(a.splits));
                 }
                 return;
@@ -859,6 +917,11 @@ struct Lowerer {
                 env.encode_tmap(&g.tmPeer[r], sp);
             }
         }
+ acc_begin();
+        rd(A); rd(B);
+        if (g.splits > 1) wr_raw(g.ws, (size_t)g.splits * bn * bc * M * N * sizeof(float));
+        else wr(C);
+        if (fuse_ar) acc.opaque = true;  // tiles go to the peers' staging slots
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
@@ -884,6 +947,9 @@ struct Lowerer {
             a.splits = gg.splits;
             a.dtype = A.dtype;
             a.act = act_final;
+            acc_begin();
+            rd_raw(gg.ws, (size_t)gg.splits * bn * bc * M * N * sizeof(float));
+            wr(C);
             push(r, "  split-K sum " + op.name + " splits=" + std::to_string(a.splits));
         }
     }
@@ -923,12 +989,18 @@ struct Lowerer {
         const size_t bytes = (size_t)B * Hkv * chunks * G * (128 + 2) * sizeof(float);
         a.ws = env.workspace ? reinterpret_cast<float *>(env.workspace + prog.workspace_bytes) : nullptr;
         prog.workspace_bytes += (bytes + 255) / 256 * 256;
-        a.phase = 0;
+ a.phase = 0;
+        acc_begin();
+        rd(q); rd(k); rd(v);
+        wr_raw(a.ws, bytes);
         push(s, "DecodeAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
                     " keys=" + std::to_string(T) + " chunks=" + std::to_string(chunks) + " x " + std::to_string(chunk_len));
         emit_sync(proc);
         Stage m = s;
         m.da.phase = 1;
+        acc_begin();
+        rd_raw(a.ws, bytes);
+        wr(o);
         push(m, "  merge of the chunks " + op.name);
     }
 
@@ -941,6 +1013,9 @@ struct Lowerer {
         if ((int)perm.size() != nd) throw Error(E_MODEL, "Transpose: permutation rank mismatch");
         Stage s = new_stage(SK_TRANSPOSE, proc);
         TransposeArgs &a = s.tp;
+        acc_begin();
+        rd(in);
+        wr(out);
         a.in = make_ref(in);
         a.out = make_ref(out);
         for (int i = 0; i < 4 - nd; ++i) a.perm[i] = i;
@@ -964,6 +1039,9 @@ struct Lowerer {
             throw Error(E_UNSUPPORTED, "Embedding: output rows must be evenly spaced");
         Stage s = new_stage(SK_EMBED, proc);
         EmbedArgs &a = s.em;
+        acc_begin();
+        rd(idx); rd(w);
+        wr(out);
         a.out = tensor_ptr(out);
         a.idx = reinterpret_cast<const int32_t *>(tensor_ptr(idx));
         a.weight = tensor_ptr(w);
@@ -1345,6 +1423,7 @@ struct Lowerer {
                 const Stage &sy = prog.stages.back();
                 --prog.syncs_per_iter[sy.sync_group];
                 prog.stages.pop_back();
+                prog.access.pop_back();
                 prog.notes.pop_back();
             } else if (prog.stages.size() != mid) {
                 first = false;
@@ -1380,6 +1459,75 @@ struct Lowerer {
             for (auto &t : op.writes) writes.insert(t.buffer_id);
             for (auto &t : op.results) writes.insert(t.buffer_id);
         }
+    }
+
+    // ---- barriers no dependency needs -----------------------------------------------------------------
+    static bool overlap(const std::pair<uintptr_t, uintptr_t> &a, const std::pair<uintptr_t, uintptr_t> &b) {
+        return a.first < b.second && b.first < a.second;
+    }
+    // Does stage y have to see (or must it not disturb) what stage x did? Two flat elementwise walks over the same
+    // CTAs with the same unit count and size touch a common operand thread by thread, so an operand both start at
+    // the same address orders itself by program order inside each thread.
+    bool depends(size_t xi, size_t yi) const {
+        const StageAccess &x = prog.access[xi], &y = prog.access[yi];
+        if (x.opaque || y.opaque) return true;
+        const Stage &sx = prog.stages[xi], &sy = prog.stages[yi];
+        const bool aligned = x.aligned_units > 0 && x.aligned_units == y.aligned_units && x.aligned_unit_bytes == y.aligned_unit_bytes &&
+                             sx.proc_b == sy.proc_b && sx.proc_e == sy.proc_e && sx.proc_s == sy.proc_s;
+        auto hit = [&](const std::pair<uintptr_t, uintptr_t> &a, const std::pair<uintptr_t, uintptr_t> &b) {
+            if (!overlap(a, b)) return false;
+            return !(aligned && a.first == b.first);
+        };
+        for (auto &w : x.writes) {
+            for (auto &r : y.reads) if (hit(w, r)) return true;
+            for (auto &v : y.writes) if (hit(w, v)) return true;
+        }
+        for (auto &r : x.reads)
+            for (auto &v : y.writes) if (hit(r, v)) return true;
+        return false;
+    }
+
+    // The straightforward lowering puts a barrier wherever the plan's rules or the op order might need one. This
+    // pass keeps a barrier only when a stage behind it (up to the next barrier) depends on a stage that ran since
+    // the last whole-grid barrier that was kept; the barrier at the end of every iteration closes the rest.
+    void elide_syncs() {
+        if (const char *e = getenv("ARKB_KEEP_SYNCS")) if (atoi(e)) return;
+        const size_t n = prog.stages.size();
+        std::vector<bool> keep(n, true);
+        std::vector<size_t> pending;
+        for (size_t i = 0; i < n; ++i) {
+            const Stage &s = prog.stages[i];
+            if (s.kind != SK_SYNC) {
+                pending.push_back(i);
+                continue;
+            }
+            bool needed = false;
+            for (size_t j = i + 1; j < n && prog.stages[j].kind != SK_SYNC && !needed; ++j)
+                for (size_t x : pending)
+                    if (depends(x, j)) { needed = true; break; }
+            if (!needed) {
+                keep[i] = false;
+                continue;
+            }
+            if (s.proc_b == 0 && s.proc_s == 1 && s.proc_e >= prog.grid) pending.clear();
+        }
+        Program out = prog;
+        out.stages.clear(); out.access.clear(); out.notes.clear();
+        for (int g = 0; g < kMaxSyncGroups; ++g) out.syncs_per_iter[g] = 0;
+        for (size_t i = 0; i < n; ++i) {
+            if (!keep[i]) { ++out.syncs_elided; continue; }
+            Stage s = prog.stages[i];
+            std::string note = prog.notes[i];
+            if (s.kind == SK_SYNC) {
+                s.sync_ord = ++out.syncs_per_iter[s.sync_group];
+                const size_t at = note.find("sync group");
+                note = note.substr(0, at) + "sync group " + std::to_string(s.sync_group) + " #" + std::to_string(s.sync_ord);
+            }
+            out.stages.push_back(s);
+            out.access.push_back(prog.access[i]);
+            out.notes.push_back(note);
+        }
+        prog = out;
     }
 
     void run() {
@@ -1434,6 +1582,7 @@ struct Lowerer {
             unsynced.push_back(pr);
             first_pg = false;
         }
+        elide_syncs();
         prog.n_sync_groups = (int)sync_ids.size();
         prog.oneshots_per_iter = oneshot_ord;
         for (auto &s : prog.stages) {
@@ -1448,7 +1597,7 @@ struct Lowerer {
 std::string Program::dump() const {
     std::ostringstream os;
     os << "grid=" << grid << (pair_mode ? " pairs" : "") << " stages=" << stages.size() << " sync_groups=" << n_sync_groups
-       << " peer_barriers=" << peersyncs_per_iter << "\n";
+       << " peer_barriers=" << peersyncs_per_iter << (syncs_elided ? " barriers_elided=" + std::to_string(syncs_elided) : "") << "\n";
     for (size_t i = 0; i < notes.size(); ++i) os << i << ": " << notes[i] << "\n";
     return os.str();
 }

@@ -161,14 +161,27 @@ struct LowerEnv {
     char *workspace = nullptr;  // scratch for split-K partials (sized by a first lowering pass: Program::workspace_bytes)
 };
 
+// What a stage reads and writes (address ranges in this process's mappings), for the pass that drops barriers no
+// data dependency needs. `opaque` stages (communication) are taken to depend on everything.
+struct StageAccess {
+    std::vector<std::pair<uintptr_t, uintptr_t>> reads, writes;  // [begin, end)
+    bool opaque = true;
+    // > 0: a flat elementwise walk in which thread t handles the same `aligned_units` units of `aligned_unit_bytes`
+    // bytes of every operand: two such stages over the same CTAs touch a common operand thread by thread
+    int64_t aligned_units = 0;
+    int aligned_unit_bytes = 0;
+};
+
 struct Program {
     std::vector<Stage> stages;
+    std::vector<StageAccess> access;  // parallel to `stages`
     std::vector<std::string> notes;  // one line per stage, for dumps and tests
     int grid = 1;
     int n_sync_groups = 0;
     int syncs_per_iter[kMaxSyncGroups] = {};
     int peersyncs_per_iter = 0;
     int oneshots_per_iter = 0;
+    int syncs_elided = 0;  // barriers of the straightforward lowering that the dependency pass removed
     size_t workspace_bytes = 0;  // scratch the program needs beyond the arena (split-K partials)
     bool pair_mode = false;  // launch clusters of 2 CTAs; matmul tiles are 256 x tile_n per pair
     std::string dump() const;
