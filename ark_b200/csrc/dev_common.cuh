@@ -53,6 +53,11 @@ __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned l
     asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
+// Asks the L2 to fetch [p, p + bytes) (16-byte aligned, a multiple of 16 bytes) from HBM; returns at once.
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // Barrier over `count` CTAs on a monotonic counter: the k-th barrier of a
 // group completes when the counter reaches k*count. Replaces the reference's
 // sense-reversing sync_gpu (ark/include/kernels/common/sync.h:36-66); the wait

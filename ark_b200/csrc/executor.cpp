@@ -579,7 +579,12 @@ std::string plan_dump(const std::string &plan_json) {
             kv.second.resolved = true;
         }
     resolve_remote(plan, lay, records);
-    return lower_plan(plan, lay, env).dump();
+    std::string text = lower_plan(plan, lay, env).dump();
+    text += "arena=" + std::to_string(lay.arena_bytes) + " bytes";
+    if (plan.arena_reuse)
+        text += " (" + std::to_string(lay.reused_buffers) + " intermediates share space by lifetime; " +
+                std::to_string(lay.arena_bytes_no_reuse) + " bytes without reuse)";
+    return text + "\n";
 }
 
 void device_info(int device_id, DeviceInfo &out) {

@@ -63,6 +63,17 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
         if (stamp && threadIdx.x == 0) stamp[0] = globaltimer();
         switch (S.kind) {
             case SK_SYNC: {
+                // while this CTA waits, the L2 fetches its share of operands that stages behind the barrier will stream
+                if (threadIdx.x >= 32 && (int)threadIdx.x < 32 + S.sy.n_pf) {
+                    const int e = threadIdx.x - 32;
+                    const unsigned long long bytes = S.sy.pf_bytes[e];
+                    const unsigned long long per = ((bytes + Pn - 1) / Pn + 127ull) & ~127ull;
+                    const unsigned long long off = (unsigned long long)p * per;
+                    if (off < bytes) {
+                        const unsigned long long len = (bytes - off < per ? bytes - off : per) & ~15ull;
+                        if (len) l2_prefetch(reinterpret_cast<const char *>(S.sy.pf_ptr[e]) + off, (uint32_t)len);
+                    }
+                }
                 const unsigned long long k = iter_local * (unsigned long long)P.syncs_per_iter[S.sync_group] + S.sync_ord;
                 if (!grid_barrier(&P.state->barrier[S.sync_group], k * (unsigned long long)S.sync_count, P.spin_limit,
                                   ctl, P.state, s))

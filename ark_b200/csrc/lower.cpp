@@ -122,6 +122,16 @@ struct Lowerer {
         return span_of(tensor_ptr(t), (size_t)(last + 1) * dtype_size(t.dtype));
     }
     void rd(const TensorDesc &t) { acc.reads.push_back(span_of(t)); }
+    // a read operand the stage streams once (weights, caches): may be fetched into L2 ahead of time if nothing writes it
+    void rd_streamed(const TensorDesc &t) {
+        auto sp = span_of(t);
+        acc.reads.push_back(sp);
+        if (sp.second - sp.first >= 32 * 1024 && (t.buffer_rank == -1 || t.buffer_rank == env.rank))
+        {
+            const uintptr_t b = (sp.first + 15) & ~(uintptr_t)15, e = sp.second & ~(uintptr_t)15;  // bulk prefetch wants 16-byte units
+            acc.streamed.push_back({reinterpret_cast<const void *>(b), (size_t)(e - b), t.buffer_id});
+        }
+    }
     void wr(const TensorDesc &t) { acc.writes.push_back(span_of(t)); }
     void rd_raw(const void *p, size_t bytes) { if (p && bytes) acc.reads.push_back(span_of(p, bytes)); }
     void wr_raw(const void *p, size_t bytes) { if (p && bytes) acc.writes.push_back(span_of(p, bytes)); }
@@ -554,7 +564,7 @@ struct Lowerer {
             Stage s = new_stage(SK_GEMM_SIMT, proc);
             GemmSimtArgs &g = s.gs;
             acc_begin();
-            rd(A); rd(B); wr(C);
+            rd(A); rd_streamed(B); wr(C);
             g.A = pa; g.B = pb; g.C = pc;
             g.lda = lda; g.ldb = ldb; g.ldc = ldc;
             g.a_stride_c = ash[1] > 1 ? ast[2] * ast[3] : 0;
@@ -675,7 +685,7 @@ struct Lowerer {
                 }
                 const GemvArgs gv = g;
                 acc_begin();
-                rd(A); rd(B);
+                rd(A); rd_streamed(B);
                 if (gf) {
                     for (const TensorDesc *t : {gf->x, gf->pro_a, gf->pro_b, gf->residual})
                         if (t) rd(*t);
@@ -918,7 +928,7 @@ struct Lowerer {
             }
         }
  acc_begin();
-        rd(A); rd(B);
+        rd(A); rd_streamed(B);
         if (g.splits > 1) wr_raw(g.ws, (size_t)g.splits * bn * bc * M * N * sizeof(float));
         else wr(C);
         if (fuse_ar) acc.opaque = true;  // tiles go to the peers' staging slots
@@ -991,7 +1001,7 @@ struct Lowerer {
         prog.workspace_bytes += (bytes + 255) / 256 * 256;
  a.phase = 0;
         acc_begin();
-        rd(q); rd(k); rd(v);
+        rd(q); rd_streamed(k); rd_streamed(v);
         wr_raw(a.ws, bytes);
         push(s, "DecodeAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
                     " keys=" + std::to_string(T) + " chunks=" + std::to_string(chunks) + " x " + std::to_string(chunk_len));
@@ -1530,6 +1540,70 @@ struct Lowerer {
         prog = out;
     }
 
+    // Barriers fetch ahead: operands that no op of the plan writes (weights, K/V caches) are asked into L2 by the
+    // barrier stages that precede their readers, as early as a budget of bytes in flight allows, so that a chain of
+    // small dependent stages (decode) waits on L2 hits instead of HBM round trips, and HBM streams while CTAs sit
+    // at barriers. The stage list is cyclic: the last barriers of an iteration fetch for the first stages of the next.
+    void plan_prefetch() {
+        if (const char *e = getenv("ARKB_PREFETCH")) if (!atoi(e)) return;
+        const size_t n = prog.stages.size();
+        std::set<int64_t> written;
+        for (auto &ti : plan.task_infos)
+            for (auto &op : ti.ops) {
+                for (auto &t : op.writes) written.insert(t.buffer_id);
+                for (auto &t : op.results) written.insert(t.buffer_id);
+            }
+        struct Item { size_t stage; const void *ptr; size_t bytes; };
+        std::vector<Item> items;
+        for (size_t i = 0; i < n; ++i)
+            for (auto &sd : prog.access[i].streamed)
+                if (!written.count(sd.buffer_id)) items.push_back({i, sd.ptr, sd.bytes});
+        std::vector<size_t> syncs;
+        for (size_t i = 0; i < n; ++i)  // barriers of at least 32 CTAs: each CTA asks for its share
+            if (prog.stages[i].kind == SK_SYNC && prog.stages[i].sync_count >= 32) syncs.push_back(i);
+        if (items.empty() || syncs.empty()) return;
+        const size_t kBudget = 32u << 20;  // bytes fetched but not yet read, well inside the 126 MB L2
+        // walk the cyclic schedule twice: the first lap only warms up the window, the second lap's choices are kept
+        size_t next = 0, outstanding = 0;
+        std::vector<std::pair<size_t, size_t>> inflight;  // (absolute consumer position, bytes)
+        const size_t ni = items.size();
+        auto abs_pos = [&](size_t lap, size_t stage) { return lap * n + stage; };
+        // items are consumed in order; `next` counts items assigned so far over both laps
+        for (size_t lap = 0; lap < 2; ++lap)
+            for (size_t si = 0; si < syncs.size(); ++si) {
+                const size_t here = abs_pos(lap, syncs[si]);
+                for (auto it = inflight.begin(); it != inflight.end();)
+                    if (it->first < here) { outstanding -= it->second; it = inflight.erase(it); } else ++it;
+                Stage &sy = prog.stages[syncs[si]];
+                if (lap == 1) sy.sy.n_pf = 0;
+                while (true) {
+                    const Item &itx = items[next % ni];
+                    size_t cons = abs_pos(next / ni, itx.stage);
+                    while (cons < here) { ++next; cons = abs_pos(next / ni, items[next % ni].stage); }
+                    const Item &it = items[next % ni];
+                    if (cons > here + n) break;                      // never more than one lap ahead
+                    if (outstanding > 0 && outstanding + it.bytes > kBudget) break;
+                    const size_t bytes = std::min(it.bytes, kBudget);  // a huge operand: its head only
+                    if (lap == 1) {
+                        if (sy.sy.n_pf >= kMaxPrefetch) break;
+                        sy.sy.pf_ptr[sy.sy.n_pf] = it.ptr;
+                        sy.sy.pf_bytes[sy.sy.n_pf] = bytes;
+                        ++sy.sy.n_pf;
+                        prog.prefetch_bytes += bytes;
+                    }
+                    inflight.push_back({cons, bytes});
+                    outstanding += bytes;
+                    ++next;
+                }
+            }
+        for (size_t i : syncs)
+            if (prog.stages[i].sy.n_pf > 0) {
+                size_t b = 0;
+                for (int k = 0; k < prog.stages[i].sy.n_pf; ++k) b += prog.stages[i].sy.pf_bytes[k];
+                prog.notes[i] += " +L2 prefetch " + std::to_string(b >> 10) + " KiB";
+            }
+    }
+
     void run() {
         if (plan.num_processors > env.num_sm)
             throw Error(E_UNSUPPORTED, "plan needs " + std::to_string(plan.num_processors) + " processors, the device has " +
@@ -1583,6 +1657,7 @@ struct Lowerer {
             first_pg = false;
         }
         elide_syncs();
+        plan_prefetch();
         prog.n_sync_groups = (int)sync_ids.size();
         prog.oneshots_per_iter = oneshot_ord;
         for (auto &s : prog.stages) {

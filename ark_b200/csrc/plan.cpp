@@ -2,6 +2,7 @@
 #include "plan.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <set>
 
 namespace arkb {
@@ -161,6 +162,8 @@ Plan Plan::parse(const std::string &text) {
         p.architecture = j.contains("Architecture") ? j.at("Architecture").as_string() : "ANY";
         p.num_processors = (int)j.at("NumProcessors").as_int();
         p.num_warps_per_processor = (int)j.at("NumWarpsPerProcessor").as_int();
+        p.arena_reuse = j.contains("ArenaReuse") ? j.at("ArenaReuse").as_bool() : false;
+        if (const char *e = getenv("ARKB_ARENA_REUSE")) p.arena_reuse = atoi(e) != 0;
         if (p.rank < 0 || p.rank >= p.world_size) throw Error(E_USAGE, "rank " + std::to_string(p.rank) + " outside world size " + std::to_string(p.world_size));
         if (p.world_size > kMaxPeers) throw Error(E_UNSUPPORTED, "world size above " + std::to_string(kMaxPeers));
         if (p.num_processors < 1) throw Error(E_PLAN, "NumProcessors must be positive");
@@ -264,15 +267,112 @@ Layout plan_layout(const Plan &plan) {
             if (op.type == "AllReduce" && !op.results.empty())
                 oneshot_max = std::max(oneshot_max, (size_t)op.results[0].nelems() * dtype_size(op.results[0].dtype));
         }
-    size_t off = 0;
+    // ---- lifetimes of intermediates (only when the plan asks for reuse) ----
+    struct Life { int first = -1, last = -1; bool ok = true, written = false, read = false, first_is_write = false; };
+    std::map<int64_t, Life> life;
+    if (plan.arena_reuse) {
+        auto whole = [&](const TensorDesc &t) {
+            const BufferInfo &b = lay.buffers.at(t.buffer_id);
+            for (auto o : t.offsets) if (o) return false;
+            return t.dense() && t.shape == t.padded && (size_t)t.nelems() * dtype_size(t.dtype) == b.bytes;
+        };
+        static const std::set<std::string> comm_ops = {"Send", "SendDone", "Recv", "DeviceSync", "AllReduce", "SendPacket",
+                                                        "RecvPacket", "RecvReduceSendPacket", "RecvReduceSend"};
+        int step = 0;
+        for (auto &pg : plan.processor_groups) {
+            for (auto &rg : pg.resource_groups)
+                for (auto &tg : rg.task_groups)
+                    for (auto &op : plan.task(tg.task_id).ops) {
+                        const bool comm = comm_ops.count(op.type) > 0;
+                        auto touch = [&](const TensorDesc &t, bool is_write) {
+                            Life &l = life[t.buffer_id];
+                            if (comm || !whole(t)) l.ok = false;
+                            if (l.first < 0) { l.first = step; l.first_is_write = is_write; }
+                            l.last = step;
+                            (is_write ? l.written : l.read) = true;
+                        };
+                        // reads first: an op that reads and writes one buffer (in place) needs the old contents
+                        if (!op.is_virtual) {
+                            for (auto &t : op.reads) touch(t, false);
+                            for (auto &t : op.writes) touch(t, true);
+                            for (auto &t : op.results) touch(t, true);
+                        } else {
+                            for (auto &t : op.reads) life[t.buffer_id].ok = life[t.buffer_id].ok && whole(t);
+                            for (auto &t : op.results) life[t.buffer_id].ok = life[t.buffer_id].ok && whole(t);
+                        }
+                    }
+            ++step;
+        }
+        // ops the schedule never runs (task infos without a task group) still pin their buffers
+        std::set<int64_t> scheduled;
+        for (auto &pg : plan.processor_groups)
+            for (auto &rg : pg.resource_groups)
+                for (auto &tg : rg.task_groups) scheduled.insert(tg.task_id);
+        for (auto &ti : plan.task_infos)
+            if (!scheduled.count(ti.id))
+                for (auto &op : ti.ops) {
+                    for (auto &t : op.reads) life[t.buffer_id].ok = false;
+                    for (auto &t : op.writes) life[t.buffer_id].ok = false;
+                    for (auto &t : op.results) life[t.buffer_id].ok = false;
+                }
+    }
+    auto reusable = [&](const BufferInfo &b) {
+        auto it = life.find(b.id);
+        if (it == life.end()) return false;
+        const Life &l = it->second;
+        return plan.arena_reuse && l.ok && l.written && l.read && l.first_is_write && l.first >= 0 && b.send_tags.empty() &&
+               b.recv_tags.empty() && (b.rank == -1 || b.rank == plan.rank);
+    };
+    size_t off = 0, off_plain = 0;
+    std::vector<BufferInfo *> pool;
     for (auto &kv : lay.buffers) {  // std::map: buffer-id order, as the reference
         BufferInfo &b = kv.second;
         if (b.rank != -1 && b.rank != plan.rank) continue;  // remote: resolved later
+        off_plain = align_up(off_plain + b.bytes, kArenaAlign);
+        if (reusable(b)) {
+            pool.push_back(&b);
+            continue;
+        }
         b.offset = off;
         b.resolved = true;
         off = align_up(off + b.bytes, kArenaAlign);
         for (auto &tg : b.send_tags) lay.published.push_back({0, tg.first, tg.second, 0, b.offset});
         for (auto &tg : b.recv_tags) lay.published.push_back({1, tg.first, tg.second, 0, b.offset});
+    }
+    lay.arena_bytes_no_reuse = off_plain;
+    if (!pool.empty()) {
+        // Intermediates in order of birth; a buffer takes the lowest-addressed hole of the shared region that is free
+        // over its whole lifetime (holes are what buffers that died earlier left), else the region grows.
+        std::sort(pool.begin(), pool.end(), [&](BufferInfo *a, BufferInfo *b) {
+            const Life &la = life[a->id], &lb = life[b->id];
+            return la.first != lb.first ? la.first < lb.first : a->bytes > b->bytes;
+        });
+        struct Placed { size_t off, size; int first, last; };
+        std::vector<Placed> placed;
+        const size_t base = off;
+        size_t top = 0;
+        for (BufferInfo *b : pool) {
+            const Life &l = life[b->id];
+            const size_t size = align_up(std::max<size_t>(b->bytes, 1), kArenaAlign);
+            // blocks alive at any step of [first, last], sorted by offset
+            std::vector<std::pair<size_t, size_t>> busy;
+            for (auto &p : placed)
+                // one step of slack on either side: stages of neighbouring processor groups may run side by side when
+                // no data dependency orders them, and sharing memory between them would create one
+                if (!(p.last + 1 < l.first || p.first > l.last + 1)) busy.push_back({p.off, p.off + p.size});
+            std::sort(busy.begin(), busy.end());
+            size_t at = 0;
+            for (auto &iv : busy) {
+                if (at + size <= iv.first) break;
+                at = std::max(at, iv.second);
+            }
+            placed.push_back({at, size, l.first, l.last});
+            top = std::max(top, at + size);
+            b->offset = base + at;
+            b->resolved = true;
+            ++lay.reused_buffers;
+        }
+        off = align_up(base + top, kArenaAlign);
     }
     // collective tags: AllReduce publishes where its tensor lives
     for (auto &ti : plan.task_infos)

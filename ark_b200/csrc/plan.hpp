@@ -85,6 +85,7 @@ struct Plan {
     int rank = 0, world_size = 1;
     std::string architecture;
     int num_processors = 1, num_warps_per_processor = 1;
+    bool arena_reuse = false;  // optional top-level plan field "ArenaReuse": intermediates with disjoint lifetimes share memory
     std::vector<TaskInfo> task_infos;
     std::vector<ProcessorGroup> processor_groups;
     static Plan parse(const std::string &text);
@@ -111,6 +112,8 @@ struct TagRecord {
 struct Layout {
     std::map<int64_t, BufferInfo> buffers;
     size_t arena_bytes = 0;
+    size_t arena_bytes_no_reuse = 0;  // what the bump allocation of the reference would take (no lifetime reuse)
+    int reused_buffers = 0;           // intermediates placed by the lifetime planner
     size_t comm_stage_bytes = 0;  // bytes of ONE one-shot staging buffer (kMaxPeers slots)
     std::vector<TagRecord> published;  // this rank's records
     // collective tag -> arena offset on every rank
@@ -129,7 +132,13 @@ bool fused_allreduce(const Plan &plan, const TaskInfo &ti, size_t i);
 // Walks the plan, sizes every buffer and bump-allocates the local ones.
 // Counterpart of Executor::Impl::init_buffers (ark/api/executor.cpp:300-408),
 // with offsets rounded up to kArenaAlign so that TMA and 128-bit accesses
-// can be used on every buffer.
+// can be used on every buffer. With Plan::arena_reuse (what the reference leaves
+// as "TODO: improve memory planning", api/executor.cpp:374) intermediates whose
+// lifetimes do not overlap share arena space: a buffer qualifies when every tensor
+// on it is a dense whole-buffer view, it carries no tags and no communication
+// operator touches it, some op writes it before any op reads it, and some op reads
+// it (inputs, outputs and everything the host may feed or fetch keep their own
+// space). Lifetimes are counted in processor groups, the unit the plan orders.
 Layout plan_layout(const Plan &plan);
 // Resolves remote buffers and collective offsets from the records of all
 // ranks (records[r] = what rank r published). Counterpart of the tag/offset
@@ -170,6 +179,13 @@ struct StageAccess {
     // bytes of every operand: two such stages over the same CTAs touch a common operand thread by thread
     int64_t aligned_units = 0;
     int aligned_unit_bytes = 0;
+    // large operands the stage streams from HBM (weights, caches): candidates for L2 prefetch at an earlier barrier
+    struct Streamed {
+        const void *ptr;
+        size_t bytes;
+        int64_t buffer_id;
+    };
+    std::vector<Streamed> streamed;
 };
 
 struct Program {
@@ -182,6 +198,7 @@ struct Program {
     int peersyncs_per_iter = 0;
     int oneshots_per_iter = 0;
     int syncs_elided = 0;  // barriers of the straightforward lowering that the dependency pass removed
+    size_t prefetch_bytes = 0;  // bytes per iteration that barrier stages ask the L2 to fetch ahead of their readers
     size_t workspace_bytes = 0;  // scratch the program needs beyond the arena (split-K partials)
     bool pair_mode = false;  // launch clusters of 2 CTAs; matmul tiles are 256 x tile_n per pair
     std::string dump() const;

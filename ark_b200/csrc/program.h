@@ -306,6 +306,15 @@ struct AllReduceArgs {
     int32_t pad;              // only those rows, and the closing cross-rank barrier is left out
 };
 
+// What a barrier stage does while it waits: L2 prefetch of operands no stage of the plan writes (weights, K/V
+// caches) that stages behind the barrier will read. Every CTA of the barrier's range asks for its share.
+constexpr int kMaxPrefetch = 6;
+struct SyncArgs {
+    const void *pf_ptr[kMaxPrefetch];
+    uint64_t pf_bytes[kMaxPrefetch];
+    int32_t n_pf, pad;
+};
+
 struct alignas(128) Stage {
     int32_t kind;
     int32_t proc_b, proc_e, proc_s;  // processor (CTA) range [b, e) step s
@@ -331,6 +340,7 @@ struct alignas(128) Stage {
         AllReduceArgs ar;
         PacketArgs pk;
         PacketReduceArgs pr;
+        SyncArgs sy;
     };
 };
 

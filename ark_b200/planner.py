@@ -154,7 +154,11 @@ def default_config(op, num_sm=DEFAULT_NUM_SM):
 class Planner:
     """ark::Planner (ark/include/ark/planner.hpp:35-51)."""
 
-    def __init__(self, device_id=0, num_sm=None, model=None):
+    def __init__(self, device_id=0, num_sm=None, model=None, reuse_memory=False):
+        """`reuse_memory`: the plan asks the executor (top-level field "ArenaReuse") to let intermediates whose
+        lifetimes do not overlap share arena space. Off by default, as in the reference, where every tensor keeps
+        its memory and can be read back after a run (ark/api/executor.cpp:374-408)."""
+        self.reuse_memory = reuse_memory
         self.device_id = device_id
         self.model = model if model is not None else Model.get_model()
         self.num_sm = num_sm
@@ -245,4 +249,6 @@ class Planner:
         plan = {"Rank": self.model.rank, "WorldSize": self.model.world_size, "Architecture": ARCH,
                 "NumProcessors": max_proc, "NumWarpsPerProcessor": max_warp, "TaskInfos": task_infos,
                 "ProcessorGroups": processor_groups}
+        if self.reuse_memory:
+            plan["ArenaReuse"] = True
         return Plan(plan)

@@ -33,8 +33,10 @@ def check(got, want, dt):
     assert float(err.max()) <= (0.05 if dt == "fp16" else 0.25), float(err.max())
 
 
-@pytest.mark.parametrize("dt,heads,kv", [("fp16", 4, 4), ("bf16", 8, 1)])
-def test_prefill_layer(dt, heads, kv):
+@pytest.mark.parametrize("dt,heads,kv,reuse", [("fp16", 4, 4, False), ("bf16", 8, 1, False), ("fp16", 4, 4, True)])
+def test_prefill_layer(dt, heads, kv, reuse):
+    """reuse: the plan lets intermediates with disjoint lifetimes share arena space; two layers, so that the
+    second one's activations land on memory the first one used."""
     cfg = LlamaConfig(dim=512, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
     batch, seq = 2, 128
     rng = np.random.default_rng(51)
@@ -49,8 +51,22 @@ def test_prefill_layer(dt, heads, kv):
     ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
     feeds = {tx: x, tr: rope, tm: mask}
     feeds.update({tw[k]: w[k] for k in w})
-    (got,) = execute([ty], feeds, loop_mode=True)
     want = layer(x, [w], cfg, batch, seq, dt, rope=rope, mask=mask)
+    if reuse:
+        w2 = make_weights(cfg, dt, 1, rng)
+        tw2 = layer_weights(cfg, NAME[dt], 1)
+        ty = decoder_layer(ty, tw2, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
+        feeds.update({tw2[k]: w2[k] for k in w2})
+        want = layer(want, [w2], cfg, batch, seq, dt, rope=rope, mask=mask)
+        plan = ark.Planner(0, reuse_memory=True).plan()
+        text = ark.plan_dump(str(plan))
+        assert "intermediates share space by lifetime" in text
+        _, arena_reuse, _ = ark.plan_check(str(plan))
+        _, arena_plain, _ = ark.plan_check(str(ark.Planner(0).plan()))
+        assert arena_reuse < 0.7 * arena_plain, (arena_reuse, arena_plain)
+        (got,) = execute([ty], feeds, loop_mode=True, iters=2, plan=plan)
+    else:
+        (got,) = execute([ty], feeds, loop_mode=True)
     check(got, want, dt)
 
 

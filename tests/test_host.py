@@ -72,7 +72,7 @@ def test_barrier_rule_between_processor_groups():
     with ark.PlannerContext(processor_range=[0, 16]):
         e = ark.add(c, d)
     text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
-    lines = text.strip().split("\n")[1:]
+    lines = [l for l in text.strip().split("\n")[1:] if not l.startswith("arena=")]
     kinds = [("sync" if "sync group" in l else "op") for l in lines]
     assert kinds == ["op", "op", "sync", "op"]
     assert "[0,16) sync" in lines[2]
@@ -256,6 +256,40 @@ def test_reference_tutorial_plans_load_unmodified():
         assert stages > 0 and procs == json.loads(s)["NumProcessors"]
         n += 1
     assert n >= 20  # 4 single-GPU tutorial plans + the two 8-rank all_reduce plan sets
+
+
+def test_arena_lifetime_planner_shares_only_dead_intermediates():
+    """"ArenaReuse": buffers some op writes before any op reads them, with whole-buffer dense tensors and no tags,
+    may share space when their lifetimes (in processor groups, with a step of slack) do not overlap. Inputs,
+    outputs and everything else keep their own space, and the default keeps the reference's layout."""
+    def build(n):
+        ark.init()
+        x = ark.tensor([256, 1024], ark.fp16)
+        t = x
+        for _ in range(n):
+            t = ark.relu(ark.add(t, 1.0))
+        return x, t
+    x, y = build(8)
+    plain = ark.Planner(0, num_sm=148).plan()
+    reuse = ark.Planner(0, num_sm=148, reuse_memory=True).plan()
+    assert "ArenaReuse" not in plain.plan and reuse.plan["ArenaReuse"] is True
+    _, a_plain, _ = ark.plan_check(str(plain))
+    _, a_reuse, _ = ark.plan_check(str(reuse))
+    one = 256 * 1024 * 2
+    assert a_plain == 17 * one          # x + 16 results, bump-allocated as in the reference
+    # x (input) and y (output, never read) keep their space; the 15 intermediates cycle through 3 blocks
+    # (alive [k, k+1], one step of slack on either side)
+    assert a_reuse == 5 * one, a_reuse // one
+    # a buffer with a tag or a sharded view is never shared
+    ark.init()
+    ark.set_rank(0)
+    ark.set_world_size(2)
+    t = ark.relu(ark.add(ark.tensor([4096], ark.fp16), 1.0))
+    t = ark.all_reduce(t, 0, 2, output=t)
+    ark.relu(ark.add(t, 1.0))
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148, reuse_memory=True).plan()))
+    ark.set_world_size(1)
+    assert "arena=" in text
 
 
 def ref_allreduce_plans():
