@@ -22,12 +22,6 @@ namespace {
 constexpr int kHeadDim = 128;     // elements per head (16 lanes x 8)
 constexpr int kMaxGroup = 8;      // query heads per K/V head
 
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
-    const T *e = reinterpret_cast<const T *>(&q);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
-}
 
 template <typename T, int G>
 __device__ __noinline__ void attn_chunks(const DecodeAttnArgs &a, int p, int P, char *smem) {
@@ -202,7 +196,7 @@ __device__ void attn_typed(const DecodeAttnArgs &a, int p, int P, char *smem) {
 
 }  // namespace
 
-__device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem) {
+__device__ __noinline__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem) {
     if (a.dtype == DT_BF16) attn_typed<__nv_bfloat16>(a, p, P, smem);
     else attn_typed<__half>(a, p, P, smem);
 }

@@ -4,7 +4,7 @@
 namespace arkb {
 
 // Dense byte copy local -> peer by all CTAs of the stage.
-__device__ void run_put(const PutArgs &a, int p, int P, unsigned long long iter_no) {
+__device__ __noinline__ void run_put(const PutArgs &a, int p, int P, unsigned long long iter_no) {
     const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)P * kThreads;
     const int64_t slot = a.iter_slots > 1 ? (int64_t)((iter_no - 1) % (unsigned long long)a.iter_slots) : 0;
     const char *s = reinterpret_cast<const char *>(a.src) + slot * a.src_iter_bytes;
@@ -120,7 +120,7 @@ __device__ __forceinline__ bool ld_packet(const void *p, uint32_t f, unsigned lo
     }
 }
 
-__device__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage) {
+__device__ __noinline__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage) {
     const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)Pn * kThreads;
     const int64_t n = a.payload_bytes / 8;
     const uint32_t f = packet_flag(a.flag, iter_no);
@@ -201,7 +201,7 @@ __device__ void packet_reduce_typed(const LaunchParams &P, const PacketReduceArg
     }
 }
 
-__device__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
+__device__ __noinline__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl,
                                   int stage) {
     switch (a.dtype) {
         case DT_F32: packet_reduce_typed<float>(P, a, p, Pn, iter_no, ctl, stage); break;
@@ -211,7 +211,7 @@ __device__ void run_packet_reduce(const LaunchParams &P, const PacketReduceArgs 
     }
 }
 
-__device__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn,
+__device__ __noinline__ void run_allreduce(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn,
                                            unsigned long long iter_no) {
     switch (a.dtype) {
         case DT_F32: allreduce_typed<float>(P, a, p, Pn, iter_no); break;

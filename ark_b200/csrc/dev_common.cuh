@@ -198,6 +198,14 @@ __device__ __forceinline__ void store_vec(T *p, const float (&f)[N]) {
     }
 }
 
+// Eight 16-bit elements held in one 16-byte register quad, widened to fp32.
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
+    const T *e = reinterpret_cast<const T *>(&q);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
+}
+
 // Element offset of 4-D index (n,c,h,w) in a view.
 __device__ __forceinline__ int64_t tref_off(const TRef &t, int64_t n, int64_t c, int64_t h, int64_t w) {
     return n * t.stride[0] + c * t.stride[1] + h * t.stride[2] + w * t.stride[3];

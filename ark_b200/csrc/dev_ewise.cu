@@ -350,7 +350,7 @@ __device__ void ewise_convert(const EwiseArgs &a, int p, int P) {
     }
 }
 
-__device__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
+__device__ __noinline__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
     const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
     if (a.op == EW_COPY && idt == a.out.dtype) {
         const int es = (idt == DT_F32 || idt == DT_I32 || idt == DT_U32) ? 4 : (idt == DT_F16 || idt == DT_BF16) ? 2 : 1;

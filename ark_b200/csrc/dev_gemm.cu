@@ -483,7 +483,7 @@ __device__ __noinline__ bool gemm_drain(const GemmRun &R, int warp, int lane) {
 }
 
 template <bool PAIR, bool GROUPED>
-__device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+__device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                            DeviceState *st, int stage_idx, unsigned long long lim) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     GemmRun R;
@@ -542,12 +542,12 @@ __device__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int 
     __syncthreads();
 }
 
-__device__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+__device__ __noinline__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                          DeviceState *st, int stage_idx, unsigned long long spin_limit) {
     if (g.kgroup > 1) run_gemm_t<false, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
     else run_gemm_t<false, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
-__device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
+__device__ __noinline__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                               DeviceState *st, int stage_idx, unsigned long long spin_limit) {
     if (g.kgroup > 1) run_gemm_t<true, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
     else run_gemm_t<true, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
@@ -584,7 +584,7 @@ __device__ void splitk_reduce_typed(const SplitKReduceArgs &a, int p, int P) {
     }
 }
 
-__device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P) {
+__device__ __noinline__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P) {
     if (a.dtype == DT_BF16) splitk_reduce_typed<__nv_bfloat16>(a, p, P);
     else splitk_reduce_typed<__half>(a, p, P);
 }
@@ -651,7 +651,7 @@ __device__ void gemm_simt_typed(const GemmSimtArgs &g, int p, int P, char *smem)
     }
 }
 
-__device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem) {
+__device__ __noinline__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem) {
     switch (g.dtype) {
         case DT_F32: gemm_simt_typed<float>(g, p, P, smem); break;
         case DT_F16: gemm_simt_typed<__half>(g, p, P, smem); break;

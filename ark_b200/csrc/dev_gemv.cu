@@ -26,12 +26,6 @@ namespace arkb {
 
 namespace {
 
-template <typename T>
-__device__ __forceinline__ void unpack8(const uint4 &q, float (&f)[8]) {
-    const T *e = reinterpret_cast<const T *>(&q);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = to_f32(e[i]);
-}
 
 // Sum over the CTA of one float per thread (all threads call it; `scratch` holds one float per warp).
 __device__ __forceinline__ float cta_sum(float v, float *scratch) {
@@ -369,7 +363,7 @@ __device__ void gemv_typed(const GemvArgs &a, int p, int P, char *smem, const Pu
 
 }  // namespace
 
-__device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no) {
+__device__ __noinline__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no) {
     const PushTo push = push_targets(a, LP, iter_no);
     if (a.dtype == DT_BF16) gemv_typed<__nv_bfloat16>(a, p, P, smem, push);
     else gemv_typed<__half>(a, p, P, smem, push);

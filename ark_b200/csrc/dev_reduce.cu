@@ -223,7 +223,7 @@ __device__ __forceinline__ void reduce_typed(const ReduceArgs &a, int p, int P, 
     }
 }
 
-__device__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem) {
+__device__ __noinline__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem) {
     float *red = reinterpret_cast<float *>(smem);  // kThreads x 8 floats at most
     switch (a.in.dtype) {
         case DT_F32: reduce_typed<float>(a, p, P, red); break;
@@ -237,6 +237,13 @@ __device__ void run_reduce(const ReduceArgs &a, int p, int P, char *smem) {
 // One warp per row. Pass 1 accumulates the row statistics in fp32, pass 2
 // re-reads the row (it is still in L2) and writes the result: HBM sees one
 // read and one write per element.
+// The scale row of a norm: in the rows' own type, or fp32 when the model keeps it so.
+template <typename T, int V>
+__device__ __forceinline__ void load_row_weight(const RowOpArgs &a, int64_t e, float (&g)[V]) {
+    if (a.weight_f32) load_vec_cached<float, V>(reinterpret_cast<const float *>(a.weight) + e, g);
+    else load_vec_cached<T, V>(reinterpret_cast<const T *>(a.weight) + e, g);
+}
+
 template <typename T>
 __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
     constexpr int V = 16 / sizeof(T);
@@ -339,7 +346,7 @@ __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
                 for (int i = 0; i < V; ++i) f[i] = (f[i] - sub) * mul;
                 if (wgt) {
                     float g[V];
-                    load_vec_cached<T, V>(wgt + v * V, g);
+                    load_row_weight<T, V>(a, (int64_t)v * V, g);
 #pragma unroll
                     for (int i = 0; i < V; ++i) f[i] *= g[i];
                 }
@@ -477,7 +484,7 @@ __device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
                     for (int i = 0; i < V; ++i) f[i] = (to_f32(e[i]) - sub) * mul;
                     if (wgt) {
                         float g[V];
-                        load_vec_cached<T, V>(wgt + v * V, g);
+                        load_row_weight<T, V>(a, (int64_t)v * V, g);
 #pragma unroll
                         for (int i = 0; i < V; ++i) f[i] *= g[i];
                     }
@@ -622,7 +629,7 @@ __device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCt
                 for (int k = 0; k < V; ++k) f[k] = (to_f32(e[k]) - sub) * mul;
                 if (wgt) {
                     float g[V];
-                    load_vec_cached<T, V>(wgt + v * V, g);
+                    load_row_weight<T, V>(a, (int64_t)v * V, g);
 #pragma unroll
                     for (int k = 0; k < V; ++k) f[k] *= g[k];
                 }
@@ -667,7 +674,7 @@ __device__ __forceinline__ void rowop_dispatch(const RowOpArgs &a, int p, int P,
     else rowop_typed<T>(a, p, P);
 }
 
-__device__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
+__device__ __noinline__ void run_rowop(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
                           unsigned long long wait_limit) {
     switch (a.dtype) {
         case DT_F32: rowop_dispatch<float>(a, p, P, smem, ctl, st, stage_idx, wait_limit); break;
@@ -716,7 +723,7 @@ __device__ void transpose_es(const TransposeArgs &a, int p, int P, char *smem) {
     }
 }
 
-__device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem) {
+__device__ __noinline__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem) {
     const int dt = a.in.dtype;
     if (dt == DT_F32 || dt == DT_I32 || dt == DT_U32) transpose_es<4>(a, p, P, smem);
     else if (dt == DT_F16 || dt == DT_BF16) transpose_es<2>(a, p, P, smem);
@@ -725,7 +732,7 @@ __device__ void run_transpose(const TransposeArgs &a, int p, int P, char *smem) 
 
 // Row gather (ark/include/kernels/embedding.h; host op ark/ops/ops_embedding.cpp:37-70):
 // one warp per index, negative indices wrap.
-__device__ void run_embed(const EmbedArgs &a, int p, int P) {
+__device__ __noinline__ void run_embed(const EmbedArgs &a, int p, int P) {
     constexpr int WPC = kThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row_bytes = a.emb_dim * a.esize;

@@ -257,7 +257,7 @@ void Executor::launch_kernel(int iters) {
     CUDA_CHECK(cudaMemsetAsync(state_, 0, sizeof(unsigned long long) * (kMaxSyncGroups + 1), stream_));  // barrier[] and run_seq
     LaunchParams P;
     fill_params(P, iters);
-    CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_));
+    CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_, program_.smem_bytes));
     ++n_launches_;
 }
 
@@ -283,7 +283,7 @@ void Executor::probe_blocking_launch() {
     P.loop_mode = 1;
     P.idle_limit_ns = 2ull * 1000000;
     P.stage_times = nullptr;
-    CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_));
+    CUDA_CHECK(loop_kernel_launch(P, program_.grid, stream_, program_.smem_bytes));
     blocking_launch_ = stream_idle();
     if (!blocking_launch_) {
         *reinterpret_cast<volatile int32_t *>(&host_flags_[0]) = -1;

@@ -9,6 +9,7 @@
 #include "dev_gemm.cuh"
 #include "loop_kernel.h"
 
+#include <algorithm>
 #include <cstring>
 
 namespace arkb {
@@ -252,12 +253,13 @@ cudaError_t loop_kernel_prepare() {
 // The grid barriers need every CTA resident at once, so the launch is cooperative: it is refused
 // (cudaErrorCooperativeLaunchTooLarge) or queued behind other work instead of deadlocking when the grid
 // does not fit beside what already runs on the device.
-cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream) {
+cudaError_t loop_kernel_launch(const LaunchParams &P, int grid, cudaStream_t stream, size_t smem_bytes) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = loop_kernel_smem_bytes();
+    // + 1 KiB: the kernel rounds its base up to 1 KiB (128-byte swizzle atoms)
+    cfg.dynamicSmemBytes = smem_bytes ? std::min(smem_bytes + 1024, loop_kernel_smem_bytes()) : loop_kernel_smem_bytes();
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;

@@ -10,6 +10,7 @@
 // otherwise ignored) — here a whole CTA works on one stage at a time and an
 // op's work is split over the CTAs of its range by the op's own kernel.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <set>
@@ -20,6 +21,8 @@
 namespace arkb {
 
 namespace {
+
+constexpr size_t kFullSmemBytes = 208 * 1024;  // operand ring (192 KiB) + epilogue staging (16 KiB) of the tensor-core matmul
 
 struct Lowerer {
     const Plan &plan;
@@ -379,7 +382,11 @@ struct Lowerer {
         a.eps = op.has_arg("Eps") ? (float)op.arg_float("Eps") : 1e-5f;
         a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
         size_t ri = 1;
-        if (a.op == RO_RMSNORM && op.reads.size() > ri && op.reads[ri].nelems() == a.cols) a.weight = tensor_ptr(op.reads[ri++]);
+        if (a.op == RO_RMSNORM && op.reads.size() > ri && op.reads[ri].nelems() == a.cols) {
+            a.weight_f32 = (op.reads[ri].dtype == DT_F32 && in.dtype != DT_F32) ? 1 : 0;
+            if (!a.weight_f32 && op.reads[ri].dtype != in.dtype) throw Error(E_MODEL, "RMSNorm: the weight must have the rows' type or be FP32");
+            a.weight = tensor_ptr(op.reads[ri++]);
+        }
         if (op.has_arg("Residual") && op.arg_bool("Residual")) {
             if (op.reads.size() <= ri || op.results.size() < 2) throw Error(E_MODEL, op.type + ": residual form needs 2 results");
             a.residual = tensor_ptr(op.reads[ri]);
@@ -470,6 +477,8 @@ struct Lowerer {
         const TensorDesc *out = nullptr;      // result tensor of the last folded operator
         int push_ord = -1;                    // >= 0: ordinal of the one-shot all_reduce whose push this matmul does
     };
+    std::vector<OpDesc> fused_ops;          // row operators that stand for a chain of the plan's operators
+    std::map<size_t, size_t> chain_pgs;     // first processor group of such a chain -> index into fused_ops
     bool gemv_pushed = false;  // set by lower_matmul when the push of a one-shot all_reduce was folded in
 
     // an AllReduce the engine runs one-shot (every rank pushes its tensor into every rank's staging slots)
@@ -1276,6 +1285,115 @@ struct Lowerer {
         }
     }
 
+    // ---- op chains the reference composes for softmax / layernorm / rmsnorm -> one row kernel --------------
+    // Unmodified reference models emit these as 5-7 operators (python/ark/ops.py:491-513,
+    // examples/llama/model.py:92-99); run one after the other each costs a pass over the tensor and a barrier. When
+    // the operators follow each other (inside one task, or as consecutive single-operator processor groups) and
+    // nothing else reads the intermediates, the chain is lowered to the fused row kernel instead.
+    bool private_to(const TensorDesc &t, const std::vector<const OpDesc *> &chain, int64_t out_buffer) const {
+        if (t.buffer_id == out_buffer) return true;  // in-place chains: outsiders see the final value
+        for (auto &ti : plan.task_infos)
+            for (auto &o : ti.ops) {
+                if (std::find(chain.begin(), chain.end(), &o) != chain.end()) continue;
+                for (auto &rd : o.reads)
+                    if (rd.buffer_id == t.buffer_id) return false;
+            }
+        return true;
+    }
+    static bool last_axis(const OpDesc &op) {
+        if (!op.has_arg("Axis") || op.reads.empty()) return false;
+        const int nd = (int)op.reads[0].shape.size();
+        int ax = (int)op.arg_int("Axis");
+        if (ax < 0) ax += nd;
+        return ax == nd - 1;
+    }
+    static bool reads_ids(const OpDesc &op, int64_t a, int64_t b = -1) {
+        if (b < 0) return op.reads.size() == 1 && op.reads[0].id == a;
+        return op.reads.size() == 2 && op.reads[0].id == a && op.reads[1].id == b;
+    }
+    static bool fp_type(int dt) { return dt == DT_F32 || dt == DT_F16 || dt == DT_BF16; }
+
+    // Tries to match a chain starting at seq[i]; on success fills `fused` (a RowOp operator) and returns its length.
+    size_t match_chain(const std::vector<const OpDesc *> &seq, size_t i, OpDesc &fused) const {
+        if (const char *e = getenv("ARKB_FUSE_CHAINS")) if (!atoi(e)) return 0;
+        auto T = [&](size_t k) -> const OpDesc & { return *seq[i + k]; };
+        auto have = [&](size_t n) { return i + n <= seq.size(); };
+        auto res = [&](size_t k) -> const TensorDesc & { return T(k).results.at(0); };
+        auto chain_of = [&](size_t n) { return std::vector<const OpDesc *>(seq.begin() + i, seq.begin() + i + n); };
+        for (size_t k = 0; have(k + 1) && k < 7; ++k)
+            if (T(k).results.empty() || T(k).reads.empty()) return 0;
+        // softmax: max = ReduceMax(x); s = Sub(x, max); e = Exp(s); z = ReduceSum(e); y = Div(e, z)
+        if (have(5) && T(0).type == "ReduceMax" && T(1).type == "Sub" && T(2).type == "Exp" && T(3).type == "ReduceSum" &&
+            T(4).type == "Div" && last_axis(T(0)) && last_axis(T(3))) {
+            const TensorDesc &x = T(0).reads[0], &y = res(4);
+            if (reads_ids(T(1), x.id, res(0).id) && reads_ids(T(2), res(1).id) && reads_ids(T(3), res(2).id) &&
+                reads_ids(T(4), res(2).id, res(3).id) && fp_type(x.dtype) && y.dtype == x.dtype && y.shape4() == x.shape4()) {
+                auto ch = chain_of(5);
+                bool ok = true;
+                for (size_t k = 0; k < 4; ++k) ok = ok && private_to(res(k), ch, y.buffer_id);
+                if (ok) {
+                    fused = OpDesc();
+                    fused.type = "Softmax";
+                    fused.name = T(0).name + "..." + T(4).name;
+                    fused.reads = {x};
+                    fused.results = {y};
+                    return 5;
+                }
+            }
+        }
+        // layernorm: m = ReduceMean(x); c = Sub(x, m); q = Mul(c, c); v = ReduceMean(q); a = ScalarAdd(v, eps);
+        //            r = Rsqrt(a); y = Mul(c, r)
+        if (have(7) && T(0).type == "ReduceMean" && T(1).type == "Sub" && T(2).type == "Mul" && T(3).type == "ReduceMean" &&
+            T(4).type == "ScalarAdd" && T(5).type == "Rsqrt" && T(6).type == "Mul" && last_axis(T(0)) && last_axis(T(3))) {
+            const TensorDesc &x = T(0).reads[0], &y = res(6);
+            if (reads_ids(T(1), x.id, res(0).id) && reads_ids(T(2), res(1).id, res(1).id) && reads_ids(T(3), res(2).id) &&
+                reads_ids(T(4), res(3).id) && reads_ids(T(5), res(4).id) && reads_ids(T(6), res(1).id, res(5).id) &&
+                fp_type(x.dtype) && y.dtype == x.dtype && y.shape4() == x.shape4()) {
+                auto ch = chain_of(7);
+                bool ok = true;
+                for (size_t k = 0; k < 6; ++k) ok = ok && private_to(res(k), ch, y.buffer_id);
+                if (ok) {
+                    fused = OpDesc();
+                    fused.type = "LayerNorm";
+                    fused.name = T(0).name + "..." + T(6).name;
+                    fused.reads = {x};
+                    fused.results = {y};
+                    {
+                        char eps[64];
+                        snprintf(eps, sizeof(eps), "%.9g", T(4).arg_float("Factor"));
+                        fused.args = Json::parse(std::string("{\"Eps\": {\"FLOAT\": ") + eps + "}}");
+                    }
+                    return 7;
+                }
+            }
+        }
+        // rmsnorm as the llama example writes it: f = Cast(x, fp32); q = Mul(f, f); m = ReduceMean(q); r = Rsqrt(m);
+        // n = Mul(f, r); w = Mul(n, weight); y = Cast(w, type of x). No epsilon is added (examples/llama/model.py:96).
+        if (have(7) && T(0).type == "Cast" && T(1).type == "Mul" && T(2).type == "ReduceMean" && T(3).type == "Rsqrt" &&
+            T(4).type == "Mul" && T(5).type == "Mul" && T(6).type == "Cast" && last_axis(T(2))) {
+            const TensorDesc &x = T(0).reads[0], &y = res(6);
+            if (res(0).dtype == DT_F32 && (x.dtype == DT_F16 || x.dtype == DT_BF16) && y.dtype == x.dtype && y.shape4() == x.shape4() &&
+                reads_ids(T(1), res(0).id, res(0).id) && reads_ids(T(2), res(1).id) && reads_ids(T(3), res(2).id) &&
+                reads_ids(T(4), res(0).id, res(3).id) && T(5).reads.size() == 2 && T(5).reads[0].id == res(4).id &&
+                reads_ids(T(6), res(5).id)) {
+                const TensorDesc &w = T(5).reads[1];
+                auto ch = chain_of(7);
+                bool ok = w.dtype == DT_F32 && w.nelems() == x.shape4()[3] && w.dense();
+                for (size_t k = 0; k < 6; ++k) ok = ok && private_to(res(k), ch, y.buffer_id);
+                if (ok) {
+                    fused = OpDesc();
+                    fused.type = "RMSNorm";
+                    fused.name = T(0).name + "..." + T(6).name;
+                    fused.reads = {x, w};
+                    fused.results = {y};
+                    fused.args = Json::parse("{\"Eps\": {\"FLOAT\": 0.0}}");
+                    return 7;
+                }
+            }
+        }
+        return 0;
+    }
+
     // ---- task dispatch --------------------------------------------------------------------
     void lower_op(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
         if (op.is_virtual) return;
@@ -1306,6 +1424,18 @@ struct Lowerer {
         for (size_t i = 0; i < ti.ops.size(); ++i) {
             const OpDesc &op = ti.ops[i];
             if (op.is_virtual) continue;
+            {   // a softmax / layernorm / rmsnorm chain inside one task (the ops were merged with Sync=false)
+                std::vector<const OpDesc *> seq;
+                for (size_t j = i; j < ti.ops.size() && j < i + 7 && !ti.ops[j].is_virtual; ++j) seq.push_back(&ti.ops[j]);
+                OpDesc fused;
+                if (const size_t n = match_chain(seq, 0, fused)) {
+                    if (!first) emit_sync(proc);
+                    lower_rowop(fused, proc);
+                    first = false;
+                    i += n - 1;
+                    continue;
+                }
+            }
             // Matmul followed by a unary activation on its result, merged into one task
             // by the planner (Sync=false): run the activation in the GEMM epilogue.
             // [RMSNorm | Mul] Matmul [activation] [Add]: one weight-streaming stage when the Matmul is one
@@ -1612,7 +1742,47 @@ struct Lowerer {
         prog.pair_mode = env.allow_pair && pair_eligible();
         std::vector<Range> unsynced;
         bool first_pg = true;
-        for (auto &pg : plan.processor_groups) {
+        // a processor group that holds exactly one operator over its full task range: the only op of the only task of
+        // its only resource group (what the planner emits for an operator outside any context)
+        auto single_op = [&](const ProcessorGroup &g) -> const OpDesc * {
+            if (g.resource_groups.size() != 1 || g.resource_groups[0].task_groups.size() != 1) return nullptr;
+            const TaskGroup &tg = g.resource_groups[0].task_groups[0];
+            const TaskInfo &ti = plan.task(tg.task_id);
+            const OpDesc *only = nullptr;
+            for (auto &o : ti.ops) {
+                if (o.is_virtual) continue;
+                if (only) return nullptr;
+                only = &o;
+            }
+            if (!only || !full_range(tg.task_range, num_tasks(*only))) return nullptr;
+            return only;
+        };
+        size_t skip_pgs = 0;
+        for (size_t pgi = 0; pgi < plan.processor_groups.size(); ++pgi) {
+            if (skip_pgs) { --skip_pgs; continue; }
+            const ProcessorGroup *pgp = &plan.processor_groups[pgi];
+            ProcessorGroup merged;
+            {   // a chain spread over consecutive single-operator processor groups becomes one group with one fused operator
+                std::vector<const OpDesc *> seq;
+                Range widest = pgp->proc;
+                for (size_t k = pgi; k < plan.processor_groups.size() && k < pgi + 7; ++k) {
+                    const OpDesc *o = single_op(plan.processor_groups[k]);
+                    if (!o) break;
+                    seq.push_back(o);
+                }
+                OpDesc fused;
+                if (const size_t n = seq.empty() ? 0 : match_chain(seq, 0, fused)) {
+                    for (size_t k = pgi; k < pgi + n; ++k) {
+                        const Range &r = plan.processor_groups[k].proc;
+                        if (r.s == 1 && r.count() > widest.count()) widest = r;
+                    }
+                    fused_ops.push_back(fused);
+                    merged.proc = widest;
+                    chain_pgs[pgi] = fused_ops.size() - 1;
+                    skip_pgs = n - 1;
+                }
+            }
+            const ProcessorGroup &pg = chain_pgs.count(pgi) ? merged : *pgp;
             const Range &pr = pg.proc;
             if (pr.count() == 0) continue;
             if (!first_pg) {
@@ -1635,6 +1805,7 @@ struct Lowerer {
                 }
                 if (need_sync) emit_sync(pr);
             }
+            if (chain_pgs.count(pgi)) lower_rowop(fused_ops[chain_pgs[pgi]], pr);
             for (auto &rg : pg.resource_groups) {
                 std::set<int64_t> prev_w;
                 bool any = false;
@@ -1658,6 +1829,36 @@ struct Lowerer {
         }
         elide_syncs();
         plan_prefetch();
+        // dynamic shared memory: the largest need of any stage
+        size_t smem = 16 * 1024;
+        for (auto &s : prog.stages) {
+            size_t need = 0;
+            switch (s.kind) {
+                case SK_GEMM: need = kFullSmemBytes; break;
+                case SK_GEMM_SIMT: need = 16 * 1024; break;
+                case SK_REDUCE: need = (size_t)kThreads * 8 * sizeof(float); break;
+                case SK_ROWOP:
+                    if (s.ro.staged_warps > 0) {
+                        const size_t row = (size_t)s.ro.cols * dtype_size(s.ro.dtype);
+                        need = (size_t)s.ro.staged_warps * s.ro.staged_bufs * ((row + 127) / 128 * 128) + 1024;
+                    } else {
+                        need = 16 * 1024;
+                    }
+                    break;
+                case SK_GEMV:
+                    need = (size_t)s.gv.M * (size_t)std::max(s.gv.kper, s.gv.K) * sizeof(float) + 4096;
+                    break;
+                case SK_DECODE_ATTN: {
+                    const size_t G = (size_t)(s.da.Hq / std::max(1, s.da.Hkv));
+                    need = (G * 128 + 16 + G * (size_t)s.da.chunk_len + 16 * G * 128) * sizeof(float) + 1024;
+                    break;
+                }
+                default: break;
+            }
+            smem = std::max(smem, need);
+        }
+        prog.smem_bytes = std::min<size_t>((smem + 1023) / 1024 * 1024, kFullSmemBytes);
+        if (const char *e = getenv("ARKB_FULL_SMEM")) if (atoi(e)) prog.smem_bytes = kFullSmemBytes;
         prog.n_sync_groups = (int)sync_ids.size();
         prog.oneshots_per_iter = oneshot_ord;
         for (auto &s : prog.stages) {

@@ -198,6 +198,8 @@ struct Program {
     int peersyncs_per_iter = 0;
     int oneshots_per_iter = 0;
     int syncs_elided = 0;  // barriers of the straightforward lowering that the dependency pass removed
+    size_t smem_bytes = 0;  // dynamic shared memory the stages of this program need (the launch asks for no more: what is
+                            // left of the SM's 256 KiB serves as L1, where the stage functions' stack frames then stay)
     size_t prefetch_bytes = 0;  // bytes per iteration that barrier stages ask the L2 to fetch ahead of their readers
     size_t workspace_bytes = 0;  // scratch the program needs beyond the arena (split-K partials)
     bool pair_mode = false;  // launch clusters of 2 CTAs; matmul tiles are 256 x tile_n per pair

@@ -102,6 +102,8 @@ struct RowOpArgs {
     int32_t mask_rows;     // softmax: logits := logits * scale + mask[row % mask_rows] first (rounded to the storage type)
     const void *mask;      // optional additive mask, mask_rows x cols, row pitch mask_ld
     int64_t mask_ld;
+    int32_t weight_f32;    // 1: `weight` holds fp32 values whatever the rows' type (the llama example keeps its norm weights in fp32)
+    int32_t pad;
 };
 
 // Shared memory the loop kernel offers a matmul stage for operand ring slots when its epilogue needs no staging

@@ -6,7 +6,7 @@ import pytest
 
 import ark_b200 as ark
 from oracle import oracle as O
-from tests.ark_util import NAME, assert_close, execute, rand
+from tests.ark_util import ulp_tol, NAME, assert_close, execute, rand
 
 pytestmark = pytest.mark.gpu
 FLOATS = ["fp32", "fp16", "bf16"]
@@ -89,17 +89,87 @@ def test_softmax_with_scale_and_additive_mask(dt, shape, mrows):
     assert_close(got, want, dt, rtol=tol, atol=1e-7 if dt == "fp32" else 1e-5, what="masked softmax")
 
 
-def test_fused_rows_match_the_reference_compositions():
-    """softmax/layernorm as the reference composes them (python/ark/ops.py:491-513) vs the fused kernels."""
+def test_fused_rows_match_the_reference_compositions(monkeypatch):
+    """softmax/layernorm as the reference composes them (python/ark/ops.py:491-513), run operator by operator
+    (chain recognition switched off), vs the fused kernels."""
+    monkeypatch.setenv("ARKB_FUSE_CHAINS", "0")
     rng = np.random.default_rng(24)
     x = rng.normal(0, 1, (16, 512)).astype(np.float32)
     ark.init()
     t = ark.tensor([16, 512], ark.fp32)
     f1, f2 = ark.softmax(t, fused=True), ark.layernorm(t, fused=True)
     c1, c2 = ark.softmax(t, fused=False), ark.layernorm(t, fused=False)
-    g = execute([f1, f2, c1, c2], {t: x})
+    plan = ark.Planner(0).plan()
+    assert ark.plan_dump(str(plan)).count("ReduceM") >= 3  # the compositions stay operator by operator
+    g = execute([f1, f2, c1, c2], {t: x}, plan=plan)
     assert np.allclose(g[0], g[2], rtol=1e-5, atol=1e-7)
     assert np.allclose(g[1], g[3], rtol=1e-4, atol=1e-5)
+
+
+def _ref_softmax(x):
+    m = ark.reduce_max(x, axis=-1)
+    o = ark.sub(x, m)
+    o = ark.exp(o, o)
+    s = ark.reduce_sum(o, axis=-1)
+    return ark.div(o, s, o)
+
+
+def _ref_layernorm(x, eps):
+    mean = ark.reduce_mean(x, axis=-1)
+    c = ark.sub(x, mean)
+    var = ark.reduce_mean(ark.mul(c, c), axis=-1)
+    return ark.mul(c, ark.rsqrt(ark.add(var, eps)))
+
+
+def _ref_rmsnorm(x, w, dt):
+    f = ark.cast(x, ark.fp32)
+    r = ark.rsqrt(ark.reduce_mean(ark.mul(f, f), axis=-1))
+    f2 = ark.mul(f, r)
+    return ark.cast(ark.mul(f2, w, f2), NAME[dt])
+
+
+@pytest.mark.parametrize("merged", [False, True])
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+def test_reference_op_chains_run_as_one_row_kernel(dt, merged):
+    """The op chains an unmodified reference model emits for softmax (python/ark/ops.py:491-500), layernorm
+    (:503-513) and the llama example's RMSNorm (examples/llama/model.py:92-99: fp32 weight, no epsilon) are
+    recognised, whether the planner left every operator in its own task or merged them (Sync=false), and lowered to
+    the fused row kernel; results against the oracle's per-operator composition in the reference's op order."""
+    rng = np.random.default_rng(27)
+    rows, cols = 96, 2048
+    x = rand(rng, (rows, cols), dt, -2.0, 2.0)
+    w = rng.normal(1.0, 0.1, (1, cols)).astype(np.float32)
+    ark.init()
+    tx, tw = ark.tensor([rows, cols], NAME[dt]), ark.tensor([1, cols], ark.fp32)
+
+    def build():
+        return _ref_softmax(tx), _ref_layernorm(tx, 1e-5), _ref_rmsnorm(tx, tw, dt)
+    if merged:
+        outs = []
+        for f in (lambda: _ref_softmax(tx), lambda: _ref_layernorm(tx, 1e-5), lambda: _ref_rmsnorm(tx, tw, dt)):
+            with ark.PlannerContext(sync=False):
+                outs.append(f())
+    else:
+        outs = list(build())
+    plan = ark.Planner(0).plan()
+    text = ark.plan_dump(str(plan))
+    assert "Softmax reduce_max...div" in text and "LayerNorm reduce_mean" in text and "RMSNorm cast" in text, text
+    assert "ReduceMax" not in text and " Exp " not in text and " Cast " not in text
+    got = execute(outs, {tx: x, tw: w}, plan=plan)
+    # the reference's own arithmetic: every operator rounds to the storage type
+    m = O.reduce("max", x, -1, dt)
+    e = O.unary("exp", O.binary("sub", x, m, dt), dt)
+    want_sm = O.binary("div", e, O.reduce("sum", e, -1, dt), dt)
+    c = O.binary("sub", x, O.reduce("mean", x, -1, dt), dt)
+    var = O.reduce("mean", O.binary("mul", c, c, dt), -1, dt)
+    want_ln = O.binary("mul", c, O.unary("rsqrt", O.scalar("add", var, 1e-5, dt), dt), dt)
+    f = O.cast(x, dt, "fp32")
+    r = O.unary("rsqrt", O.reduce("mean", O.binary("mul", f, f, "fp32"), -1, "fp32"), "fp32")
+    want_rn = O.cast(O.binary("mul", O.binary("mul", f, r, "fp32"), w, "fp32"), "fp32", dt)
+    tol = 4 * ulp_tol(dt)  # the chain rounds its intermediates, the row kernel rounds once
+    assert_close(got[0], want_sm, dt, rtol=tol, atol=tol * 0.01, what="softmax chain")
+    assert_close(got[1], want_ln, dt, rtol=tol, atol=tol * 2.0, what="layernorm chain")
+    assert_close(got[2], want_rn, dt, rtol=tol, atol=tol * 0.1, what="rmsnorm chain")
 
 
 @pytest.mark.parametrize("dt", ["fp32", "fp16"])
