@@ -58,10 +58,9 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
             scores = O.binary("add", scores, mask, dt)
             probs = O.softmax(scores, dt)
         else:
-            # the engine's softmax multiplies by the scale in fp32 before the max/exp
-            sf = f32(scores) * np.float32(scale)
-            e = np.exp(sf - sf.max(-1, keepdims=True))
-            probs = st(e / e.sum(-1, keepdims=True))
+            # the engine's softmax multiplies by the scale in fp32 before the max/exp: the oracle's operators on the
+            # fp32 values, one rounding at the end
+            probs = st(O.softmax(O.scalar("mul", f32(scores), scale, "fp32"), "fp32"))
         o = O.matmul(probs, v, dt)
         o = np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(bt, hl * hd)
         attn_parts.append(O.matmul(o, w["wo"], dt, trans_b=True))
@@ -71,9 +70,9 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
     for r in range(p):
         w = ws[r]
         h2 = O.rmsnorm(x1, w["ffn_norm"], dt, cfg.norm_eps)
-        # SiLU runs on the fp32 accumulator in the epilogue: recompute the gate in fp32
-        a32 = f32(h2).astype(np.float32) @ f32(w["w1"]).astype(np.float32).T
-        gate = st(a32 / (1.0 + np.exp(-a32)))
+        # SiLU runs on the fp32 accumulator in the epilogue: the oracle's matmul, sigmoid and mul on fp32 values
+        a32 = O.matmul(f32(h2), f32(w["w1"]), "fp32", trans_b=True)
+        gate = st(O.binary("mul", a32, O.unary("sigmoid", a32, "fp32"), "fp32"))
         up = O.matmul(h2, w["w3"], dt, trans_b=True)
         g = O.binary("mul", gate, up, dt)
         down_parts.append(O.matmul(g, w["w2"], dt, trans_b=True))

@@ -116,3 +116,60 @@ def test_decode_attention_against_float64(dt, b, hq, hkv, t):
     err = np.abs(O.to_f32(got, dt).astype(np.float64) - want)
     tol = 2e-3 if dt == "fp16" else 1.6e-2   # one rounding of outputs of magnitude <= ~1
     assert float(err.max()) <= tol, float(err.max())
+
+
+# Per-rank shapes of the two Llama-shaped benchmark configurations at tensor-parallel degree 8 (one rank's share of
+# the heads and of the feed-forward width, full d_model, full sequence / cache lengths), against the oracle's per-op
+# composition of the whole layer. (The sum over ranks is covered by the multi-GPU tests.)
+REAL = {
+    "7b": dict(cfg=dict(dim=4096, n_heads=4, n_kv_heads=4, ffn_dim=1376), dt="fp16", prefill=(1, 2048), decode=(1, 2048)),
+    "70b": dict(cfg=dict(dim=8192, n_heads=8, n_kv_heads=1, ffn_dim=3584), dt="bf16", prefill=(4, 1024), decode=(16, 4096)),
+}
+
+
+@pytest.mark.parametrize("model", ["7b", "70b"])
+def test_decode_layer_at_benchmark_shapes(model):
+    spec = REAL[model]
+    dt, (batch, t_kv) = spec["dt"], spec["decode"]
+    cfg = LlamaConfig(**spec["cfg"])
+    rng = np.random.default_rng(61)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(1, cfg.head_dim, start=t_kv), dt)
+    kc = O.to_storage(rng.normal(0, 1, (batch, cfg.n_kv_heads, t_kv, cfg.head_dim)).astype(np.float32), dt)
+    vc = O.to_storage(rng.normal(0, 1, (batch, cfg.n_kv_heads, t_kv, cfg.head_dim)).astype(np.float32), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx, tr = ark.tensor([batch, cfg.dim], NAME[dt]), ark.tensor([1, 1, 1, cfg.head_dim], NAME[dt])
+    tk, tv = ark.tensor(list(kc.shape), NAME[dt]), ark.tensor(list(vc.shape), NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, 1, 0, 1, rope=tr, k_cache=tk, v_cache=tv)
+    feeds = {tx: x, tr: rope, tk: kc, tv: vc}
+    feeds.update({tw[k]: w[k] for k in w if k not in ("wk", "wv")})
+    (got,) = execute([ty], feeds, loop_mode=True, iters=2)
+    want = layer(x, [w], cfg, batch, 1, dt, rope=rope, k_caches=[kc], v_caches=[vc])
+    check(got, want, dt)
+
+
+@pytest.mark.parametrize("model", ["7b", "70b"])
+def test_prefill_layer_at_benchmark_shapes(model):
+    spec = REAL[model]
+    dt, (batch, seq) = spec["dt"], spec["prefill"]
+    cfg = LlamaConfig(**spec["cfg"])
+    rng = np.random.default_rng(62)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), dt)
+    mask = O.to_storage(causal_mask(seq, dt), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx = ark.tensor([batch * seq, cfg.dim], NAME[dt])
+    tr, tm = ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt]), ark.tensor([1, 1, seq, seq], NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
+    feeds = {tx: x, tr: rope, tm: mask}
+    feeds.update({tw[k]: w[k] for k in w})
+    (got,) = execute([ty], feeds, loop_mode=True)
+    # the oracle composes the whole layer of ONE sequence on the host cores (sequences are independent); the engine
+    # ran all of them, the last one is compared
+    b = batch - 1
+    want = layer(np.ascontiguousarray(x[b * seq:(b + 1) * seq]), [w], cfg, 1, seq, dt, rope=rope, mask=mask)
+    check(got[b * seq:(b + 1) * seq], want, dt)
