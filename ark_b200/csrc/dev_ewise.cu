@@ -350,7 +350,11 @@ __device__ void ewise_convert(const EwiseArgs &a, int p, int P) {
     }
 }
 
-__device__ __noinline__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
+// The full walkers above keep many loads in flight and need most of the register file; a function that uses many
+// registers saves and restores them on every call (they live in the caller's hands by the calling convention),
+// which costs ~2 us per stage whatever the tensor size. Small problems (a few units per thread: decode) therefore
+// take a walker written for few registers; the dispatcher itself stays tiny.
+__device__ __noinline__ void ewise_heavy(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
     const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
     if (a.op == EW_COPY && idt == a.out.dtype) {
         const int es = (idt == DT_F32 || idt == DT_I32 || idt == DT_U32) ? 4 : (idt == DT_F16 || idt == DT_BF16) ? 2 : 1;
@@ -369,6 +373,75 @@ __device__ __noinline__ void run_ewise(const EwiseArgs &a, int p, int P, unsigne
         case DT_BF16: ewise_typed<__nv_bfloat16, __nv_bfloat16>(a, p, P); break;
         default: break;
     }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void ewise_light_walk(const EwiseArgs &a, int p, int P) {
+    const int op = a.op;
+    const bool bin = ewise_is_binary(op), rd0 = ewise_reads_in0(op);
+    T *out = reinterpret_cast<T *>(a.out.ptr);
+    const T *in0 = reinterpret_cast<const T *>(a.in0.ptr);
+    const T *in1 = reinterpret_cast<const T *>(a.in1.ptr);
+    const int nth = P * kThreads;
+    const int n_units = (int)a.n_units;
+    const int WV = (a.out.shape[3] + V - 1) / V, H = a.out.shape[2], C = a.out.shape[1];
+    for (int u = p * kThreads + threadIdx.x; u < n_units; u += nth) {
+        int64_t oo, o0, o1;
+        if (a.flat) {
+            oo = o0 = o1 = (int64_t)u * V;
+        } else {
+            const int wv = u % WV;
+            int row = u / WV;
+            const int h = row % H;
+            row /= H;
+            const int c = row % C, n = row / C;
+            const int w = wv * V;
+            oo = tref_off(a.out, n, c, h, w);
+            o0 = tref_off(a.in0, n, c, h, a.in0.stride[3] ? w : 0);
+            o1 = tref_off(a.in1, n, c, h, a.in1.stride[3] ? w : 0);
+        }
+        float x[V], y[V], r[V];
+        if (rd0) {
+            if (a.flat || a.in0.stride[3]) load_vec_cached<T, V>(in0 + o0, x);
+            else {
+                const float s = to_f32(in0[o0]);
+#pragma unroll
+                for (int i = 0; i < V; ++i) x[i] = s;
+            }
+        }
+        if (bin) {
+            if (a.flat || a.in1.stride[3]) load_vec_cached<T, V>(in1 + o1, y);
+            else {
+                const float s = to_f32(in1[o1]);
+#pragma unroll
+                for (int i = 0; i < V; ++i) y[i] = s;
+            }
+        }
+        ewise_math<V, sizeof(T) == 2>(op, a.scalar, x, y, r);
+        store_vec<T, V>(out + oo, r);
+    }
+}
+
+template <typename T>
+__device__ __noinline__ void ewise_light(const EwiseArgs &a, int p, int P) {
+    constexpr int VS = 16 / sizeof(T);
+    if (a.vec > 1) ewise_light_walk<T, VS>(a, p, P);
+    else ewise_light_walk<T, 1>(a, p, P);
+}
+
+__device__ __noinline__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
+    const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
+    const bool light = a.n_units <= (int64_t)4 * P * kThreads && idt == a.out.dtype && a.op != EW_COPY && a.op != EW_CAST &&
+                       a.iter_slots <= 1;
+    if (light) {
+        switch (idt) {
+            case DT_F32: ewise_light<float>(a, p, P); return;
+            case DT_F16: ewise_light<__half>(a, p, P); return;
+            case DT_BF16: ewise_light<__nv_bfloat16>(a, p, P); return;
+            default: break;
+        }
+    }
+    ewise_heavy(a, p, P, iter_no);
 }
 
 }  // namespace arkb

@@ -630,7 +630,11 @@ struct Lowerer {
                     // k-ranges with the least such time: fewer rows per group when there are not enough rows to go
                     // round (the activations are then re-read from shared memory more often), more than one k-range
                     // only when it pays for the barrier and the pass over the partials it adds.
-                    const int64_t warps = kThreads / 32, loads = M == 1 ? 8 : 4;  // 16-byte loads per lane and step
+                    // small matrices (per CTA at most 384 KiB of weights) take the light walker: half the loads per step
+                    bool light = (int64_t)N * K * (int64_t)es <= P * (384ll << 10);
+                    if (const char *e = getenv("ARKB_GEMV_LIGHT")) light = atoi(e) != 0;
+                    g.light = light ? 1 : 0;
+                    const int64_t warps = kThreads / 32, loads = (M == 1 ? 8 : 4) / (light ? 2 : 1);  // 16-byte loads per lane and step
                     auto kper_of = [&](int64_t sp) { return ((K + sp - 1) / sp + 255) / 256 * 256; };
                     const double step_us = 256.0 * loads * es * (double)(P * warps) / 6.5e6;
                     int64_t splits = 0, best_rw = loads;
@@ -705,7 +709,7 @@ struct Lowerer {
                 if (gv.push_ord) acc.opaque = true;  // also stores into every rank's all_reduce slots
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
-                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) : "") +
+                            std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) + (gv.light ? " light" : "") : "") +
                             (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : "") + (gv.residual ? " +residual" : "") +
                             (gv.push_ord ? " ->all_reduce slots" : "") +
                             (gv.act ? " act=" + std::to_string(gv.act) : ""));
@@ -1692,7 +1696,8 @@ struct Lowerer {
         for (size_t i = 0; i < n; ++i)  // barriers of at least 32 CTAs: each CTA asks for its share
             if (prog.stages[i].kind == SK_SYNC && prog.stages[i].sync_count >= 32) syncs.push_back(i);
         if (items.empty() || syncs.empty()) return;
-        const size_t kBudget = 32u << 20;  // bytes fetched but not yet read, well inside the 126 MB L2
+        size_t kBudget = 16u << 20;  // bytes fetched but not yet read: more than this ahead cost time (measured on decode)
+        if (const char *e = getenv("ARKB_PREFETCH_MB")) kBudget = (size_t)std::max(1, atoi(e)) << 20;
         // walk the cyclic schedule twice: the first lap only warms up the window, the second lap's choices are kept
         size_t next = 0, outstanding = 0;
         std::vector<std::pair<size_t, size_t>> inflight;  // (absolute consumer position, bytes)

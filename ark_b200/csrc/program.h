@@ -193,6 +193,8 @@ struct GemvArgs {
     // staging buffer (the all_reduce's own push stage and its barrier are then left out). push_ord = its ordinal + 1, 0: none.
     int32_t push_ord, push_per_iter;
     uint64_t push_stage_bytes;
+    int32_t light;           // [N, K]: the walker with half the loads in flight and a third of the registers (small matrices)
+    int32_t pad4;
 };
 enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2 };
 constexpr int kGemvMaxM = 2;

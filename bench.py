@@ -208,6 +208,8 @@ def main():
                     help="run the W2 matmul and the all_reduce as separate stages (two-shot) instead of fusing them")
     ap.add_argument("--no-e2e", action="store_true", help="device-timed leg only (profiler captures)")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the result (profiler captures)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the other two parts of the metric (Llama-shaped layers, all_reduce sweep points)")
     ap.add_argument("--tokens", type=int, default=TOKENS, help="reduced size for profiler captures only")
     ap.add_argument("--procs", type=int, default=0, help="experiment: plan for this many SMs instead of all")
     ap.add_argument("--weights-nk", action="store_true", help="store the weights [out, in] (K-major B operands)")
@@ -368,6 +370,33 @@ def main():
     ex2.stop()
     ex2.destroy()
 
+    # ---- the other two parts of the metric, measured in the same run with their own drivers' code: Llama-shaped layer
+    # stacks (tokens/s; tensor-parallel over all ranks) and points of the in-kernel all_reduce sweep (bus GB/s) ----
+    extras = {}
+    if not args.no_extras and tokens == TOKENS:
+        import bench_llama
+        extras["llama"] = []
+        for model, phase in (("7b", "decode"), ("7b", "prefill"), ("70b", "decode"), ("70b", "prefill")):
+            try:
+                if model == "70b" and phase == "prefill" and world not in (8,):
+                    # 64 query / 8 KV heads: the layer graph needs one (or all) KV heads per rank
+                    raise ValueError("needs tensor-parallel degree 8 (one KV head per rank)")
+                line = bench_llama.run_case(model, phase, rank, world, local, allgather, host_group)
+            except Exception as e:  # one failing case must not lose the headline
+                line = {"metric": f"llama_{model}_{phase}_tokens_per_s", "error": f"{type(e).__name__}: {e}"[:200]}
+            if rank == 0:
+                extras["llama"].append(line)
+        if world > 1:
+            import bench_allreduce
+            extras["all_reduce"] = []
+            for size in (8 << 10, 256 << 10, 16 << 20, 64 << 20, 1 << 30):
+                try:
+                    line = bench_allreduce.run_size(size, rank, world, local, allgather, host_group)
+                except Exception as e:
+                    line = {"bytes": size, "error": f"{type(e).__name__}: {e}"[:200]}
+                if rank == 0:
+                    extras["all_reduce"].append(line)
+
     if world > 1:
         t = torch.tensor([e2e_s, 0.0 if same else 1.0], device="cuda", dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -416,6 +445,7 @@ def main():
                          "note": f"per-GPU tensor-core rate of the loop kernel (both GEMMs of the step), of {which} "
                                  f"{'sustained' if (capped or timed_s >= 1.0) else 'burst'} cuBLAS bf16 peak; median of "
                                  f"{repeats} launches of {args.steps} iterations"}}
+    line.update(extras)
     if not args.no_cpu_baseline:
         tf, dt, _ = cpu_sample(8)
         nrows = int(max(8, min(tokens, 12.0 / (dt / 8))))

@@ -60,29 +60,18 @@ def to_f32(a, dt):
     return (a.astype(np.uint32) << 16).view(np.float32)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--model", choices=list(MODELS), default="7b")
-    ap.add_argument("--phase", choices=["prefill", "decode"], default="prefill")
-    ap.add_argument("--layers", type=int, default=0)
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--stage-times", action="store_true",
-                    help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
-    args = ap.parse_args()
+def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, layers=0, iters=10, warmup=3,
+             stage_times=False):
+    """Builds the layer stack, runs it and returns the result line (a dict) on rank 0, None on the other ranks.
+    The caller owns the process group (`ag`: bootstrap callback, `host_group`: a gloo group for host rendezvous)."""
     import torch
     import ark_b200 as ark
     from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    ag = host_group = None
-    if world > 1:
-        import torch.distributed as dist
-        from ark_b200.executor import torch_allgather
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-        host_group = dist.new_group(backend="gloo")
-        ag = torch_allgather(host_group)
+
+    class A:
+        pass
+    args = A()
+    args.model, args.phase, args.layers, args.iters, args.warmup, args.stage_times = model, phase, layers, iters, warmup, stage_times
     spec = MODELS[args.model]
     cfg = LlamaConfig(**spec["cfg"])
     dt, nlayers = spec["dtype"], args.layers or spec["layers"]
@@ -151,7 +140,7 @@ def main():
         ex.barrier()
         ex.stop()
         ex.destroy()
-        return
+        return None
     stream = torch.cuda.ExternalStream(ex.stream())
     ex.launch()
     ex.barrier()
@@ -199,6 +188,33 @@ def main():
             tf = flops / (ms * 1e-3) / 1e12
             line["roofline"] = {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                                 "frac": tf / pk["bf16_tflops"], "note": f"per-rank matmul FLOPs per step, of {which} peak"}
+        return line
+    return None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", choices=list(MODELS), default="7b")
+    ap.add_argument("--phase", choices=["prefill", "decode"], default="prefill")
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--stage-times", action="store_true",
+                    help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
+    args = ap.parse_args()
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    ag = host_group = None
+    if world > 1:
+        import torch.distributed as dist
+        from ark_b200.executor import torch_allgather
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        host_group = dist.new_group(backend="gloo")
+        ag = torch_allgather(host_group)
+    line = run_case(args.model, args.phase, rank, world, local, ag, host_group, args.layers, args.iters, args.warmup, args.stage_times)
+    if line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:
         import torch.distributed as dist

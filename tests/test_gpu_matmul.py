@@ -190,3 +190,4 @@ def test_mul_and_residual_add_folded_into_weight_streaming_matmul(dt, tb):
     (got,) = execute([y], {ta_: a, tb_: b, tres: res, tw: w})
     want = O.binary("add", O.matmul(O.binary("mul", a, b, dt), w, dt, False, tb), res, dt)
     assert_matmul_close(got, want, dt, "mul -> gemv -> add")
+
