@@ -17,12 +17,54 @@ __device__ __noinline__ void run_put(const PutArgs &a, int p, int P, unsigned lo
     }
 }
 
+// ---- NVSwitch multicast (NVLS) -------------------------------------------------------------------------
+// One 16-byte vector summed over the copies that all ranks hold at this multicast address (fp32 accumulation in the
+// switch for the 16-bit types), and one 16-byte store that lands in every rank's copy.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add(const void *mc);
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add<__half>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add<__nv_bfloat16>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce_add<float>(const void *mc) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st16(void *mc, const uint4 &v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
 template <typename T>
 __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, int p, int Pn, unsigned long long iter_no) {
     constexpr int V = 16 / sizeof(T);
     const int R = P.nranks, me = P.rank;
     const int64_t tid = (int64_t)p * kThreads + threadIdx.x, nth = (int64_t)Pn * kThreads;
     const int64_t nv = a.nelem / V;  // host guarantees nelem % V == 0 and 16-byte alignment
+    if (a.algo == 3) {
+        // the tensor sits at the same offset in every rank's arena (checked by the host): one multicast address
+        char *mc = P.mc_arena + a.buf_off[me];
+        const int64_t per = (nv + R - 1) / R;
+        const int64_t lo = per * me, hi = min(nv, lo + per);
+        for (int64_t i = lo + tid; i < hi; i += nth) {
+            const uint4 v = multimem_ld_reduce_add<T>(mc + i * 16);
+            multimem_st16(mc + i * 16, v);
+        }
+        return;
+    }
     if (a.algo == 0) {
         const uint64_t par = (iter_no * (unsigned long long)a.per_iter + (unsigned long long)a.ord) & 1;
         const uint64_t base = kCommDataOff + par * a.stage_bytes;
@@ -85,6 +127,10 @@ __device__ void allreduce_typed(const LaunchParams &P, const AllReduceArgs &a, i
         for (int k = 0; k < V; ++k) o.e[k] = from_f32<T>(acc[k]);
         if (a.no_gather) {
             reinterpret_cast<uint4 *>(P.arena[me] + a.buf_off[me])[i] = o.q;
+            continue;
+        }
+        if (a.mc_store) {  // one store, replicated by the switch into every rank's tensor
+            multimem_st16(P.mc_arena + a.buf_off[me] + i * 16, o.q);
             continue;
         }
 #pragma unroll

@@ -422,6 +422,117 @@ __device__ __forceinline__ void ewise_light_walk(const EwiseArgs &a, int p, int 
     }
 }
 
+// Integer tensors: Add / Sub / Mul / Div and the scalar forms in the tensors' own arithmetic (wrapping, truncating
+// division), never through fp32, so that results are exact over the whole range of the type.
+template <typename T>
+__device__ __forceinline__ T int_math(int op, T x, T y, T s) {
+    switch (op) {
+        case EW_ADD: return (T)(x + y);
+        case EW_SUB: return (T)(x - y);
+        case EW_MUL: return (T)(x * y);
+        case EW_DIV: return y != 0 ? (T)(x / y) : (T)0;
+        case EW_SCALAR_ASSIGN: return s;
+        case EW_SCALAR_ADD: return (T)(x + s);
+        case EW_SCALAR_MUL: return (T)(x * s);
+        case EW_RELU: return x > 0 ? x : (T)0;
+        default: return x;
+    }
+}
+
+template <typename T>
+__device__ __noinline__ void ewise_int(const EwiseArgs &a, int p, int P) {
+    const int op = a.op;
+    T *out = reinterpret_cast<T *>(a.out.ptr);
+    const T *in0 = reinterpret_cast<const T *>(a.in0.ptr);
+    const T *in1 = reinterpret_cast<const T *>(a.in1.ptr);
+    const bool bin = ewise_is_binary(op), rd0 = ewise_reads_in0(op);
+    const T s = (T)a.scalar;
+    const int64_t W = a.out.shape[3], H = a.out.shape[2], C = a.out.shape[1];
+    const int64_t total = (int64_t)a.out.shape[0] * C * H * W;
+    for (int64_t i = (int64_t)p * kThreads + threadIdx.x; i < total; i += (int64_t)P * kThreads) {
+        int64_t oo = i, o0 = i, o1 = i;
+        if (!a.flat) {
+            const int64_t w = i % W;
+            int64_t r = i / W;
+            const int64_t h = r % H;
+            r /= H;
+            const int64_t c = r % C, n = r / C;
+            oo = tref_off(a.out, n, c, h, w);
+            o0 = tref_off(a.in0, n, c, h, w);
+            o1 = tref_off(a.in1, n, c, h, w);
+        }
+        out[oo] = int_math<T>(op, rd0 ? in0[o0] : (T)0, bin ? in1[o1] : (T)0, s);
+    }
+}
+
+// Part of an operator's tasks only (see EwiseArgs::task_b): an element walk over the un-collapsed 4-D output
+// that keeps the elements whose tile belongs to the task range. Correct for every operator and type; plans use
+// partial ranges to spread one operator over several processor groups, each part is small.
+__device__ __noinline__ void ewise_masked(const EwiseArgs &a, int p, int P) {
+    const int op = a.op;
+    const bool bin = ewise_is_binary(op), rd0 = ewise_reads_in0(op);
+    const int idt = rd0 ? a.in0.dtype : a.out.dtype, odt = a.out.dtype;
+    const bool integer = idt >= DT_I32 && idt == odt && op != EW_COPY && op != EW_CAST;
+    const int64_t W = a.out.shape[3], H = a.out.shape[2], C = a.out.shape[1];
+    const int64_t total = (int64_t)a.out.shape[0] * C * H * W;
+    for (int64_t i = (int64_t)p * kThreads + threadIdx.x; i < total; i += (int64_t)P * kThreads) {
+        const int64_t w = i % W;
+        int64_t r = i / W;
+        const int64_t h = r % H;
+        r /= H;
+        const int64_t c = r % C, n = r / C;
+        const int64_t task = ((n * C + c) * a.tiles_h + h / a.tile_h) * a.tiles_w + w / a.tile_w;
+        if (task < a.task_b || task >= a.task_e || (task - a.task_b) % a.task_s) continue;
+        if (op == EW_ROPE && (w & 1)) continue;  // pairs are handled by their even element
+        const int64_t oo = tref_off(a.out, n, c, h, w), o0 = tref_off(a.in0, n, c, h, w), o1 = tref_off(a.in1, n, c, h, w);
+        if (integer) {
+            switch (idt) {
+                case DT_I32: {
+                    auto *o = reinterpret_cast<int32_t *>(a.out.ptr);
+                    o[oo] = int_math<int32_t>(op, rd0 ? reinterpret_cast<const int32_t *>(a.in0.ptr)[o0] : 0,
+                                              bin ? reinterpret_cast<const int32_t *>(a.in1.ptr)[o1] : 0, (int32_t)a.scalar);
+                    break;
+                }
+                case DT_U32: {
+                    auto *o = reinterpret_cast<uint32_t *>(a.out.ptr);
+                    o[oo] = int_math<uint32_t>(op, rd0 ? reinterpret_cast<const uint32_t *>(a.in0.ptr)[o0] : 0u,
+                                               bin ? reinterpret_cast<const uint32_t *>(a.in1.ptr)[o1] : 0u, (uint32_t)a.scalar);
+                    break;
+                }
+                case DT_I8: {
+                    auto *o = reinterpret_cast<int8_t *>(a.out.ptr);
+                    o[oo] = int_math<int8_t>(op, rd0 ? reinterpret_cast<const int8_t *>(a.in0.ptr)[o0] : (int8_t)0,
+                                             bin ? reinterpret_cast<const int8_t *>(a.in1.ptr)[o1] : (int8_t)0, (int8_t)a.scalar);
+                    break;
+                }
+                default: {
+                    auto *o = reinterpret_cast<uint8_t *>(a.out.ptr);
+                    o[oo] = int_math<uint8_t>(op, rd0 ? reinterpret_cast<const uint8_t *>(a.in0.ptr)[o0] : (uint8_t)0,
+                                              bin ? reinterpret_cast<const uint8_t *>(a.in1.ptr)[o1] : (uint8_t)0, (uint8_t)a.scalar);
+                    break;
+                }
+            }
+            continue;
+        }
+        if (op == EW_ROPE) {  // complex multiply of the pair (w, w + 1)
+            float xr[1], xi[1], yr[1], yi[1];
+            load_any<1>(a.in0.ptr, idt, o0, xr);
+            load_any<1>(a.in0.ptr, idt, o0 + a.in0.stride[3], xi);
+            load_any<1>(a.in1.ptr, idt, o1, yr);
+            load_any<1>(a.in1.ptr, idt, o1 + a.in1.stride[3], yi);
+            const float re[1] = {xr[0] * yr[0] - xi[0] * yi[0]}, im[1] = {xr[0] * yi[0] + xi[0] * yr[0]};
+            store_any<1>(a.out.ptr, odt, oo, re);
+            store_any<1>(a.out.ptr, odt, oo + a.out.stride[3], im);
+            continue;
+        }
+        float x[1] = {0.0f}, y[1] = {0.0f}, rr[1];
+        if (rd0) load_any<1>(a.in0.ptr, idt, o0, x);
+        if (bin) load_any<1>(a.in1.ptr, idt, o1, y);
+        ewise_math<1, false>(op, a.scalar, x, y, rr);
+        store_any<1>(a.out.ptr, odt, oo, rr);
+    }
+}
+
 template <typename T>
 __device__ __noinline__ void ewise_light(const EwiseArgs &a, int p, int P) {
     constexpr int VS = 16 / sizeof(T);
@@ -430,7 +541,16 @@ __device__ __noinline__ void ewise_light(const EwiseArgs &a, int p, int P) {
 }
 
 __device__ __noinline__ void run_ewise(const EwiseArgs &a, int p, int P, unsigned long long iter_no) {
+    if (a.task_s > 0) return ewise_masked(a, p, P);
     const int idt = (a.op == EW_SCALAR_ASSIGN) ? a.out.dtype : a.in0.dtype;
+    if (idt == a.out.dtype && a.op != EW_COPY && a.op != EW_CAST && idt >= DT_I32) {
+        switch (idt) {
+            case DT_I32: ewise_int<int32_t>(a, p, P); return;
+            case DT_U32: ewise_int<uint32_t>(a, p, P); return;
+            case DT_I8: ewise_int<int8_t>(a, p, P); return;
+            default: ewise_int<uint8_t>(a, p, P); return;
+        }
+    }
     const bool light = a.n_units <= (int64_t)4 * P * kThreads && idt == a.out.dtype && a.op != EW_COPY && a.op != EW_CAST &&
                        a.iter_slots <= 1;
     if (light) {

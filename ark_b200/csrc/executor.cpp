@@ -10,6 +10,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cstddef>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <thread>
@@ -111,8 +112,26 @@ void Executor::init_memory() {
     const int R = plan_.world_size, me = plan_.rank;
     // arena: zero-filled like the reference (ark/gpu/gpu_memory.cpp:75-77); padded regions rely on it
     arena_bytes_ = (layout_.arena_bytes + 65535) / 65536 * 65536;
-    CUDA_CHECK(cudaMalloc(&arena_, arena_bytes_));
-    CUDA_CHECK(cudaMemset(arena_, 0, arena_bytes_));
+    // NVLS on request: the arena becomes a symmetric allocation bound to an NVSwitch multicast object (in-switch
+    // reduction and one-store broadcast for the large all_reduce). Every rank takes the same decision: the set-up
+    // is collective and fails on all ranks or on none; on failure the plain arena below is used.
+    if (R > 1) {
+        const char *e = getenv("ARKB_NVLS");
+        if (e && atoi(e) != 0) {
+            try {
+                CUDA_CHECK(cudaFree(nullptr));  // the device's context exists before driver calls are made
+                symm_.create(device_id_, me, R, arena_bytes_, allgather_);
+                arena_ = symm_.local();
+                arena_bytes_ = symm_.bytes();
+            } catch (const Error &err) {
+                fprintf(stderr, "ark_b200: NVLS not used (%s)\n", err.what());
+            }
+        }
+    }
+    if (!symm_.active()) {
+        CUDA_CHECK(cudaMalloc(&arena_, arena_bytes_));
+        CUDA_CHECK(cudaMemset(arena_, 0, arena_bytes_));
+    }
     comm_bytes_ = kCommDataOff + 2 * layout_.comm_stage_bytes + 256;
     CUDA_CHECK(cudaMalloc(&comm_, comm_bytes_));
     CUDA_CHECK(cudaMemset(comm_, 0, comm_bytes_));
@@ -157,7 +176,8 @@ void Executor::init_memory() {
             uint64_t arena_bytes;
         };
         Handles h;
-        CUDA_CHECK(cudaIpcGetMemHandle(&h.arena, arena_));
+        std::memset(&h, 0, sizeof(h));
+        if (!symm_.active()) CUDA_CHECK(cudaIpcGetMemHandle(&h.arena, arena_));
         CUDA_CHECK(cudaIpcGetMemHandle(&h.comm, comm_));
         h.arena_bytes = arena_bytes_;
         std::vector<Handles> hs(R);
@@ -165,7 +185,8 @@ void Executor::init_memory() {
         for (int r = 0; r < R; ++r) {
             if (r == me) continue;
             void *pa = nullptr, *pc = nullptr;
-            CUDA_CHECK(cudaIpcOpenMemHandle(&pa, hs[r].arena, cudaIpcMemLazyEnablePeerAccess));
+            if (symm_.active()) pa = symm_.peer(r);
+            else CUDA_CHECK(cudaIpcOpenMemHandle(&pa, hs[r].arena, cudaIpcMemLazyEnablePeerAccess));
             CUDA_CHECK(cudaIpcOpenMemHandle(&pc, hs[r].comm, cudaIpcMemLazyEnablePeerAccess));
             peer_arena_[r] = reinterpret_cast<char *>(pa);
             peer_comm_[r] = reinterpret_cast<char *>(pc);
@@ -187,6 +208,7 @@ void Executor::compile() {
         env.comm[r] = peer_comm_[r];
     }
     env.encode_tmap = encode_tmap_cuda;
+    env.mc_arena = symm_.active() ? symm_.multicast() : nullptr;
     env.num_sm = num_sm_;
     env.allow_pair = getenv("ARKB_NO_PAIR") == nullptr;
     // first pass sizes the scratch (split-K partials) against a stand-in address, second pass uses the real one
@@ -223,6 +245,7 @@ void Executor::fill_params(LaunchParams &P, int iters) const {
         P.arena[r] = peer_arena_[r];
         P.comm[r] = peer_comm_[r];
     }
+    P.mc_arena = symm_.active() ? symm_.multicast() : nullptr;
     P.spin_limit = spin_limit_ ? spin_limit_ : kDefaultSpinLimit;
     // serialised launches: the kernel serves the request that is already posted and leaves at once
     P.idle_limit_ns = blocking_launch_ ? 0 : (idle_limit_ ? idle_limit_ : kDefaultIdleNs);
@@ -442,7 +465,7 @@ void Executor::destroy() {
     }
     for (int r = 0; r < kMaxPeers; ++r) {
         if (r == plan_.rank) continue;
-        if (peer_arena_[r]) cudaIpcCloseMemHandle(peer_arena_[r]);
+        if (peer_arena_[r] && !symm_.active()) cudaIpcCloseMemHandle(peer_arena_[r]);
         if (peer_comm_[r]) cudaIpcCloseMemHandle(peer_comm_[r]);
         peer_arena_[r] = peer_comm_[r] = nullptr;
     }
@@ -451,7 +474,8 @@ void Executor::destroy() {
     workspace_ = nullptr;
     if (stage_times_) cudaFree(stage_times_);
     stage_times_ = nullptr;
-    if (arena_) cudaFree(arena_);
+    if (symm_.active()) symm_.destroy(allgather_);  // collective: no rank unbinds while another may still use the multicast address
+    else if (arena_) cudaFree(arena_);
     if (comm_) cudaFree(comm_);
     if (state_) cudaFree(state_);
     if (host_flags_) cudaFreeHost(host_flags_);

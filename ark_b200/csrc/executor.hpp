@@ -6,6 +6,7 @@
 #include <string>
 
 #include "plan.hpp"
+#include "symm_arena.hpp"
 
 namespace arkb {
 
@@ -75,6 +76,7 @@ class Executor {
     int32_t *host_flags_ = nullptr;          // [0] run flag, [1] status mirror, [2..3] 64-bit count of finished iterations (mapped host memory)
     volatile int32_t *dev_flags_ = nullptr;  // device view of host_flags_
     char *peer_arena_[kMaxPeers], *peer_comm_[kMaxPeers];
+    SymmArena symm_;  // the arena as a multicast-bound allocation, when NVLS was asked for (ARKB_NVLS=1) and is available
     bool compiled_ = false, launched_ = false, stopped_ = false, destroyed_ = false, pending_ = false;
     bool kernel_live_ = false;
     float elapsed_ms_ = -1;

@@ -193,8 +193,7 @@ struct Lowerer {
         const int code = ewise_code(op.type);
         const bool binary = (code >= EW_ADD && code <= EW_DIV) || code == EW_ROPE;
         const bool has_in = code != EW_SCALAR_ASSIGN;
-        if (!full_range(tg.task_range, num_tasks(op)))
-            throw Error(E_UNSUPPORTED, op.type + ": partial TaskRange is supported for Matmul only");
+        const bool partial = !full_range(tg.task_range, num_tasks(op));
         const TensorDesc &out = op.results.at(0);
         if ((has_in && op.reads.size() < (binary ? 2u : 1u))) throw Error(E_MODEL, op.type + ": missing operand");
         Stage s = new_stage(SK_EWISE, proc);
@@ -212,7 +211,19 @@ struct Lowerer {
         if (binary) same = same && (op.reads[1].shape4() == osh);
         // Collapse adjacent dimensions that every operand walks contiguously (or broadcasts
         // together), so that e.g. [N,C,H,W] + [1,1,1,W] is walked as [rows, W] with one division.
-        {
+        if (partial) {
+            // only the tiles of this task group: the walk keeps the 4-D form the task ids refer to
+            if (!op.config.is_object() || !op.config.contains("Tile")) throw Error(E_PLAN, op.type + ": a partial TaskRange needs the Tile of the tasks");
+            auto tile = op.config.at("Tile").as_int_vec();
+            if (tile.size() != 2 || tile[0] <= 0 || tile[1] <= 0) throw Error(E_PLAN, "Tile should have 2 positive elements");
+            a.task_b = (int32_t)tg.task_range.b;
+            a.task_e = (int32_t)tg.task_range.e;
+            a.task_s = (int32_t)tg.task_range.s;
+            a.tile_h = (int32_t)tile[0];
+            a.tile_w = (int32_t)tile[1];
+            a.tiles_h = (int32_t)((osh[2] + tile[0] - 1) / tile[0]);
+            a.tiles_w = (int32_t)((osh[3] + tile[1] - 1) / tile[1]);
+        } else {
             TRef *refs[3] = {&a.out, has_in ? &a.in0 : nullptr, binary ? &a.in1 : nullptr};
             int64_t shp[4] = {osh[0], osh[1], osh[2], osh[3]};
             bool changed = true;
@@ -254,8 +265,14 @@ struct Lowerer {
         const int idt = has_in ? op.reads[0].dtype : out.dtype;
         if (binary && op.reads[1].dtype != idt) throw Error(E_MODEL, op.type + ": operand data types differ");
         const bool convert = (code == EW_CAST) || idt != out.dtype;
-        if (!convert && code != EW_COPY && !(idt == DT_F32 || idt == DT_F16 || idt == DT_BF16))
-            throw Error(E_UNSUPPORTED, op.type + ": arithmetic on integer tensors is not supported");
+        const bool integer = !(idt == DT_F32 || idt == DT_F16 || idt == DT_BF16);
+        if (!convert && integer && !(code == EW_COPY || (code >= EW_ADD && code <= EW_DIV) || code == EW_SCALAR_ASSIGN ||
+                                     code == EW_SCALAR_ADD || code == EW_SCALAR_MUL || code == EW_RELU))
+            throw Error(E_UNSUPPORTED, op.type + ": not defined on integer tensors");
+        if (!convert && integer && code != EW_COPY) {  // the scalar in the tensor's own arithmetic: T(factor), truncated
+            if (code == EW_SCALAR_ASSIGN) a.scalar = (float)(int64_t)op.arg_float("Value");
+            if (code == EW_SCALAR_ADD || code == EW_SCALAR_MUL) a.scalar = (float)(int64_t)op.arg_float("Factor");
+        }
         int V = convert ? 4 : (int)(16 / dtype_size(out.dtype));
         if (code == EW_COPY && !convert) V = (int)(16 / dtype_size(out.dtype));
         const int64_t nelem = out.nelems();
@@ -288,6 +305,10 @@ struct Lowerer {
             throw Error(E_UNSUPPORTED, "Rope needs 16-byte aligned rows");
         }
         a.vec = vec_ok ? V : 1;
+        if (partial) {
+            a.vec = 1;
+            a.flat = 0;
+        }
         if (int64_t slots = config_int(op, "IterSlots", 1); slots > 1) {
             // ring of buffers walked by the iteration number (streaming input / output of a resident kernel)
             if (code != EW_COPY || convert) throw Error(E_UNSUPPORTED, op.type + ": IterSlots is for Copy between tensors of one type");
@@ -300,12 +321,13 @@ struct Lowerer {
         else a.n_units = osh[0] * osh[1] * osh[2] * ((osh[3] + a.vec - 1) / a.vec);
         if (a.iter_slots > 1) {
             acc.opaque = true;  // the ring slots move with the iteration number
-        } else if (a.flat && !convert && code != EW_ROPE) {
+        } else if (a.flat && !convert && code != EW_ROPE && !(integer && code != EW_COPY)) {
             acc.aligned_units = a.n_units;
             acc.aligned_unit_bytes = (int)(a.vec * dtype_size(out.dtype));
         }
         push(s, op.type + " " + op.name + " units=" + std::to_string(a.n_units) + " vec=" + std::to_string(a.vec) +
-                    (a.flat ? " flat" : " strided"));
+                    (a.flat ? " flat" : " strided") +
+                    (partial ? " tasks [" + std::to_string(a.task_b) + "," + std::to_string(a.task_e) + (a.task_s != 1 ? "," + std::to_string(a.task_s) : "") + ")" : ""));
     }
 
     // ---- reduce ------------------------------------------------------------------
@@ -1197,6 +1219,12 @@ struct Lowerer {
         push(s, op.type + " " + op.name + " peers=" + std::to_string(npeers) + " bytes=" + std::to_string(bytes) + (packets ? " packets" : ""));
     }
 
+    bool same_offset_everywhere(const AllReduceArgs &a) const {
+        for (int r = 1; r < env.nranks; ++r)
+            if (a.buf_off[r] != a.buf_off[0]) return false;
+        return true;
+    }
+
     void emit_peersync(const Range &proc, const std::string &why) {
         Stage s = new_stage(SK_PEERSYNC, proc);
         s.ps.ord = ++prog.peersyncs_per_iter;
@@ -1247,10 +1275,12 @@ struct Lowerer {
             a.stage_off = st->second[env.rank];
             a.stage_bytes = bytes / env.nranks;
             a.no_gather = gather ? 0 : 1;
+            a.mc_store = (gather && env.mc_arena && same_offset_everywhere(a)) ? 1 : 0;
             emit_sync(proc);
             emit_peersync(proc, "partial tiles pushed");
             emit_sync(proc);
-            push(s, "AllReduce " + op.name + (gather ? " sum of staging slots + all-gather bytes=" : " sum of staging slots, own rows only bytes=") + std::to_string(bytes));
+            push(s, "AllReduce " + op.name + (gather ? (a.mc_store ? " sum of staging slots + multicast store bytes=" : " sum of staging slots + all-gather bytes=")
+                                                 : " sum of staging slots, own rows only bytes=") + std::to_string(bytes));
             emit_sync(proc);
             emit_peersync(proc, "all_reduce outputs stored");
             emit_sync(proc);
@@ -1278,11 +1308,15 @@ struct Lowerer {
             }
             push(s2, "AllReduce " + op.name + " one-shot reduce" + (add ? " +residual" : ""));
         } else {
-            a.algo = 1;
+            // NVLS when the arenas are bound to a multicast object (the executor was asked for it) and the tensor has
+            // one offset on all ranks; "Algo": "twoshot" keeps the peer loads and stores
+            const bool nvls = env.mc_arena && same_offset_everywhere(a) && (algo == "auto" || algo == "nvls");
+            if (algo == "nvls" && !nvls) throw Error(E_UNSUPPORTED, "AllReduce: NVLS needs a multicast-bound arena (ARKB_NVLS=1) and one tensor offset on all ranks");
+            a.algo = nvls ? 3 : 1;
             emit_sync(proc);
             emit_peersync(proc, "all_reduce inputs ready");
             emit_sync(proc);
-            push(s, "AllReduce " + op.name + " two-shot bytes=" + std::to_string(bytes));
+            push(s, "AllReduce " + op.name + (nvls ? " NVLS (multimem.ld_reduce + multimem.st) bytes=" : " two-shot bytes=") + std::to_string(bytes));
             emit_sync(proc);
             emit_peersync(proc, "all_reduce outputs stored");
             emit_sync(proc);

@@ -164,6 +164,7 @@ struct LowerEnv {
     int rank = 0, nranks = 1;
     char *arena[kMaxPeers] = {};  // arena base of every rank in this process's address space
     char *comm[kMaxPeers] = {};
+    char *mc_arena = nullptr;     // multicast address of the arenas when they are bound to an NVSwitch multicast object
     TmapEncoder encode_tmap;
     int num_sm = kDefaultNumSm;
     bool allow_pair = true;  // let matmul tiles span CTA pairs (tcgen05 cta_group::2) when the plan permits

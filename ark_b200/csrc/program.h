@@ -74,6 +74,11 @@ struct EwiseArgs {
     // so the host can fill or drain the other slots while the iteration runs. iter_slots <= 1: fixed addresses.
     int32_t iter_slots, pad;
     int64_t in_iter_bytes, out_iter_bytes;
+    // A task group that covers only part of the operator's tasks (TaskRange [b, e) step s): task id -> output tile
+    // (n, c, tile row, tile column), column fastest, as the reference's UnitOp enumerates them
+    // (ark/include/kernels/common/unit_op.h); only elements of those tiles are written. task_s == 0: all of it.
+    int32_t task_b, task_e, task_s;
+    int32_t tile_h, tile_w, tiles_h, tiles_w, pad2;
 };
 
 struct ReduceArgs {
@@ -293,6 +298,11 @@ struct PacketReduceArgs {
 //   algo 1 (two-shot, large): after a cross-rank barrier every rank sums its
 //     1/p shard from all ranks' tensors (peer loads, rank order, fp32) and
 //     stores the rounded result into every rank's tensor (peer stores).
+//   algo 3 (NVLS, large, needs LaunchParams::mc_arena): the same split of the
+//     tensor, but the sum of a 16-byte vector over all ranks is one
+//     multimem.ld_reduce (the NVSwitch adds the ranks' copies, fp32
+//     accumulation) and its broadcast one multimem.st: a rank moves 1/p of the
+//     tensor in and 1/p out instead of (p-1)/p each way.
 struct AllReduceArgs {
     uint64_t buf_off[kMaxPeers];  // byte offset of the tensor in each rank's arena
     int64_t nelem;
@@ -307,7 +317,8 @@ struct AllReduceArgs {
     const void *residual;
     void *sum_out;
     int32_t no_gather;        // slots (algo 2): the sum of this rank's rows stays local (a reduce-scatter); the caller reads
-    int32_t pad;              // only those rows, and the closing cross-rank barrier is left out
+                              // only those rows
+    int32_t mc_store;         // two-shot / slots: the result goes out through the multicast address (one store for all ranks)
 };
 
 // What a barrier stage does while it waits: L2 prefetch of operands no stage of the plan writes (weights, K/V
@@ -393,6 +404,7 @@ struct LaunchParams {
     int32_t syncs_per_iter[kMaxSyncGroups];
     char *arena[kMaxPeers];       // arena base of every rank as mapped here (own included)
     char *comm[kMaxPeers];        // comm allocation of every rank as mapped here (own included)
+    char *mc_arena;               // NVSwitch multicast address of offset 0 of every rank's arena; null when NVLS is off
     unsigned long long spin_limit;     // nanoseconds a device-side wait may last before it gives up
     unsigned long long idle_limit_ns;  // loop mode: return after this long without a run request
     unsigned long long *stage_times;   // optional [n_stages][grid][2]: when each CTA entered / left each stage of the last iteration (ns)

@@ -110,3 +110,54 @@ def test_strided_and_offset_views():
     out = ark.add(ta, tb)
     (got,) = execute([out], {ta: a, tb: b})
     assert_close(got, O.binary("add", a, b, "fp16"), "fp16", what="strided add")
+
+
+@pytest.mark.parametrize("dt,npdt", [("int32", np.int32), ("uint32", np.uint32), ("int8", np.int8), ("uint8", np.uint8)])
+def test_integer_arithmetic_is_exact(dt, npdt):
+    """Add / Sub / Mul / Div and the scalar forms on integer tensors run in the tensors' own arithmetic (wrap-around,
+    truncating division): bit-exact over the whole range, also beyond 2^24 where fp32 could not hold the values."""
+    rng = np.random.default_rng(44)
+    info = np.iinfo(npdt)
+    a = rng.integers(info.min, info.max, size=(3, 5, 64, 96), dtype=npdt, endpoint=True)
+    b = rng.integers(info.min, info.max, size=(1, 5, 1, 96), dtype=npdt, endpoint=True)
+    b[b == 0] = 1
+    adt = getattr(ark, dt)
+    ark.init()
+    ta, tb = ark.tensor(list(a.shape), adt), ark.tensor(list(b.shape), adt)
+    outs = [ark.add(ta, tb), ark.sub(ta, tb), ark.mul(ta, tb), ark.div(ta, tb), ark.add(ta, 3.0), ark.mul(ta, 5.0)]
+    got = execute(outs, {ta: a, tb: b})
+    with np.errstate(over="ignore"):
+        q = (np.trunc(a.astype(np.float64) / b.astype(np.float64))).astype(np.int64).astype(npdt)  # C++ division truncates
+        want = [a + b, a - b, a * b, q, a + npdt(3), a * npdt(5)]
+    for g, w, name in zip(got, want, ("add", "sub", "mul", "div", "scalar add", "scalar mul")):
+        assert np.array_equal(g, w.astype(npdt)), f"{dt} {name}"
+
+
+@pytest.mark.parametrize("split", ["halves", "interleaved"])
+def test_elementwise_partial_task_ranges_follow_plan_tiles(split):
+    """A plan may give one operator's tasks to several processor groups (TaskRange [b, e) or [b, e, step]); task id ->
+    output tile (n, c, tile row, tile column), column fastest. Each group writes exactly its tiles; together they
+    give the whole result (hand-edited plan, as ark/codegen.cpp:318-385 allows for any operator)."""
+    import json
+    rng = np.random.default_rng(45)
+    a, b = rand(rng, (3, 40, 200), "fp16"), rand(rng, (3, 40, 200), "fp16")
+    ark.init()
+    ta, tb = ark.tensor([3, 40, 200], ark.fp16), ark.tensor([3, 40, 200], ark.fp16)
+    out = ark.gelu(ark.add(ta, tb))
+    plan = ark.Planner(0).plan().plan
+    new_groups = []
+    for ti in plan["TaskInfos"]:
+        nt = ti["Ops"][0]["Config"]["NumTasks"]
+        assert ti["Ops"][0]["Config"]["Tile"] == [1, 64] and nt == 3 * 40 * 4
+        ranges = ([0, nt // 3], [nt // 3, nt]) if split == "halves" else ([0, nt, 2], [1, nt, 2])
+        rgs = [{"ProcessorRange": pr, "WarpRange": [0, 1], "SramRange": [0, 0],
+                "TaskGroups": [{"TaskId": ti["Id"], "TaskRange": tr, "Granularity": 1}]}
+               for pr, tr in zip(([0, 48], [48, 148]), ranges)]
+        new_groups.append({"ProcessorRange": [0, 148], "ResourceGroups": rgs})
+    plan["ProcessorGroups"] = new_groups
+    plan["NumProcessors"] = 148
+    text = ark.plan_dump(json.dumps(plan))
+    assert text.count("tasks [") == 4, text
+    (got,) = execute([out], {ta: a, tb: b}, plan=json.dumps(plan))
+    want = O.unary("gelu", O.binary("add", a, b, "fp16"), "fp16")
+    assert_close(got, want, "fp16", what=f"partial task ranges ({split})")

@@ -46,3 +46,18 @@ def test_peer_wait_runs_out_and_reports(same_device):
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert p.stdout.count("bounded-wait checks passed") == 2
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_nvls_all_reduce(world):
+    """The large all_reduce through the NVSwitch (multimem.ld_reduce / multimem.st over a multicast-bound arena),
+    against the oracle; falls back, and says so, where the GPUs offer no multicast."""
+    if _ngpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ)
+    port = 29670 + world
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "nvls_worker.py")]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert p.stdout.count("nvls checks passed") == world
