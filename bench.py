@@ -396,6 +396,19 @@ def main():
                     line = {"bytes": size, "error": f"{type(e).__name__}: {e}"[:200]}
                 if rank == 0:
                     extras["all_reduce"].append(line)
+            # the same points through the NVSwitch (multicast-bound arena, multimem.ld_reduce / multimem.st) where the
+            # GPUs offer it; from 4 ranks on (with 2 the direct exchange moves fewer bytes)
+            if world >= 4:
+                os.environ["ARKB_NVLS"] = "1"
+                extras["all_reduce_nvls"] = []
+                for size in (16 << 20, 64 << 20, 1 << 30):
+                    try:
+                        line = bench_allreduce.run_size(size, rank, world, local, allgather, host_group)
+                    except Exception as e:
+                        line = {"bytes": size, "error": f"{type(e).__name__}: {e}"[:200]}
+                    if rank == 0:
+                        extras["all_reduce_nvls"].append(line)
+                os.environ.pop("ARKB_NVLS", None)
 
     if world > 1:
         t = torch.tensor([e2e_s, 0.0 if same else 1.0], device="cuda", dtype=torch.float64)

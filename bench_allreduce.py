@@ -76,7 +76,7 @@ def run_size(size, rank, world, local, ag, host_group, iters=20, nccl=False):
     bus = size * 2 * (world - 1) / world / (ms * 1e-3) / 1e9
     line = {"bytes": size, "n_gpus": world, "us": ms * 1e3, "alg_GB/s": size / (ms * 1e-3) / 1e9, "bus_GB/s": bus,
             "frac_of_peer_copy": bus / NVLINK_PEER_GBS, "frac_of_nominal_900": bus / 900.0,
-            "algo": "one-shot" if "one-shot" in text else "two-shot"}
+            "algo": "one-shot" if "one-shot" in text else "nvls" if "NVLS" in text else "two-shot"}
     if nccl_ms:
         line["nccl_us"] = nccl_ms * 1e3
         line["nccl_bus_GB/s"] = size * 2 * (world - 1) / world / (nccl_ms * 1e-3) / 1e9
