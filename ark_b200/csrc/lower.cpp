@@ -762,7 +762,17 @@ struct Lowerer {
         // Skinny problems (few rows of activations against a large weight matrix, the
         // decode case) are run swapped: the weights become the 128-row A operand that fills
         // the shared-memory ring, the activations the narrow B operand.
-        const bool swapped = full && !ta && M <= 64;
+        // up to 128 rows too when the ordinary form could not spread over half of the CTAs (few, long tiles: the split-K
+        // of the swapped form then puts every SM to work on the weights)
+        bool swapped = full && !ta && M <= 64;
+        if (full && !ta && !swapped && M <= 128 && !fuse_ar) {
+            const int64_t Pq = prog.pair_mode ? proc.count() / 2 : proc.count();
+            const int64_t min_n = tb ? (prog.pair_mode ? 32 : 16) : (prog.pair_mode ? 128 : 64);
+            const int64_t units = bn * bc * ((N + min_n - 1) / min_n);
+            int factor = 3;
+            if (const char *e = getenv("ARKB_SWAP128_FACTOR")) factor = atoi(e);
+            swapped = units * factor < Pq;
+        }
         Stage s = new_stage(SK_GEMM, proc);
         GemmArgs &g = s.gm;
         g.C = pc;
@@ -1617,12 +1627,17 @@ struct Lowerer {
     bool pair_eligible() const {
         if (plan.num_processors % 2) return false;
         bool any = false;
+        int64_t max_rows = 0;  // pairs share 256-row tiles: with at most 128 rows everywhere half of every pair would idle
         for (auto &pg : plan.processor_groups)
             for (auto &rg : pg.resource_groups)
                 for (auto &tg : rg.task_groups)
                     for (auto &op : plan.task(tg.task_id).ops) {
                         if (op.type != "Matmul") continue;
                         any = true;
+                        if (!op.reads.empty() && !op.results.empty()) {
+                            auto csh = op.results[0].shape4();
+                            max_rows = std::max(max_rows, csh[2]);
+                        }
                         if (rg.proc.s != 1 || rg.proc.b % 2 || rg.proc.count() % 2) return false;
                         if (!full_range(tg.task_range, num_tasks(op))) {
                             if (!op.config.is_object() || !op.config.contains("TileShapeMNK")) return false;
@@ -1630,7 +1645,7 @@ struct Lowerer {
                             if (tile.size() != 3 || tile[0] % 256 || tile[1] % 32) return false;
                         }
                     }
-        return any;
+        return any && max_rows > 128;
     }
 
     static void touched(const TaskInfo &ti, std::set<int64_t> &reads, std::set<int64_t> &writes) {

@@ -56,8 +56,10 @@ def test_plan_lowering_fuses_activation_and_places_barriers():
     plan = _ffn_plan()
     n_stages, arena, procs = ark.plan_check(str(plan))
     text = ark.plan_dump(str(plan))
-    assert procs == 148 and n_stages == 3
-    assert "act=1" in text and text.count("sync group") == 1
+    # X W1 with the ReLU in its epilogue; the second matmul (128 rows, 8 column tiles, K = 4096) runs swapped with K
+    # cut into ranges so that every SM streams weights, then the sum of the partials
+    assert procs == 148 and n_stages == 5
+    assert "act=1" in text and text.count("sync group") == 2 and "swapped" in text and "split-K sum" in text
     assert arena >= (128 * 1024 + 2 * 1024 * 4096 + 128 * 4096 + 128 * 1024) * 2
 
 
