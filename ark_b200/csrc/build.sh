@@ -9,7 +9,7 @@ NVCC=${NVCC:-nvcc}
 ARCH="-gencode arch=compute_100a,code=sm_100a"
 CUFLAGS="$ARCH ${ARKB_DEFS:-} -lineinfo -O3 -std=c++17 -rdc=true -maxrregcount=128 -Xcompiler -fPIC ${ARKB_PTXAS_V:+-Xptxas -v}"
 pids=()
-for f in loop_kernel dev_ewise dev_reduce dev_gemm dev_gemv dev_attn dev_comm; do
+for f in loop_kernel dev_ewise dev_reduce dev_gemm dev_gemv dev_attn dev_attn_prefill dev_comm; do
   if [ "$HERE/$f.cu" -nt "$OUT/obj/$f.o" ] || [ -n "$(find "$HERE" -maxdepth 1 \( -name '*.h' -o -name '*.cuh' \) -newer "$OUT/obj/$f.o" 2>/dev/null)" ] || [ ! -f "$OUT/obj/$f.o" ]; then
     $NVCC $CUFLAGS -dc "$HERE/$f.cu" -o "$OUT/obj/$f.o" > "$OUT/obj/$f.log" 2>&1 &
     pids+=($!)

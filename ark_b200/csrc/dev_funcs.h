@@ -20,6 +20,8 @@ __device__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, i
 __device__ void run_splitk_reduce(const SplitKReduceArgs &a, int p, int P);
 __device__ void run_gemv(const GemvArgs &a, int p, int P, char *smem, const LaunchParams &LP, unsigned long long iter_no);
 __device__ void run_decode_attn(const DecodeAttnArgs &a, int p, int P, char *smem);
+__device__ void run_prefill_attn(const PrefillAttnArgs &a, const PrefillAttnArgs *amaps, int p, int P, char *smem, CtaCtl *ctl,
+                                 DeviceState *st, int stage_idx, unsigned long long spin_limit);
 __device__ void run_gemm_simt(const GemmSimtArgs &g, int p, int P, char *smem);
 __device__ void run_put(const PutArgs &a, int p, int P, unsigned long long iter_no);
 __device__ void run_packet(const LaunchParams &P, const PacketArgs &a, int p, int Pn, unsigned long long iter_no, CtaCtl *ctl, int stage);

@@ -90,6 +90,9 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
                 break;
             case SK_GEMV: run_gemv(S.gv, p, Pn, smem, P, iter_no); break;
             case SK_DECODE_ATTN: run_decode_attn(S.da, p, Pn, smem); break;
+            case SK_PREFILL_ATTN:
+                if constexpr (!PAIR) run_prefill_attn(S.pa, &P.stages[s].pa, p, Pn, smem, ctl, P.state, s, P.spin_limit);
+                break;
             case SK_GEMM_SIMT: run_gemm_simt(S.gs, p, Pn, smem); break;
             case SK_SPLITK_REDUCE: run_splitk_reduce(S.sr, p, Pn); break;
             case SK_TRANSPOSE: run_transpose(S.tp, p, Pn, smem); break;

@@ -1059,6 +1059,68 @@ struct Lowerer {
         push(m, "  merge of the chunks " + op.name);
     }
 
+    // ---- prefill attention ----------------------------------------------------------------
+    // q [B, Hq, Tq, 128], k and v [B, Hkv, Tkv, 128], out as q; with "TokenMajor": 1 all four have the head and token
+    // axes exchanged ([B, T, H, 128], the layout the projections produce).
+    void lower_prefill_attention(const OpDesc &op, const Range &proc) {
+        const TensorDesc &q = op.reads.at(0), &k = op.reads.at(1), &v = op.reads.at(2), &o = op.results.at(0);
+        if (q.dtype != k.dtype || q.dtype != v.dtype || q.dtype != o.dtype || (q.dtype != DT_F16 && q.dtype != DT_BF16))
+            throw Error(E_UNSUPPORTED, "PrefillAttention: fp16 or bf16 operands of one type");
+        if (prog.pair_mode) throw Error(E_UNSUPPORTED, "PrefillAttention: not available in a plan lowered for CTA pairs");
+        if (!env.encode_tmap) throw Error(E_UNSUPPORTED, "PrefillAttention: needs tensor maps");
+        const bool bthd = op.has_arg("TokenMajor") && op.arg_int("TokenMajor") != 0;
+        const std::string layout = bthd ? "bthd" : "bhtd";
+        const int hx = bthd ? 2 : 1, tx = bthd ? 1 : 2;  // which axis holds heads / tokens
+        auto qs = q.shape4(), ks = k.shape4(), vs = v.shape4(), os = o.shape4();
+        const int64_t B = qs[0], Hq = qs[hx], Tq = qs[tx], Hkv = ks[hx], Tkv = ks[tx];
+        if (qs[3] != 128 || ks[3] != 128 || vs != ks || os != qs || ks[0] != B || Hkv <= 0 || Hq % Hkv || Tq <= 0 || Tkv <= 0)
+            throw Error(E_UNSUPPORTED, "PrefillAttention: q [B, Hq, Tq, 128], k and v [B, Hkv, Tkv, 128], Hq a multiple of Hkv");
+        const int es = 2;
+        // element strides of the (b, h, t) axes of a tensor
+        auto strides = [&](const TensorDesc &T, int64_t &sb, int64_t &sh, int64_t &st) {
+            auto s4 = T.strides4();
+            const int64_t s1 = s4[2] * s4[3], s2 = s4[3];
+            sb = s4[1] * s4[2] * s4[3];
+            sh = bthd ? s2 : s1;
+            st = bthd ? s1 : s2;
+        };
+        Stage s = new_stage(SK_PREFILL_ATTN, proc);
+        PrefillAttnArgs &a = s.pa;
+        auto mk = [&](const TensorDesc &T, int64_t H, int64_t Tn, uint32_t box_rows, CUtensorMap *out, const char *what) {
+            int64_t sb, sh, st;
+            strides(T, sb, sh, st);
+            char *base = tensor_ptr(T);
+            if (!aligned16(base) || (st * es) % 16 || (sh * es) % 16 || (sb * es) % 16)
+                throw Error(E_UNSUPPORTED, std::string("PrefillAttention: ") + what + " rows must be 16-byte aligned");
+            TmapSpec sp;
+            sp.base = base;
+            sp.dtype = T.dtype;
+            sp.dims[0] = 128; sp.dims[1] = (uint64_t)Tn; sp.dims[2] = (uint64_t)H; sp.dims[3] = (uint64_t)B;
+            sp.strides_bytes[0] = (uint64_t)st * es; sp.strides_bytes[1] = (uint64_t)sh * es; sp.strides_bytes[2] = (uint64_t)sb * es;
+            sp.box[0] = 64; sp.box[1] = box_rows; sp.box[2] = 1; sp.box[3] = 1;
+            env.encode_tmap(out, sp);
+        };
+        mk(q, Hq, Tq, 128, &a.tmQ, "q");
+        mk(k, Hkv, Tkv, 128, &a.tmK, "k");
+        mk(v, Hkv, Tkv, 64, &a.tmV, "v");
+        a.out = tensor_ptr(o);
+        strides(o, a.o_stride_b, a.o_stride_h, a.o_stride_t);
+        if (!aligned16(a.out) || a.o_stride_t % 8 || a.o_stride_h % 8 || a.o_stride_b % 8)
+            throw Error(E_UNSUPPORTED, "PrefillAttention: output rows must be 16-byte aligned");
+        a.B = (int32_t)B; a.Hq = (int32_t)Hq; a.Hkv = (int32_t)Hkv; a.Tq = (int32_t)Tq; a.Tkv = (int32_t)Tkv;
+        a.causal = op.has_arg("Causal") ? (int32_t)op.arg_int("Causal") : 0;
+        a.dtype = q.dtype;
+        a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
+        a.q_tiles = (int32_t)((Tq + 127) / 128);
+        a.n_units = (int32_t)(B * Hq * a.q_tiles);
+        acc_begin();
+        rd(q); rd(k); rd(v);
+        wr(o);
+        push(s, "PrefillAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
+                    " rows=" + std::to_string(Tq) + " keys=" + std::to_string(Tkv) + (a.causal ? " causal" : "") + " " + layout +
+                    " units=" + std::to_string(a.n_units));
+    }
+
     // ---- transpose / embedding ---------------------------------------------------------
     void lower_transpose(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
         if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Transpose: partial TaskRange");
@@ -1455,6 +1517,7 @@ struct Lowerer {
         if (t == "Transpose") return lower_transpose(op, proc, tg);
         if (t == "Embedding") return lower_embedding(op, proc, tg);
         if (t == "DecodeAttention") return lower_decode_attention(op, proc);
+        if (t == "PrefillAttention") return lower_prefill_attention(op, proc);
         if (t == "RMSNorm" || t == "LayerNorm" || t == "Softmax") return lower_rowop(op, proc);
         if (t == "Send") return lower_send(op, proc);
         if (t == "Recv") return lower_recv(op, proc);
@@ -1632,6 +1695,7 @@ struct Lowerer {
             for (auto &rg : pg.resource_groups)
                 for (auto &tg : rg.task_groups)
                     for (auto &op : plan.task(tg.task_id).ops) {
+                        if (op.type == "PrefillAttention") return false;  // its MMAs are issued per CTA (cta_group::1)
                         if (op.type != "Matmul") continue;
                         any = true;
                         if (!op.reads.empty() && !op.results.empty()) {
@@ -1891,6 +1955,7 @@ struct Lowerer {
             size_t need = 0;
             switch (s.kind) {
                 case SK_GEMM: need = kFullSmemBytes; break;
+                case SK_PREFILL_ATTN: need = kFullSmemBytes; break;
                 case SK_GEMM_SIMT: need = 16 * 1024; break;
                 case SK_REDUCE: need = (size_t)kThreads * 8 * sizeof(float); break;
                 case SK_ROWOP:

@@ -40,6 +40,7 @@ enum StageKind : int32_t {
     SK_DECODE_ATTN = 15,    // one query row per head against a K/V cache: scores, softmax and output in one pass over the cache
     SK_PACKET = 16,         // flag-carrying packets: local data -> a peer's packet buffer, or local packet buffer -> local data
     SK_PACKET_REDUCE = 17,  // own shard + the shards the peers sent (packets or plain) -> local output and every peer's output
+    SK_PREFILL_ATTN = 18,   // many query rows per head: S = Q K^T, online softmax and O = P V per 128-row tile, scores stay on chip
 };
 
 enum EwiseOp : int32_t {
@@ -218,6 +219,21 @@ struct DecodeAttnArgs {
     int32_t pad;
 };
 
+// Self-attention over Tq query rows per head (head dimension 128). The tensors are addressed through tensor maps
+// of dims {128, T, H, B}, so both [B, H, T, 128] and [B, T, H, 128] storage work.
+struct PrefillAttnArgs {
+    alignas(64) CUtensorMap tmQ;  // box {64, 128}: K-major operand blocks
+    alignas(64) CUtensorMap tmK;  // box {64, 128}
+    alignas(64) CUtensorMap tmV;  // box {64, 64}: MN-major operand chunks
+    void *out;
+    int64_t o_stride_b, o_stride_h, o_stride_t;  // elements
+    int32_t B, Hq, Hkv, Tq, Tkv;
+    int32_t causal;   // 1: row i attends to keys [0, i + Tkv - Tq]
+    int32_t dtype;
+    float scale;      // applied to q.k before the softmax
+    int32_t n_units, q_tiles;
+};
+
 struct GemmSimtArgs {
     void *C;
     const void *A;
@@ -344,6 +360,7 @@ struct alignas(128) Stage {
         GemmArgs gm;
         GemvArgs gv;
         DecodeAttnArgs da;
+        PrefillAttnArgs pa;
         SplitKReduceArgs sr;
         GemmSimtArgs gs;
         TransposeArgs tp;

@@ -49,12 +49,15 @@ def layer_weights(cfg, dtype, world_size, prefix=""):
     }
 
 
-def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None):
+def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None, causal=False):
     """One layer on `x` [batch*seq, dim].
 
     Prefill: `mask` [1, 1, seq, seq] (additive, -inf above the diagonal) and `rope` [1, seq, 1, head_dim]
     (interleaved cos/sin pairs, examples/llama/model_test.py:379-384). Decode (seq == 1): `k_cache`/`v_cache`
     [batch, kv_heads_local, t_kv, head_dim] hold the keys/values attended to; `rope` is [1, 1, 1, head_dim].
+    Prefill with causal=True (and no `mask` tensor; head_dim 128): the attention block is one fused stage that reads
+    q, k, v in the [batch, seq, heads, head_dim] layout the projections leave and keeps the scores on chip, so the
+    four transposes, the scores tensor and the mask tensor of the reference's chain disappear.
     Returns the layer output [batch*seq, dim]."""
     p = world_size
     hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
@@ -69,6 +72,18 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     q = ops.reshape(q, [batch, seq, hl, hd])
     if rope is not None:
         q = ops.rope(q, rope)
+    scale = 1.0 / math.sqrt(hd)
+    if causal and mask is None and k_cache is None and seq > 1:
+        if hd != 128 or hl % kvl:
+            raise ValueError("causal=True needs head_dim 128 and a whole number of query heads per K/V head; pass a mask tensor otherwise")
+        k = ops.matmul(h, w["wk"], transpose_other=True)
+        v = ops.matmul(h, w["wv"], transpose_other=True)
+        k = ops.reshape(k, [batch, seq, kvl, hd])
+        if rope is not None:
+            k = ops.rope(k, rope)
+        v = ops.reshape(v, [batch, seq, kvl, hd])
+        o = ops.prefill_attention(q, k, v, scale, causal=True, token_major=True)   # [b, seq, hl, hd]
+        return _after_attention(ops.reshape(o, [bt, hl * hd]), x, w, cfg, rank, p)
     # [b, hl, seq, hd]; with one token per sequence the two layouts are the same memory
     q = ops.reshape(q, [batch, hl, 1, hd]) if seq == 1 else ops.transpose(q, [0, 2, 1, 3])
     if k_cache is None:
@@ -81,7 +96,6 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
         v = ops.transpose(ops.reshape(v, [batch, seq, kvl, hd]), [0, 2, 1, 3])
     else:
         k, v = k_cache, v_cache
-    scale = 1.0 / math.sqrt(hd)
     if seq == 1 and k_cache is not None and hd == 128 and hl % kvl == 0 and hl // kvl in (1, 2, 4, 8):
         o = ops.decode_attention(q, k, v, scale)            # one pass over the cache: scores, softmax, output
     elif kvl == hl or kvl == 1:
@@ -106,6 +120,11 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
             if p > 1:
                 down = ops.all_reduce(down, rank, p, output=down)
             return ops.add(down, x1)
+    return _after_attention(o, x, w, cfg, rank, p)
+
+
+def _after_attention(o, x, w, cfg, rank, p):
+    """Output projection, residual, and the feed-forward block of a prefill layer; `o` is [batch*seq, heads_local*head_dim]."""
     with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
         attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
         if p > 1:

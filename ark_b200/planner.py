@@ -132,6 +132,9 @@ def default_config(op, num_sm=DEFAULT_NUM_SM):
     if t in ("RMSNorm", "LayerNorm", "Softmax"):
         sh = _dims4(op.reads[0].shape)
         return {"NumWarps": 1, "SramBytes": 0, "NumTasks": sh[0] * sh[1] * sh[2]}
+    if t == "PrefillAttention":
+        sh = _dims4(op.results[0].shape)
+        return {"NumWarps": 16, "SramBytes": 0, "NumTasks": sh[0] * (sh[1] * sh[2] + 127) // 128}
     if t == "DecodeAttention":
         sh = _dims4(op.results[0].shape)
         return {"NumWarps": 16, "SramBytes": 0, "NumTasks": sh[0] * sh[1]}

@@ -61,9 +61,10 @@ def to_f32(a, dt):
 
 
 def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, layers=0, iters=10, warmup=3,
-             stage_times=False):
+             stage_times=False, attention="fused"):
     """Builds the layer stack, runs it and returns the result line (a dict) on rank 0, None on the other ranks.
-    The caller owns the process group (`ag`: bootstrap callback, `host_group`: a gloo group for host rendezvous)."""
+    attention: "fused" = the prefill attention block is one stage with the scores kept on chip; "chain" = the
+    reference's matmul -> scale/mask/softmax -> matmul chain with a mask tensor. The caller owns the process group (`ag`: bootstrap callback, `host_group`: a gloo group for host rendezvous)."""
     import torch
     import ark_b200 as ark
     from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
@@ -86,7 +87,8 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
     ark.set_world_size(world)
     x = ark.tensor([batch * seq, cfg.dim], adt)
     rope = ark.tensor([1, seq, 1, hd], adt)
-    mask = None if decode else ark.tensor([1, 1, seq, seq], adt)
+    fused = attention == "fused" and not decode and hd == 128
+    mask = None if decode or fused else ark.tensor([1, 1, seq, seq], adt)
     layers, caches = [], []
     h = x
     for li in range(nlayers):
@@ -95,7 +97,7 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
         if decode:
             kc, vc = ark.tensor([batch, kvl, span, hd], adt), ark.tensor([batch, kvl, span, hd], adt)
             caches.append((kc, vc))
-        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc)
+        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc, causal=fused)
         layers.append(w)
     ex = ark.Executor(local, 0, "llama", str(ark.Planner(local).plan()), loop_mode=False, allgather=ag)
     ex.compile()
@@ -180,6 +182,8 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
                 "config": {"workload": f"llama2-{args.model}-shaped x{nlayers} layers, tp{world}, {args.phase} batch {batch} "
                                        f"x {seq} tokens, {t_kv} keys", "stages": n_stages},
                 "output_finite": finite}
+        if not decode:
+            line["config"]["attention"] = "fused" if fused else "chain"
         if decode:
             gbs = wbytes / (ms * 1e-3) / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
@@ -201,6 +205,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--stage-times", action="store_true",
                     help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
+    ap.add_argument("--attention", choices=["fused", "chain"], default="fused",
+                    help="prefill: one fused attention stage (scores on chip) or the reference's matmul/softmax/matmul chain")
     args = ap.parse_args()
     import torch
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -213,7 +219,8 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         host_group = dist.new_group(backend="gloo")
         ag = torch_allgather(host_group)
-    line = run_case(args.model, args.phase, rank, world, local, ag, host_group, args.layers, args.iters, args.warmup, args.stage_times)
+    line = run_case(args.model, args.phase, rank, world, local, ag, host_group, args.layers, args.iters, args.warmup, args.stage_times,
+                    args.attention)
     if line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -26,7 +26,7 @@ def causal_mask(seq, dt):
     return m.reshape(1, 1, seq, seq)
 
 
-def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_caches=None):
+def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_caches=None, causal=False):
     """Full layer over all ranks: ws is a list (one dict of numpy weights per rank);
     returns the layer output (identical on all ranks)."""
     p = len(ws)
@@ -52,8 +52,18 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
             v = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
         else:
             k, v = k_caches[r], v_caches[r]
-        scores = O.matmul(q, k, dt, trans_b=True)
-        if mask is not None:
+        if causal:
+            # the fused attention stage: scores, scale and mask in fp32 (never stored), probabilities rounded once
+            if k.shape[1] != q.shape[1]:
+                k, v = np.repeat(k, q.shape[1] // k.shape[1], axis=1), np.repeat(v, q.shape[1] // v.shape[1], axis=1)
+            s32 = O.scalar("mul", O.matmul(f32(q), f32(k), "fp32", trans_b=True), scale, "fp32")
+            s32 = np.where(np.tril(np.ones((seq, seq), bool))[None, None], s32, np.float32(-np.inf))
+            scores, probs = None, st(O.softmax(s32, "fp32"))
+        else:
+            scores = O.matmul(q, k, dt, trans_b=True)
+        if causal:
+            pass
+        elif mask is not None:
             scores = O.scalar("mul", scores, scale, dt)
             scores = O.binary("add", scores, mask, dt)
             probs = O.softmax(scores, dt)

@@ -87,6 +87,28 @@ def test_prefill_layer(dt, heads, kv, reuse):
     check(got, want, dt)
 
 
+@pytest.mark.parametrize("dt,dim,heads,kv,batch,seq", [("fp16", 512, 4, 4, 2, 128), ("bf16", 1024, 8, 2, 2, 200)])
+def test_prefill_layer_with_fused_attention(dt, dim, heads, kv, batch, seq):
+    """causal=True: q, k, v go from the projections (and RoPE) straight into the fused attention stage, no mask
+    tensor, no transposes; grouped-query heads and a sequence that is not a multiple of the tile."""
+    cfg = LlamaConfig(dim=dim, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
+    rng = np.random.default_rng(54)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx, tr = ark.tensor([batch * seq, cfg.dim], NAME[dt]), ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, causal=True)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert "PrefillAttention" in text and "Transpose" not in text and "Softmax" not in text
+    feeds = {tx: x, tr: rope}
+    feeds.update({tw[k]: w[k] for k in w})
+    (got,) = execute([ty], feeds, loop_mode=True)
+    want = layer(x, [w], cfg, batch, seq, dt, rope=rope, causal=True)
+    check(got, want, dt)
+
+
 @pytest.mark.parametrize("dt,heads,kv,batch", [("fp16", 4, 4, 1), ("bf16", 8, 1, 16)])
 def test_decode_layer_with_kv_cache(dt, heads, kv, batch):
     cfg = LlamaConfig(dim=512, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
@@ -135,6 +157,50 @@ def test_decode_attention_against_float64(dt, b, hq, hkv, t):
     assert float(err.max()) <= tol, float(err.max())
 
 
+@pytest.mark.parametrize("dt,b,hq,hkv,tq,tkv,causal,token_major", [
+    ("fp16", 1, 4, 4, 256, 256, True, False),     # two tiles, every head its own K/V
+    ("bf16", 2, 8, 2, 384, 384, True, True),      # grouped-query heads, [B, T, H, 128] storage
+    ("fp16", 1, 3, 1, 333, 333, True, False),     # ragged last tile
+    ("bf16", 1, 2, 2, 200, 456, False, False),    # no mask, more keys than rows, both ragged
+    ("fp16", 1, 2, 1, 128, 640, True, True),      # a block of new rows against a longer history (row i sees keys up to i + 512)
+    ("fp16", 1, 32, 32, 2048, 2048, True, True),  # more units than CTAs: several units per CTA, barriers wrap
+    ("fp16", 1, 1, 1, 40, 40, True, False),       # a single partial tile
+])
+def test_prefill_attention_against_float64(dt, b, hq, hkv, tq, tkv, causal, token_major):
+    """S = q k^T and O = P v on the tensor cores with the scores kept on chip, against softmax attention in float64
+    on the same (rounded) inputs. Tolerance: P is rounded to the storage type before P v (as the unfused chain rounds
+    its probabilities) and the output once more: outputs of magnitude <= ~1, a few spacings of the type."""
+    rng = np.random.default_rng(71)
+    shape = lambda h, t: (b, t, h, 128) if token_major else (b, h, t, 128)
+    q = O.to_storage(rng.normal(0, 1, shape(hq, tq)).astype(np.float32), dt)
+    k = O.to_storage(rng.normal(0, 1, shape(hkv, tkv)).astype(np.float32), dt)
+    v = O.to_storage(rng.normal(0, 1, shape(hkv, tkv)).astype(np.float32), dt)
+    scale = 1.0 / np.sqrt(128.0)
+    ark.init()
+    tq_, tk_, tv_ = ark.tensor(list(q.shape), NAME[dt]), ark.tensor(list(k.shape), NAME[dt]), ark.tensor(list(v.shape), NAME[dt])
+    out = ark.prefill_attention(tq_, tk_, tv_, scale, causal=causal, token_major=token_major)
+    (got,) = execute([out], {tq_: q, tk_: k, tv_: v}, loop_mode=True)
+    g = hq // hkv
+    qf, kf, vf = (O.to_f32(x, dt).astype(np.float64) for x in (q, k, v))
+    if token_major:
+        qf, kf, vf = (x.transpose(0, 2, 1, 3) for x in (qf, kf, vf))
+    kf, vf = np.repeat(kf, g, axis=1), np.repeat(vf, g, axis=1)
+    s = np.einsum("bhqd,bhtd->bhqt", qf, kf) * scale
+    if causal:
+        visible = np.arange(tkv)[None, :] <= (np.arange(tq)[:, None] + tkv - tq)
+        s = np.where(visible[None, None], s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bhqt,bhtd->bhqd", p, vf)
+    gotf = O.to_f32(got, dt).astype(np.float64)
+    if token_major:
+        gotf = gotf.transpose(0, 2, 1, 3)
+    err = np.abs(gotf - want)
+    tol = 4e-3 if dt == "fp16" else 3e-2
+    assert float(err.max()) <= tol, (float(err.max()), np.unravel_index(err.argmax(), err.shape))
+    assert float(err.mean()) <= tol / 20, float(err.mean())
+
+
 # Per-rank shapes of the two Llama-shaped benchmark configurations at tensor-parallel degree 8 (one rank's share of
 # the heads and of the feed-forward width, full d_model, full sequence / cache lengths), against the oracle's per-op
 # composition of the whole layer. (The sum over ranks is covered by the multi-GPU tests.)
@@ -167,8 +233,9 @@ def test_decode_layer_at_benchmark_shapes(model):
     check(got, want, dt, spacings=2.5 if cfg.dim >= 8192 else 1.5)
 
 
-@pytest.mark.parametrize("model,dt_override", [("7b", None), ("70b", None), ("70b", "fp16")])
-def test_prefill_layer_at_benchmark_shapes(model, dt_override):
+@pytest.mark.parametrize("model,dt_override,fused", [("7b", None, False), ("70b", None, False), ("70b", "fp16", False),
+                                                     ("7b", None, True), ("70b", None, True)])
+def test_prefill_layer_at_benchmark_shapes(model, dt_override, fused):
     spec = REAL[model]
     dt, (batch, seq) = dt_override or spec["dt"], spec["prefill"]
     cfg = LlamaConfig(**spec["cfg"])
@@ -181,12 +248,17 @@ def test_prefill_layer_at_benchmark_shapes(model, dt_override):
     tw = layer_weights(cfg, NAME[dt], 1)
     tx = ark.tensor([batch * seq, cfg.dim], NAME[dt])
     tr, tm = ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt]), ark.tensor([1, 1, seq, seq], NAME[dt])
-    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
-    feeds = {tx: x, tr: rope, tm: mask}
+    if fused:
+        ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, causal=True)
+        feeds = {tx: x, tr: rope}
+    else:
+        ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm)
+        feeds = {tx: x, tr: rope, tm: mask}
     feeds.update({tw[k]: w[k] for k in w})
     (got,) = execute([ty], feeds, loop_mode=True)
     # the oracle composes the whole layer of ONE sequence on the host cores (sequences are independent); the engine
     # ran all of them, the last one is compared
     b = batch - 1
-    want = layer(np.ascontiguousarray(x[b * seq:(b + 1) * seq]), [w], cfg, 1, seq, dt, rope=rope, mask=mask)
+    want = layer(np.ascontiguousarray(x[b * seq:(b + 1) * seq]), [w], cfg, 1, seq, dt, rope=rope,
+                 mask=None if fused else mask, causal=fused)
     check(got[b * seq:(b + 1) * seq], want, dt, spacings=2.5 if cfg.dim >= 8192 else 1.5)

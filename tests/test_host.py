@@ -195,6 +195,34 @@ def test_decode_layer_folds_small_operators_into_the_weight_streaming_matmuls():
     assert "Matmul(gemv)" not in text and text.count("RMSNorm") == 2 and "Softmax" in text
 
 
+def test_causal_prefill_layer_lowers_to_one_attention_stage():
+    """causal=True: no mask tensor, no transposes, no scores tensor; the attention block is one stage of 128-row units;
+    its tensor-core instructions are per CTA, so the plan is not lowered for CTA pairs."""
+    from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+    cfg = LlamaConfig(dim=8192, n_heads=8, n_kv_heads=1, ffn_dim=3584)   # one rank's share of the 70B shape at TP8
+    ark.init()
+    x, rope = ark.tensor([4 * 1024, 8192], ark.bf16), ark.tensor([1, 1024, 1, 128], ark.bf16)
+    w = layer_weights(cfg, ark.bf16, 1)
+    decoder_layer(x, w, cfg, 4, 1024, 0, 1, rope=rope, causal=True)
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    assert "PrefillAttention prefill_attention B=4 heads=8/1 rows=1024 keys=1024 causal bthd units=256" in text
+    assert "Transpose" not in text and "Softmax" not in text and " pairs" not in text.splitlines()[0]
+    # shapes the stage does not take are refused when the model is built / lowered, not at run time
+    ark.init()
+    q, k = ark.tensor([1, 4, 256, 64], ark.fp16), ark.tensor([1, 4, 256, 64], ark.fp16)
+    with pytest.raises(ark.ModelError):
+        ark.prefill_attention(q, k, k)
+    ark.init()
+    q, k = ark.tensor([1, 4, 256, 128], ark.fp32), ark.tensor([1, 4, 256, 128], ark.fp32)
+    ark.prefill_attention(q, k, k)
+    with pytest.raises(ark.UnsupportedError):
+        ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    with pytest.raises(ValueError):
+        ark.init()
+        cfg64 = LlamaConfig(dim=512, n_heads=8, n_kv_heads=8, head_dim=64, ffn_dim=1376)
+        decoder_layer(ark.tensor([256, 512], ark.fp16), layer_weights(cfg64, ark.fp16, 1), cfg64, 1, 256, 0, 1, causal=True)
+
+
 def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
     """With several ranks the small all_reduces of a decode layer take their input straight from the weight-streaming
     matmul (no push stage) and add the residual in their sum stage."""
