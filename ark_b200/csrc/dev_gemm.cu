@@ -43,7 +43,7 @@ struct GemmLocal {
     void *C;
     const void *bias;
     int64_t ldc, c_stride_c, c_stride_n;
-    int M, N, K, tile_n, act, c_vec, c_tma, dtype, out_transposed, splits, batch_c;
+    int M, N, K, tile_n, act, c_vec, c_tma, dtype, out_transposed, splits, batch_c, bias_mul, rope_rows, rope_cols;
     float *ws;
     int64_t splits_stride;  // elements between the partials of consecutive k-ranges
     int a_mn_major, b_mn_major, a_bc, a_bn, b_bc, b_bn;
@@ -52,14 +52,47 @@ struct GemmLocal {
 
 template <typename T>
 __device__ __forceinline__ void gemm_store_row(const GemmLocal &g, T *crow, const T *brow, int col, int ncols,
-                                               uint32_t (&r)[32], int cnt) {
+                                               uint32_t (&r)[32], int cnt, int bcol0 = 0) {
     // cnt accumulator values (16 or 32) for columns [col, col+cnt) of one row
     float f[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) f[i] = (i < cnt) ? __uint_as_float(r[i]) : 0.0f;
     const bool full = (col + cnt <= ncols) && g.c_vec;
+    if (g.bias_mul == 2) {
+        // rotary embedding on the accumulator: brow is the table row of this output row, bcol0 the absolute column of
+        // column 0 of `crow` (even; the table row length is a multiple of 8, so an 8-vector never wraps)
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (v * 8 < cnt) {
+                float b[8];
+                load_vec<T, 8>(brow + (bcol0 + col + v * 8) % g.rope_cols, b);
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float x0 = f[v * 8 + i], x1 = f[v * 8 + i + 1];
+                    f[v * 8 + i] = x0 * b[i] - x1 * b[i + 1];
+                    f[v * 8 + i + 1] = x0 * b[i + 1] + x1 * b[i];
+                }
+            }
+        }
+        if (full) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                if (v * 8 < cnt) {
+                    float o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[i] = f[v * 8 + i];
+                    store_vec<T, 8>(crow + col + v * 8, o);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (i < cnt && col + i < ncols) crow[col + i] = from_f32<T>(f[i]);
+        }
+        return;
+    }
     if (full) {
-        if (brow) {
+        if (brow && !g.bias_mul) {
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
                 if (v * 8 < cnt) {
@@ -73,6 +106,17 @@ __device__ __forceinline__ void gemm_store_row(const GemmLocal &g, T *crow, cons
         if (g.act != ACT_NONE) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] = apply_act_fast(g.act, f[i]);
+        }
+        if (brow && g.bias_mul) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                if (v * 8 < cnt) {
+                    float b[8];
+                    load_vec<T, 8>(brow + col + v * 8, b);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[v * 8 + i] *= b[i];
+                }
+            }
         }
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -88,8 +132,10 @@ __device__ __forceinline__ void gemm_store_row(const GemmLocal &g, T *crow, cons
         for (int i = 0; i < 32; ++i) {
             if (i < cnt && col + i < ncols) {
                 float v = f[i];
-                if (brow) v += to_f32(brow[col + i]);
-                crow[col + i] = from_f32<T>(apply_act_fast(g.act, v));
+                if (brow && !g.bias_mul) v += to_f32(brow[col + i]);
+                v = apply_act_fast(g.act, v);
+                if (brow && g.bias_mul) v *= to_f32(brow[col + i]);
+                crow[col + i] = from_f32<T>(v);
             }
         }
     }
@@ -136,6 +182,7 @@ __device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint
     const int64_t boff = (int64_t)tc.bn * g.c_stride_n + (int64_t)tc.bc * g.c_stride_c + (int64_t)row * g.ldc;
     T *crow = reinterpret_cast<T *>(g.C) + boff;
     const T *brow = g.bias ? reinterpret_cast<const T *>(g.bias) + boff : nullptr;
+    if (g.bias_mul == 2) brow = reinterpret_cast<const T *>(g.bias) + (int64_t)(row_ok ? row % g.rope_rows : 0) * g.rope_cols - tc.n0;
     const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
     const int ncols_tile = min(g.tile_n, g.N - tc.n0);  // valid columns of this tile
     for (int c = 0; c < g.tile_n; c += 32) {
@@ -145,7 +192,7 @@ __device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint
         if (cnt == 32) tmem_ld32(lane_addr + c, r);
         else tmem_ld16(lane_addr + c, r);
         tmem_ld_wait();
-        if (row_ok) gemm_store_row<T>(g, crow + tc.n0, brow ? brow + tc.n0 : nullptr, c, ncols_tile, r, cnt);
+        if (row_ok) gemm_store_row<T>(g, crow + tc.n0, brow ? brow + tc.n0 : nullptr, c, ncols_tile, r, cnt, tc.n0);
     }
 }
 
@@ -175,8 +222,10 @@ __device__ void gemm_epilogue_tile_swapped(const GemmLocal &g, const TileCoord &
                 const int m = tc.n0 + c + i;
                 if (i < cnt && m < g.N) {
                     float v = __uint_as_float(r[i]);
-                    if (bbase) v += to_f32(bbase[(int64_t)m * g.ldc + n]);
-                    cbase[(int64_t)m * g.ldc + n] = from_f32<T>(apply_act_fast(g.act, v));
+                    if (bbase && !g.bias_mul) v += to_f32(bbase[(int64_t)m * g.ldc + n]);
+                    v = apply_act_fast(g.act, v);
+                    if (bbase && g.bias_mul) v *= to_f32(bbase[(int64_t)m * g.ldc + n]);
+                    cbase[(int64_t)m * g.ldc + n] = from_f32<T>(v);
                 }
             }
         }
@@ -495,6 +544,7 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
     L.a_mn_major = g.a_mn_major; L.b_mn_major = g.b_mn_major;
     L.a_bc = g.a_bc; L.a_bn = g.a_bn; L.b_bc = g.b_bc; L.b_bn = g.b_bn;
     L.peer_rows = g.peer_rows;
+    L.bias_mul = (int)g.bias_mul; L.rope_rows = g.rope_rows; L.rope_cols = g.rope_cols;
     R.g = &g; R.gmaps = gmaps; R.smem = smem; R.pp = pp; R.ctl = ctl; R.st = st; R.lim = lim; R.stage_idx = stage_idx;
     R.STAGES = g.stages;
     R.G = GROUPED ? g.kgroup : 1;

@@ -560,8 +560,29 @@ struct Lowerer {
                gemv_shape_ok(full_range(tg.task_range, num_tasks(op)), ta, tb, M, N, K, csh[0] * csh[1], ast[3]);
     }
 
+    // A tensor-core matmul (the ordinary tiled form: more than 128 rows, operands the tensor maps can describe, the
+    // whole task range) whose epilogue can combine the accumulator with a tensor of the result's layout.
+    bool matmul_takes_epilogue_operand(const OpDesc &op, const TaskGroup &tg, const TensorDesc &other, const TensorDesc &out) const {
+        if (op.type != "Matmul" || op.reads.size() < 2 || op.results.empty() || !env.encode_tmap) return false;
+        const TensorDesc &A = op.reads[0], &B = op.reads[1], &C = op.results[0];
+        if (A.dtype != B.dtype || A.dtype != C.dtype || (A.dtype != DT_F16 && A.dtype != DT_BF16)) return false;
+        if (other.dtype != C.dtype || out.dtype != C.dtype || other.shape4() != C.shape4() || out.shape4() != C.shape4() ||
+            other.strides4() != out.strides4())
+            return false;
+        if (!full_range(tg.task_range, num_tasks(op)) || matmul_is_gemv(op, tg)) return false;
+        const bool ta = op.arg_bool("TransposeInput");
+        auto ash = A.shape4(), ast = A.strides4(), bst = B.strides4();
+        const int64_t M = ta ? ash[3] : (A.shape.size() == 1 ? 1 : ash[2]);
+        if (M <= 128) return false;  // those may run in the swapped / split-K forms
+        const size_t es = 2;
+        return aligned16(tensor_ptr(A)) && aligned16(tensor_ptr(B)) && aligned16(tensor_ptr(other)) && (ast[3] * es) % 16 == 0 &&
+               (bst[3] * es) % 16 == 0 && (ast[2] * ast[3] * es) % 16 == 0 && (bst[2] * bst[3] * es) % 16 == 0;
+    }
+
     void lower_matmul(const OpDesc &op, const Range &proc, const TaskGroup &tg, int act, const TensorDesc *act_out,
-                      const OpDesc *fuse_ar = nullptr, const GemvFuse *gf = nullptr) {
+                      const OpDesc *fuse_ar = nullptr, const GemvFuse *gf = nullptr, const TensorDesc *epi = nullptr,
+                      int epi_mode = 0 /* 0: add, 1: multiply, 2: rotary table [rope_rows][rope_cols] */, int64_t rope_rows = 0,
+                      int64_t rope_cols = 0) {
         const TensorDesc &A = op.reads.at(0), &B = op.reads.at(1);
         const TensorDesc &C = act_out ? *act_out : op.results.at(0);
         const bool ta = op.arg_bool("TransposeInput");
@@ -592,6 +613,7 @@ struct Lowerer {
         const bool full = full_range(tg.task_range, ntasks);
         if (!tma_ok) {
             if (!full) throw Error(E_UNSUPPORTED, "Matmul: partial TaskRange needs 16-byte aligned fp16/bf16 operands");
+            if (epi) throw Error(E_INTERNAL, "Matmul: epilogue operand on the CUDA-core form");
             Stage s = new_stage(SK_GEMM_SIMT, proc);
             GemmSimtArgs &g = s.gs;
             acc_begin();
@@ -773,9 +795,13 @@ struct Lowerer {
             if (const char *e = getenv("ARKB_SWAP128_FACTOR")) factor = atoi(e);
             swapped = units * factor < Pq;
         }
+        if (epi && swapped) throw Error(E_INTERNAL, "Matmul: epilogue operand on the swapped form");
         Stage s = new_stage(SK_GEMM, proc);
         GemmArgs &g = s.gm;
         g.C = pc;
+        g.bias = epi ? tensor_ptr(*epi) : nullptr;
+        g.bias_mul = epi ? epi_mode : 0;
+        g.rope_rows = (int32_t)rope_rows; g.rope_cols = (int32_t)rope_cols;
         g.ldc = ldc;
         g.c_stride_c = cst[2] * cst[3];
         g.c_stride_n = cst[1] * cst[2] * cst[3];
@@ -972,8 +998,19 @@ struct Lowerer {
                 env.encode_tmap(&g.tmPeer[r], sp);
             }
         }
- acc_begin();
+        acc_begin();
         rd(A); rd_streamed(B);
+        if (epi) rd(*epi);
+        if (!swapped && full && g.splits <= 1 && !fuse_ar) {
+            // tile -> CTA mapping of the output (and of an epilogue operand of the output's layout)
+            uint64_t h = 1469598103934665603ull;
+            for (int64_t v : {M, N, (int64_t)g.tile_n, (int64_t)g.tiles_m, (int64_t)g.tiles_n, (int64_t)g.raster_group, bn, bc, ldc,
+                              (int64_t)g.c_stride_c, (int64_t)g.c_stride_n, (int64_t)g.tile_m})
+                h = (h ^ (uint64_t)v) * 1099511628211ull;
+            acc.tile_sig = h | 1;
+            acc.tiled.push_back(span_of(C));
+            if (epi && epi_mode != 2) acc.tiled.push_back(span_of(*epi));
+        }
         if (g.splits > 1) wr_raw(g.ws, (size_t)g.splits * bn * bc * M * N * sizeof(float));
         else wr(C);
         if (fuse_ar) acc.opaque = true;  // tiles go to the peers' staging slots
@@ -981,7 +1018,7 @@ struct Lowerer {
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
                     (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
                     (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K") + (swapped ? " swapped" : "") +
-                    (g.peer_rows ? " tiles->peer slots" : "") +
+                    (g.peer_rows ? " tiles->peer slots" : "") + (epi ? (epi_mode == 2 ? " rope" : epi_mode == 1 ? " *operand" : " +operand") : "") +
                     " stages=" + std::to_string(g.stages) + (g.kgroup > 1 ? "x" + std::to_string(g.kgroup) + "kb" : "") + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
         if (g.splits > 1) {
             // the activation and the rounding belong to the sum, not to the partials
@@ -1646,6 +1683,60 @@ struct Lowerer {
                 ++i;
                 continue;
             }
+            if (op.type == "Matmul" && !op.results.empty() && op.results[0].shape.size() == 2) {
+                // Matmul [rows, heads * d] -> (reshape to [b, seq, heads, d]) -> Rope with a table [1, seq, 1, d]: the
+                // rotation is applied to the accumulator, the unrotated projection is never stored
+                size_t j = i + 1;
+                while (j < ti.ops.size() && (ti.ops[j].is_virtual || ti.ops[j].type == "Reshape" || ti.ops[j].type == "Identity")) ++j;
+                const bool fold_ok = []() { const char *e = getenv("ARKB_FOLD_EPILOGUE"); return e ? atoi(e) != 0 : true; }();
+                if (fold_ok && j < ti.ops.size() && ti.ops[j].type == "Rope" && ti.ops[j].reads.size() == 2 && !ti.ops[j].results.empty()) {
+                    const OpDesc &rp = ti.ops[j];
+                    const TensorDesc &mmr = op.results[0], &x = rp.reads[0], &tab = rp.reads[1], &out = rp.results[0];
+                    auto xs = x.shape4(), ts = tab.shape4();
+                    const int64_t rows = mmr.shape[0], cols = mmr.shape[1];
+                    const bool shapes = x.buffer_id == mmr.buffer_id && x.dense() && mmr.dense() && out.dense() && tab.dense() &&
+                                        out.shape4() == xs && x.nelems() == rows * cols && xs[2] * xs[3] == cols && xs[0] * xs[1] == rows &&
+                                        ts[0] == 1 && ts[2] == 1 && ts[1] == xs[1] && ts[3] == xs[3] && xs[3] % 8 == 0 &&
+                                        tab.dtype == mmr.dtype && out.dtype == mmr.dtype && out.buffer_id != mmr.buffer_id;
+                    int64_t org_x[4], o_x, org_m[4], o_m;
+                    x.elem_strides(org_x, o_x);
+                    mmr.elem_strides(org_m, o_m);
+                    if (shapes && o_x == o_m && other_readers(mmr.buffer_id, &rp) == 0) {
+                        TensorDesc view = out;  // the rope's result seen as the matmul's [rows, cols] output
+                        view.shape = {rows, cols};
+                        view.strides = {rows, cols};
+                        view.offsets = {0, 0};
+                        view.padded = {rows, cols};
+                        if (out.offsets4() == std::vector<int64_t>{0, 0, 0, 0} && aligned16(tensor_ptr(tab)) &&
+                            matmul_takes_epilogue_operand(op, tg, view, view)) {
+                            if (!first) emit_sync(proc);
+                            lower_matmul(op, proc, tg, -1, &view, nullptr, nullptr, &tab, 2, ts[1], ts[3]);
+                            first = false;
+                            i = j;
+                            continue;
+                        }
+                    }
+                }
+            }
+            if (op.type == "Matmul" && i + 1 < ti.ops.size() && (ti.ops[i + 1].type == "Add" || ti.ops[i + 1].type == "Mul")) {
+                // Matmul -> Add / Mul with a tensor of the result's layout, the product having no other reader: the
+                // tensor is read in the epilogue (residual add; gate * up of a SwiGLU block) and the product is never stored
+                const OpDesc &nx = ti.ops[i + 1];
+                if (nx.reads.size() == 2 && !nx.results.empty() && !op.results.empty()) {
+                    const bool first_is_mm = nx.reads[0].id == op.results[0].id, second_is_mm = nx.reads[1].id == op.results[0].id;
+                    const bool fold_ok = []() { const char *e = getenv("ARKB_FOLD_EPILOGUE"); return e ? atoi(e) != 0 : true; }();
+                    if (fold_ok && first_is_mm != second_is_mm && other_readers(op.results[0].buffer_id, &nx) == 0) {
+                        const TensorDesc &other = first_is_mm ? nx.reads[1] : nx.reads[0];
+                        if (other.buffer_id != op.results[0].buffer_id && matmul_takes_epilogue_operand(op, tg, other, nx.results[0])) {
+                            if (!first) emit_sync(proc);
+                            lower_matmul(op, proc, tg, -1, &nx.results[0], nullptr, nullptr, &other, nx.type == "Mul" ? 1 : 0);
+                            first = false;
+                            ++i;
+                            continue;
+                        }
+                    }
+                }
+            }
             if (op.type == "Matmul" && i + 1 < ti.ops.size()) {
                 const OpDesc &nx = ti.ops[i + 1];
                 const int act = act_code(nx.type);
@@ -1733,9 +1824,18 @@ struct Lowerer {
         const Stage &sx = prog.stages[xi], &sy = prog.stages[yi];
         const bool aligned = x.aligned_units > 0 && x.aligned_units == y.aligned_units && x.aligned_unit_bytes == y.aligned_unit_bytes &&
                              sx.proc_b == sy.proc_b && sx.proc_e == sy.proc_e && sx.proc_s == sy.proc_s;
+        const bool same_tiles = x.tile_sig != 0 && x.tile_sig == y.tile_sig && sx.proc_b == sy.proc_b && sx.proc_e == sy.proc_e &&
+                                sx.proc_s == sy.proc_s;
+        auto in = [](const std::vector<std::pair<uintptr_t, uintptr_t>> &v, const std::pair<uintptr_t, uintptr_t> &a) {
+            for (auto &e : v) if (e == a) return true;
+            return false;
+        };
         auto hit = [&](const std::pair<uintptr_t, uintptr_t> &a, const std::pair<uintptr_t, uintptr_t> &b) {
             if (!overlap(a, b)) return false;
-            return !(aligned && a.first == b.first);
+            if (aligned && a.first == b.first) return false;
+            // a matmul's output tile read back as the epilogue operand of a matmul with the same tiles: same CTA
+            if (same_tiles && a == b && in(x.tiled, a) && in(y.tiled, b)) return false;
+            return true;
         };
         for (auto &w : x.writes) {
             for (auto &r : y.reads) if (hit(w, r)) return true;

@@ -180,6 +180,11 @@ struct StageAccess {
     // bytes of every operand: two such stages over the same CTAs touch a common operand thread by thread
     int64_t aligned_units = 0;
     int aligned_unit_bytes = 0;
+    // != 0: a tiled matmul whose output tiles (and epilogue operand) are touched tile by tile with this tile -> CTA
+    // mapping; `tiled` lists those operands. Two such stages with one signature over the same CTAs hand a common
+    // operand from a CTA to itself.
+    uint64_t tile_sig = 0;
+    std::vector<std::pair<uintptr_t, uintptr_t>> tiled;
     // large operands the stage streams from HBM (weights, caches): candidates for L2 prefetch at an earlier barrier
     struct Streamed {
         const void *ptr;

@@ -127,7 +127,12 @@ struct GemmArgs {
     // tmPeer[r]: dims {N, peer_rows}, rank r's slot for this rank; rows [r * peer_rows, (r+1) * peer_rows) go there.
     CUtensorMap tmPeer[kMaxPeers];
     void *C;
-    const void *bias;     // optional tensor added in the epilogue (same layout as C)
+    const void *bias;     // optional tensor combined with the result in the epilogue (same layout as C)
+    int32_t bias_mul;     // 0: result = act(acc + bias); 1: result = act(acc) * bias;
+                          // 2: rotary embedding: `bias` is a table [rope_rows][rope_cols] of (cos, sin) pairs, row r of the
+                          //    result uses table row r % rope_rows, column c pairs with table column c % rope_cols:
+                          //    (x0, x1) -> (x0 cos - x1 sin, x0 sin + x1 cos)
+    int32_t rope_rows, rope_cols, pad_b;
     int64_t ldc;
     int64_t c_stride_c, c_stride_n;  // batch strides of C in elements
     int32_t M, N, K;

@@ -66,32 +66,31 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     # or two rows of activations the engine folds them into the weight-streaming stage (norm and gate*up while the
     # activations are staged, the residual add on the way out) and otherwise runs them one after the other.
     decode = seq == 1 and k_cache is not None
-    with PlannerContext(sync=False):
+    with PlannerContext(sync=False):                        # prefill: RoPE is applied in the projection's epilogue
         h = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps)
         q = ops.matmul(h, w["wq"], transpose_other=True)   # [bt, hl*hd]
-    q = ops.reshape(q, [batch, seq, hl, hd])
-    if rope is not None:
-        q = ops.rope(q, rope)
+        q = ops.reshape(q, [batch, seq, hl, hd])
+        if rope is not None:
+            q = ops.rope(q, rope)
     scale = 1.0 / math.sqrt(hd)
     if causal and mask is None and k_cache is None and seq > 1:
         if hd != 128 or hl % kvl:
             raise ValueError("causal=True needs head_dim 128 and a whole number of query heads per K/V head; pass a mask tensor otherwise")
-        k = ops.matmul(h, w["wk"], transpose_other=True)
-        v = ops.matmul(h, w["wv"], transpose_other=True)
-        k = ops.reshape(k, [batch, seq, kvl, hd])
-        if rope is not None:
-            k = ops.rope(k, rope)
-        v = ops.reshape(v, [batch, seq, kvl, hd])
+        with PlannerContext(sync=False):
+            k = ops.reshape(ops.matmul(h, w["wk"], transpose_other=True), [batch, seq, kvl, hd])
+            if rope is not None:
+                k = ops.rope(k, rope)
+        v = ops.reshape(ops.matmul(h, w["wv"], transpose_other=True), [batch, seq, kvl, hd])
         o = ops.prefill_attention(q, k, v, scale, causal=True, token_major=True)   # [b, seq, hl, hd]
         return _after_attention(ops.reshape(o, [bt, hl * hd]), x, w, cfg, rank, p)
     # [b, hl, seq, hd]; with one token per sequence the two layouts are the same memory
     q = ops.reshape(q, [batch, hl, 1, hd]) if seq == 1 else ops.transpose(q, [0, 2, 1, 3])
     if k_cache is None:
-        k = ops.matmul(h, w["wk"], transpose_other=True)
+        with PlannerContext(sync=False):
+            k = ops.reshape(ops.matmul(h, w["wk"], transpose_other=True), [batch, seq, kvl, hd])
+            if rope is not None:
+                k = ops.rope(k, rope)
         v = ops.matmul(h, w["wv"], transpose_other=True)
-        k = ops.reshape(k, [batch, seq, kvl, hd])
-        if rope is not None:
-            k = ops.rope(k, rope)
         k = ops.transpose(k, [0, 2, 1, 3])             # [b, kvl, seq, hd]
         v = ops.transpose(ops.reshape(v, [batch, seq, kvl, hd]), [0, 2, 1, 3])
     else:
@@ -132,10 +131,10 @@ def _after_attention(o, x, w, cfg, rank, p):
     h2, x1 = ops.rmsnorm(attn, w["ffn_norm"], eps=cfg.norm_eps, residual=x)
     with PlannerContext(sync=False):                        # SiLU in the W1 epilogue
         gate = ops.silu(ops.matmul(h2, w["w1"], transpose_other=True))
-    up = ops.matmul(h2, w["w3"], transpose_other=True)
-    g = ops.mul(gate, up)
+    with PlannerContext(sync=False):                        # gate * up in the W3 epilogue: `up` is never stored
+        g = ops.mul(gate, ops.matmul(h2, w["w3"], transpose_other=True))
     with PlannerContext(sync=False):
         down = ops.matmul(g, w["w2"], transpose_other=True)  # partial [bt, dim]
         if p > 1:
             down = ops.all_reduce(down, rank, p, output=down)
-    return ops.add(x1, down)
+        return ops.add(x1, down)                            # one rank: the residual is added in the W2 epilogue

@@ -378,9 +378,9 @@ def main():
         extras["llama"] = []
         for model, phase in (("7b", "decode"), ("7b", "prefill"), ("70b", "decode"), ("70b", "prefill")):
             try:
-                if model == "70b" and phase == "prefill" and world not in (8,):
-                    # 64 query / 8 KV heads: the layer graph needs one (or all) KV heads per rank
-                    raise ValueError("needs tensor-parallel degree 8 (one KV head per rank)")
+                if model == "70b" and world not in (1, 2, 4, 8):
+                    # 64 query / 8 KV heads: every rank needs a whole number of query heads per K/V head
+                    raise ValueError("needs a tensor-parallel degree that divides 8 K/V heads")
                 line = bench_llama.run_case(model, phase, rank, world, local, allgather, host_group)
             except Exception as e:  # one failing case must not lose the headline
                 line = {"metric": f"llama_{model}_{phase}_tokens_per_s", "error": f"{type(e).__name__}: {e}"[:200]}

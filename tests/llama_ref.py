@@ -39,15 +39,21 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
     for r in range(p):
         w = ws[r]
         h = O.rmsnorm(x, w["attn_norm"], dt, cfg.norm_eps)
-        q = O.matmul(h, w["wq"], dt, trans_b=True).reshape(batch, seq, hl, hd)
-        if rope is not None:
-            q = O.rope(q, np.ascontiguousarray(np.broadcast_to(rope, q.shape)), dt)
+        def project(wn, heads):
+            """x W^T [+ RoPE]. Prefill: the rotation is applied to the fp32 accumulator in the matmul's epilogue (one
+            rounding); decode: the projection is stored and a separate operator rotates it."""
+            if rope is not None and seq > 1:
+                a32 = O.matmul(f32(h), f32(w[wn]), "fp32", trans_b=True).reshape(batch, seq, heads, hd)
+                return st(O.rope(a32, np.ascontiguousarray(np.broadcast_to(f32(rope), a32.shape)), "fp32"))
+            a = O.matmul(h, w[wn], dt, trans_b=True).reshape(batch, seq, heads, hd)
+            if rope is not None:
+                a = O.rope(a, np.ascontiguousarray(np.broadcast_to(rope, a.shape)), dt)
+            return a
+        q = project("wq", hl)
         q = np.ascontiguousarray(q.transpose(0, 2, 1, 3))
         if k_caches is None:
-            k = O.matmul(h, w["wk"], dt, trans_b=True).reshape(batch, seq, kvl, hd)
+            k = project("wk", kvl)
             v = O.matmul(h, w["wv"], dt, trans_b=True).reshape(batch, seq, kvl, hd)
-            if rope is not None:
-                k = O.rope(k, np.ascontiguousarray(np.broadcast_to(rope, k.shape)), dt)
             k = np.ascontiguousarray(k.transpose(0, 2, 1, 3))
             v = np.ascontiguousarray(v.transpose(0, 2, 1, 3))
         else:
@@ -83,8 +89,17 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
         # SiLU runs on the fp32 accumulator in the epilogue: the oracle's matmul, sigmoid and mul on fp32 values
         a32 = O.matmul(f32(h2), f32(w["w1"]), "fp32", trans_b=True)
         gate = st(O.binary("mul", a32, O.unary("sigmoid", a32, "fp32"), "fp32"))
-        up = O.matmul(h2, w["w3"], dt, trans_b=True)
-        g = O.binary("mul", gate, up, dt)
+        if seq > 1:
+            # prefill: gate * up happens on the fp32 accumulator of the W3 matmul (its epilogue reads the gate)
+            up32 = O.matmul(f32(h2), f32(w["w3"]), "fp32", trans_b=True)
+            g = st(O.binary("mul", f32(gate), up32, "fp32"))
+        else:
+            up = O.matmul(h2, w["w3"], dt, trans_b=True)
+            g = O.binary("mul", gate, up, dt)
+        if seq > 1 and p == 1:
+            # one rank: the residual is added to the fp32 accumulator of the W2 matmul
+            d32 = O.matmul(f32(g), f32(w["w2"]), "fp32", trans_b=True)
+            return st(O.binary("add", f32(x1), d32, "fp32"))
         down_parts.append(O.matmul(g, w["w2"], dt, trans_b=True))
     down = O.all_reduce(down_parts, dt) if p > 1 else down_parts[0]
     return O.binary("add", x1, down, dt)

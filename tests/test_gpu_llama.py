@@ -42,7 +42,9 @@ def check(got, want, dt, spacings=1.5):
     ok = float(err.mean()) <= 2e-3 * max(1.0, float(np.abs(w).mean())) or float(rel.max()) <= 1e-2
     if not ok and dt == "bf16":
         step = 2.0 ** -7 * max(float(np.abs(w).mean()), 2.0 ** -7)
-        ok = float(err.mean()) <= spacings * step and float((err > 6 * 2.0 ** -7 * np.maximum(np.abs(w), 1.0)).mean()) <= 2e-3
+        tail = float((err > 6 * 2.0 ** -7 * np.maximum(np.abs(w), 1.0)).mean())
+        ok = float(err.mean()) <= spacings * step and tail <= 2e-3
+        assert ok, (float(err.mean()), spacings * step, tail, float(np.abs(w).mean()))
     assert ok, (float(err.mean()), float(rel.max()), float(np.abs(w).mean()))
     # never grossly wrong anywhere: a few spacings of the storage type at the element's own magnitude
     spacing = (2.0 ** -10 if dt == "fp16" else 2.0 ** -7) * np.maximum(np.abs(w), 1.0)

@@ -191,3 +191,75 @@ def test_mul_and_residual_add_folded_into_weight_streaming_matmul(dt, tb):
     want = O.binary("add", O.matmul(O.binary("mul", a, b, dt), w, dt, False, tb), res, dt)
     assert_matmul_close(got, want, dt, "mul -> gemv -> add")
 
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("kind", ["add", "mul"])
+@pytest.mark.parametrize("mnk", [(256, 512, 256), (1000, 1376, 512)])
+def test_add_and_mul_folded_into_tensor_core_matmul_epilogue(dt, kind, mnk):
+    """Matmul -> Add / Mul with a tensor of the result's shape in one task: the tensor is read in the epilogue and
+    combined with the fp32 accumulator (one rounding), the product itself is never stored. Against the oracle's
+    matmul and add / mul on fp32 values."""
+    m, n, k = mnk
+    rng = np.random.default_rng(43)
+    a, other = rand(rng, (m, k), dt), rand(rng, (m, n), dt)
+    w = O.to_storage(rng.normal(0, 0.05, (n, k)).astype(np.float32), dt)
+    ark.init()
+    ta_, to_, tw = (ark.tensor(list(t.shape), NAME[dt]) for t in (a, other, w))
+    with ark.PlannerContext(sync=False):
+        mm = ark.matmul(ta_, tw, transpose_other=True)
+        y = ark.add(mm, to_) if kind == "add" else ark.mul(to_, mm)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert ("+operand" if kind == "add" else "*operand") in text and " Add " not in text and " Mul " not in text
+    (got,) = execute([y], {ta_: a, to_: other, tw: w})
+    acc = O.matmul(O.to_f32(a, dt), O.to_f32(w, dt), "fp32", False, True)
+    want = O.to_storage(O.binary(kind, acc, O.to_f32(other, dt), "fp32"), dt)
+    assert_matmul_close(got, want, dt, f"matmul -> {kind} {mnk}")
+
+
+def test_gate_times_up_needs_no_barrier_between_the_two_matmuls():
+    """SwiGLU: gate = silu(x W1) and g = gate * (x W3) have the same tiles on the same CTAs, so the W3 epilogue reads
+    the gate tile its own CTA stored: no barrier between the two stages. Run twice in loop mode (the second iteration
+    overwrites what the first one read)."""
+    m, d, f = 512, 512, 1536
+    rng = np.random.default_rng(44)
+    x = rand(rng, (m, d), "fp16")
+    w1, w3 = (O.to_storage(rng.normal(0, 0.05, (f, d)).astype(np.float32), "fp16") for _ in range(2))
+    ark.init()
+    tx, t1, t3 = ark.tensor([m, d], ark.fp16), ark.tensor([f, d], ark.fp16), ark.tensor([f, d], ark.fp16)
+    with ark.PlannerContext(sync=False):
+        gate = ark.silu(ark.matmul(tx, t1, transpose_other=True))
+    with ark.PlannerContext(sync=False):
+        g = ark.mul(gate, ark.matmul(tx, t3, transpose_other=True))
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    lines = text.splitlines()
+    i = next(k for k, l in enumerate(lines) if "act=4" in l)
+    assert "*operand" in lines[i + 1], text
+    (got,) = execute([g], {tx: x, t1: w1, t3: w3}, loop_mode=True, iters=2)
+    a32 = O.matmul(O.to_f32(x, "fp16"), O.to_f32(w1, "fp16"), "fp32", False, True)
+    gate_ref = O.to_storage(O.binary("mul", a32, O.unary("sigmoid", a32, "fp32"), "fp32"), "fp16")
+    up32 = O.matmul(O.to_f32(x, "fp16"), O.to_f32(w3, "fp16"), "fp32", False, True)
+    want = O.to_storage(O.binary("mul", O.to_f32(gate_ref, "fp16"), up32, "fp32"), "fp16")
+    assert_matmul_close(got, want, "fp16", "silu(x W1) * (x W3)")
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("b,seq,heads,k", [(2, 128, 4, 256), (1, 300, 3, 512)])
+def test_rope_folded_into_tensor_core_matmul_epilogue(dt, b, seq, heads, k):
+    """Projection -> reshape to [b, seq, heads, 128] -> RoPE in one task: the (cos, sin) table is read in the matmul's
+    epilogue and the rotation applied to the fp32 accumulator; tiles of 240 columns straddle head boundaries."""
+    hd = 128
+    rng = np.random.default_rng(45)
+    x = rand(rng, (b * seq, k), dt)
+    w = O.to_storage(rng.normal(0, 0.05, (heads * hd, k)).astype(np.float32), dt)
+    tab = O.to_storage(rng.uniform(-1, 1, (1, seq, 1, hd)).astype(np.float32), dt)
+    ark.init()
+    tx, tw, tt = ark.tensor([b * seq, k], NAME[dt]), ark.tensor([heads * hd, k], NAME[dt]), ark.tensor([1, seq, 1, hd], NAME[dt])
+    with ark.PlannerContext(sync=False):
+        q = ark.rope(ark.reshape(ark.matmul(tx, tw, transpose_other=True), [b, seq, heads, hd]), tt)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert " rope " in text and "Rope" not in text, text
+    (got,) = execute([q], {tx: x, tw: w, tt: tab})
+    acc = O.matmul(O.to_f32(x, dt), O.to_f32(w, dt), "fp32", False, True).reshape(b, seq, heads, hd)
+    want = O.to_storage(O.rope(acc, np.ascontiguousarray(np.broadcast_to(O.to_f32(tab, dt), acc.shape)), "fp32"), dt)
+    assert_matmul_close(got.reshape(b * seq, heads * hd), want.reshape(b * seq, heads * hd), dt, "matmul -> rope")

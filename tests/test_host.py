@@ -207,6 +207,13 @@ def test_causal_prefill_layer_lowers_to_one_attention_stage():
     text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
     assert "PrefillAttention prefill_attention B=4 heads=8/1 rows=1024 keys=1024 causal bthd units=256" in text
     assert "Transpose" not in text and "Softmax" not in text and " pairs" not in text.splitlines()[0]
+    # RoPE in the Q and K projections' epilogues, gate * up in W3's, the residual in W2's: no elementwise stage is left,
+    # and W3 follows W1 without a barrier (same tiles on the same CTAs)
+    assert text.count(" rope ") == 2 and "Rope" not in text and " Mul " not in text and " Add " not in text
+    assert "*operand" in text and "+operand" in text
+    lines = text.splitlines()
+    w1 = next(i for i, l in enumerate(lines) if "act=4" in l)
+    assert "*operand" in lines[w1 + 1]
     # shapes the stage does not take are refused when the model is built / lowered, not at run time
     ark.init()
     q, k = ark.tensor([1, 4, 256, 64], ark.fp16), ark.tensor([1, 4, 256, 64], ark.fp16)
