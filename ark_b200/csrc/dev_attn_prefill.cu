@@ -11,9 +11,10 @@
 //   warp 4 lane 0 : TMA producer — Q once per unit, K and V tiles into a two-slot ring;
 //   warp 5 lane 0 : MMA issuer   — S(j+1) = Q K(j+1)^T is issued before it waits for P(j), so the tensor cores
 //                   work on the next scores while the softmax warps work on the current ones (two S buffers);
-//   warps 0..3    : softmax — thread r owns query row r (TMEM lane r): running maximum m and sum l, O rescaled in
-//                   TMEM by exp2(m_old - m_new) when the maximum moved, P = exp2(s*c - m) rounded and written into
-//                   the 128-byte-swizzled K-major layout the MMA reads; after the last tile O / l goes to global.
+//   warps 0..3, 8..11 : softmax — two warps per 32 query rows (TMEM lanes), 64 columns each: running maximum m
+//                   (exchanged between the two through shared memory) and sum l, O rescaled in TMEM by
+//                   exp2(m_old - m_new) when the maximum moved, P = exp2(s*c - m) rounded and written into the
+//                   128-byte-swizzled K-major layout the MMA reads; after the last tile O / l goes to global.
 // TMEM columns: S0 [0,128), S1 [128,256), O [256,384). Shared memory: Q 32 KiB, 2 x (K 32 KiB + V 32 KiB), P 32 KiB.
 // The barriers live behind the tiles and exist only for the duration of the stage. Every wait is bounded.
 #include "dev_gemm.cuh"
@@ -28,12 +29,14 @@ constexpr int kAtQOff = 0;
 constexpr int kAtKvOff = kAtTileBytes;              // slot s: K at +s*64 KiB, V 32 KiB behind it
 constexpr int kAtPOff = kAtKvOff + 4 * kAtTileBytes;
 constexpr int kAtBarOff = kAtPOff + kAtTileBytes;   // 192 KiB
+constexpr int kAtXchOff = kAtBarOff + 256;          // row maxima [2][2][128] and row sums [2][2][128] exchanged between the two warps of a row
+constexpr int kAtSoftmaxWarps = 8;
 constexpr uint32_t kAtS0 = 0, kAtO = 256;
 
 struct AttnBars {
     unsigned long long q_full, q_empty, kv_full[2], kv_empty[2], s_full[2], s_free[2], p_ready, o_done, o_free;
 };
-static_assert(kAtBarOff + (int)sizeof(AttnBars) <= kGemmSmemBytes, "attention tiles and barriers fit the kernel's shared memory");
+static_assert(sizeof(AttnBars) <= 256 && kAtXchOff + 1024 * (int)sizeof(float) <= kGemmSmemBytes, "attention tiles and barriers fit the kernel's shared memory");
 
 struct AttnRun {
     const PrefillAttnArgs *a;      // stage record (shared-memory copy)
@@ -196,22 +199,28 @@ __device__ __noinline__ bool attn_issue(const AttnRun &R) {
 }
 
 // ---- softmax and output -------------------------------------------------------------------------
+// Eight warps: warps 0-3 (half 0) and 8-11 (half 1). Warp q + 8*half owns TMEM lanes 32q..32q+31 (the only ones a warp
+// with index = q mod 4 can reach) = query rows 32q.. of the tile, and columns 64*half..+63 of S, P and O. The two warps
+// of a row exchange their partial row maxima through shared memory; the partial sums stay apart until the end.
 template <typename T>
 __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) {
     const PrefillAttnArgs &a = *R.a;
     AttnBars *B = R.bars;
-    const int row = warp * 32 + lane;
-    const uint32_t lane_addr = R.tmem_base + ((uint32_t)(warp * 32) << 16);
+    const int quarter = warp & 3, half = warp >> 3;
+    const int row = quarter * 32 + lane;
+    const int col0 = half * 64;
+    const uint32_t lane_addr = R.tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float c = a.scale * 1.4426950408889634f;  // scores are kept in units of log2(e): exp(x) = exp2(x * log2 e)
     char *sP = R.smem + kAtPOff;
-    unsigned int uc = 0, sc = 0, oc = 0;  // units; S tiles consumed; PV commits waited for
+    float *xch = reinterpret_cast<float *>(R.smem + kAtXchOff);  // [2 parities][2 halves][128 rows]
+    unsigned int sc = 0, oc = 0;  // S tiles consumed; PV commits waited for
     for (int u = R.p; u < a.n_units; u += R.P) {
         const AttnUnit t = attn_unit(a, u);
         const int qi = t.qt * kAtTile + row;
-        T *orow = reinterpret_cast<T *>(a.out) + (int64_t)t.b * a.o_stride_b + (int64_t)t.h * a.o_stride_h + (int64_t)qi * a.o_stride_t;
+        T *orow = reinterpret_cast<T *>(a.out) + (int64_t)t.b * a.o_stride_b + (int64_t)t.h * a.o_stride_h + (int64_t)qi * a.o_stride_t + col0;
         if (t.n_tiles == 0) {  // no key visible to any row of the tile: zeros
             if (qi < a.Tq)
-                for (int i = 0; i < kAtTile; i += 8) *reinterpret_cast<uint4 *>(orow + i) = make_uint4(0, 0, 0, 0);
+                for (int i = 0; i < 64; i += 8) *reinterpret_cast<uint4 *>(orow + i) = make_uint4(0, 0, 0, 0);
             continue;
         }
         const int last_key = a.causal ? min(a.Tkv - 1, qi + a.Tkv - a.Tq) : a.Tkv - 1;  // last key this row may see
@@ -224,26 +233,34 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
                 return false;
             }
             tc_fence_after();
-            const uint32_t s_addr = lane_addr + kAtS0 + sb * kAtTile;
-            const int key0 = j * kAtTile;
-            // the tile needs masking when it holds a key some row of this warp may not see
-            const bool masked = key0 + kAtTile - 1 > __shfl_sync(0xffffffffu, last_key, 0);
-            float mx = m;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + cc * 32, r);
-                tmem_ld_wait();
+            const uint32_t s_addr = lane_addr + kAtS0 + sb * kAtTile + col0;
+            const int key0 = j * kAtTile + col0;  // first key of this warp's columns
+            // masking is needed when these columns hold a key some row of this warp may not see
+            const bool masked = key0 + 63 > __shfl_sync(0xffffffffu, last_key, 0);
+            uint32_t r0[32], r1[32];
+            tmem_ld32(s_addr, r0);
+            tmem_ld32(s_addr + 32, r1);
+            tmem_ld_wait();
+            // scaled (and masked) scores stay in r0 / r1 as float bits until the exponentials
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                float a0 = __uint_as_float(r0[i]) * c, a1 = __uint_as_float(r1[i]) * c;
                 if (masked) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (key0 + cc * 32 + i <= last_key) mx = fmaxf(mx, __uint_as_float(r[i]) * c);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]) * c);
+                    if (key0 + i > last_key) a0 = -INFINITY;
+                    if (key0 + 32 + i > last_key) a1 = -INFINITY;
                 }
+                r0[i] = __float_as_uint(a0);
+                r1[i] = __float_as_uint(a1);
             }
-            // a row with no visible key so far keeps m = -inf; exp2 below then sees -inf - 0 and gives 0
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], fmaxf(__uint_as_float(r0[i]), __uint_as_float(r1[i])));
+            const float mx_own = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float *x = xch + (sc & 1) * 256;
+            x[half * 128 + row] = mx_own;
+            named_barrier(1 + quarter, 64);
+            const float mx = fmaxf(m, fmaxf(mx_own, x[(half ^ 1) * 128 + row]));
+            // a row with no visible key so far keeps m = -inf; the exponentials below then see -inf - 0 and give 0
             const float m_use = mx == -INFINITY ? 0.0f : mx;
             const float alpha = ex2(m - m_use);  // m = -inf on the first tile: 0
             // PV of the previous tile must be complete: it reads P and writes O
@@ -256,38 +273,37 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
                 ++oc;
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+                    // r0 / r1 still hold the scores: O passes through registers of its own, 32 columns at a time
 #pragma unroll 1
-                    for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t r[32];
-                        tmem_ld32(lane_addr + kAtO + cc * 32, r);
+                    for (int cc = 0; cc < 2; ++cc) {
+                        uint32_t t32[32];
+                        tmem_ld32(lane_addr + kAtO + col0 + cc * 32, t32);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(lane_addr + kAtO + cc * 32, r);
+                        for (int i = 0; i < 32; ++i) t32[i] = __float_as_uint(__uint_as_float(t32[i]) * alpha);
+                        tmem_st32(lane_addr + kAtO + col0 + cc * 32, t32);
                     }
                     tmem_st_wait();
                 }
             }
             l *= alpha;
             m = mx;
-#pragma unroll 1
-            for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld32(s_addr + cc * 32, r);
-                tmem_ld_wait();
-                union { uint4 q[4]; T e[32]; } o;
+            // P = exp2(v - m), rounded to the storage type; this warp's 64 keys are k-block `half` of the A operand:
+            // row `row`, 16-byte chunks 0..7 of its 128-byte line, 128-byte swizzle
+            char *prow = sP + half * kGemmABytes + row * 128;
+            float l4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float pv = ex2(fmaf(__uint_as_float(r[i]), c, -m_use));
-                    if (masked && key0 + cc * 32 + i > last_key) pv = 0.0f;
-                    o.e[i] = from_f32<T>(pv);
-                    l += to_f32(o.e[i]);  // the sum of what the MMA will multiply
+            for (int q = 0; q < 8; ++q) {  // eight values = one 16-byte chunk of the line
+                union { uint4 v; T e[8]; } o;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint32_t bits = q < 4 ? r0[q * 8 + i] : r1[(q - 4) * 8 + i];
+                    o.e[i] = from_f32<T>(ex2(__uint_as_float(bits) - m_use));
+                    l4[i & 3] += to_f32(o.e[i]);  // the sum of what the MMA will multiply
                 }
-                // row `row`, keys cc*32..+31: block of 64 keys cc/2, 16-byte chunks (cc&1)*4 .. +3, 128-byte swizzle
-                char *prow = sP + (cc >> 1) * kGemmABytes + row * 128;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4 *>(prow + ((((cc & 1) * 4 + q) ^ (row & 7)) << 4)) = o.q[q];
+                *reinterpret_cast<uint4 *>(prow + ((q ^ (row & 7)) << 4)) = o.v;
             }
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             tc_fence_before();
             fence_async_smem();  // P was written through the generic proxy; the MMA reads it through the async proxy
             __syncwarp();
@@ -304,26 +320,31 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
         }
         ++oc;
         tc_fence_after();
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-#pragma unroll 1
-        for (int cc = 0; cc < 4; ++cc) {
-            uint32_t r[32];
-            tmem_ld32(lane_addr + kAtO + cc * 32, r);
-            tmem_ld_wait();
-            if (qi < a.Tq) {
-                union { uint4 q[4]; T e[32]; } o;
+        // the row's sum: both halves, added in the same order by both warps
+        float *x = xch + 512 + (oc & 1) * 256;
+        x[half * 128 + row] = l;
+        named_barrier(1 + quarter, 64);
+        const float lsum = x[row] + x[128 + row];
+        const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(lane_addr + kAtO + col0, r0);
+        tmem_ld32(lane_addr + kAtO + col0 + 32, r1);
+        tmem_ld_wait();
+        if (qi < a.Tq) {
+            union { uint4 q[4]; T e[32]; } o;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o.e[i] = from_f32<T>(__uint_as_float(r[i]) * inv);
+            for (int i = 0; i < 32; ++i) o.e[i] = from_f32<T>(__uint_as_float(r0[i]) * inv);
 #pragma unroll
-                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4 *>(orow + cc * 32 + q * 8) = o.q[q];
-            }
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4 *>(orow + q * 8) = o.q[q];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o.e[i] = from_f32<T>(__uint_as_float(r1[i]) * inv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4 *>(orow + 32 + q * 8) = o.q[q];
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&B->o_free);
-        ++uc;
     }
-    (void)uc;
     return true;
 }
 
@@ -340,9 +361,9 @@ __device__ __noinline__ void run_prefill_attn(const PrefillAttnArgs &a, const Pr
         mbar_init(&B->q_full, 1); mbar_init(&B->q_empty, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&B->kv_full[s], 1); mbar_init(&B->kv_empty[s], 1);
-            mbar_init(&B->s_full[s], 1); mbar_init(&B->s_free[s], kEpiWarps);
+            mbar_init(&B->s_full[s], 1); mbar_init(&B->s_free[s], kAtSoftmaxWarps);
         }
-        mbar_init(&B->p_ready, kEpiWarps); mbar_init(&B->o_done, 1); mbar_init(&B->o_free, kEpiWarps);
+        mbar_init(&B->p_ready, kAtSoftmaxWarps); mbar_init(&B->o_done, 1); mbar_init(&B->o_free, kAtSoftmaxWarps);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -350,7 +371,7 @@ __device__ __noinline__ void run_prefill_attn(const PrefillAttnArgs &a, const Pr
         if (lane == 0) attn_produce(R);
     } else if (warp == kMmaWarp) {
         if (lane == 0) attn_issue(R);
-    } else if (warp < kEpiWarps) {
+    } else if (warp < kEpiWarps || (warp >= 8 && warp < 12)) {
         if (a.dtype == DT_BF16) attn_softmax<__nv_bfloat16>(R, warp, lane);
         else attn_softmax<__half>(R, warp, lane);
     }

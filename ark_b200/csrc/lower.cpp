@@ -887,6 +887,10 @@ struct Lowerer {
                     }
                 }
             }
+            if (const char *e = getenv("ARKB_TILE_N")) {  // experiments: force the tile width (rounded to what the mode allows)
+                const int want = atoi(e);
+                if (want >= min_n && want <= 256) tile_n = want / step * step;
+            }
             if (N < tile_n) tile_n = (int)((N + step - 1) / step * step);  // narrow outputs: one tile covers N
             g.tile_n = tile_n;
             g.plan_tiles = 0;

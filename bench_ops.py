@@ -198,7 +198,22 @@ def main():
     case("matmul_fp16_8192x8192x8192", mm(8192, 8192, 8192, ark.fp16, 2))
     case("matmul_bf16_nk_4096x8192x8192", mm(4096, 8192, 8192, ark.bf16, 2, nk=True))
     case("matmul_fp16_2048x4096x4096", mm(2048, 4096, 4096, ark.fp16, 2))
+    case("matmul_fp16_nk_2048x4096x4096", mm(2048, 4096, 4096, ark.fp16, 2, nk=True))     # Llama-7B Q/K/V/O projection, 2048 tokens
+    case("matmul_fp16_nk_2048x11008x4096", mm(2048, 11008, 4096, ark.fp16, 2, nk=True))   # W1 / W3
+    case("matmul_fp16_nk_2048x4096x11008", mm(2048, 4096, 11008, ark.fp16, 2, nk=True))   # W2
     case("matmul_fp16_128x4096x1024", mm(128, 4096, 1024, ark.fp16, 2))
+
+    # ---- fused prefill attention: FLOPs = the (causal) part of q k^T and p v that is needed ----
+    def attn(b, hq, hkv, t, dt):
+        def f():
+            q = ark.tensor([b, t, hq, 128], dt)
+            k, v = ark.tensor([b, t, hkv, 128], dt), ark.tensor([b, t, hkv, 128], dt)
+            ark.prefill_attention(q, k, v, 1.0 / 128 ** 0.5, causal=True, token_major=True)
+            return (2 * b * t * hq * 128 + 2 * b * t * hkv * 128) * 2, 4.0 * b * hq * (t * (t + 1) / 2) * 128
+        return f
+    case("prefill_attn_fp16_32h_1x2048", attn(1, 32, 32, 2048, ark.fp16))
+    case("prefill_attn_bf16_gqa_64h_8kv_4x1024", attn(4, 64, 8, 1024, ark.bf16))
+    case("prefill_attn_fp16_32h_1x8192", attn(1, 32, 32, 8192, ark.fp16))
 
     if args.only and args.only in "ffn_cfg1":
         us, nbytes, flops, notes = time_ffn_cfg1(ark, args.iters)
