@@ -1152,6 +1152,7 @@ struct Lowerer {
         a.causal = op.has_arg("Causal") ? (int32_t)op.arg_int("Causal") : 0;
         a.dtype = q.dtype;
         a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
+        if (!(a.scale > 0.0f)) throw Error(E_UNSUPPORTED, "PrefillAttention: Scale must be positive");
         a.q_tiles = (int32_t)((Tq + 127) / 128);
         a.n_units = (int32_t)(B * Hq * a.q_tiles);
         acc_begin();
