@@ -86,6 +86,12 @@ __device__ __forceinline__ AttnUnit attn_unit(const PrefillAttnArgs &a, int u) {
     return t;
 }
 
+// Units are sorted by length (longest first); CTA p takes one unit per round, walking the rounds back and forth, so
+// that the CTA with the longest unit of one round gets the shortest of the next.
+__device__ __forceinline__ int attn_unit_of(const AttnRun &R, int rnd) {
+    return rnd * R.P + ((rnd & 1) ? R.P - 1 - R.p : R.p);
+}
+
 __device__ __forceinline__ bool attn_fail(const AttnRun &R) {
     R.ctl->abort = 1;
     report(R.st, ST_MBAR_TIMEOUT, R.stage_idx);
@@ -164,7 +170,9 @@ __device__ __noinline__ bool attn_produce(const AttnRun &R, bool is_v) {
     const int slots = is_v ? kAtVSlots : kAtKSlots;
     int s = 0;
     uint32_t wrap = 0;  // completed laps of the ring (phase of slot s)
-    for (int u = R.p; u < a.n_units; u += R.P) {
+    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
+        const int u = attn_unit_of(R, rnd);
+        if (u >= a.n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         if (t.n_tiles == 0) continue;
         if (!is_v) {
@@ -237,7 +245,9 @@ __device__ __noinline__ bool attn_issue(const AttnRun &R) {
         return true;
     };
 
-    for (int u = R.p; u < a.n_units; u += R.P) {
+    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
+        const int u = attn_unit_of(R, rnd);
+        if (u >= a.n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         if (t.n_tiles == 0) continue;
         if (!mbar_wait(&B->q_full, uc & 1, R.lim)) return attn_fail(R);
@@ -303,7 +313,9 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
         }
         return true;
     };
-    for (int u = R.p; u < a.n_units; u += R.P) {
+    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
+        const int u = attn_unit_of(R, rnd);
+        if (u >= a.n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         const int qi = t.qt * kAtTile + row;
         T *orow = reinterpret_cast<T *>(a.out) + (int64_t)t.b * a.o_stride_b + (int64_t)t.h * a.o_stride_h + (int64_t)qi * a.o_stride_t + col0;

@@ -211,9 +211,46 @@ __device__ void reduce_other_axis(const ReduceArgs &a, int p, int P, float *red)
     }
 }
 
+// A subset of the outputs (a plan's partial task range): one warp per output element, the lanes stride along the
+// reduced axis, a shuffle tree adds the partial results (fixed order: deterministic).
+template <typename T>
+__device__ void reduce_tasks(const ReduceArgs &a, int p, int P) {
+    constexpr int WPC = kThreads / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int32_t osh[4] = {a.in.shape[0], a.in.shape[1], a.in.shape[2], a.in.shape[3]};
+    const int64_t len = osh[a.axis];
+    osh[a.axis] = 1;
+    const int64_t astr = a.in.stride[a.axis];
+    const T *in = reinterpret_cast<const T *>(a.in.ptr);
+    T *out = reinterpret_cast<T *>(a.out.ptr);
+    const int64_t n_tasks = a.task_e > a.task_b ? (a.task_e - a.task_b + a.task_s - 1) / a.task_s : 0;
+    for (int64_t k = (int64_t)p * WPC + warp; k < n_tasks; k += (int64_t)P * WPC) {
+        int64_t r = a.task_b + k * a.task_s;
+        const int64_t w = r % osh[3];
+        r /= osh[3];
+        const int64_t h = r % osh[2];
+        r /= osh[2];
+        const int64_t c = r % osh[1], n = r / osh[1];
+        if (n >= osh[0]) continue;
+        const T *src = in + tref_off(a.in, n, c, h, w);
+        float acc = (a.op == RD_MAX) ? -3.402823466e+38f : 0.0f;
+        for (int64_t i = lane; i < len; i += 32) {
+            const float v = to_f32(src[i * astr]);
+            acc = (a.op == RD_MAX) ? fmaxf(acc, v) : acc + v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, acc, o);
+            acc = (a.op == RD_MAX) ? fmaxf(acc, other) : acc + other;
+        }
+        if (lane == 0) out[tref_off(a.out, n, c, h, w)] = from_f32<T>(a.op == RD_MEAN ? acc / (float)len : acc);
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ void reduce_typed(const ReduceArgs &a, int p, int P, float *red) {
     constexpr int V = 16 / sizeof(T);
+    if (a.partial) return reduce_tasks<T>(a, p, P);
     if (a.axis == 3) {
         if (a.vec > 1) reduce_last_axis<T, V>(a, p, P);
         else reduce_last_axis<T, 1>(a, p, P);
@@ -696,7 +733,7 @@ __device__ void transpose_es(const TransposeArgs &a, int p, int P, char *smem) {
     const int64_t O0 = a.out.shape[0], O1 = a.out.shape[1], O2 = a.out.shape[2], O3 = a.out.shape[3];
     int64_t is[4];  // input stride seen from each output dim
     for (int i = 0; i < 4; ++i) is[i] = a.in.stride[a.perm[i]];
-    if (a.perm[3] == 3) {
+    if (a.perm[3] == 3 && !a.partial) {
         constexpr int V = 16 / ES;
         const bool vec = (O3 % V == 0) && a.out.contiguous == 2;  // host: 2 = rows 16-byte aligned on both sides
         if (vec) {
@@ -719,6 +756,11 @@ __device__ void transpose_es(const TransposeArgs &a, int p, int P, char *smem) {
         int64_t i2 = r % O2;
         r /= O2;
         int64_t i1 = r % O1, i0 = r / O1;
+        if (a.partial) {
+            const int64_t th = (O2 + a.tile_h - 1) / a.tile_h, tw = (O3 + a.tile_w - 1) / a.tile_w;
+            const int64_t task = ((i0 * O1 + i1) * th + i2 / a.tile_h) * tw + i3 / a.tile_w;
+            if (task < a.task_b || task >= a.task_e || (task - a.task_b) % a.task_s) continue;
+        }
         out[tref_off(a.out, i0, i1, i2, i3)] = in[i0 * is[0] + i1 * is[1] + i2 * is[2] + i3 * is[3]];
     }
 }
@@ -736,7 +778,8 @@ __device__ __noinline__ void run_embed(const EmbedArgs &a, int p, int P) {
     constexpr int WPC = kThreads / 32;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t row_bytes = a.emb_dim * a.esize;
-    for (int64_t i = (int64_t)p * WPC + warp; i < a.n_idx; i += (int64_t)P * WPC) {
+    for (int64_t k = (int64_t)p * WPC + warp; k < a.n_idx; k += (int64_t)P * WPC) {
+        const int64_t i = a.task_b + k * a.task_s;
         int64_t r = a.idx[i];
         if (r < 0) r += a.num_emb;
         const char *src = reinterpret_cast<const char *>(a.weight) + r * a.w_ld * a.esize;

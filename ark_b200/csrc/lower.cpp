@@ -332,8 +332,7 @@ struct Lowerer {
 
     // ---- reduce ------------------------------------------------------------------
     void lower_reduce(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
-        if (!full_range(tg.task_range, num_tasks(op)))
-            throw Error(E_UNSUPPORTED, op.type + ": partial TaskRange is supported for Matmul only");
+        const bool partial = !full_range(tg.task_range, num_tasks(op));
         const TensorDesc &in = op.reads.at(0);
         TensorDesc out = op.results.at(0);
         int axis = (int)op.arg_int("Axis");
@@ -368,11 +367,19 @@ struct Lowerer {
             for (int i = 0; i < 3; ++i) ok = ok && (a.out.stride[i] % V == 0);
         }
         a.vec = ok ? V : 1;
-        push(s, op.type + " " + op.name + " axis=" + std::to_string(ax4) + " vec=" + std::to_string(a.vec));
+        if (partial) {
+            // a task is one output element (ark/ops/ops_reduce.cpp: NumTasks = elements of the result)
+            if (num_tasks(op) != out.nelems()) throw Error(E_UNSUPPORTED, op.type + ": a partial TaskRange needs one task per output element");
+            a.partial = 1;
+            a.task_b = tg.task_range.b; a.task_e = std::min<int64_t>(tg.task_range.e, out.nelems()); a.task_s = std::max<int64_t>(1, tg.task_range.s);
+            acc.opaque = false;
+        }
+        push(s, op.type + " " + op.name + " axis=" + std::to_string(ax4) + " vec=" + std::to_string(a.vec) +
+                    (partial ? " tasks [" + std::to_string(a.task_b) + "," + std::to_string(a.task_e) + (a.task_s != 1 ? "," + std::to_string(a.task_s) : "") + ")" : ""));
     }
 
     // ---- fused row operators (engine extensions) -----------------------------------------
-    void lower_rowop(const OpDesc &op, const Range &proc) {
+    void lower_rowop(const OpDesc &op, const Range &proc, const TaskGroup *tg = nullptr) {
         const TensorDesc &in = op.reads.at(0);
         const TensorDesc &out = op.results.at(0);
         Stage s = new_stage(SK_ROWOP, proc);
@@ -433,6 +440,25 @@ struct Lowerer {
         if (a.residual) ok = ok && aligned16(a.residual) && aligned16(a.res_out);
         if (!ok) throw Error(E_UNSUPPORTED, op.type + ": rows must be 16-byte aligned and a multiple of 16 bytes long");
         if (!(in.dtype == DT_F32 || in.dtype == DT_F16 || in.dtype == DT_BF16)) throw Error(E_UNSUPPORTED, op.type + ": floating-point only");
+        std::string part_note;
+        if (tg && !full_range(tg->task_range, num_tasks(op))) {
+            // a task is one row: the rows task_b, task_b + task_s, ... are a view with a larger row pitch
+            if (num_tasks(op) != a.rows) throw Error(E_UNSUPPORTED, op.type + ": a partial TaskRange needs one task per row");
+            const int64_t b = tg->task_range.b, st = std::max<int64_t>(1, tg->task_range.s), e = std::min<int64_t>(tg->task_range.e, a.rows);
+            if (a.mask && a.mask_rows > 1 && (st != 1 || b % a.mask_rows))
+                throw Error(E_UNSUPPORTED, "Softmax: a partial TaskRange must start on a mask period and have step 1");
+            const size_t es = dtype_size(in.dtype);
+            a.in = reinterpret_cast<const char *>(a.in) + (size_t)b * a.in_ld * es;
+            a.out = reinterpret_cast<char *>(a.out) + (size_t)b * a.out_ld * es;
+            if (a.residual) {
+                a.residual = reinterpret_cast<const char *>(a.residual) + (size_t)b * a.in_ld * es;
+                a.res_out = reinterpret_cast<char *>(a.res_out) + (size_t)b * a.in_ld * es;  // res_out rows follow the input's pitch
+            }
+            a.rows = e > b ? (e - b + st - 1) / st : 0;
+            a.in_ld *= st;
+            a.out_ld *= st;
+            part_note = " tasks [" + std::to_string(b) + "," + std::to_string(e) + (st != 1 ? "," + std::to_string(st) : "") + ")";
+        }
         // warps that share a row so that each lane keeps at most 8 16-byte vectors of it in registers
         {
             const int64_t nv = a.cols / V;
@@ -456,7 +482,7 @@ struct Lowerer {
         }
         push(s, op.type + " " + op.name + " rows=" + std::to_string(a.rows) + " cols=" + std::to_string(a.cols) +
                     " warps/row=" + std::to_string(a.warps_per_row) +
-                    (a.staged_warps ? " staged(" + std::to_string(a.staged_warps) + " warps x " + std::to_string(a.staged_bufs) + " rows)" : ""));
+                    (a.staged_warps ? " staged(" + std::to_string(a.staged_warps) + " warps x " + std::to_string(a.staged_bufs) + " rows)" : "") + part_note);
     }
 
     // ---- matmul --------------------------------------------------------------------
@@ -1076,11 +1102,21 @@ struct Lowerer {
         a.B = (int32_t)B; a.Hq = (int32_t)Hq; a.Hkv = (int32_t)Hkv; a.T = (int32_t)T;
         a.dtype = q.dtype;
         a.scale = op.has_arg("Scale") ? (float)op.arg_float("Scale") : 1.0f;
-        // chunks of the cache: about two work items per CTA, at least 128 and at most 2048 keys each
+        // chunks of the cache: at most two work items per CTA (one more would cost a third round), at least 128 and at
+        // most 2048 keys each; among the candidates the one with the least makespan (rounds x keys per item)
         const int64_t P = proc.count();
-        int64_t chunks = std::max<int64_t>(1, std::min<int64_t>((2 * P + B * Hkv - 1) / (B * Hkv), (T + 127) / 128));
-        int64_t chunk_len = std::min<int64_t>(2048, ((T + chunks - 1) / chunks + 31) / 32 * 32);
-        chunks = (T + chunk_len - 1) / chunk_len;
+        const int64_t max_chunks = std::max<int64_t>(1, std::min<int64_t>(2 * P / (B * Hkv), (T + 127) / 128));
+        int64_t chunks = 1, chunk_len = 0;
+        {
+            int64_t best = -1;
+            for (int64_t c = 1; c <= max_chunks; ++c) {
+                const int64_t len = std::min<int64_t>(2048, ((T + c - 1) / c + 31) / 32 * 32);
+                const int64_t n = (T + len - 1) / len;
+                const int64_t rounds = (B * Hkv * n + P - 1) / P;
+                const int64_t cost = rounds * (len + 64);  // 64 keys' worth of fixed cost per item
+                if (best < 0 || cost < best) { best = cost; chunks = n; chunk_len = len; }
+            }
+        }
         a.chunks = (int32_t)chunks; a.chunk_len = (int32_t)chunk_len;
         const size_t bytes = (size_t)B * Hkv * chunks * G * (128 + 2) * sizeof(float);
         a.ws = env.workspace ? reinterpret_cast<float *>(env.workspace + prog.workspace_bytes) : nullptr;
@@ -1165,7 +1201,7 @@ struct Lowerer {
 
     // ---- transpose / embedding ---------------------------------------------------------
     void lower_transpose(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
-        if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Transpose: partial TaskRange");
+        const bool partial = !full_range(tg.task_range, num_tasks(op));
         const TensorDesc &in = op.reads.at(0), &out = op.results.at(0);
         auto perm = op.arg_dims("Permutation");
         const int nd = (int)in.shape.size();
@@ -1185,11 +1221,20 @@ struct Lowerer {
         bool vec = a.perm[3] == 3 && aligned16(a.in.ptr) && aligned16(a.out.ptr) && a.out.shape[3] % V == 0;
         for (int i = 0; i < 3; ++i) vec = vec && a.in.stride[i] % V == 0 && a.out.stride[i] % V == 0;
         a.out.contiguous = vec ? 2 : a.out.contiguous;
-        push(s, "Transpose " + op.name + (vec ? " vec" : ""));
+        if (partial) {
+            if (!op.config.is_object() || !op.config.contains("Tile")) throw Error(E_PLAN, "Transpose: a partial TaskRange needs the Tile of the tasks");
+            auto tile = op.config.at("Tile").as_int_vec();
+            if (tile.size() != 2 || tile[0] <= 0 || tile[1] <= 0) throw Error(E_PLAN, "Transpose: Tile should have 2 positive elements");
+            a.partial = 1;
+            a.tile_h = (int32_t)tile[0]; a.tile_w = (int32_t)tile[1];
+            a.task_b = tg.task_range.b; a.task_e = tg.task_range.e; a.task_s = std::max<int64_t>(1, tg.task_range.s);
+        }
+        push(s, "Transpose " + op.name + (vec && !partial ? " vec" : "") +
+                    (partial ? " tasks [" + std::to_string(a.task_b) + "," + std::to_string(a.task_e) + (a.task_s != 1 ? "," + std::to_string(a.task_s) : "") + ")" : ""));
     }
 
     void lower_embedding(const OpDesc &op, const Range &proc, const TaskGroup &tg) {
-        if (!full_range(tg.task_range, num_tasks(op))) throw Error(E_UNSUPPORTED, "Embedding: partial TaskRange");
+        const bool partial = !full_range(tg.task_range, num_tasks(op));
         const TensorDesc &idx = op.reads.at(0), &w = op.reads.at(1), &out = op.results.at(0);
         if (idx.dtype != DT_I32) throw Error(E_MODEL, "Embedding: indices must be INT32");
         if (!idx.dense()) throw Error(E_UNSUPPORTED, "Embedding: strided index tensor");
@@ -1210,7 +1255,16 @@ struct Lowerer {
         a.w_ld = wst[3];
         a.out_ld = ost[3];
         a.esize = (int32_t)dtype_size(w.dtype);
-        push(s, "Embedding " + op.name + " n=" + std::to_string(a.n_idx));
+        a.task_b = 0; a.task_s = 1;
+        if (partial) {
+            // a task gathers one row (ark/ops/ops_embedding.cpp: NumTasks = indices)
+            if (num_tasks(op) != idx.nelems()) throw Error(E_UNSUPPORTED, "Embedding: a partial TaskRange needs one task per index");
+            const int64_t e = std::min<int64_t>(tg.task_range.e, idx.nelems());
+            a.task_b = tg.task_range.b; a.task_s = std::max<int64_t>(1, tg.task_range.s);
+            a.n_idx = e > a.task_b ? (e - a.task_b + a.task_s - 1) / a.task_s : 0;
+        }
+        push(s, "Embedding " + op.name + " n=" + std::to_string(a.n_idx) +
+                    (partial ? " tasks from " + std::to_string(a.task_b) + " step " + std::to_string(a.task_s) : ""));
     }
 
     // ---- communication ------------------------------------------------------------------
@@ -1560,7 +1614,7 @@ struct Lowerer {
         if (t == "Embedding") return lower_embedding(op, proc, tg);
         if (t == "DecodeAttention") return lower_decode_attention(op, proc);
         if (t == "PrefillAttention") return lower_prefill_attention(op, proc);
-        if (t == "RMSNorm" || t == "LayerNorm" || t == "Softmax") return lower_rowop(op, proc);
+        if (t == "RMSNorm" || t == "LayerNorm" || t == "Softmax") return lower_rowop(op, proc, &tg);
         if (t == "Send") return lower_send(op, proc);
         if (t == "Recv") return lower_recv(op, proc);
         if (t == "DeviceSync") return lower_device_sync(op, proc);

@@ -87,7 +87,8 @@ struct ReduceArgs {
     int32_t op;
     int32_t axis;       // 0..3 in 4-D form
     int32_t vec;        // vector width usable on the innermost dim
-    int32_t pad;
+    int32_t partial;    // 1: only the tasks task_b, task_b + task_s, ... < task_e run (a task = one output element, in the order of the 4-D output)
+    int64_t task_b, task_e, task_s;
 };
 
 struct RowOpArgs {
@@ -254,6 +255,10 @@ struct GemmSimtArgs {
 struct TransposeArgs {
     TRef out, in;      // out.shape[i] == in.shape[perm[i]]
     int32_t perm[4];
+    // partial != 0: only the tasks task_b, task_b + task_s, ... < task_e run; a task is a tile_h x tile_w tile of the two
+    // innermost output dims, numbered (n, c, tile row, tile column) with the column fastest
+    int32_t partial, tile_h, tile_w, pad;
+    int64_t task_b, task_e, task_s;
 };
 
 struct EmbedArgs {
@@ -263,6 +268,7 @@ struct EmbedArgs {
     int64_t n_idx, num_emb, emb_dim;  // emb_dim in elements
     int64_t w_ld, out_ld;
     int32_t esize, pad;
+    int64_t task_b, task_s;  // the rows gathered are task_b, task_b + task_s, ... (n_idx of them); 0, 1: all
 };
 
 struct PutArgs {

@@ -194,3 +194,46 @@ def test_embedding_exact(dt):
     out = ark.embedding(ti, tw)
     (got,) = execute([out], {ti: idx, tw: w})
     assert np.array_equal(got.view(np.uint8), O.embedding(idx, w).view(np.uint8))
+
+
+def _split_plan(split):
+    """Gives every operator's tasks to two processor groups' worth of CTAs: [0, n/3) + [n/3, n), or even / odd."""
+    import json
+    plan = ark.Planner(0).plan().plan
+    groups = []
+    for ti in plan["TaskInfos"]:
+        nt = ti["Ops"][0]["Config"]["NumTasks"]
+        ranges = ([0, nt // 3], [nt // 3, nt]) if split == "halves" else ([0, nt, 2], [1, nt, 2])
+        rgs = [{"ProcessorRange": pr, "WarpRange": [0, 1], "SramRange": [0, 0],
+                "TaskGroups": [{"TaskId": ti["Id"], "TaskRange": tr, "Granularity": 1}]}
+               for pr, tr in zip(([0, 48], [48, 148]), ranges)]
+        groups.append({"ProcessorRange": [0, 148], "ResourceGroups": rgs})
+    plan["ProcessorGroups"] = groups
+    plan["NumProcessors"] = 148
+    return json.dumps(plan)
+
+
+@pytest.mark.parametrize("split", ["halves", "interleaved"])
+def test_partial_task_ranges_of_reductions_rows_transposes_and_gathers(split):
+    """A plan may hand any operator's tasks to several groups of processors (ark/codegen.cpp:318-385): a reduction's
+    task is one output element, a row operator's one row, a transpose's one 8 x 8 tile of the output, an embedding's
+    one index. Each group writes exactly its share; together they give the whole result."""
+    rng = np.random.default_rng(46)
+    x = O.to_storage(rng.normal(0, 1, (3, 20, 72)).astype(np.float32), "fp16")
+    w = O.to_storage(rng.normal(0, 1, (50, 64)).astype(np.float32), "fp16")
+    idx = rng.integers(-50, 50, size=(2, 9), dtype=np.int32)
+    ark.init()
+    tx, tw, ti = ark.tensor([3, 20, 72], ark.fp16), ark.tensor([50, 64], ark.fp16), ark.tensor([2, 9], ark.int32)
+    outs = [ark.reduce_sum(tx, axis=-1), ark.reduce_max(tx, axis=1), ark.reduce_mean(tx, axis=0), ark.softmax(tx),
+            ark.rmsnorm(tx), ark.transpose(tx, [1, 0, 2]), ark.transpose(tx, [0, 2, 1]), ark.embedding(ti, tw)]
+    plan = _split_plan(split)
+    text = ark.plan_dump(plan)
+    assert text.count("tasks ") == 2 * len(outs), text
+    got = execute(outs, {tx: x, tw: w, ti: idx}, plan=plan)
+    want = [O.reduce("sum", x, 2, "fp16"), O.reduce("max", x, 1, "fp16"), O.reduce("mean", x, 0, "fp16"),
+            O.softmax(x, "fp16"), O.rmsnorm(x, None, "fp16", 1e-5)]
+    for g, wv, name in zip(got[:5], want, ("sum w", "max h", "mean c", "softmax", "rmsnorm")):
+        err = np.abs(O.to_f32(g, "fp16").reshape(wv.shape) - O.to_f32(wv, "fp16"))
+        assert float(err.max()) <= 2e-2, (name, float(err.max()))
+    assert np.array_equal(got[5], x.transpose(1, 0, 2)) and np.array_equal(got[6], x.transpose(0, 2, 1))
+    assert np.array_equal(got[7], w[idx])
