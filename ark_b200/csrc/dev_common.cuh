@@ -63,26 +63,32 @@ __device__ __forceinline__ void l2_prefetch(const void *p, uint32_t bytes) {
 // sense-reversing sync_gpu (ark/include/kernels/common/sync.h:36-66); the wait
 // is bounded (`spin_limit` nanoseconds) and reports instead of spinning forever.
 // Returns false on abort.
+// One thread waits until the counter reaches `target` (acquire); bounded.
+__device__ __forceinline__ void counter_wait(unsigned long long *ctr, unsigned long long target, unsigned long long spin_limit,
+                                             CtaCtl *ctl, DeviceState *st, int stage) {
+    unsigned long long spins = 0, t0 = 0;
+    while (ld_acquire_gpu(ctr) < target) {
+        ++spins;
+        if ((spins & 1023) == 0) {
+            const unsigned long long now = globaltimer();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > spin_limit) {
+                ctl->abort = 1;
+                report(st, ST_BARRIER_TIMEOUT, stage);
+                break;
+            }
+        }
+        if (spins > 64) __nanosleep(spins > 4096 ? 256 : 32);
+    }
+}
+
 __device__ __forceinline__ bool grid_barrier(unsigned long long *ctr, unsigned long long target,
                                              unsigned long long spin_limit, CtaCtl *ctl, DeviceState *st,
                                              int stage) {
     __syncthreads();
     if (threadIdx.x == 0) {
         red_release_gpu_add(ctr, 1ull);
-        unsigned long long spins = 0, t0 = 0;
-        while (ld_acquire_gpu(ctr) < target) {
-            ++spins;
-            if ((spins & 1023) == 0) {
-                const unsigned long long now = globaltimer();
-                if (t0 == 0) t0 = now;
-                if (now - t0 > spin_limit) {
-                    ctl->abort = 1;
-                    report(st, ST_BARRIER_TIMEOUT, stage);
-                    break;
-                }
-            }
-            if (spins > 64) __nanosleep(spins > 4096 ? 256 : 32);
-        }
+        counter_wait(ctr, target, spin_limit, ctl, st, stage);
     }
     __syncthreads();
     return ctl->abort == 0;

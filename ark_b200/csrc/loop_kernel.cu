@@ -100,10 +100,29 @@ __device__ __forceinline__ void run_body(const LaunchParams &P, char *smem, Gemm
             case SK_PUT: run_put(S.put, p, Pn, iter_no); break;
             case SK_SIGNAL: if (p == 0) run_signal(P, S.sg, iter_no); break;
             case SK_WAITFLAG: if (p == 0) run_wait(P, S.wt, iter_no, ctl, s); break;
-            case SK_PEERSYNC:
-                if (p == 0)
-                    run_peersync(P, (iter_no - 1) * (unsigned long long)P.peersyncs_per_iter + S.ps.ord, ctl, s);
+            case SK_PEERSYNC: {
+                const unsigned long long epoch = (iter_no - 1) * (unsigned long long)P.peersyncs_per_iter + S.ps.ord;
+                if (!S.ps.with_grid) {
+                    if (p == 0) run_peersync(P, epoch, ctl, s);
+                    break;
+                }
+                unsigned long long *ctr = &P.state->barrier[S.sync_group];
+                const unsigned long long k = iter_local * (unsigned long long)P.syncs_per_iter[S.sync_group] + S.sync_ord;
+                const unsigned long long done = k * (unsigned long long)S.sync_count;
+                __syncthreads();
+                if (threadIdx.x == 0) red_release_gpu_add(ctr, 1ull);
+                if (p == 0) {
+                    if (threadIdx.x == 0) counter_wait(ctr, done - 1, P.spin_limit, ctl, P.state, s);  // every CTA has arrived
+                    __syncthreads();
+                    if (!ctl->abort) run_peersync(P, epoch, ctl, s);
+                    // a failed exchange releases nobody: the other CTAs give up at this barrier, not on incomplete data
+                    if (threadIdx.x == 0 && !ctl->abort) red_release_gpu_add(ctr, 1ull);
+                }
+                if (threadIdx.x == 0) counter_wait(ctr, done, P.spin_limit, ctl, P.state, s);
+                __syncthreads();
+                if (ctl->abort) return;
                 break;
+            }
             case SK_ALLREDUCE: run_allreduce(P, S.ar, p, Pn, iter_no); break;
             case SK_PACKET: run_packet(P, S.pk, p, Pn, iter_no, ctl, s); break;
             case SK_PACKET_REDUCE: run_packet_reduce(P, S.pr, p, Pn, iter_no, ctl, s); break;

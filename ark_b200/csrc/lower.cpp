@@ -898,17 +898,26 @@ struct Lowerer {
             // pick the width whose makespan (waves x tile width, plus a fixed cost per tile) is least,
             // so that skinny and small problems spread evenly over the CTAs.
             // a CTA stages whole 64-column chunks of a row-major (MN-major) B, so its share stays a multiple of 64
-            const int step = g.b_mn_major ? (prog.pair_mode ? 128 : 64) : (prog.pair_mode ? 32 : 16);
+            // (a matmul fused with the all_reduce behind it stores its tiles as 32-column blocks)
+            const int step = g.b_mn_major ? (prog.pair_mode ? 128 : 64) : (prog.pair_mode || fuse_ar ? 32 : 16);
             const int min_n = step;
             int tile_n = 256;
             {
+                // Time model of a tile (microseconds), fitted to measurements of 2048 x 4096 x 4096 at every width: a
+                // k-block takes the longer of its MMAs (0.4 us at width 256) and of its operand loads (the CTA's A rows
+                // plus its share of B, at ~90 GB/s per SM; CTA pairs were measured 1.35x slower per byte), a tile
+                // ~2 us more (pipeline fill, epilogue tail). Rounds x tile time picks the width.
                 const int64_t units256 = bn * bc * tiles_m * ((N + 255) / 256);
-                if (units256 < 4 * P) {
+                static const bool old_model = []() { const char *e = getenv("ARKB_TILE_MODEL"); return e && atoi(e) == 0; }();
+                if (units256 < 8 * P) {
+                    const double kblocks = (double)((K + 63) / 64);
                     double best = 1e30;
                     for (int c = 256; c >= min_n; c -= step) {
                         const int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
                         const int64_t waves = (units + P - 1) / P;
-                        const double cost = (double)waves * (c + 24);
+                        const double load = prog.pair_mode ? 1.35 * 1.42e-3 * (128 + c / 2.0) : 1.42e-3 * (128 + c);
+                        const double tk = std::max(0.4 * c / 256.0, load);
+                        const double cost = old_model ? (double)waves * (c + 24) : (double)waves * (kblocks * tk + 2.0);
                         if (cost < best - 1e-9) { best = cost; tile_n = c; }
                     }
                 }
@@ -1399,11 +1408,39 @@ struct Lowerer {
         push(s, "peer barrier #" + std::to_string(s.ps.ord) + " (" + why + ")");
     }
 
+    // Grid barrier, exchange with the peers, grid barrier: one stage when the range is a dense run of CTAs starting at
+    // CTA 0 of the range (CTA 0 does the exchange between the two halves of the barrier), three stages otherwise.
+    void emit_grid_peer_barrier(const Range &proc, const std::string &why) {
+        static const bool merged = []() { const char *e = getenv("ARKB_MERGED_PEER_BARRIER"); return e ? atoi(e) != 0 : true; }();
+        if (!merged || proc.s != 1 || proc.count() < 2) {
+            emit_sync(proc);
+            emit_peersync(proc, why);
+            emit_sync(proc);
+            return;
+        }
+        auto key = std::make_tuple(proc.b, proc.e, (int64_t)-1);  // a counter of its own: it advances by CTAs + 1
+        auto it = sync_ids.find(key);
+        int id;
+        if (it == sync_ids.end()) {
+            id = (int)sync_ids.size();
+            if (id >= kMaxSyncGroups - 1) throw Error(E_UNSUPPORTED, "too many distinct processor ranges need a barrier");
+            sync_ids[key] = id;
+        } else {
+            id = it->second;
+        }
+        Stage s = new_stage(SK_PEERSYNC, proc);
+        s.ps.ord = ++prog.peersyncs_per_iter;
+        s.ps.with_grid = 1;
+        s.sync_group = id;
+        s.sync_count = (int32_t)proc.count() + 1;
+        s.sync_ord = ++prog.syncs_per_iter[id];
+        acc_begin();  // touches no tensor; the dependency pass treats it as a whole-range barrier
+        push(s, "grid + peer barrier #" + std::to_string(s.ps.ord) + " (" + why + ")");
+    }
+
     void lower_device_sync(const OpDesc &op, const Range &proc) {
         if (env.nranks == 1) return;
-        emit_sync(proc);
-        emit_peersync(proc, "DeviceSync " + op.name);
-        emit_sync(proc);
+        emit_grid_peer_barrier(proc, "DeviceSync " + op.name);
     }
 
     // fused: the partials already sit in this rank's staging slots (put there by every rank's Matmul epilogue)
@@ -1444,14 +1481,10 @@ struct Lowerer {
             a.stage_bytes = bytes / env.nranks;
             a.no_gather = gather ? 0 : 1;
             a.mc_store = (gather && env.mc_arena && same_offset_everywhere(a)) ? 1 : 0;
-            emit_sync(proc);
-            emit_peersync(proc, "partial tiles pushed");
-            emit_sync(proc);
+            emit_grid_peer_barrier(proc, "partial tiles pushed");
             push(s, "AllReduce " + op.name + (gather ? (a.mc_store ? " sum of staging slots + multicast store bytes=" : " sum of staging slots + all-gather bytes=")
                                                  : " sum of staging slots, own rows only bytes=") + std::to_string(bytes));
-            emit_sync(proc);
-            emit_peersync(proc, "all_reduce outputs stored");
-            emit_sync(proc);
+            emit_grid_peer_barrier(proc, "all_reduce outputs stored");
             return;
         }
         const size_t slot = lay.comm_stage_bytes / kMaxPeers;
@@ -1463,9 +1496,7 @@ struct Lowerer {
             a.ord = oneshot_ord++;
             a.phase = 0;
             if (!pushed) push(s, "AllReduce " + op.name + " one-shot push bytes=" + std::to_string(bytes));
-            emit_sync(proc);
-            emit_peersync(proc, "all_reduce data pushed");
-            emit_sync(proc);
+            emit_grid_peer_barrier(proc, "all_reduce data pushed");
             Stage s2 = s;
             s2.ar.phase = 1;
             if (add) {
@@ -1483,13 +1514,9 @@ struct Lowerer {
             const bool nvls = env.mc_arena && same_offset_everywhere(a) && (algo == "nvls" || (algo == "auto" && env.nranks >= 4));
             if (algo == "nvls" && !nvls) throw Error(E_UNSUPPORTED, "AllReduce: NVLS needs a multicast-bound arena (ARKB_NVLS=1) and one tensor offset on all ranks");
             a.algo = nvls ? 3 : 1;
-            emit_sync(proc);
-            emit_peersync(proc, "all_reduce inputs ready");
-            emit_sync(proc);
+            emit_grid_peer_barrier(proc, "all_reduce inputs ready");
             push(s, "AllReduce " + op.name + (nvls ? " NVLS (multimem.ld_reduce + multimem.st) bytes=" : " two-shot bytes=") + std::to_string(bytes));
-            emit_sync(proc);
-            emit_peersync(proc, "all_reduce outputs stored");
-            emit_sync(proc);
+            emit_grid_peer_barrier(proc, "all_reduce outputs stored");
         }
     }
 
@@ -1915,12 +1942,20 @@ struct Lowerer {
         std::vector<size_t> pending;
         for (size_t i = 0; i < n; ++i) {
             const Stage &s = prog.stages[i];
+            if (s.kind == SK_PEERSYNC && s.ps.with_grid) {  // a barrier that is never elided
+                if (s.proc_b == 0 && s.proc_s == 1 && s.proc_e >= prog.grid) pending.clear();
+                else pending.push_back(i);
+                continue;
+            }
             if (s.kind != SK_SYNC) {
                 pending.push_back(i);
                 continue;
             }
             bool needed = false;
-            for (size_t j = i + 1; j < n && prog.stages[j].kind != SK_SYNC && !needed; ++j)
+            auto whole_grid_barrier = [&](const Stage &b) {
+                return b.kind == SK_PEERSYNC && b.ps.with_grid && b.proc_b == 0 && b.proc_s == 1 && b.proc_e >= prog.grid;
+            };
+            for (size_t j = i + 1; j < n && prog.stages[j].kind != SK_SYNC && !whole_grid_barrier(prog.stages[j]) && !needed; ++j)
                 for (size_t x : pending)
                     if (depends(x, j)) { needed = true; break; }
             if (!needed) {
@@ -1936,6 +1971,7 @@ struct Lowerer {
             if (!keep[i]) { ++out.syncs_elided; continue; }
             Stage s = prog.stages[i];
             std::string note = prog.notes[i];
+            if (s.kind == SK_PEERSYNC && s.ps.with_grid) s.sync_ord = ++out.syncs_per_iter[s.sync_group];
             if (s.kind == SK_SYNC) {
                 s.sync_ord = ++out.syncs_per_iter[s.sync_group];
                 const size_t at = note.find("sync group");

@@ -289,7 +289,10 @@ struct WaitArgs {
 };
 struct PeerSyncArgs {
     int32_t ord;         // 1-based ordinal of this cross-rank barrier within an iteration
-    int32_t pad;
+    // 1: the stage is also the grid barrier before and after the exchange: every CTA arrives on the stage's counter,
+    // CTA 0 waits for all of them, signals and waits for the peers, and arrives once more, which releases the others
+    // (the counter advances by sync_count = CTAs + 1 per barrier)
+    int32_t with_grid;
 };
 // Packets (the reference's SendPacket / RecvPacket, ark/include/kernels/comm.h:376-396): every 8 bytes of payload
 // travel as one 16-byte store {d0, flag, d1, flag}, so data and "it has arrived" are the same write and the receiver

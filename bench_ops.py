@@ -201,6 +201,8 @@ def main():
     case("matmul_fp16_nk_2048x4096x4096", mm(2048, 4096, 4096, ark.fp16, 2, nk=True))     # Llama-7B Q/K/V/O projection, 2048 tokens
     case("matmul_fp16_nk_2048x11008x4096", mm(2048, 11008, 4096, ark.fp16, 2, nk=True))   # W1 / W3
     case("matmul_fp16_nk_2048x4096x11008", mm(2048, 4096, 11008, ark.fp16, 2, nk=True))   # W2
+    case("matmul_fp16_kn_4096x4096x8192", mm(4096, 4096, 8192, ark.fp16, 2))              # one rank's W1 of the FFN block at TP8
+    case("matmul_fp16_kn_4096x8192x4096", mm(4096, 8192, 4096, ark.fp16, 2))              # one rank's W2
     case("matmul_fp16_128x4096x1024", mm(128, 4096, 1024, ark.fp16, 2))
 
     # ---- fused prefill attention: FLOPs = the (causal) part of q k^T and p v that is needed ----

@@ -238,6 +238,24 @@ def main():
     err = np.abs(got.astype(np.float32) - want.astype(np.float32))
     assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("llama layer", err.mean(), err.max())
 
+    # ---- the same layer with the fused attention stage (causal=True: no mask tensor, no CTA pairs), 512 tokens: the
+    # output projection and W2 push their tiles into the summing rank's slots when 512 splits into 128-row blocks per rank
+    seq = 512
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), "fp16")
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), "fp16")
+    fresh()
+    tw = layer_weights(cfg, ark.fp16, world)
+    tx, tr = ark.tensor([batch * seq, cfg.dim], ark.fp16), ark.tensor([1, seq, 1, cfg.head_dim], ark.fp16)
+    ty = decoder_layer(tx, tw, cfg, batch, seq, rank, world, rope=tr, causal=True)
+    text = ark.plan_dump(str(ark.Planner(local).plan()))
+    assert "PrefillAttention" in text and text.count(" rope ") == 2 and "*operand" in text, text
+    feeds = {tx: x, tr: rope}
+    feeds.update({tw[k]: ws[rank][k] for k in tw})
+    (got,) = run([ty], feeds)
+    want = layer(x, ws, cfg, batch, seq, "fp16", rope=rope, causal=True)
+    err = np.abs(got.astype(np.float32) - want.astype(np.float32))
+    assert err.mean() <= 2e-3 and err.max() <= 5e-2, ("llama layer, fused attention", err.mean(), err.max())
+
     # ---- the same layer, one token against a K/V cache (decode): the one-shot all_reduces ride on the weight-streaming
     # matmuls (result stored straight into every rank's staging slots) and the residual adds on their sum stages ----
     # 4 heads per rank so that every weight matrix keeps >= 512 columns per rank at any world size
