@@ -161,9 +161,6 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
     const int kr = min(a.K, k0 + a.kper) - k0;
     const int nv = kr / 8;
     float *rstd = reinterpret_cast<float *>(xs + (size_t)a.M * 2 * nv);  // [M], then one float per warp of scratch
-    if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
-    stage_x<T>(a, xs, nv, k0, rstd);
-    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
     const int row_lo = (int)((int64_t)q * a.N / cps), row_hi = (int)((int64_t)(q + 1) * a.N / cps);
@@ -230,10 +227,14 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
     };
     Cursor ld{row_lo + warp * RW, 0}, cp = ld;
     uint4 qa[RW][VC], qb[RW][VC];
+    // the weights do not depend on the activations: the first loads are in flight while x is normalised and staged
     if (valid(ld)) {
         issue(qa, ld);
         advance(ld);
     }
+    if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
+    stage_x<T>(a, xs, nv, k0, rstd);
+    __syncthreads();
     while (valid(cp)) {
         if (valid(ld)) {
             issue(qb, ld);

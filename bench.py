@@ -29,7 +29,7 @@ FLOPS_PER_STEP = 4.0 * TOKENS * D_MODEL * D_FF  # two GEMMs, 2 flops per MAC
 METRIC, UNIT = "ffn_tflops", "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one iteration of the loop kernel, from ncu captures of this file's
 # device-timed leg (key: (tokens, GPUs)); the summaries are in profiles/loop_kernel_ffn_tp1.md
-NCU_DRAM_BYTES_PER_STEP = {(1024, 1): 1.546e9}
+NCU_DRAM_BYTES_PER_STEP = {(1024, 1): 1.520e9, (4096, 1): 6.831e9}
 
 
 def measured_peaks():
