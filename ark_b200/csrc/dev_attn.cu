@@ -46,6 +46,18 @@ __device__ __noinline__ void attn_chunks(const DecodeAttnArgs &a, int p, int P, 
             const uint4 q4 = *reinterpret_cast<const uint4 *>(qb + (int64_t)b * a.q_stride_b + (int64_t)(kvh * G + g) * a.q_stride_h + v * 8);
             float f[8];
             unpack8<T>(q4, f);
+            if (a.rope) {
+                // rotary embedding of the new token's query (complex multiply of adjacent pairs with the position's
+                // (cos, sin) pairs), rounded like the separate operator would have stored it
+                float t[8];
+                unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.rope) + v * 8), t);
+#pragma unroll
+                for (int e = 0; e < 8; e += 2) {
+                    const float re = f[e] * t[e] - f[e + 1] * t[e + 1], im = f[e] * t[e + 1] + f[e + 1] * t[e];
+                    f[e] = to_f32(from_f32<T>(re));
+                    f[e + 1] = to_f32(from_f32<T>(im));
+                }
+            }
 #pragma unroll
             for (int e = 0; e < 8; ++e) qs[g * D + v * 8 + e] = f[e] * a.scale;
         }

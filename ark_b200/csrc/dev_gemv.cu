@@ -44,6 +44,32 @@ __device__ __forceinline__ float cta_sum(float v, float *scratch) {
 // the separate operator would have stored them. `rstd` is per activation row (GP_RMSNORM only).
 template <typename T>
 __device__ __forceinline__ void load_x8(const GemvArgs &a, int m, int k, float rstd, float (&f)[8]) {
+    if (a.pro == GP_ATTN_MERGE) {
+        // the attention's chunks of head k / 128 of sequence m, merged with the usual max / sum rescaling and rounded
+        // like the merge stage would have stored them
+        const int G = a.mg_group, h = k >> 7, d = k & 127, kvh = h / G, g = h % G;
+        const size_t stride = (size_t)G * 130;
+        const float *w = reinterpret_cast<const float *>(a.pro_a) + ((size_t)(m * a.mg_kv_heads + kvh) * a.mg_chunks) * stride;
+        float mx = -3.402823466e+38f;
+        for (int c = 0; c < a.mg_chunks; ++c) mx = fmaxf(mx, w[c * stride + G * 128 + 2 * g]);
+        float l = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.0f;
+        for (int c = 0; c < a.mg_chunks; ++c) {
+            const float e = __expf(w[c * stride + G * 128 + 2 * g] - mx);
+            l += w[c * stride + G * 128 + 2 * g + 1] * e;
+            const float2 *o = reinterpret_cast<const float2 *>(w + c * stride + g * 128 + d);  // records are 8-byte aligned
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 v = o[i];
+                f[2 * i] += v.x * e;
+                f[2 * i + 1] += v.y * e;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] / l));
+        return;
+    }
     const T *x = reinterpret_cast<const T *>(a.x);
     unpack8<T>(*reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k), f);
     if (a.pro == GP_MUL) {

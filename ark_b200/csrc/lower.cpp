@@ -528,6 +528,41 @@ struct Lowerer {
     std::vector<OpDesc> fused_ops;          // row operators that stand for a chain of the plan's operators
     std::map<size_t, size_t> chain_pgs;     // first processor group of such a chain -> index into fused_ops
     bool gemv_pushed = false;  // set by lower_matmul when the push of a one-shot all_reduce was folded in
+    // Operators folded across processor groups in the decode chain:
+    const OpDesc *rope_for_attention = nullptr;  // a Rope whose only reader is the DecodeAttention of the next group
+    struct PendingMerge {                        // a DecodeAttention whose chunks the weight-streaming matmul of the next group merges
+        int64_t buffer_id = -1;
+        const float *ws = nullptr;
+        size_t ws_bytes = 0;
+        int chunks = 0, group = 0, kv_heads = 0;
+        int64_t B = 0, Hq = 0;
+    } pending_merge;
+    size_t cur_pg = 0, pending_merge_pg = 0;
+    static bool fold_decode_chain() { const char *e = getenv("ARKB_FOLD_DECODE"); return e ? atoi(e) != 0 : true; }
+    // Rope of the new token's query whose only reader is the DecodeAttention that opens the next processor group: the
+    // attention rotates q while it loads it (no stage, no barrier for the rotation)
+    bool rope_feeds_next_attention(const OpDesc &o) const {
+        if (!fold_decode_chain() || o.type != "Rope" || o.reads.size() != 2 || o.results.empty()) return false;
+        const OpDesc *nx = first_op_of(cur_pg + 1);
+        return nx && nx->type == "DecodeAttention" && nx->reads.at(0).buffer_id == o.results[0].buffer_id &&
+               o.results[0].buffer_id != o.reads[0].buffer_id && o.reads[0].dense() && o.results[0].dense() && nx->reads[0].dense() &&
+               o.reads[0].dtype == nx->reads[0].dtype && o.reads[1].dtype == o.reads[0].dtype && o.reads[1].dense() &&
+               o.reads[1].nelems() == 128 && o.reads[0].shape4()[3] == 128 && o.reads[0].nelems() == nx->reads[0].nelems() &&
+               other_readers(o.results[0].buffer_id, nx) == 0;
+    }
+    // first operator that does something of processor group `k` (null when the group is not a plain single-task group)
+    const OpDesc *first_op_of(size_t k, const TaskGroup **tg_out = nullptr) const {
+        if (k >= plan.processor_groups.size()) return nullptr;
+        const ProcessorGroup &g = plan.processor_groups[k];
+        if (g.resource_groups.size() != 1 || g.resource_groups[0].task_groups.size() != 1) return nullptr;
+        const TaskGroup &tg = g.resource_groups[0].task_groups[0];
+        for (auto &o : plan.task(tg.task_id).ops) {
+            if (o.is_virtual || o.type == "Reshape" || o.type == "Identity" || o.type == "Refer" || o.type == "Noop") continue;
+            if (tg_out) *tg_out = &tg;
+            return &o;
+        }
+        return nullptr;
+    }
 
     // an AllReduce the engine runs one-shot (every rank pushes its tensor into every rank's staging slots)
     bool all_reduce_is_one_shot(const OpDesc &op) const {
@@ -670,6 +705,14 @@ struct Lowerer {
                 Stage s = new_stage(SK_GEMV, proc);
                 GemvArgs &g = s.gv;
                 g.out = pc; g.x = pa; g.w = pb;
+                const bool merge_here = pending_merge.buffer_id >= 0 && pending_merge.buffer_id == A.buffer_id;
+                if (merge_here) {
+                    if ((gf && gf->pro != GP_NONE) || M != pending_merge.B || K != pending_merge.Hq * 128 || !A.dense())
+                        throw Error(E_INTERNAL, "decode attention merge folded into a matmul that cannot take it");
+                    g.pro = GP_ATTN_MERGE;
+                    g.pro_a = pending_merge.ws;
+                    g.mg_chunks = pending_merge.chunks; g.mg_group = pending_merge.group; g.mg_kv_heads = pending_merge.kv_heads;
+                }
                 if (gf) {
                     // the prologue's input stands in for the first operand; every folded operand shares its row pitch
                     auto same_rows = [&](const TensorDesc *t) { return !t || (t->strides4()[3] == gf->x->strides4()[3] && aligned16(tensor_ptr(*t))); };
@@ -679,8 +722,8 @@ struct Lowerer {
                             throw Error(E_UNSUPPORTED, "folded operands of a weight-streaming matmul must share one 16-byte aligned row pitch");
                         g.x = tensor_ptr(*gf->x);
                     }
-                    g.pro = gf->pro;
-                    g.pro_a = gf->pro_a ? tensor_ptr(*gf->pro_a) : nullptr;
+                    if (!merge_here) g.pro = gf->pro;
+                    if (!merge_here) g.pro_a = gf->pro_a ? tensor_ptr(*gf->pro_a) : nullptr;
                     g.pro_b = gf->pro_b ? tensor_ptr(*gf->pro_b) : nullptr;
                     g.pro_out = gf->pro_out ? tensor_ptr(*gf->pro_out) : nullptr;
                     g.pro_eps = gf->eps;
@@ -768,7 +811,13 @@ struct Lowerer {
                 }
                 const GemvArgs gv = g;
                 acc_begin();
-                rd(A); rd_streamed(B);
+                if (merge_here) {
+                    rd_raw(pending_merge.ws, pending_merge.ws_bytes);
+                    pending_merge = PendingMerge();
+                } else {
+                    rd(A);
+                }
+                rd_streamed(B);
                 if (gf) {
                     for (const TensorDesc *t : {gf->x, gf->pro_a, gf->pro_b, gf->residual})
                         if (t) rd(*t);
@@ -780,7 +829,7 @@ struct Lowerer {
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
                             std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) + (gv.light ? " light" : "") : "") +
-                            (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : "") + (gv.residual ? " +residual" : "") +
+                            (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : gv.pro == GP_ATTN_MERGE ? " <-attention merge" : "") + (gv.residual ? " +residual" : "") +
                             (gv.push_ord ? " ->all_reduce slots" : "") +
                             (gv.act ? " act=" + std::to_string(gv.act) : ""));
                 if (gv.splits > 1) {
@@ -1102,6 +1151,16 @@ struct Lowerer {
         DecodeAttnArgs &a = s.da;
         a.out = tensor_ptr(o); a.q = tensor_ptr(q); a.k = tensor_ptr(k); a.v = tensor_ptr(v);
         a.q_stride_h = qst[2] * qst[3]; a.q_stride_b = qst[1] * qst[2] * qst[3];
+        const OpDesc *rope = rope_for_attention;
+        rope_for_attention = nullptr;
+        if (rope) {
+            // the unrotated query (dense, the rotated one's layout) and the position's table take the place of q
+            if (rope->results[0].buffer_id != q.buffer_id || !q.dense() || !rope->reads[0].dense())
+                throw Error(E_INTERNAL, "rotary embedding folded into an attention that does not read it");
+            a.q = tensor_ptr(rope->reads[0]);
+            a.rope = tensor_ptr(rope->reads[1]);
+            if (!aligned16(a.rope)) throw Error(E_UNSUPPORTED, "DecodeAttention: the rotary table must be 16-byte aligned");
+        }
         a.o_stride_h = ost[2] * ost[3]; a.o_stride_b = ost[1] * ost[2] * ost[3];
         a.k_ld = kst[3]; a.k_stride_h = kst[2] * kst[3]; a.k_stride_b = kst[1] * kst[2] * kst[3];
         a.v_ld = vst[3]; a.v_stride_h = vst[2] * vst[3]; a.v_stride_b = vst[1] * vst[2] * vst[3];
@@ -1130,12 +1189,29 @@ struct Lowerer {
         const size_t bytes = (size_t)B * Hkv * chunks * G * (128 + 2) * sizeof(float);
         a.ws = env.workspace ? reinterpret_cast<float *>(env.workspace + prog.workspace_bytes) : nullptr;
         prog.workspace_bytes += (bytes + 255) / 256 * 256;
- a.phase = 0;
+        a.phase = 0;
         acc_begin();
-        rd(q); rd_streamed(k); rd_streamed(v);
+        if (rope) { rd(rope->reads[0]); rd(rope->reads[1]); } else rd(q);
+        rd_streamed(k); rd_streamed(v);
         wr_raw(a.ws, bytes);
         push(s, "DecodeAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
-                    " keys=" + std::to_string(T) + " chunks=" + std::to_string(chunks) + " x " + std::to_string(chunk_len));
+                    " keys=" + std::to_string(T) + " chunks=" + std::to_string(chunks) + " x " + std::to_string(chunk_len) + (rope ? " <-rope" : ""));
+        // When the only reader of the result is the weight-streaming matmul of the next processor group (one or two
+        // sequences), that stage merges the chunks while it stages its activations: no merge stage, one barrier less.
+        if (fold_decode_chain() && env.workspace) {
+            const TaskGroup *ntg = nullptr;
+            const OpDesc *nx = first_op_of(cur_pg + 1, &ntg);
+            if (nx && nx->type == "Matmul" && !nx->reads.empty() && nx->reads[0].buffer_id == o.buffer_id && nx->reads[0].dense() &&
+                nx->reads[0].shape4()[2] == B && nx->reads[0].shape4()[3] == Hq * 128 && o.dense() && matmul_is_gemv(*nx, *ntg) &&
+                other_readers(o.buffer_id, nx) == 0) {
+                pending_merge.buffer_id = o.buffer_id;
+                pending_merge.ws = a.ws; pending_merge.ws_bytes = bytes;
+                pending_merge.chunks = (int)chunks; pending_merge.group = (int)G; pending_merge.kv_heads = (int)Hkv;
+                pending_merge.B = B; pending_merge.Hq = Hq;
+                pending_merge_pg = cur_pg;
+                return;
+            }
+        }
         emit_sync(proc);
         Stage m = s;
         m.da.phase = 1;
@@ -1634,6 +1710,10 @@ struct Lowerer {
         if (op.is_virtual) return;
         const std::string &t = op.type;
         if (t == "Noop" || t == "SendDone" || t == "Tensor" || t == "Refer" || t == "Reshape" || t == "Identity") return;
+        if (t == "Rope" && rope_feeds_next_attention(op)) {  // the last operator of its task: nothing of this group follows it
+            rope_for_attention = &op;
+            return;
+        }
         if (ewise_code(t) >= 0) return lower_ewise(op, proc, tg);
         if (t == "ReduceSum" || t == "ReduceMax" || t == "ReduceMean") return lower_reduce(op, proc, tg);
         if (t == "Matmul") return lower_matmul(op, proc, tg, -1, nullptr);
@@ -2075,7 +2155,14 @@ struct Lowerer {
         size_t skip_pgs = 0;
         for (size_t pgi = 0; pgi < plan.processor_groups.size(); ++pgi) {
             if (skip_pgs) { --skip_pgs; continue; }
+            cur_pg = pgi;
             const ProcessorGroup *pgp = &plan.processor_groups[pgi];
+            if (const OpDesc *o = single_op(*pgp)) {
+                if (rope_feeds_next_attention(*o)) {
+                    rope_for_attention = o;
+                    continue;
+                }
+            }
             ProcessorGroup merged;
             {   // a chain spread over consecutive single-operator processor groups becomes one group with one fused operator
                 std::vector<const OpDesc *> seq;
@@ -2141,7 +2228,10 @@ struct Lowerer {
             }
             unsynced.push_back(pr);
             first_pg = false;
+            if (pending_merge.buffer_id >= 0 && pending_merge_pg != pgi)
+                throw Error(E_INTERNAL, "decode attention merge was left without its consumer");
         }
+        if (pending_merge.buffer_id >= 0) throw Error(E_INTERNAL, "decode attention merge was left without its consumer");
         elide_syncs();
         plan_prefetch();
         // dynamic shared memory: the largest need of any stage

@@ -206,9 +206,12 @@ struct GemvArgs {
     int32_t push_ord, push_per_iter;
     uint64_t push_stage_bytes;
     int32_t light;           // [N, K]: the walker with half the loads in flight and a third of the registers (small matrices)
-    int32_t pad4;
+    // GP_ATTN_MERGE: x is the output of a decode attention whose chunks have not been merged yet: x[b, h * 128 + d] is
+    // put together from the chunk records (pro_a = the attention's scratch: per (b, kv head, chunk) G x (128 outputs +
+    // maximum + sum), fp32) while the activations are staged; M = sequences
+    int32_t mg_chunks, mg_group, mg_kv_heads, pad5;
 };
-enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2 };
+enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2, GP_ATTN_MERGE = 3 };
 constexpr int kGemvMaxM = 2;
 
 // softmax(scale * q . K^T) . V for one query row per head (decode); phase 0: per cache chunk, phase 1: merge the chunks
@@ -223,6 +226,8 @@ struct DecodeAttnArgs {
     int32_t dtype, phase;
     float scale;
     int32_t pad;
+    const void *rope;          // optional: 128 (cos, sin) values of the token's position; q is rotated while it is loaded
+    int64_t pad6;
 };
 
 // Self-attention over Tq query rows per head (head dimension 128). The tensors are addressed through tensor maps

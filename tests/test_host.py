@@ -185,6 +185,10 @@ def test_decode_layer_folds_small_operators_into_the_weight_streaming_matmuls():
     text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
     assert text.count("Matmul(gemv)") == 5 and text.count("<-rmsnorm") == 3 and text.count("+residual") == 2
     assert "<-mul" in text and "DecodeAttention" in text
+    # the query's rotary embedding is applied by the attention stage while it loads q, and the attention's chunks are
+    # merged by the output projection while it stages its activations: six compute stages and four barriers per layer
+    assert "<-rope" in text and "<-attention merge" in text and "Rope rope" not in text and "merge of the chunks" not in text
+    assert text.count("sync group") == 4 and len(text.splitlines()) == 12, text
     assert "RMSNorm" not in text and " Add " not in text and " Mul " not in text
     ark.init()
     x, rope = ark.tensor([256, 4096], ark.fp16), ark.tensor([1, 256, 1, 128], ark.fp16)
