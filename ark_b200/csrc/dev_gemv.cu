@@ -39,11 +39,61 @@ __device__ __forceinline__ float cta_sum(float v, float *scratch) {
     return r;
 }
 
+// Where a folded one-shot all_reduce wants the result: slot [rank] of every rank's staging buffer (dense [M, N]).
+struct PushTo {
+    char *slot[kMaxPeers];  // this rank's slot on every rank, null when nothing is pushed
+    int nranks;
+    // The activations are the sum of a one-shot all_reduce that has not been added up yet (src_ord of the stage):
+    // slot q of this rank's staging area holds rank q's dense [M, K] partial. Null otherwise.
+    const char *src;
+    uint64_t src_slot_bytes;
+    int src_ranks;
+};
+__device__ __forceinline__ PushTo push_targets(const GemvArgs &a, const LaunchParams &P, unsigned long long iter_no) {
+    PushTo t;
+    t.nranks = 0;
+    t.src = nullptr; t.src_slot_bytes = 0; t.src_ranks = 0;
+    if (a.src_ord > 0) {
+        const uint64_t par = (iter_no * (unsigned long long)a.push_per_iter + (unsigned long long)(a.src_ord - 1)) & 1;
+        t.src = P.comm[P.rank] + kCommDataOff + par * a.push_stage_bytes;
+        t.src_slot_bytes = a.push_stage_bytes / kMaxPeers;
+        t.src_ranks = P.nranks;
+    }
+    if (a.push_ord > 0) {
+        const uint64_t par = (iter_no * (unsigned long long)a.push_per_iter + (unsigned long long)(a.push_ord - 1)) & 1;
+        const uint64_t base = kCommDataOff + par * a.push_stage_bytes + (uint64_t)P.rank * (a.push_stage_bytes / kMaxPeers);
+        t.nranks = P.nranks;
+        for (int q = 0; q < kMaxPeers; ++q) t.slot[q] = q < P.nranks ? P.comm[q] + base : nullptr;
+    }
+    return t;
+}
+
+// Eight activations as the producer left them: read from x, or — when the one-shot all_reduce that produces x was
+// folded into this stage — added up over the ranks' slots in rank order and rounded where the all_reduce would
+// have stored the sum.
+template <typename T>
+__device__ __forceinline__ void load_raw8(const GemvArgs &a, const PushTo &c, int m, int k, float (&f)[8]) {
+    if (c.src) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.0f;
+        for (int q = 0; q < c.src_ranks; ++q) {
+            float g[8];
+            unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(c.src + q * c.src_slot_bytes) + (int64_t)m * a.K + k), g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] += g[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i]));
+        return;
+    }
+    unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.x) + (int64_t)m * a.ldx + k), f);
+}
+
 // The activations as this stage consumes them: the raw x, or the operator folded in before it
 // (GP_MUL: x * other; GP_RMSNORM: (x [+ residual]) * rstd * weight), rounded to the storage type like
 // the separate operator would have stored them. `rstd` is per activation row (GP_RMSNORM only).
 template <typename T>
-__device__ __forceinline__ void load_x8(const GemvArgs &a, int m, int k, float rstd, float (&f)[8]) {
+__device__ __forceinline__ void load_x8(const GemvArgs &a, const PushTo &c, int m, int k, float rstd, float (&f)[8]) {
     if (a.pro == GP_ATTN_MERGE) {
         // the attention's chunks of head k / 128 of sequence m, merged with the usual max / sum rescaling and rounded
         // like the merge stage would have stored them
@@ -70,8 +120,7 @@ __device__ __forceinline__ void load_x8(const GemvArgs &a, int m, int k, float r
         for (int i = 0; i < 8; ++i) f[i] = to_f32(from_f32<T>(f[i] / l));
         return;
     }
-    const T *x = reinterpret_cast<const T *>(a.x);
-    unpack8<T>(*reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k), f);
+    load_raw8<T>(a, c, m, k, f);
     if (a.pro == GP_MUL) {
         float g[8];
         unpack8<T>(*reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(a.pro_a) + (int64_t)m * a.ldx + k), g);
@@ -99,15 +148,14 @@ __device__ __forceinline__ void load_x8(const GemvArgs &a, int m, int k, float r
 // 1 / rms of every activation row over the WHOLE of K (GP_RMSNORM), into rstd[0..M). With a residual, CTA 0
 // also stores x + residual (the value the norm is taken of) for the operators that follow.
 template <typename T>
-__device__ __forceinline__ void row_rstd(const GemvArgs &a, int p, float *rstd, float *scratch) {
-    const T *x = reinterpret_cast<const T *>(a.x);
+__device__ __forceinline__ void row_rstd(const GemvArgs &a, const PushTo &c, int p, float *rstd, float *scratch) {
     const T *r = reinterpret_cast<const T *>(a.pro_b);
     T *ro = reinterpret_cast<T *>(a.pro_out);
     for (int m = 0; m < a.M; ++m) {
         float ss = 0.0f;
         for (int k = threadIdx.x * 8; k < a.K; k += blockDim.x * 8) {
             float f[8];
-            unpack8<T>(*reinterpret_cast<const uint4 *>(x + (int64_t)m * a.ldx + k), f);
+            load_raw8<T>(a, c, m, k, f);
             if (r) {
                 float g[8];
                 unpack8<T>(*reinterpret_cast<const uint4 *>(r + (int64_t)m * a.ldx + k), g);
@@ -118,6 +166,11 @@ __device__ __forceinline__ void row_rstd(const GemvArgs &a, int p, float *rstd, 
                     f[i] = to_f32(o.e[i]);
                 }
                 if (ro && p == 0) *reinterpret_cast<uint4 *>(ro + (int64_t)m * a.ldx + k) = o.q;
+            } else if (ro && p == 0) {  // a folded all_reduce without a residual: its sum is kept
+                union { uint4 q; T e[8]; } o;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o.e[i] = from_f32<T>(f[i]);
+                *reinterpret_cast<uint4 *>(ro + (int64_t)m * a.ldx + k) = o.q;
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
@@ -132,31 +185,14 @@ __device__ __forceinline__ void row_rstd(const GemvArgs &a, int p, float *rstd, 
 // kept as two float4 in separate planes, xs[(m * 2 + h) * nv + v], so that lanes reading consecutive vectors
 // touch consecutive 16-byte words (no bank conflicts).
 template <typename T>
-__device__ __forceinline__ void stage_x(const GemvArgs &a, float4 *xs, int nv, int k0, const float *rstd) {
+__device__ __forceinline__ void stage_x(const GemvArgs &a, const PushTo &c, float4 *xs, int nv, int k0, const float *rstd) {
     for (int i = threadIdx.x; i < a.M * nv; i += blockDim.x) {
         const int m = i / nv, v = i % nv;
         float f[8];
-        load_x8<T>(a, m, k0 + v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
+        load_x8<T>(a, c, m, k0 + v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
         xs[((size_t)m * 2 + 0) * nv + v] = make_float4(f[0], f[1], f[2], f[3]);
         xs[((size_t)m * 2 + 1) * nv + v] = make_float4(f[4], f[5], f[6], f[7]);
     }
-}
-
-// Where a folded one-shot all_reduce wants the result: slot [rank] of every rank's staging buffer (dense [M, N]).
-struct PushTo {
-    char *slot[kMaxPeers];  // this rank's slot on every rank, null when nothing is pushed
-    int nranks;
-};
-__device__ __forceinline__ PushTo push_targets(const GemvArgs &a, const LaunchParams &P, unsigned long long iter_no) {
-    PushTo t;
-    t.nranks = 0;
-    if (a.push_ord > 0) {
-        const uint64_t par = (iter_no * (unsigned long long)a.push_per_iter + (unsigned long long)(a.push_ord - 1)) & 1;
-        const uint64_t base = kCommDataOff + par * a.push_stage_bytes + (uint64_t)P.rank * (a.push_stage_bytes / kMaxPeers);
-        t.nranks = P.nranks;
-        for (int q = 0; q < kMaxPeers; ++q) t.slot[q] = q < P.nranks ? P.comm[q] + base : nullptr;
-    }
-    return t;
 }
 
 template <typename T>
@@ -258,8 +294,8 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
         issue(qa, ld);
         advance(ld);
     }
-    if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
-    stage_x<T>(a, xs, nv, k0, rstd);
+    if (a.pro == GP_RMSNORM) row_rstd<T>(a, push, p, rstd, rstd + 8);
+    stage_x<T>(a, push, xs, nv, k0, rstd);
     __syncthreads();
     while (valid(cp)) {
         if (valid(ld)) {
@@ -291,12 +327,12 @@ __device__ __noinline__ void gemv_kn(const GemvArgs &a, int p, int P, T *xs, con
     const int K = a.K;
     {
         float *rstd = reinterpret_cast<float *>(xs + (size_t)rows_m * K);  // [M], then one float per warp of scratch (K is a multiple of 8)
-        if (a.pro == GP_RMSNORM) row_rstd<T>(a, p, rstd, rstd + 8);
+        if (a.pro == GP_RMSNORM) row_rstd<T>(a, push, p, rstd, rstd + 8);
         const int nvk = K / 8;
         for (int i = threadIdx.x; i < rows_m * nvk; i += blockDim.x) {
             const int m = i / nvk, v = i % nvk;
             float f[8];
-            load_x8<T>(a, m, v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
+            load_x8<T>(a, push, m, v * 8, a.pro == GP_RMSNORM ? rstd[m] : 1.0f, f);
             union { uint4 q; T e[8]; } o;
 #pragma unroll
             for (int e = 0; e < 8; ++e) o.e[e] = from_f32<T>(f[e]);

@@ -538,6 +538,32 @@ struct Lowerer {
         int64_t B = 0, Hq = 0;
     } pending_merge;
     size_t cur_pg = 0, pending_merge_pg = 0;
+    // A one-shot all_reduce (with the Add that consumes it) whose sum stage was left out: the weight-streaming matmuls of
+    // the processor groups that follow (RMSNorm folded in) add the slots up themselves; the first of them also stores
+    // the sum (+ residual) for later readers.
+    struct PendingSum {
+        int64_t buffer_id = -1;     // buffer of the tensor the sum stage would have written
+        int ord = 0;                // ordinal of the all_reduce + 1
+        bool has_residual = false, stored = false;
+        TensorDesc residual, out;   // the Add's other operand; the tensor to store
+        int64_t rows = 0, cols = 0;
+    } pending_sum;
+    // processor group `k` is [RMSNorm(x), Matmul] that lower_task_group folds into one weight-streaming stage, x on `buffer`
+    bool sum_consumer(size_t k, int64_t buffer, int64_t rows, int64_t cols) const {
+        if (k >= plan.processor_groups.size()) return false;
+        const ProcessorGroup &g = plan.processor_groups[k];
+        if (g.resource_groups.size() != 1 || g.resource_groups[0].task_groups.size() != 1) return false;
+        const TaskGroup &tg = g.resource_groups[0].task_groups[0];
+        const TaskInfo &ti = plan.task(tg.task_id);
+        if (ti.ops.size() < 2) return false;
+        const OpDesc &n = ti.ops[0], &m = ti.ops[1];
+        if (n.type != "RMSNorm" || m.type != "Matmul" || n.reads.empty() || n.results.empty() || m.reads.empty()) return false;
+        if (n.has_arg("Residual") && n.arg_bool("Residual")) return false;
+        const TensorDesc &x = n.reads[0], &mx = m.reads[0];
+        if (x.buffer_id != buffer || !x.dense() || x.shape4()[2] != rows || x.shape4()[3] != cols || x.shape4()[0] * x.shape4()[1] != 1) return false;
+        if (m.reads[0].id != n.results[0].id || other_readers(n.results[0].buffer_id, &m) != 0) return false;
+        return matmul_is_gemv(m, tg) && x.shape4() == mx.shape4() && x.dtype == mx.dtype;
+    }
     static bool fold_decode_chain() { const char *e = getenv("ARKB_FOLD_DECODE"); return e ? atoi(e) != 0 : true; }
     // Rope of the new token's query whose only reader is the DecodeAttention that opens the next processor group: the
     // attention rotates q while it loads it (no stage, no barrier for the rotation)
@@ -713,6 +739,10 @@ struct Lowerer {
                     g.pro_a = pending_merge.ws;
                     g.mg_chunks = pending_merge.chunks; g.mg_group = pending_merge.group; g.mg_kv_heads = pending_merge.kv_heads;
                 }
+                const bool sum_here = gf && gf->pro == GP_RMSNORM && gf->x && pending_sum.buffer_id >= 0 &&
+                                      gf->x->buffer_id == pending_sum.buffer_id && !merge_here;
+                if (sum_here && (gf->pro_b || M != pending_sum.rows || K != pending_sum.cols))
+                    throw Error(E_INTERNAL, "one-shot all_reduce sum folded into a matmul that cannot take it");
                 if (gf) {
                     // the prologue's input stands in for the first operand; every folded operand shares its row pitch
                     auto same_rows = [&](const TensorDesc *t) { return !t || (t->strides4()[3] == gf->x->strides4()[3] && aligned16(tensor_ptr(*t))); };
@@ -727,6 +757,13 @@ struct Lowerer {
                     g.pro_b = gf->pro_b ? tensor_ptr(*gf->pro_b) : nullptr;
                     g.pro_out = gf->pro_out ? tensor_ptr(*gf->pro_out) : nullptr;
                     g.pro_eps = gf->eps;
+                    if (sum_here) {
+                        g.src_ord = pending_sum.ord;
+                        if (pending_sum.has_residual) g.pro_b = tensor_ptr(pending_sum.residual);
+                        if (!pending_sum.stored) g.pro_out = tensor_ptr(pending_sum.out);
+                        if ((g.pro_b && !aligned16(g.pro_b)) || (g.pro_out && !aligned16(g.pro_out)))
+                            throw Error(E_UNSUPPORTED, "AllReduce folded into a weight-streaming matmul: operands must be 16-byte aligned");
+                    }
                     if (gf->residual) {
                         if (gf->residual->strides4()[3] != ldc) throw Error(E_UNSUPPORTED, "residual of a weight-streaming matmul must have the result's row pitch");
                         g.residual = tensor_ptr(*gf->residual);
@@ -817,9 +854,14 @@ struct Lowerer {
                 } else {
                     rd(A);
                 }
+                if (sum_here) {
+                    if (pending_sum.has_residual) rd(pending_sum.residual);
+                    if (!pending_sum.stored) wr(pending_sum.out);
+                    pending_sum.stored = true;
+                }
                 rd_streamed(B);
                 if (gf) {
-                    for (const TensorDesc *t : {gf->x, gf->pro_a, gf->pro_b, gf->residual})
+                    for (const TensorDesc *t : {sum_here ? nullptr : gf->x, gf->pro_a, gf->pro_b, gf->residual})  // a folded sum is read from the staging slots, not from x
                         if (t) rd(*t);
                     if (gf->pro_out) wr(*gf->pro_out);
                 }
@@ -829,6 +871,7 @@ struct Lowerer {
                 push(s, std::string("Matmul(gemv) ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                             std::to_string(K) + (tb ? " W:[N,K]" : " W:[K,N]") + " k-ranges=" + std::to_string(gv.splits) + " x " +
                             std::to_string(gv.kper) + (tb ? " ctas/range=" + std::to_string(gv.ctas_per_split) + " rows/warp-step=" + std::to_string(gv.rows_together) + (gv.light ? " light" : "") : "") +
+                            (gv.src_ord ? (gv.pro_b ? " <-all_reduce sum +residual" : " <-all_reduce sum") : "") +
                             (gv.pro == GP_RMSNORM ? " <-rmsnorm" : gv.pro == GP_MUL ? " <-mul" : gv.pro == GP_ATTN_MERGE ? " <-attention merge" : "") + (gv.residual ? " +residual" : "") +
                             (gv.push_ord ? " ->all_reduce slots" : "") +
                             (gv.act ? " act=" + std::to_string(gv.act) : ""));
@@ -1573,6 +1616,30 @@ struct Lowerer {
             a.phase = 0;
             if (!pushed) push(s, "AllReduce " + op.name + " one-shot push bytes=" + std::to_string(bytes));
             emit_grid_peer_barrier(proc, "all_reduce data pushed");
+            {
+                // the consumers add the slots up themselves when they are the weight-streaming matmuls that open the next
+                // processor group(s) and the tensor is one or two dense rows
+                const TensorDesc &res = add ? add->results.at(0) : t;
+                auto rs = res.shape4();
+                if (fold_decode_chain() && res.dense() && t.dense() && rs[0] * rs[1] == 1 && rs[2] <= kGemvMaxM && rs[3] % 8 == 0 &&
+                    res.nelems() == t.nelems() && sum_consumer(cur_pg + 1, res.buffer_id, rs[2], rs[3])) {
+                    pending_sum = PendingSum();
+                    pending_sum.buffer_id = res.buffer_id;
+                    pending_sum.ord = a.ord + 1;
+                    pending_sum.out = res;
+                    pending_sum.rows = rs[2]; pending_sum.cols = rs[3];
+                    if (add) {
+                        pending_sum.has_residual = true;
+                        pending_sum.residual = add->reads[0].id == t.id ? add->reads[1] : add->reads[0];
+                    }
+                    if (!add || (pending_sum.residual.dense() && pending_sum.residual.nelems() == res.nelems() &&
+                                 pending_sum.residual.dtype == res.dtype)) {
+                        prog.notes.back() += " (sum left to the consumers)";
+                        return;
+                    }
+                    pending_sum = PendingSum();
+                }
+            }
             Stage s2 = s;
             s2.ar.phase = 1;
             if (add) {
@@ -2156,6 +2223,10 @@ struct Lowerer {
         for (size_t pgi = 0; pgi < plan.processor_groups.size(); ++pgi) {
             if (skip_pgs) { --skip_pgs; continue; }
             cur_pg = pgi;
+            if (pending_sum.buffer_id >= 0 && !sum_consumer(pgi, pending_sum.buffer_id, pending_sum.rows, pending_sum.cols)) {
+                if (!pending_sum.stored) throw Error(E_INTERNAL, "one-shot all_reduce sum was left without a consumer");
+                pending_sum = PendingSum();
+            }
             const ProcessorGroup *pgp = &plan.processor_groups[pgi];
             if (const OpDesc *o = single_op(*pgp)) {
                 if (rope_feeds_next_attention(*o)) {
@@ -2232,6 +2303,7 @@ struct Lowerer {
                 throw Error(E_INTERNAL, "decode attention merge was left without its consumer");
         }
         if (pending_merge.buffer_id >= 0) throw Error(E_INTERNAL, "decode attention merge was left without its consumer");
+        if (pending_sum.buffer_id >= 0 && !pending_sum.stored) throw Error(E_INTERNAL, "one-shot all_reduce sum was left without a consumer");
         elide_syncs();
         plan_prefetch();
         // dynamic shared memory: the largest need of any stage
@@ -2269,7 +2341,10 @@ struct Lowerer {
         prog.oneshots_per_iter = oneshot_ord;
         for (auto &s : prog.stages) {
             if (s.kind == SK_ALLREDUCE && s.ar.algo == 0) s.ar.per_iter = oneshot_ord;
-            if (s.kind == SK_GEMV && s.gv.push_ord > 0) s.gv.push_per_iter = oneshot_ord;
+            if (s.kind == SK_GEMV && (s.gv.push_ord > 0 || s.gv.src_ord > 0)) {
+                s.gv.push_per_iter = oneshot_ord;
+                s.gv.push_stage_bytes = lay.comm_stage_bytes;
+            }
         }
     }
 };

@@ -199,7 +199,8 @@ struct GemvArgs {
     const void *pro_b;       // GP_RMSNORM: optional residual [M, K] added first (row pitch ldx)
     void *pro_out;           // GP_RMSNORM with residual: x + residual is also stored here (by CTA 0), row pitch ldx
     float pro_eps;
-    int32_t pad;
+    int32_t src_ord;         // > 0: x is the sum of the one-shot all_reduce number src_ord - 1, whose partials still lie in this
+                             // rank's staging slots (dense [M, K] per rank): the stage adds them up itself
     const void *residual;    // epilogue: y := act(x . W) + residual [M, N] (row pitch ldo); with k-ranges the sum stage adds it
     // The one-shot all_reduce that follows in the same task: the result is also stored into slot [rank] of every rank's
     // staging buffer (the all_reduce's own push stage and its barrier are then left out). push_ord = its ordinal + 1, 0: none.

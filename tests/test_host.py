@@ -236,7 +236,9 @@ def test_causal_prefill_layer_lowers_to_one_attention_stage():
 
 def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
     """With several ranks the small all_reduces of a decode layer take their input straight from the weight-streaming
-    matmul (no push stage) and add the residual in their sum stage."""
+    matmul (no push stage); the sum (+ residual) of the first one is left to the two matmuls that consume it (they add
+    the staging slots up while they stage their activations: no sum stage, no barrier between the two); the last one of
+    the plan, which nothing of the plan consumes, keeps its sum stage."""
     from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
     cfg = LlamaConfig(dim=4096, n_heads=32, n_kv_heads=32, ffn_dim=11008)
     ark.init()
@@ -249,8 +251,12 @@ def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
     text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
     ark.set_rank(0)
     ark.set_world_size(1)
-    assert text.count("->all_reduce slots") == 2 and text.count("one-shot reduce +residual") == 2
+    assert text.count("->all_reduce slots") == 2 and text.count("one-shot reduce +residual") == 1
+    assert text.count("<-all_reduce sum +residual <-rmsnorm") == 2 and text.count("sum left to the consumers") == 1
     assert "one-shot push" not in text and " Add " not in text and text.count("peer barrier") == 2
+    lines = text.splitlines()
+    w1 = next(i for i, l in enumerate(lines) if "<-all_reduce sum" in l)
+    assert "<-all_reduce sum" in lines[w1 + 1] and len(lines) == 14, text
 
 
 def test_unfolded_one_shot_push_waits_for_the_split_k_sum():
