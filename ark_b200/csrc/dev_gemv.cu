@@ -199,6 +199,8 @@ template <typename T>
 __device__ __forceinline__ void emit(const GemvArgs &a, const PushTo &push, int split, int m, int n, float v) {
     if (a.splits > 1) {
         a.ws[((int64_t)split * a.M + m) * a.N + n] = v;
+    } else if (n >= a.N) {  // a row of the second matrix
+        reinterpret_cast<T *>(a.out_b)[(int64_t)m * a.ldo + (n - a.N)] = from_f32<T>(apply_act_fast(a.act_b, v));
     } else {
         v = apply_act_fast(a.act, v);
         if (a.residual) v = to_f32(from_f32<T>(v)) + to_f32(reinterpret_cast<const T *>(a.residual)[(int64_t)m * a.ldo + n]);
@@ -225,7 +227,10 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
     float *rstd = reinterpret_cast<float *>(xs + (size_t)a.M * 2 * nv);  // [M], then one float per warp of scratch
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nwarps = blockDim.x >> 5;
-    const int row_lo = (int)((int64_t)q * a.N / cps), row_hi = (int)((int64_t)(q + 1) * a.N / cps);
+    const int n_rows = a.w_b ? 2 * a.N : a.N;  // with a second matrix the row space is both matrices' rows
+    const int row_lo = (int)((int64_t)q * n_rows / cps), row_hi = (int)((int64_t)(q + 1) * n_rows / cps);
+    const T *w_b = reinterpret_cast<const T *>(a.w_b) + k0;
+    const int n_first = a.N;
     const int steps = (nv + 32 * VC - 1) / (32 * VC);  // per row group
     const T *w = reinterpret_cast<const T *>(a.w) + k0;
     const int64_t ldw = a.ldw;
@@ -247,7 +252,9 @@ __device__ __noinline__ void gemv_nk(const GemvArgs &a, int p, int P, float4 *xs
 #pragma unroll
             for (int v = 0; v < VC; ++v) {
                 const int vi = lane + 32 * (c.j * VC + v);
-                if (c.r0 + r < row_hi && vi < nv) buf[r][v] = ldg16_stream(w + (int64_t)(c.r0 + r) * ldw + vi * 8);
+                const int row = c.r0 + r;
+                if (row < row_hi && vi < nv)
+                    buf[r][v] = ldg16_stream((row < n_first ? w + (int64_t)row * ldw : w_b + (int64_t)(row - n_first) * ldw) + vi * 8);
                 else buf[r][v] = make_uint4(0, 0, 0, 0);
             }
     };

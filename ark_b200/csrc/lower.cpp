@@ -2131,6 +2131,57 @@ struct Lowerer {
         prog = out;
     }
 
+    // Two weight-streaming matmuls that follow each other without a barrier, over the same activations with the same
+    // prologue and of the same shape (W1 and W3 of a SwiGLU block), become one stage: x is normalised and staged once,
+    // and the CTAs' row shares are cut from both matrices together, so that the pipeline ramps up and drains once.
+    void pair_weight_streams() {
+        static const bool on = []() { const char *e = getenv("ARKB_PAIR_GEMV"); return e ? atoi(e) != 0 : true; }();
+        if (!on) return;
+        for (size_t i = 0; i + 1 < prog.stages.size(); ++i) {
+            Stage &s0 = prog.stages[i];
+            const Stage &s1 = prog.stages[i + 1];
+            if (s0.kind != SK_GEMV || s1.kind != SK_GEMV) continue;
+            GemvArgs &a = s0.gv;
+            const GemvArgs &b = s1.gv;
+            if (s0.proc_b != s1.proc_b || s0.proc_e != s1.proc_e || s0.proc_s != s1.proc_s) continue;
+            if (!a.w_is_nk || !b.w_is_nk || a.w_b || b.w_b || a.splits != 1 || b.splits != 1) continue;
+            if (a.x != b.x || a.pro != b.pro || a.pro_a != b.pro_a || a.pro_b != b.pro_b || a.src_ord != b.src_ord || a.pro_eps != b.pro_eps ||
+                a.pro == GP_ATTN_MERGE)
+                continue;
+            if (a.M != b.M || a.N != b.N || a.K != b.K || a.ldx != b.ldx || a.ldw != b.ldw || a.ldo != b.ldo || a.dtype != b.dtype ||
+                a.rows_together != b.rows_together || a.light != b.light || a.kper != b.kper || a.ctas_per_split != b.ctas_per_split)
+                continue;
+            if (a.residual || b.residual || a.push_ord || b.push_ord || b.pro_out) continue;
+            a.w_b = b.w;
+            a.out_b = b.out;
+            a.act_b = b.act;
+            {   // rows a warp walks together, for twice the rows (the time model of lower_matmul, one k-range)
+                const int64_t warps = kThreads / 32, loads = (a.M == 1 ? 8 : 4) / (a.light ? 2 : 1);
+                const int64_t rows_cta = (2 * (int64_t)a.N + a.ctas_per_split - 1) / a.ctas_per_split;
+                double best = 1e30;
+                for (int64_t RW = loads; RW >= 1; RW /= 2) {
+                    const int64_t VC = loads / RW;
+                    const int64_t rounds = ((rows_cta + RW - 1) / RW + warps - 1) / warps;
+                    const double steps = (double)((a.kper + 256 * VC - 1) / (256 * VC));
+                    const double t = (double)rounds * (steps + 1.5) * (1.0 + 0.03 * (double)(VC - 1));
+                    if (t < best - 1e-9) { best = t; a.rows_together = (int32_t)RW; }
+                }
+            }
+            // the stage touches what both touched
+            StageAccess &x = prog.access[i];
+            const StageAccess &y = prog.access[i + 1];
+            x.reads.insert(x.reads.end(), y.reads.begin(), y.reads.end());
+            x.writes.insert(x.writes.end(), y.writes.begin(), y.writes.end());
+            x.streamed.insert(x.streamed.end(), y.streamed.begin(), y.streamed.end());
+            x.opaque = x.opaque || y.opaque;
+            prog.notes[i] += "  + " + prog.notes[i + 1].substr(prog.notes[i + 1].find("Matmul(gemv) ") + 13, prog.notes[i + 1].find(" M=") - prog.notes[i + 1].find("Matmul(gemv) ") - 13) +
+                             " (second matrix, act=" + std::to_string(b.act) + ", rows/warp-step=" + std::to_string(a.rows_together) + ")";
+            prog.stages.erase(prog.stages.begin() + i + 1);
+            prog.access.erase(prog.access.begin() + i + 1);
+            prog.notes.erase(prog.notes.begin() + i + 1);
+        }
+    }
+
     // Barriers fetch ahead: operands that no op of the plan writes (weights, K/V caches) are asked into L2 by the
     // barrier stages that precede their readers, as early as a budget of bytes in flight allows, so that a chain of
     // small dependent stages (decode) waits on L2 hits instead of HBM round trips, and HBM streams while CTAs sit
@@ -2305,6 +2356,7 @@ struct Lowerer {
         if (pending_merge.buffer_id >= 0) throw Error(E_INTERNAL, "decode attention merge was left without its consumer");
         if (pending_sum.buffer_id >= 0 && !pending_sum.stored) throw Error(E_INTERNAL, "one-shot all_reduce sum was left without a consumer");
         elide_syncs();
+        pair_weight_streams();
         plan_prefetch();
         // dynamic shared memory: the largest need of any stage
         size_t smem = 16 * 1024;

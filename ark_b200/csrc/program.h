@@ -210,7 +210,13 @@ struct GemvArgs {
     // GP_ATTN_MERGE: x is the output of a decode attention whose chunks have not been merged yet: x[b, h * 128 + d] is
     // put together from the chunk records (pro_a = the attention's scratch: per (b, kv head, chunk) G x (128 outputs +
     // maximum + sum), fp32) while the activations are staged; M = sequences
-    int32_t mg_chunks, mg_group, mg_kv_heads, pad5;
+    int32_t mg_chunks, mg_group, mg_kv_heads;
+    // A second matrix of the same shape over the same activations ([N, K] layout, one k-range): rows N .. 2N-1 of the
+    // stage's row space are rows of w_b, their results go to out_b with activation act_b (W1 and W3 of a SwiGLU block:
+    // one stage, one staging of x, the CTAs' shares are halves of both)
+    int32_t act_b;
+    const void *w_b;
+    void *out_b;
 };
 enum GemvPrologue : int32_t { GP_NONE = 0, GP_RMSNORM = 1, GP_MUL = 2, GP_ATTN_MERGE = 3 };
 constexpr int kGemvMaxM = 2;

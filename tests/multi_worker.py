@@ -283,10 +283,10 @@ def main():
     ty1 = decoder_layer(tx, tw, cfg, 1, 1, rank, world, rope=tr, k_cache=tk, v_cache=tv)
     ty = decoder_layer(ty1, tw2, cfg, 1, 1, rank, world, rope=tr, k_cache=tk, v_cache=tv)
     text = ark.plan_dump(str(ark.Planner(local).plan()))
-    # the sums (+ residual) of the first three all_reduces are added up by the matmuls that consume them (two each for
-    # the ones in front of W1 / W3, one for the one in front of the next layer's Wq); the last one keeps its sum stage
+    # the sums (+ residual) of the first three all_reduces are added up by the stages that consume them (W1 and W3 as one
+    # stage over both matrices, the next layer's Wq); the last one keeps its sum stage
     assert text.count("->all_reduce slots") == 4 and text.count("one-shot reduce +residual") == 1 and \
-        text.count("<-all_reduce sum +residual") == 5, text
+        text.count("<-all_reduce sum +residual") == 3 and text.count("(second matrix") == 2, text
     feeds = {tx: xd, tr: rope1, tk: kcs[rank], tv: vcs[rank]}
     feeds.update({tw[k]: ws[rank][k] for k in tw if k not in ("wk", "wv")})
     feeds.update({tw2[k]: ws2[rank][k] for k in tw2 if k not in ("wk", "wv")})
