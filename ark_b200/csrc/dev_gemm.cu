@@ -147,7 +147,7 @@ __device__ __forceinline__ void gemm_store_row(const GemmLocal &g, T *crow, cons
 // blocks per warp alternate so that the conversion of block i+1 overlaps the
 // store of block i. Rows and columns outside the tensor are clipped by TMA.
 template <typename T>
-__device__ void gemm_epilogue_tile_tma(const GemmLocal &g, const CUtensorMap *tmC, const TileCoord &tc, uint32_t tmem_acc,
+__device__ __noinline__ void gemm_epilogue_tile_tma(const GemmLocal &g, const CUtensorMap *tmC, const TileCoord &tc, uint32_t tmem_acc,
                                        int warp, int lane, char *stage, unsigned int &blk, int row_shift = 0) {
     const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
     const int ncols_tile = min(g.tile_n, g.N - tc.n0);
@@ -176,7 +176,7 @@ __device__ void gemm_epilogue_tile_tma(const GemmLocal &g, const CUtensorMap *tm
 }
 
 template <typename T>
-__device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint32_t tmem_acc, int warp, int lane) {
+__device__ __noinline__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint32_t tmem_acc, int warp, int lane) {
     const int row = tc.m0 + warp * 32 + lane;
     const bool row_ok = row < g.M;
     const int64_t boff = (int64_t)tc.bn * g.c_stride_n + (int64_t)tc.bc * g.c_stride_c + (int64_t)row * g.ldc;
@@ -201,7 +201,7 @@ __device__ void gemm_epilogue_tile(const GemmLocal &g, const TileCoord &tc, uint
 // the 32 lanes of a warp write 32 consecutive n: coalesced without staging.
 // In this form g.M / g.N hold the swapped problem (M' = columns of C, N' = rows of C).
 template <typename T>
-__device__ void gemm_epilogue_tile_swapped(const GemmLocal &g, const TileCoord &tc, uint32_t tmem_acc, int warp, int lane) {
+__device__ __noinline__ void gemm_epilogue_tile_swapped(const GemmLocal &g, const TileCoord &tc, uint32_t tmem_acc, int warp, int lane) {
     const int n = tc.m0 + warp * 32 + lane;
     const bool n_ok = n < g.M;
     const int64_t boff = (int64_t)tc.bn * g.c_stride_n + (int64_t)tc.bc * g.c_stride_c;
@@ -234,7 +234,7 @@ __device__ void gemm_epilogue_tile_swapped(const GemmLocal &g, const TileCoord &
 
 // Split-K epilogue of the swapped form: the fp32 partial of k-range `split` goes to
 // ws[split][batch][m][n] unrounded; run_splitk_reduce finishes the job.
-__device__ void gemm_epilogue_tile_partial(const GemmLocal &g, const TileCoord &tc, int split, uint32_t tmem_acc, int warp,
+__device__ __noinline__ void gemm_epilogue_tile_partial(const GemmLocal &g, const TileCoord &tc, int split, uint32_t tmem_acc, int warp,
                                            int lane) {
     const int n = tc.m0 + warp * 32 + lane;   // column of C
     const bool n_ok = n < g.M;                // g.M / g.N hold the swapped problem
@@ -535,7 +535,13 @@ template <bool PAIR, bool GROUPED>
 __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                            DeviceState *st, int stage_idx, unsigned long long lim) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    GemmRun R;
+    // the record is the same for every thread: one thread builds it in shared memory (per-thread copies would be
+    // ~250 bytes of local memory each, written and read back through an L1 that the operand ring leaves little of)
+    __shared__ GemmRun Rs;
+    __shared__ int my_tiles_s;
+    __shared__ unsigned int my_slots_s;
+    if (threadIdx.x == 0) {
+    GemmRun &R = Rs;
     GemmLocal &L = R.L;
     L.C = g.C; L.bias = g.bias; L.ldc = g.ldc; L.c_stride_c = g.c_stride_c; L.c_stride_n = g.c_stride_n;
     L.M = g.M; L.N = g.N; L.K = g.K; L.tile_n = g.tile_n; L.act = g.act; L.c_vec = g.c_vec; L.c_tma = g.c_tma;
@@ -572,6 +578,11 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
         my_slots += (unsigned int)((min(R.kblocks, lo + R.kper) - lo + R.G - 1) / R.G);
     }
     R.tmem_base = ctl->tmem_base;
+    my_tiles_s = my_tiles;
+    my_slots_s = my_slots;
+    }
+    __syncthreads();
+    const GemmRun &R = Rs;
 
     if (warp == kProducerWarp || warp == kProducerWarpB) {
         if (lane == 0) gemm_produce<PAIR, GROUPED>(R, warp);
@@ -582,23 +593,44 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int total = my_slots;
+        const unsigned int total = my_slots_s;
         for (int s = 0; s < R.STAGES; ++s)
             if (total > (unsigned int)s) pp->use[s] += (total - s + R.STAGES - 1) / R.STAGES;
-        pp->tile_count = R.t0 + (unsigned int)my_tiles;
+        pp->tile_count = R.t0 + (unsigned int)my_tiles_s;
     }
     // the partner may still read this CTA's shared memory / signal its barriers
     if constexpr (PAIR) cluster_sync_all();
     __syncthreads();
 }
 
+// Warps without a role in the matmul (7..15) do not enter the stage function: its register save area and the
+// GemmRun record are ~0.5 KB of local memory per thread, and with 208 KiB of the SM's memory configured as shared
+// there is little L1 left to hold them (an idle pass through the function measured 5.5 us). They only take part in
+// the function's three CTA-wide barriers (and the cluster barrier of a pair).
+__device__ __forceinline__ bool gemm_warp_has_role() {
+    const int warp = threadIdx.x >> 5;
+    return warp < kEpiWarps || warp == kProducerWarp || warp == kMmaWarp || warp == kProducerWarpB;
+}
 __device__ __noinline__ void run_gemm(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                          DeviceState *st, int stage_idx, unsigned long long spin_limit) {
+    if (!gemm_warp_has_role()) {
+        __syncthreads();
+        __syncthreads();
+        __syncthreads();
+        return;
+    }
     if (g.kgroup > 1) run_gemm_t<false, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
     else run_gemm_t<false, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }
 __device__ __noinline__ void run_gemm_pair(const GemmArgs &g, const GemmArgs *gmaps, int p, int P, char *smem, GemmPipe *pp, CtaCtl *ctl,
                               DeviceState *st, int stage_idx, unsigned long long spin_limit) {
+    if (!gemm_warp_has_role()) {
+        __syncthreads();
+        __syncthreads();
+        cluster_sync_all();
+        __syncthreads();
+        return;
+    }
     if (g.kgroup > 1) run_gemm_t<true, true>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
     else run_gemm_t<true, false>(g, gmaps, p, P, smem, pp, ctl, st, stage_idx, spin_limit);
 }

@@ -211,6 +211,10 @@ def main():
     case("matmul_fp16_nk_2048x4096x4096", mm(2048, 4096, 4096, ark.fp16, 2, nk=True))     # Llama-7B Q/K/V/O projection, 2048 tokens
     case("matmul_fp16_nk_2048x11008x4096", mm(2048, 11008, 4096, ark.fp16, 2, nk=True))   # W1 / W3
     case("matmul_fp16_nk_2048x4096x11008", mm(2048, 4096, 11008, ark.fp16, 2, nk=True))   # W2
+    case("matmul_fp16_nk_2048x512x4096", mm(2048, 512, 4096, ark.fp16, 2, nk=True))       # Llama-7B Q/K/V projection of one rank at TP8
+    case("matmul_fp16_nk_2048x4096x512", mm(2048, 4096, 512, ark.fp16, 2, nk=True))       # ... output projection
+    case("matmul_fp16_nk_2048x1376x4096", mm(2048, 1376, 4096, ark.fp16, 2, nk=True))     # ... W1 / W3
+    case("matmul_fp16_nk_2048x4096x1376", mm(2048, 4096, 1376, ark.fp16, 2, nk=True))     # ... W2
     case("matmul_fp16_kn_4096x4096x8192", mm(4096, 4096, 8192, ark.fp16, 2))              # one rank's W1 of the FFN block at TP8
     case("matmul_fp16_kn_4096x8192x4096", mm(4096, 8192, 4096, ark.fp16, 2))              # one rank's W2
     case("matmul_fp16_128x4096x1024", mm(128, 4096, 1024, ark.fp16, 2))
