@@ -88,8 +88,8 @@ __device__ __forceinline__ AttnUnit attn_unit(const PrefillAttnArgs &a, int u) {
 
 // Units are sorted by length (longest first); CTA p takes one unit per round, walking the rounds back and forth, so
 // that the CTA with the longest unit of one round gets the shortest of the next.
-__device__ __forceinline__ int attn_unit_of(const AttnRun &R, int rnd) {
-    return rnd * R.P + ((rnd & 1) ? R.P - 1 - R.p : R.p);
+__device__ __forceinline__ int attn_unit_of(int p, int P, int rnd) {
+    return rnd * P + ((rnd & 1) ? P - 1 - p : p);
 }
 
 __device__ __forceinline__ bool attn_fail(const AttnRun &R) {
@@ -165,20 +165,26 @@ __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi, flo
 __device__ __noinline__ bool attn_produce(const AttnRun &R, bool is_v) {
     const PrefillAttnArgs &a = *R.a;
     AttnBars *B = R.bars;
+    // the record's fields in registers: the barrier and MMA instructions below are asm statements that clobber memory,
+    // so fields read through `R` would be re-read from the caller's stack frame after every one of them
+    const unsigned long long lim = R.lim;
+    char *const smem = R.smem;
+    const int cta = R.p, cta_count = R.P;
+    const int n_units = a.n_units;
     const CUtensorMap *tmQ = &R.amaps->tmQ, *tmK = &R.amaps->tmK, *tmV = &R.amaps->tmV;
     unsigned int uc = 0, kc = 0;  // units and key tiles this CTA has staged
     const int slots = is_v ? kAtVSlots : kAtKSlots;
     int s = 0;
     uint32_t wrap = 0;  // completed laps of the ring (phase of slot s)
-    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
-        const int u = attn_unit_of(R, rnd);
-        if (u >= a.n_units) continue;
+    for (int rnd = 0; rnd * cta_count < n_units; ++rnd) {
+        const int u = attn_unit_of(cta, cta_count, rnd);
+        if (u >= n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         if (t.n_tiles == 0) continue;
         if (!is_v) {
-            if (!mbar_wait(&B->q_empty, (uc & 1) ^ 1, R.lim)) return attn_fail(R);
+            if (!mbar_wait(&B->q_empty, (uc & 1) ^ 1, lim)) return attn_fail(R);
             mbar_expect_tx(&B->q_full, kAtTileBytes);
-            char *sQ = R.smem + kAtQOff;
+            char *sQ = smem + kAtQOff;
             tma_load_4d(sQ, tmQ, &B->q_full, 0, t.qt * kAtTile, t.h, t.b);
             tma_load_4d(sQ + kGemmABytes, tmQ, &B->q_full, 64, t.qt * kAtTile, t.h, t.b);
         }
@@ -186,16 +192,16 @@ __device__ __noinline__ bool attn_produce(const AttnRun &R, bool is_v) {
         for (int j = 0; j < t.n_tiles; ++j, ++kc) {
             const int key0 = j * kAtTile;
             if (!is_v) {
-                if (!mbar_wait(&B->k_empty[s], (wrap & 1) ^ 1, R.lim)) return attn_fail(R);
+                if (!mbar_wait(&B->k_empty[s], (wrap & 1) ^ 1, lim)) return attn_fail(R);
                 mbar_expect_tx(&B->k_full[s], kAtTileBytes);
-                char *sK = R.smem + kAtKOff + s * kAtTileBytes;
+                char *sK = smem + kAtKOff + s * kAtTileBytes;
                 // K as the K-major B operand of S = Q K^T: two blocks of 64 head-dimension elements x 128 keys
                 tma_load_4d(sK, tmK, &B->k_full[s], 0, key0, t.hkv, t.b);
                 tma_load_4d(sK + kGemmABytes, tmK, &B->k_full[s], 64, key0, t.hkv, t.b);
             } else {
-                if (!mbar_wait(&B->v_empty[s], (wrap & 1) ^ 1, R.lim)) return attn_fail(R);
+                if (!mbar_wait(&B->v_empty[s], (wrap & 1) ^ 1, lim)) return attn_fail(R);
                 mbar_expect_tx(&B->v_full[s], kAtTileBytes);
-                char *sV = R.smem + kAtVOff + s * kAtTileBytes;
+                char *sV = smem + kAtVOff + s * kAtTileBytes;
                 // V as the MN-major B operand of O = P V: per block of 64 keys two chunks of 64 head-dimension columns
                 for (int kb = 0; kb < 2; ++kb)
                     for (int c = 0; c < 2; ++c)
@@ -208,9 +214,9 @@ __device__ __noinline__ bool attn_produce(const AttnRun &R, bool is_v) {
     // the barriers are given up at the end of the stage
     for (unsigned int i = kc >= (unsigned)slots ? kc - slots : 0; i < kc; ++i) {
         unsigned long long *bar = is_v ? &B->v_empty[i % slots] : &B->k_empty[i % slots];
-        if (!mbar_wait(bar, (i / slots) & 1, R.lim)) return attn_fail(R);
+        if (!mbar_wait(bar, (i / slots) & 1, lim)) return attn_fail(R);
     }
-    if (!is_v && uc > 0 && !mbar_wait(&B->q_empty, (uc - 1) & 1, R.lim)) return attn_fail(R);
+    if (!is_v && uc > 0 && !mbar_wait(&B->q_empty, (uc - 1) & 1, lim)) return attn_fail(R);
     return true;
 }
 
@@ -218,19 +224,25 @@ __device__ __noinline__ bool attn_produce(const AttnRun &R, bool is_v) {
 __device__ __noinline__ bool attn_issue(const AttnRun &R) {
     const PrefillAttnArgs &a = *R.a;
     AttnBars *B = R.bars;
+    // the record's fields in registers: the barrier and MMA instructions below are asm statements that clobber memory,
+    // so fields read through `R` would be re-read from the caller's stack frame after every one of them
+    const unsigned long long lim = R.lim;
+    char *const smem = R.smem;
+    const int cta = R.p, cta_count = R.P;
+    const int n_units = a.n_units;
     const int bf16 = a.dtype == DT_BF16;
     const uint32_t idesc_s = umma_idesc(bf16, 0, 0, kAtTile, kAtTile);   // Q, K both K-major
     const uint32_t idesc_o = umma_idesc(bf16, 0, 1, kAtTile, kAtTile);   // P K-major (tensor memory), V MN-major
-    const uint32_t sQ = smem_u32(R.smem + kAtQOff);
+    const uint32_t sQ = smem_u32(smem + kAtQOff);
     const uint32_t tm = R.tmem_base;
     unsigned int uc = 0, sc = 0, pc = 0;  // units; S tiles issued; P tiles consumed (= P V issued)
     int ks = 0, vs = 0;                   // ring slots of the next K / V tile
     uint32_t kwrap = 0, vwrap = 0;
 
     auto issue_s = [&]() -> bool {
-        if (!mbar_wait(&B->k_full[ks], kwrap & 1, R.lim)) return false;
+        if (!mbar_wait(&B->k_full[ks], kwrap & 1, lim)) return false;
         tc_fence_after();
-        const uint32_t sK = smem_u32(R.smem + kAtKOff + ks * kAtTileBytes);
+        const uint32_t sK = smem_u32(smem + kAtKOff + ks * kAtTileBytes);
         const uint32_t d = tm + kAtS0 + (sc & 1) * kAtTile;
 #pragma unroll
         for (int kb = 0; kb < 2; ++kb) {
@@ -245,22 +257,22 @@ __device__ __noinline__ bool attn_issue(const AttnRun &R) {
         return true;
     };
 
-    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
-        const int u = attn_unit_of(R, rnd);
-        if (u >= a.n_units) continue;
+    for (int rnd = 0; rnd * cta_count < n_units; ++rnd) {
+        const int u = attn_unit_of(cta, cta_count, rnd);
+        if (u >= n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         if (t.n_tiles == 0) continue;
-        if (!mbar_wait(&B->q_full, uc & 1, R.lim)) return attn_fail(R);
+        if (!mbar_wait(&B->q_full, uc & 1, lim)) return attn_fail(R);
         // both S buffers are free: every P V of the previous unit has been issued, and the pipe runs in issue order
         if (!issue_s()) return attn_fail(R);
         if (t.n_tiles > 1 && !issue_s()) return attn_fail(R);
         if (t.n_tiles <= 2) umma_commit(&B->q_empty);  // the unit's last S is issued: Q may be replaced once it is done
         for (int j = 0; j < t.n_tiles; ++j, ++pc) {
-            if (!mbar_wait(&B->p_ready[pc & 1], (pc >> 1) & 1, R.lim)) return attn_fail(R);
-            if (j == 0 && !mbar_wait(&B->o_free, (uc & 1) ^ 1, R.lim)) return attn_fail(R);
-            if (!mbar_wait(&B->v_full[vs], vwrap & 1, R.lim)) return attn_fail(R);
+            if (!mbar_wait(&B->p_ready[pc & 1], (pc >> 1) & 1, lim)) return attn_fail(R);
+            if (j == 0 && !mbar_wait(&B->o_free, (uc & 1) ^ 1, lim)) return attn_fail(R);
+            if (!mbar_wait(&B->v_full[vs], vwrap & 1, lim)) return attn_fail(R);
             tc_fence_after();
-            const uint32_t sV = smem_u32(R.smem + kAtVOff + vs * kAtTileBytes);
+            const uint32_t sV = smem_u32(smem + kAtVOff + vs * kAtTileBytes);
             const uint32_t pa = tm + kAtS0 + (pc & 1) * kAtTile;  // P(j) sits where S(j) was
 #pragma unroll
             for (int kb = 0; kb < 2; ++kb) {
@@ -290,12 +302,18 @@ template <typename T>
 __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) {
     const PrefillAttnArgs &a = *R.a;
     AttnBars *B = R.bars;
+    // the record's fields in registers: the barrier and MMA instructions below are asm statements that clobber memory,
+    // so fields read through `R` would be re-read from the caller's stack frame after every one of them
+    const unsigned long long lim = R.lim;
+    char *const smem = R.smem;
+    const int cta = R.p, cta_count = R.P;
+    const int n_units = a.n_units;
     const int quarter = warp & 3, half = warp >> 3;
     const int row = quarter * 32 + lane;
     const int col0 = half * 64;
     const uint32_t lane_addr = R.tmem_base + ((uint32_t)(quarter * 32) << 16);
     const float c = a.scale * 1.4426950408889634f;  // scores are kept in units of log2(e): exp(x) = exp2(x * log2 e)
-    float *xch = reinterpret_cast<float *>(R.smem + kAtXchOff);  // [2 parities][2 halves][128 rows], twice
+    float *xch = reinterpret_cast<float *>(smem + kAtXchOff);  // [2 parities][2 halves][128 rows], twice
     unsigned int sc = 0;   // S tiles consumed = number of the P V that will use this tile's P
     // P V number i completes phase i / 2 of o_done[i & 1]. A parity wait can tell a phase from the next one only, so
     // every phase of both barriers is observed in turn: tile n always observes P V n-2 (long complete: it costs
@@ -304,7 +322,7 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
     auto observe = [&](unsigned int i) -> bool {  // returns once P V number i is complete
         const unsigned int b = i & 1;
         while (oc[b] <= (i >> 1)) {
-            const bool ok = mbar_wait(&B->o_done[b], oc[b] & 1, R.lim);
+            const bool ok = mbar_wait(&B->o_done[b], oc[b] & 1, lim);
             if (!__all_sync(0xffffffffu, ok)) {
                 if (lane == 0) attn_fail(R);
                 return false;
@@ -313,9 +331,9 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
         }
         return true;
     };
-    for (int rnd = 0; rnd * R.P < a.n_units; ++rnd) {
-        const int u = attn_unit_of(R, rnd);
-        if (u >= a.n_units) continue;
+    for (int rnd = 0; rnd * cta_count < n_units; ++rnd) {
+        const int u = attn_unit_of(cta, cta_count, rnd);
+        if (u >= n_units) continue;
         const AttnUnit t = attn_unit(a, u);
         const int qi = t.qt * kAtTile + row;
         T *orow = reinterpret_cast<T *>(a.out) + (int64_t)t.b * a.o_stride_b + (int64_t)t.h * a.o_stride_h + (int64_t)qi * a.o_stride_t + col0;
@@ -328,7 +346,7 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
         float m = -INFINITY, l = 0.0f;
         for (int j = 0; j < t.n_tiles; ++j, ++sc) {
             const int sb = sc & 1;
-            bool ok = mbar_wait(&B->s_full[sb], (sc >> 1) & 1, R.lim);
+            bool ok = mbar_wait(&B->s_full[sb], (sc >> 1) & 1, lim);
             if (!__all_sync(0xffffffffu, ok)) {
                 if (lane == 0) attn_fail(R);
                 return false;

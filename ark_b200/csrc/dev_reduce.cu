@@ -615,6 +615,22 @@ __device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCt
             }
             __syncwarp();
         }
+        if (a.residual) {
+            // x := x + residual, rounded to the storage type, kept (res_out) for the next block and normalised below
+            const T *rr = reinterpret_cast<const T *>(a.residual) + (first + i * step) * in_ld;
+            T *ro = reinterpret_cast<T *>(a.res_out) + (first + i * step) * in_ld;
+            for (int64_t v = lane; v < nv; v += 32) {
+                uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+                const uint4 g4 = *reinterpret_cast<const uint4 *>(rr + v * V);
+                T *e = reinterpret_cast<T *>(&q);
+                const T *ge = reinterpret_cast<const T *>(&g4);
+#pragma unroll
+                for (int k = 0; k < V; ++k) e[k] = from_f32<T>(to_f32(e[k]) + to_f32(ge[k]));
+                *reinterpret_cast<uint4 *>(row + v * V) = q;
+                *reinterpret_cast<uint4 *>(ro + v * V) = q;
+            }
+            __syncwarp();
+        }
         float s1 = 0.0f, s2 = 0.0f, mx = -3.402823466e+38f;
         for (int64_t v = lane; v < nv; v += 32) {
             const uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);

@@ -466,14 +466,14 @@ struct Lowerer {
             while (gw < 16 && nv > (int64_t)32 * gw * 8) gw *= 2;
             a.warps_per_row = nv <= (int64_t)32 * gw * 8 ? gw : 0;
         }
-        // streaming through shared memory (bulk copies): rows of 1 KiB .. 48 KiB, no residual form, enough rows
+        // streaming through shared memory (bulk copies): rows of 1 KiB .. 48 KiB, enough rows
         // to give every warp several; 16 warps first, then up to 3 row buffers per warp, within 192 KiB
         {
             const int64_t row_bytes = a.cols * (int64_t)dtype_size(in.dtype);
             const int64_t buf = (row_bytes + 127) / 128 * 128;
             const char *e = getenv("ARKB_ROW_STAGED");
             const bool want = e ? atoi(e) != 0 : true;
-            if (want && !a.residual && row_bytes >= 1024 && buf <= 96 * 1024 && a.rows >= 4 * proc.count()) {
+            if (want && row_bytes >= 1024 && buf <= 96 * 1024 && a.rows >= 4 * proc.count()) {
                 // all row buffers that fit are kept in flight; warps first (they do the arithmetic), then depth
                 const int64_t total = (192 * 1024) / buf;
                 a.staged_bufs = (int32_t)std::max<int64_t>(1, std::min<int64_t>(3, total / 16));
@@ -2135,8 +2135,7 @@ struct Lowerer {
     // prologue and of the same shape (W1 and W3 of a SwiGLU block), become one stage: x is normalised and staged once,
     // and the CTAs' row shares are cut from both matrices together, so that the pipeline ramps up and drains once.
     void pair_weight_streams() {
-        static const bool on = []() { const char *e = getenv("ARKB_PAIR_GEMV"); return e ? atoi(e) != 0 : true; }();
-        if (!on) return;
+        if (const char *e = getenv("ARKB_PAIR_GEMV")) if (!atoi(e)) return;
         for (size_t i = 0; i + 1 < prog.stages.size(); ++i) {
             Stage &s0 = prog.stages[i];
             const Stage &s1 = prog.stages[i + 1];

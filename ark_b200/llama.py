@@ -124,11 +124,15 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
 
 def _after_attention(o, x, w, cfg, rank, p):
     """Output projection, residual, and the feed-forward block of a prefill layer; `o` is [batch*seq, heads_local*head_dim]."""
-    with PlannerContext(sync=False):                        # one task: the all_reduce starts in the matmul epilogue
-        attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
-        if p > 1:
+    if p == 1:
+        with PlannerContext(sync=False):                    # one rank: the residual is added in the Wo epilogue ...
+            x1 = ops.add(ops.matmul(o, w["wo"], transpose_other=True), x)
+        h2 = ops.rmsnorm(x1, w["ffn_norm"], eps=cfg.norm_eps)  # ... and the norm streams plain rows
+    else:
+        with PlannerContext(sync=False):                    # one task: the all_reduce starts in the matmul epilogue
+            attn = ops.matmul(o, w["wo"], transpose_other=True)  # partial [bt, dim]
             attn = ops.all_reduce(attn, rank, p, output=attn)
-    h2, x1 = ops.rmsnorm(attn, w["ffn_norm"], eps=cfg.norm_eps, residual=x)
+        h2, x1 = ops.rmsnorm(attn, w["ffn_norm"], eps=cfg.norm_eps, residual=x)
     with PlannerContext(sync=False):                        # SiLU in the W1 epilogue
         gate = ops.silu(ops.matmul(h2, w["w1"], transpose_other=True))
     with PlannerContext(sync=False):                        # gate * up in the W3 epilogue: `up` is never stored

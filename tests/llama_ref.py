@@ -80,8 +80,14 @@ def layer(x, ws, cfg, batch, seq, dt, rope=None, mask=None, k_caches=None, v_cac
         o = O.matmul(probs, v, dt)
         o = np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(bt, hl * hd)
         attn_parts.append(O.matmul(o, w["wo"], dt, trans_b=True))
-    attn = O.all_reduce(attn_parts, dt) if p > 1 else attn_parts[0]
-    x1 = O.binary("add", attn, x, dt)
+        if seq > 1 and p == 1:
+            # prefill on one rank: the residual is added to the fp32 accumulator of the output projection
+            o32 = O.matmul(f32(o), f32(w["wo"]), "fp32", trans_b=True)
+    if seq > 1 and p == 1:
+        x1 = st(O.binary("add", o32, f32(x), "fp32"))
+    else:
+        attn = O.all_reduce(attn_parts, dt) if p > 1 else attn_parts[0]
+        x1 = O.binary("add", attn, x, dt)
     down_parts = []
     for r in range(p):
         w = ws[r]

@@ -268,3 +268,34 @@ def test_prefill_layer_at_benchmark_shapes(model, dt_override, fused):
                  mask=None if fused else mask, causal=fused)
     check(got[b * seq:(b + 1) * seq], want, dt, spacings=2.5 if cfg.dim >= 8192 else 1.5,
           tail_limit=2e-2 if (dt == "bf16" and cfg.dim >= 8192 and not fused) else 2e-3)
+
+
+def test_decode_chain_folds_keep_the_bits(monkeypatch):
+    """The folds of the decode chain (rotary embedding applied by the attention stage, attention chunks merged by the
+    output projection, W1 and W3 as one stage) reproduce the roundings of the separate operators: the layer's output is
+    bit-identical with and without them."""
+    cfg = LlamaConfig(dim=1024, n_heads=8, n_kv_heads=2, ffn_dim=2752)
+    t_kv, batch = 700, 2
+    rng = np.random.default_rng(55)
+    w = make_weights(cfg, "fp16", 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch, cfg.dim)).astype(np.float32), "fp16")
+    rope = O.to_storage(rope_table(1, cfg.head_dim, start=t_kv), "fp16")
+    kc = O.to_storage(rng.normal(0, 1, (batch, cfg.n_kv_heads, t_kv, cfg.head_dim)).astype(np.float32), "fp16")
+    vc = O.to_storage(rng.normal(0, 1, (batch, cfg.n_kv_heads, t_kv, cfg.head_dim)).astype(np.float32), "fp16")
+    outs, texts = [], []
+    for folds in ("1", "0"):
+        monkeypatch.setenv("ARKB_FOLD_DECODE", folds)
+        monkeypatch.setenv("ARKB_PAIR_GEMV", folds)
+        ark.init()
+        tw = layer_weights(cfg, ark.fp16, 1)
+        tx, tr = ark.tensor([batch, cfg.dim], ark.fp16), ark.tensor([1, 1, 1, cfg.head_dim], ark.fp16)
+        tk, tv = ark.tensor(list(kc.shape), ark.fp16), ark.tensor(list(vc.shape), ark.fp16)
+        ty = decoder_layer(tx, tw, cfg, batch, 1, 0, 1, rope=tr, k_cache=tk, v_cache=tv)
+        texts.append(ark.plan_dump(str(ark.Planner(0).plan())))
+        feeds = {tx: x, tr: rope, tk: kc, tv: vc}
+        feeds.update({tw[k]: w[k] for k in w if k not in ("wk", "wv")})
+        (got,) = execute([ty], feeds, loop_mode=True, iters=2)
+        outs.append(got)
+    assert "<-rope" in texts[0] and "<-attention merge" in texts[0] and "(second matrix" in texts[0]
+    assert "<-rope" not in texts[1] and "merge of the chunks" in texts[1] and "(second matrix" not in texts[1]
+    assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))

@@ -237,3 +237,23 @@ def test_partial_task_ranges_of_reductions_rows_transposes_and_gathers(split):
         assert float(err.max()) <= 2e-2, (name, float(err.max()))
     assert np.array_equal(got[5], x.transpose(1, 0, 2)) and np.array_equal(got[6], x.transpose(0, 2, 1))
     assert np.array_equal(got[7], w[idx])
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("rows,cols", [(8, 512), (1024, 2048), (700, 4096)])
+def test_rmsnorm_with_residual(dt, rows, cols):
+    """h, x1 = rmsnorm(x, weight, residual=r): x1 = x + r (rounded, kept for the next block), h = rmsnorm(x1) * weight.
+    Few rows run in registers, many rows stream through shared memory (the residual is added when a row lands)."""
+    rng = np.random.default_rng(47)
+    x, r = rand(rng, (rows, cols), dt, -2.0, 2.0), rand(rng, (rows, cols), dt, -2.0, 2.0)
+    w = rand(rng, (cols,), dt, 0.5, 1.5)
+    ark.init()
+    tx, tr, tw = ark.tensor([rows, cols], NAME[dt]), ark.tensor([rows, cols], NAME[dt]), ark.tensor([cols], NAME[dt])
+    h, x1 = ark.rmsnorm(tx, tw, residual=tr)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert ("staged" in text) == (rows >= 4 * 148), text
+    got_h, got_x1 = execute([h, x1], {tx: x, tr: r, tw: w})
+    want_x1 = O.binary("add", x, r, dt)
+    assert np.array_equal(got_x1.view(np.uint16), want_x1.view(np.uint16))
+    tol = 2e-3 if dt == "fp16" else 1.6e-2
+    assert_close(got_h, O.rmsnorm(want_x1, w, dt, 1e-5), dt, rtol=tol, atol=tol, what=f"rmsnorm + residual {rows}x{cols}")
