@@ -260,6 +260,37 @@ __device__ __noinline__ void gemm_epilogue_tile_partial(const GemmLocal &g, cons
     }
 }
 
+// Split-K epilogue of the ordinary form: accumulator row = row of C (one per lane), accumulator column = column of C;
+// the fp32 partial of k-range `split` goes to ws[split][batch][m][n] unrounded.
+__device__ __noinline__ void gemm_epilogue_tile_partial_rows(const GemmLocal &g, const TileCoord &tc, int split, uint32_t tmem_acc,
+                                                             int warp, int lane) {
+    const int m = tc.m0 + warp * 32 + lane;
+    const bool m_ok = m < g.M;
+    const int64_t batch = (int64_t)tc.bn * g.batch_c + tc.bc;
+    float *w = g.ws + (int64_t)split * g.splits_stride + batch * (int64_t)g.M * g.N + (int64_t)m * g.N + tc.n0;
+    const uint32_t lane_addr = tmem_acc + ((uint32_t)(warp * 32) << 16);
+    const int ncols_tile = min(g.tile_n, g.N - tc.n0);
+    for (int c = 0; c < g.tile_n; c += 32) {
+        if (c >= ncols_tile) break;
+        uint32_t r[32];
+        const int cnt = (g.tile_n - c >= 32) ? 32 : 16;
+        if (cnt == 32) tmem_ld32(lane_addr + c, r);
+        else tmem_ld16(lane_addr + c, r);
+        tmem_ld_wait();
+        if (m_ok) {
+            if (c + cnt <= ncols_tile && (g.N % 4) == 0) {  // rows of the scratch are 16-byte aligned
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    if (i < cnt) *reinterpret_cast<uint4 *>(w + c + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (i < cnt && c + i < ncols_tile) w[c + i] = __uint_as_float(r[i]);
+            }
+        }
+    }
+}
+
 // Runs the tiles of one GEMM stage assigned to CTA p of P. All threads of the
 // CTA call this; it returns with the pipeline drained.
 //
@@ -501,7 +532,8 @@ __device__ __noinline__ bool gemm_drain(const GemmRun &R, int warp, int lane) {
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * 256;
         if (L.splits > 1) {
-            gemm_epilogue_tile_partial(L, tc, split, tmem_acc, warp, lane);
+            if (L.out_transposed) gemm_epilogue_tile_partial(L, tc, split, tmem_acc, warp, lane);
+            else gemm_epilogue_tile_partial_rows(L, tc, split, tmem_acc, warp, lane);
         } else if (L.out_transposed) {
             if (L.dtype == DT_BF16) gemm_epilogue_tile_swapped<__nv_bfloat16>(L, tc, tmem_acc, warp, lane);
             else gemm_epilogue_tile_swapped<__half>(L, tc, tmem_acc, warp, lane);

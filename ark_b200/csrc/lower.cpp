@@ -994,23 +994,34 @@ struct Lowerer {
             const int step = g.b_mn_major ? (prog.pair_mode ? 128 : 64) : (prog.pair_mode || fuse_ar ? 32 : 16);
             const int min_n = step;
             int tile_n = 256;
+            int64_t want_splits = 1;
             {
                 // Time model of a tile (microseconds), fitted to measurements of 2048 x 4096 x 4096 at every width: a
-                // k-block takes the longer of its MMAs (0.4 us at width 256) and of its operand loads (the CTA's A rows
-                // plus its share of B, at ~90 GB/s per SM; CTA pairs were measured 1.35x slower per byte), a tile
-                // ~2 us more (pipeline fill, epilogue tail). Rounds x tile time picks the width.
+                // k-block takes the longest of its MMAs (0.4 us at width 256), of its operand loads (the CTA's A rows
+                // plus its share of B, at ~90 GB/s per SM; CTA pairs were measured 1.35x slower per byte) and of a
+                // floor of ~0.42 us that no tile width went below; a tile ~2 us more (pipeline fill, epilogue tail).
+                // Few, long tiles (a narrow output with a long K: one rank's K/V projection) may also cut K into
+                // ranges: fp32 partials go to scratch and a sum stage follows (~6 us for its barrier and pass, plus
+                // the partials read back at ~4 TB/s). Rounds x tile time picks width and ranges together.
                 const int64_t units256 = bn * bc * tiles_m * ((N + 255) / 256);
                 static const bool old_model = []() { const char *e = getenv("ARKB_TILE_MODEL"); return e && atoi(e) == 0; }();
+                static const bool splitk_on = []() { const char *e = getenv("ARKB_SPLITK_TILES"); return e ? atoi(e) != 0 : true; }();
+                const bool may_split = splitk_on && env.workspace && !fuse_ar && !(epi && epi_mode != 0) && (N % 4) == 0 && !old_model;
                 if (units256 < 8 * P) {
-                    const double kblocks = (double)((K + 63) / 64);
+                    const int64_t kblocks = (K + 63) / 64;
                     double best = 1e30;
                     for (int c = 256; c >= min_n; c -= step) {
                         const int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
-                        const int64_t waves = (units + P - 1) / P;
                         const double load = prog.pair_mode ? 1.35 * 1.42e-3 * (128 + c / 2.0) : 1.42e-3 * (128 + c);
-                        const double tk = std::max(0.4 * c / 256.0, load);
-                        const double cost = old_model ? (double)waves * (c + 24) : (double)waves * (kblocks * tk + 2.0);
-                        if (cost < best - 1e-9) { best = cost; tile_n = c; }
+                        const double tk = std::max(std::max(0.4 * c / 256.0, load), old_model ? 0.0 : 0.42);
+                        for (int64_t sp = 1; sp <= (may_split ? 16 : 1); ++sp) {
+                            if (sp > 1 && (units * sp > P || kblocks / sp < 8)) break;
+                            const int64_t kp = (kblocks + sp - 1) / sp;
+                            const int64_t waves = (units * sp + P - 1) / P;
+                            double cost = old_model ? (double)waves * (c + 24) : (double)waves * ((double)kp * tk + 1.0 + 2.0 * c / 256.0);  // + fill, epilogue
+                            if (sp > 1) cost += 6.0 + (double)sp * bn * bc * M * N * 4.0 / 4.0e6;
+                            if (cost < best * (sp > 1 ? 0.9 : 1.0) - 1e-9) { best = cost; tile_n = c; want_splits = sp; }
+                        }
                     }
                 }
             }
@@ -1025,6 +1036,19 @@ struct Lowerer {
             g.tiles_n = (int32_t)((N + tile_n - 1) / tile_n);
             g.raster_group = (int32_t)std::min<int64_t>(tiles_m, 16);  // ~sqrt(#CTAs * tile_n / tile_m): least A+B bytes per wave
             g.n_units = (int32_t)(bn * bc * tiles_m * g.tiles_n);
+            if (want_splits > 1) {
+                const int64_t kblocks = (K + 63) / 64, units = g.n_units;
+                const int64_t kp = (kblocks + want_splits - 1) / want_splits;
+                const int64_t eff = (kblocks + kp - 1) / kp;
+                if (eff > 1) {
+                    g.splits = (int32_t)eff;
+                    g.kper = (int32_t)kp;
+                    g.n_units = (int32_t)(units * eff);
+                    const size_t bytes = (size_t)eff * bn * bc * M * N * sizeof(float);
+                    g.ws = reinterpret_cast<float *>(env.workspace + prog.workspace_bytes);
+                    prog.workspace_bytes += (bytes + 255) / 256 * 256;
+                }
+            }
         } else {
             // honour the plan's task ids: tile id -> (n, c, tile_h, tile_w), w fastest
             auto tile = op.config.at("TileShapeMNK").as_int_vec();
@@ -1156,11 +1180,12 @@ struct Lowerer {
             GemmArgs &gg = prog.stages.back().gm;
             const int act_final = gg.act;
             gg.act = ACT_NONE;
+            gg.bias = nullptr;
             emit_sync(proc);
             Stage r = new_stage(SK_SPLITK_REDUCE, proc);
             SplitKReduceArgs &a = r.sr;
             a.C = pc;
-            a.bias = nullptr;
+            a.bias = (epi && epi_mode == 0) ? tensor_ptr(*epi) : nullptr;  // an added epilogue operand moves to the sum
             a.ws = gg.ws;
             a.ldc = ldc;
             a.c_stride_c = cst[2] * cst[3];

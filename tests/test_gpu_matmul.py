@@ -263,3 +263,32 @@ def test_rope_folded_into_tensor_core_matmul_epilogue(dt, b, seq, heads, k):
     acc = O.matmul(O.to_f32(x, dt), O.to_f32(w, dt), "fp32", False, True).reshape(b, seq, heads, hd)
     want = O.to_storage(O.rope(acc, np.ascontiguousarray(np.broadcast_to(O.to_f32(tab, dt), acc.shape)), "fp32"), dt)
     assert_matmul_close(got.reshape(b * seq, heads * hd), want.reshape(b * seq, heads * hd), dt, "matmul -> rope")
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("mnk,tb,fuse", [((512, 256, 4096), True, None), ((512, 128, 8192), False, "relu"), ((300, 200, 2056), True, "gelu")])
+def test_matmul_few_long_tiles_split_k(dt, mnk, tb, fuse):
+    """A narrow output with a long K gives few tiles with long main loops: K is cut into ranges, the fp32 partials go to
+    scratch and a sum stage adds them in range order (deterministic), applies the activation and rounds once."""
+    m, n, k = mnk
+    got, want = run_mm((m, k), (n, k) if tb else (k, n), dt, False, tb, fuse=fuse)
+    assert_matmul_close(got, want, dt, f"split-K tiles {mnk}")
+
+
+def test_matmul_split_k_tiles_are_chosen():
+    """The lowering cuts K only where the model says it pays (a [4096, 128] output over K = 8192), and an Add folded into
+    the epilogue moves to the sum stage."""
+    rng = np.random.default_rng(48)
+    m, n, k = 1024, 128, 8192
+    a, other = rand(rng, (m, k), "fp16"), rand(rng, (m, n), "fp16")
+    w = O.to_storage(rng.normal(0, 0.05, (n, k)).astype(np.float32), "fp16")
+    ark.init()
+    ta_, to_, tw = (ark.tensor(list(t.shape), ark.fp16) for t in (a, other, w))
+    with ark.PlannerContext(sync=False):
+        y = ark.add(ark.matmul(ta_, tw, transpose_other=True), to_)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert "splitK=" in text and "split-K sum" in text and " Add " not in text, text
+    (got,) = execute([y], {ta_: a, to_: other, tw: w})
+    acc = O.matmul(O.to_f32(a, "fp16"), O.to_f32(w, "fp16"), "fp32", False, True)
+    want = O.to_storage(O.binary("add", acc, O.to_f32(other, "fp16"), "fp32"), "fp16")
+    assert_matmul_close(got, want, "fp16", "split-K + added operand")
