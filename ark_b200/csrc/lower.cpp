@@ -1001,7 +1001,7 @@ struct Lowerer {
                 // plus its share of B, at ~90 GB/s per SM; CTA pairs were measured 1.35x slower per byte) and of a
                 // floor of ~0.42 us that no tile width went below; a tile ~2 us more (pipeline fill, epilogue tail).
                 // Few, long tiles (a narrow output with a long K: one rank's K/V projection) may also cut K into
-                // ranges: fp32 partials go to scratch and a sum stage follows (~6 us for its barrier and pass, plus
+                // ranges: fp32 partials go to scratch and a sum stage follows (~12 us for the barrier and the second stage, plus
                 // the partials read back at ~4 TB/s). Rounds x tile time picks width and ranges together.
                 const int64_t units256 = bn * bc * tiles_m * ((N + 255) / 256);
                 static const bool old_model = []() { const char *e = getenv("ARKB_TILE_MODEL"); return e && atoi(e) == 0; }();
@@ -1019,7 +1019,7 @@ struct Lowerer {
                             const int64_t kp = (kblocks + sp - 1) / sp;
                             const int64_t waves = (units * sp + P - 1) / P;
                             double cost = old_model ? (double)waves * (c + 24) : (double)waves * ((double)kp * tk + 1.0 + 2.0 * c / 256.0);  // + fill, epilogue
-                            if (sp > 1) cost += 6.0 + (double)sp * bn * bc * M * N * 4.0 / 4.0e6;
+                            if (sp > 1) cost += 12.0 + (double)sp * bn * bc * M * N * 4.0 / 4.0e6;  // measured: 2048 x 512 x 4096 gains nothing from 3 ranges
                             if (cost < best * (sp > 1 ? 0.9 : 1.0) - 1e-9) { best = cost; tile_n = c; want_splits = sp; }
                         }
                     }
