@@ -282,7 +282,7 @@ __device__ __forceinline__ void load_row_weight(const RowOpArgs &a, int64_t e, f
 }
 
 template <typename T>
-__device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
+__device__ __noinline__ void rowop_typed(const RowOpArgs &a, int p, int P) {
     constexpr int V = 16 / sizeof(T);
     constexpr int WPC = kThreads / 32;
     constexpr int U = 4;
@@ -398,7 +398,7 @@ __device__ void rowop_typed(const RowOpArgs &a, int p, int P) {
 // of shared memory and a named barrier per warp group. HBM sees exactly one
 // read and one write per element.
 template <typename T>
-__device__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
+__device__ __noinline__ void rowop_regs(const RowOpArgs &a, int p, int P, const int G) {
     constexpr int V = 16 / sizeof(T);
     constexpr int MAXV = 8;
     constexpr int WPC = kThreads / 32;
@@ -556,7 +556,7 @@ __device__ __forceinline__ void bulk_store_row(void *gdst, const void *smem_src,
 }
 
 template <typename T>
-__device__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
+__device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char *smem, CtaCtl *ctl, DeviceState *st, int stage_idx,
                              unsigned long long wait_limit) {
     constexpr int V = 16 / sizeof(T);
     __shared__ RowStageBars bars;
