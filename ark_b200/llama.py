@@ -14,7 +14,7 @@ K/V cache (the reference example has none).
 import math
 
 from . import ops
-from .planner import PlannerContext
+from .planner import DEFAULT_NUM_SM, PlannerContext
 
 
 class LlamaConfig:
@@ -49,7 +49,8 @@ def layer_weights(cfg, dtype, world_size, prefix=""):
     }
 
 
-def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None, causal=False):
+def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None, causal=False,
+                  qkv_side_by_side=None):
     """One layer on `x` [batch*seq, dim].
 
     Prefill: `mask` [1, 1, seq, seq] (additive, -inf above the diagonal) and `rope` [1, seq, 1, head_dim]
@@ -58,6 +59,13 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     Prefill with causal=True (and no `mask` tensor; head_dim 128): the attention block is one fused stage that reads
     q, k, v in the [batch, seq, heads, head_dim] layout the projections leave and keeps the scores on chip, so the
     four transposes, the scores tensor and the mask tensor of the reference's chain disappear.
+    qkv_side_by_side (fused-attention prefill only; None = decide here): projections run next to each other on a share
+    of the processors each instead of one after the other on all of them: Wq, Wk, Wv on a third each when there are as
+    many K/V heads as query heads, else Wk and Wv on a half each after Wq. That pays when a projection has too few
+    columns per rank to fill half the grid with 128 x 256 tiles (the 7B shape from tensor-parallel degree 4 on, the K/V
+    projections of the 70B shape from degree 2 on): a narrow tile costs as much per k-block as a wide one, so 49 CTAs
+    with 176-wide tiles finish a projection in the time 148 CTAs with 64-wide tiles need (measured on one rank's
+    share of the 7B shape at degree 8: 98 -> 42 microseconds for the three).
     Returns the layer output [batch*seq, dim]."""
     p = world_size
     hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
@@ -66,21 +74,34 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     # or two rows of activations the engine folds them into the weight-streaming stage (norm and gate*up while the
     # activations are staged, the residual add on the way out) and otherwise runs them one after the other.
     decode = seq == 1 and k_cache is not None
-    with PlannerContext(sync=False):                        # prefill: RoPE is applied in the projection's epilogue
-        h = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps)
+    fused_prefill = causal and mask is None and k_cache is None and seq > 1
+    if qkv_side_by_side is None:
+        qkv_side_by_side = -(-bt // 128) * -(-(kvl * hd) // 256) <= DEFAULT_NUM_SM // 2
+    side = fused_prefill and qkv_side_by_side
+    third, half = DEFAULT_NUM_SM // 3, DEFAULT_NUM_SM // 2
+    if kvl == hl:
+        rq, rk, rv = [0, third], [third, 2 * third], [2 * third, 3 * third]
+    else:
+        rq, rk, rv = None, [0, half], [half, 2 * half]
+    if side:
+        h = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps)   # on all processors; the projections share them out
+    with PlannerContext(sync=False, processor_range=rq if side else None):  # prefill: RoPE in the projection's epilogue
+        if not side:
+            h = ops.rmsnorm(x, w["attn_norm"], eps=cfg.norm_eps)
         q = ops.matmul(h, w["wq"], transpose_other=True)   # [bt, hl*hd]
         q = ops.reshape(q, [batch, seq, hl, hd])
         if rope is not None:
             q = ops.rope(q, rope)
     scale = 1.0 / math.sqrt(hd)
-    if causal and mask is None and k_cache is None and seq > 1:
+    if fused_prefill:
         if hd != 128 or hl % kvl:
             raise ValueError("causal=True needs head_dim 128 and a whole number of query heads per K/V head; pass a mask tensor otherwise")
-        with PlannerContext(sync=False):
+        with PlannerContext(sync=False, processor_range=rk if side else None):
             k = ops.reshape(ops.matmul(h, w["wk"], transpose_other=True), [batch, seq, kvl, hd])
             if rope is not None:
                 k = ops.rope(k, rope)
-        v = ops.reshape(ops.matmul(h, w["wv"], transpose_other=True), [batch, seq, kvl, hd])
+        with PlannerContext(sync=False, processor_range=rv if side else None):
+            v = ops.reshape(ops.matmul(h, w["wv"], transpose_other=True), [batch, seq, kvl, hd])
         o = ops.prefill_attention(q, k, v, scale, causal=True, token_major=True)   # [b, seq, hl, hd]
         return _after_attention(ops.reshape(o, [bt, hl * hd]), x, w, cfg, rank, p)
     # [b, hl, seq, hd]; with one token per sequence the two layouts are the same memory

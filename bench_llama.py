@@ -61,7 +61,7 @@ def to_f32(a, dt):
 
 
 def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, layers=0, iters=10, warmup=3,
-             stage_times=False, attention="fused"):
+             stage_times=False, attention="fused", qkv_side_by_side=None):
     """Builds the layer stack, runs it and returns the result line (a dict) on rank 0, None on the other ranks.
     attention: "fused" = the prefill attention block is one stage with the scores kept on chip; "chain" = the
     reference's matmul -> scale/mask/softmax -> matmul chain with a mask tensor. The caller owns the process group (`ag`: bootstrap callback, `host_group`: a gloo group for host rendezvous)."""
@@ -97,7 +97,8 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
         if decode:
             kc, vc = ark.tensor([batch, kvl, span, hd], adt), ark.tensor([batch, kvl, span, hd], adt)
             caches.append((kc, vc))
-        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc, causal=fused)
+        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc, causal=fused,
+                          qkv_side_by_side=qkv_side_by_side)
         layers.append(w)
     ex = ark.Executor(local, 0, "llama", str(ark.Planner(local).plan()), loop_mode=False, allgather=ag)
     ex.compile()
@@ -207,6 +208,9 @@ def main():
                     help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
     ap.add_argument("--attention", choices=["fused", "chain"], default="fused",
                     help="prefill: one fused attention stage (scores on chip) or the reference's matmul/softmax/matmul chain")
+    ap.add_argument("--qkv", choices=["auto", "side", "sequential"], default="auto",
+                    help="prefill with fused attention: Wq, Wk, Wv next to each other on a third of the processors each, "
+                         "or one after the other on all of them (auto: side by side from tensor-parallel degree 4 on)")
     args = ap.parse_args()
     import torch
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -220,7 +224,7 @@ def main():
         host_group = dist.new_group(backend="gloo")
         ag = torch_allgather(host_group)
     line = run_case(args.model, args.phase, rank, world, local, ag, host_group, args.layers, args.iters, args.warmup, args.stage_times,
-                    args.attention)
+                    args.attention, {"auto": None, "side": True, "sequential": False}[args.qkv])
     if line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -92,10 +92,13 @@ def test_prefill_layer(dt, heads, kv, reuse):
     check(got, want, dt)
 
 
-@pytest.mark.parametrize("dt,dim,heads,kv,batch,seq", [("fp16", 512, 4, 4, 2, 128), ("bf16", 1024, 8, 2, 2, 200)])
-def test_prefill_layer_with_fused_attention(dt, dim, heads, kv, batch, seq):
+@pytest.mark.parametrize("dt,dim,heads,kv,batch,seq,side", [("fp16", 512, 4, 4, 2, 128, False), ("bf16", 1024, 8, 2, 2, 200, False),
+                                                            ("fp16", 512, 4, 4, 2, 640, True), ("bf16", 1024, 8, 2, 2, 200, True)])
+def test_prefill_layer_with_fused_attention(dt, dim, heads, kv, batch, seq, side):
     """causal=True: q, k, v go from the projections (and RoPE) straight into the fused attention stage, no mask
-    tensor, no transposes; grouped-query heads and a sequence that is not a multiple of the tile."""
+    tensor, no transposes; grouped-query heads and a sequence that is not a multiple of the tile. side: the three
+    projections run next to each other on a third of the processors each (Wk and Wv on a half each when there are fewer
+    K/V heads than query heads), with no barrier between them."""
     cfg = LlamaConfig(dim=dim, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
     rng = np.random.default_rng(54)
     w = make_weights(cfg, dt, 1, rng)
@@ -104,9 +107,15 @@ def test_prefill_layer_with_fused_attention(dt, dim, heads, kv, batch, seq):
     ark.init()
     tw = layer_weights(cfg, NAME[dt], 1)
     tx, tr = ark.tensor([batch * seq, cfg.dim], NAME[dt]), ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt])
-    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, causal=True)
+    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, causal=True, qkv_side_by_side=side)
     text = ark.plan_dump(str(ark.Planner(0).plan()))
     assert "PrefillAttention" in text and "Transpose" not in text and "Softmax" not in text
+    lines = text.splitlines()
+    first = next(i for i, l in enumerate(lines) if " Matmul " in l)
+    if side:
+        want_ranges = ["[0,49)", "[49,98)", "[98,147)"] if kv == heads else ["[0,148)", "[0,74)", "[74,148)"]
+        assert want_ranges == [l.split()[1] for l in lines[first:first + 3]], lines[first:first + 3]
+        assert all(" Matmul " in l for l in lines[first:first + 3])
     feeds = {tx: x, tr: rope}
     feeds.update({tw[k]: w[k] for k in w})
     (got,) = execute([ty], feeds, loop_mode=True)

@@ -235,6 +235,40 @@ def test_causal_prefill_layer_lowers_to_one_attention_stage():
         decoder_layer(ark.tensor([256, 512], ark.fp16), layer_weights(cfg64, ark.fp16, 1), cfg64, 1, 256, 0, 1, causal=True)
 
 
+def test_narrow_prefill_projections_run_side_by_side():
+    """At tensor-parallel degree 8 a rank's share of Wq, Wk and Wv is 512 columns: each runs on a third of the processors
+    with wide tiles, no barrier between the three; the plan still keeps the barrier after the norm and before the
+    attention stage. At degree 1 the projections keep the whole grid."""
+    from ark_b200.llama import LlamaConfig, decoder_layer, layer_weights
+    cfg = LlamaConfig(dim=4096, n_heads=32, n_kv_heads=32, ffn_dim=11008)
+    for world in (8, 1):
+        ark.init()
+        ark.set_rank(0)
+        ark.set_world_size(world)
+        x, rope = ark.tensor([2048, 4096], ark.fp16), ark.tensor([1, 2048, 1, 128], ark.fp16)
+        w = layer_weights(cfg, ark.fp16, world)
+        decoder_layer(x, w, cfg, 1, 2048, 0, world, rope=rope, causal=True)
+        lines = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan())).splitlines()
+        first = next(i for i, l in enumerate(lines) if " Matmul " in l)
+        if world == 8:
+            assert [l.split()[1] for l in lines[first:first + 3]] == ["[0,49)", "[49,98)", "[98,147)"], lines[first:first + 3]
+            assert all("N=512" in l and "units=48" in l for l in lines[first:first + 3])
+            assert "sync group" in lines[first - 1] and "sync group" in lines[first + 3] and "PrefillAttention" in lines[first + 4]
+        else:
+            assert all(l.split()[1] == "[0,148)" for l in lines[first:first + 3])
+    # fewer K/V heads than query heads (70B shape at degree 8): Wq keeps the grid, Wk and Wv take a half each
+    cfg = LlamaConfig(dim=8192, n_heads=64, n_kv_heads=8, ffn_dim=28672)
+    ark.init()
+    ark.set_rank(0)
+    ark.set_world_size(8)
+    x, rope = ark.tensor([4096, 8192], ark.bf16), ark.tensor([1, 1024, 1, 128], ark.bf16)
+    decoder_layer(x, layer_weights(cfg, ark.bf16, 8), cfg, 4, 1024, 0, 8, rope=rope, causal=True)
+    lines = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan())).splitlines()
+    first = next(i for i, l in enumerate(lines) if " Matmul " in l)
+    assert [l.split()[1] for l in lines[first:first + 3]] == ["[0,148)", "[0,74)", "[74,148)"], lines[first:first + 3]
+    ark.init()
+
+
 def test_tensor_parallel_decode_layer_folds_the_one_shot_all_reduces():
     """With several ranks the small all_reduces of a decode layer take their input straight from the weight-streaming
     matmul (no push stage); the sum (+ residual) of the first one is left to the two matmuls that consume it (W1 and
