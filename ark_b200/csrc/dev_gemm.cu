@@ -317,6 +317,7 @@ struct GemmRun {
     int stage_idx;
     int STAGES, G, blk_b_bytes, stage_bytes;  // a ring slot holds G consecutive k-blocks of both operands: [G blocks of A][G blocks of B]
     int n_units, kblocks, crank, up, UP, n_half, splits, kper;
+    int tall, a_slot;  // tall: 256-row tiles as two halves; a_slot: bytes of operand A in a ring slot (B follows)
     uint32_t base_par, tmem_base;
     unsigned int t0;
 };
@@ -346,7 +347,8 @@ __device__ __noinline__ bool gemm_produce(const GemmRun &R, int warp) {
 
     const bool is_a = warp == kProducerWarp;
     const int mn_major = is_a ? L.a_mn_major : L.b_mn_major;
-    const int span = is_a ? kGemmTileM : n_half;              // rows (K-major) or columns (MN-major) staged
+    const int tall = PAIR ? 0 : R.tall, a_slot = R.a_slot;
+    const int span = is_a ? kGemmTileM * (1 + tall) : n_half;  // rows (K-major) or columns (MN-major) staged
     const int chunks = mn_major ? (span + 63) / 64 : 1;       // 64-wide MN chunks
     // a slot always receives G whole k-blocks (those past the end of K arrive as zeros)
     const uint32_t bytes = (uint32_t)G * (mn_major ? (uint32_t)chunks * 64 * kGemmBK * 2 : (uint32_t)span * kGemmBK * 2);
@@ -366,13 +368,17 @@ __device__ __noinline__ bool gemm_produce(const GemmRun &R, int warp) {
                 report(st, ST_MBAR_TIMEOUT, stage_idx);
                 return false;
             }
-            char *dst = smem + s * stage_bytes + (is_a ? 0 : G * kGemmABytes);
+            char *dst = smem + s * stage_bytes + (is_a ? 0 : a_slot);
             const int chunk_stride = G * 64 * kGemmBK * 2;  // MN-major: G k-blocks of one 64-wide chunk are contiguous
             if constexpr (!PAIR) {
                 mbar_expect_tx(&pp->full[s], bytes);
                 if (!mn_major) {
-                    if (G == 1) tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
-                    else tma_load_5d(dst, tm, &pp->full[s], 0, mn0, k, bc, bn);
+                    if (G == 1) {
+                        tma_load_4d(dst, tm, &pp->full[s], k * kGemmBK, mn0, bc, bn);
+                        if (is_a && tall) tma_load_4d(dst + kGemmABytes, tm, &pp->full[s], k * kGemmBK, mn0 + kGemmTileM, bc, bn);
+                    } else {
+                        tma_load_5d(dst, tm, &pp->full[s], 0, mn0, k, bc, bn);
+                    }
                 } else {
                     for (int c = 0; c < chunks; ++c)
                         tma_load_4d(dst + c * chunk_stride, tm, &pp->full[s], mn0 + c * 64, k * kGemmBK, bc, bn);
@@ -411,6 +417,8 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
     const int splits = R.splits, kper = R.kper;
     const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
     const unsigned int t0 = R.t0;
+    const int tall = PAIR ? 0 : R.tall, a_slot = R.a_slot;
+    (void)a_slot;
     const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
     (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
     (void)stage_bytes; (void)n_units; (void)kblocks; (void)crank; (void)up; (void)UP; (void)n_half; (void)splits; (void)kper;
@@ -435,8 +443,14 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
             report(st, ST_MBAR_TIMEOUT, stage_idx);
             return false;
         }
+        if (tall && !mbar_wait(&pp->acc_empty[acc ^ 1], (((t + 1) >> 1) & 1) ^ 1, lim)) {  // the second half: the other buffer
+            ctl->abort = 1;
+            report(st, ST_MBAR_TIMEOUT, stage_idx);
+            return false;
+        }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * 256;
+        const uint32_t tmem_d2 = tmem_base + (acc ^ 1) * 256;
         for (int k = kb_lo; k < kb_hi; k += G, s = (s + 1 == STAGES ? 0 : s + 1), wrap ^= (s == 0)) {
             if (!mbar_wait(&pp->full[s], ((base_par >> s) ^ wrap) & 1, lim)) {
                 ctl->abort = 1;
@@ -446,7 +460,7 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
             tc_fence_after();
             const uint32_t sa0 = smem_u32(smem + s * stage_bytes);
             if (G == 1) {
-                const uint32_t sb = sa0 + kGemmABytes;
+                const uint32_t sb = sa0 + a_slot;
                 const uint64_t da = L.a_mn_major ? umma_desc(sa0, chunk_bytes, 1024) : umma_desc(sa0, 16, 1024);
                 const uint64_t db = L.b_mn_major ? umma_desc(sb, chunk_bytes, 1024) : umma_desc(sb, 16, 1024);
 #pragma unroll
@@ -455,8 +469,19 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
                     if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                     else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                 }
+                if constexpr (!PAIR) {
+                    if (tall) {  // rows 128..255 of the tile against the same B block (both layouts put them 16 KiB further on)
+                        const uint32_t sa2 = sa0 + kGemmABytes;
+                        const uint64_t da2 = L.a_mn_major ? umma_desc(sa2, chunk_bytes, 1024) : umma_desc(sa2, 16, 1024);
+#pragma unroll
+                        for (int kk = 0; kk < kGemmBK / 16; ++kk) {
+                            const uint32_t accum = (k > kb_lo || kk > 0) ? 1u : 0u;
+                            umma_f16(tmem_d2, da2 + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
+                        }
+                    }
+                }
             } else {
-                const uint32_t sb0 = sa0 + G * kGemmABytes;
+                const uint32_t sb0 = sa0 + a_slot;
                 const int nblk = min(G, kb_hi - k);
                 for (int j = 0; j < nblk; ++j) {
                     const uint32_t sa = sa0 + j * a_blk, sb = sb0 + j * b_blk;
@@ -485,6 +510,10 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
             umma_commit_pair(mapa_u32(f, 1));
         } else {
             umma_commit(&pp->acc_full[acc]);
+            if (tall) {
+                umma_commit(&pp->acc_full[acc ^ 1]);
+                ++t;  // a tall tile takes two accumulator turns
+            }
         }
     }
     return true;
@@ -508,6 +537,8 @@ __device__ __noinline__ bool gemm_drain(const GemmRun &R, int warp, int lane) {
     const int splits = R.splits, kper = R.kper;
     const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
     const unsigned int t0 = R.t0;
+    const int tall = PAIR ? 0 : R.tall, a_slot = R.a_slot;
+    (void)a_slot;
     const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
     (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
     (void)stage_bytes; (void)n_units; (void)kblocks; (void)crank; (void)up; (void)UP; (void)n_half; (void)splits; (void)kper;
@@ -515,10 +546,12 @@ __device__ __noinline__ bool gemm_drain(const GemmRun &R, int warp, int lane) {
     char *epi_stage = smem + kGemmPipeBytes;
     unsigned int epi_blk = 0;
     unsigned int t = t0;
-    for (int u = up; u < n_units; u += UP, ++t) {
+    for (int u = up, half = 0; u < n_units; ++t) {
+        // a tall tile is drained as two tiles of 128 rows, one per accumulator buffer
         TileCoord tc = gemm_unit(g, u / splits);
-        tc.m0 += crank * kGemmTileM;
+        tc.m0 += crank * kGemmTileM + half * kGemmTileM;
         const int split = u % splits;
+        if (half == tall) { u += UP; half = 0; } else { half = 1; }
         const int acc = t & 1;
         bool ok = mbar_wait(&pp->acc_full[acc], (t >> 1) & 1, lim);
         ok = __all_sync(0xffffffffu, ok);
@@ -599,6 +632,9 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
     R.up = PAIR ? (p >> 1) : p;             // which tile walker this CTA belongs to
     R.UP = PAIR ? (P >> 1) : P;
     R.n_half = PAIR ? L.tile_n / 2 : L.tile_n;  // B columns staged by this CTA
+    R.tall = (!PAIR && !GROUPED && g.tall) ? 1 : 0;
+    R.a_slot = R.G * kGemmABytes * (1 + R.tall);
+    R.stage_bytes = R.G * (kGemmABytes * (1 + R.tall) + R.blk_b_bytes);
     // split-K: unit = tile * splits + range; a unit runs k-blocks [kb_lo, kb_hi) of its tile
     R.splits = L.splits > 1 ? L.splits : 1;
     R.kper = g.kper > 0 ? g.kper : (R.kblocks + R.splits - 1) / R.splits;
@@ -628,7 +664,7 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
         const unsigned int total = my_slots_s;
         for (int s = 0; s < R.STAGES; ++s)
             if (total > (unsigned int)s) pp->use[s] += (total - s + R.STAGES - 1) / R.STAGES;
-        pp->tile_count = R.t0 + (unsigned int)my_tiles_s;
+        pp->tile_count = R.t0 + (unsigned int)my_tiles_s * (unsigned int)(1 + R.tall);
     }
     // the partner may still read this CTA's shared memory / signal its barriers
     if constexpr (PAIR) cluster_sync_all();

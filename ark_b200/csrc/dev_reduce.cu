@@ -562,7 +562,7 @@ __device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char
     __shared__ RowStageBars bars;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int W = a.staged_warps, NB = a.staged_bufs;
-    if (warp >= W) return;
+    const bool active = warp < W;
     const int64_t cols = a.cols, nv = cols / V;
     const uint32_t row_bytes = (uint32_t)(cols * sizeof(T));
     const uint32_t buf_bytes = (row_bytes + 127) & ~127u;
@@ -579,7 +579,11 @@ __device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char
     const int64_t in_ld = a.in_ld, out_ld = a.out_ld;
     const int64_t first = (int64_t)p * W + warp, step = (int64_t)P * W;
     const int64_t mine = first < a.rows ? (a.rows - first + step - 1) / step : 0;
-    if (lane == 0) {
+    // the weight row, once per CTA, behind the row buffers: read from L2 by every warp for every row it cost one L2
+    // round trip per 16-byte vector (the loads cannot move above the stores of the iteration before)
+    char *wsm = smem + (size_t)W * NB * buf_bytes;
+    const bool wsm_on = a.weight_smem != 0;
+    if (active && lane == 0) {
         for (int b = 0; b < NB; ++b) mbar_init(&mybar[b], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -588,6 +592,13 @@ __device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char
             bulk_load_row(mybuf + i * buf_bytes, in + (first + i * step) * in_ld, row_bytes, &mybar[i]);
         }
     }
+    if (wsm_on) {
+        const int64_t n16 = cols * (a.weight_f32 ? 4 : (int64_t)sizeof(T)) / 16;
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.weight);
+        for (int64_t v = threadIdx.x; v < n16; v += kThreads) reinterpret_cast<uint4 *>(wsm)[v] = __ldg(src + v);
+        __syncthreads();
+    }
+    if (!active) return;
     __syncwarp();
     for (int64_t i = 0; i < mine; ++i) {
         const int b = (int)(i % NB);
@@ -619,15 +630,24 @@ __device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char
             // x := x + residual, rounded to the storage type, kept (res_out) for the next block and normalised below
             const T *rr = reinterpret_cast<const T *>(a.residual) + (first + i * step) * in_ld;
             T *ro = reinterpret_cast<T *>(a.res_out) + (first + i * step) * in_ld;
-            for (int64_t v = lane; v < nv; v += 32) {
-                uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
-                const uint4 g4 = *reinterpret_cast<const uint4 *>(rr + v * V);
-                T *e = reinterpret_cast<T *>(&q);
-                const T *ge = reinterpret_cast<const T *>(&g4);
+            for (int64_t v0 = lane; v0 < nv; v0 += 128) {  // four residual loads in flight per lane before the stores
+                uint4 g4[4];
 #pragma unroll
-                for (int k = 0; k < V; ++k) e[k] = from_f32<T>(to_f32(e[k]) + to_f32(ge[k]));
-                *reinterpret_cast<uint4 *>(row + v * V) = q;
-                *reinterpret_cast<uint4 *>(ro + v * V) = q;
+                for (int u = 0; u < 4; ++u)
+                    if (v0 + 32 * u < nv) g4[u] = ldg16_stream(rr + (v0 + 32 * u) * V);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int64_t v = v0 + 32 * u;
+                    if (v < nv) {
+                        uint4 q = *reinterpret_cast<const uint4 *>(row + v * V);
+                        T *e = reinterpret_cast<T *>(&q);
+                        const T *ge = reinterpret_cast<const T *>(&g4[u]);
+#pragma unroll
+                        for (int k = 0; k < V; ++k) e[k] = from_f32<T>(to_f32(e[k]) + to_f32(ge[k]));
+                        *reinterpret_cast<uint4 *>(row + v * V) = q;
+                        *reinterpret_cast<uint4 *>(ro + v * V) = q;
+                    }
+                }
             }
             __syncwarp();
         }
@@ -682,7 +702,9 @@ __device__ __noinline__ void rowop_staged(const RowOpArgs &a, int p, int P, char
                 for (int k = 0; k < V; ++k) f[k] = (to_f32(e[k]) - sub) * mul;
                 if (wgt) {
                     float g[V];
-                    load_row_weight<T, V>(a, (int64_t)v * V, g);
+                    if (!wsm_on) load_row_weight<T, V>(a, (int64_t)v * V, g);
+                    else if (a.weight_f32) load_vec_cached<float, V>(reinterpret_cast<const float *>(wsm) + v * V, g);  // plain (generic) loads
+                    else load_vec_cached<T, V>(reinterpret_cast<const T *>(wsm) + v * V, g);
 #pragma unroll
                     for (int k = 0; k < V; ++k) f[k] *= g[k];
                 }

@@ -595,6 +595,7 @@ std::string plan_dump(const std::string &plan_json) {
         env.comm[r] = reinterpret_cast<char *>(((uintptr_t)(r + 1) << 40) + ((uintptr_t)1 << 39));
     }
     env.encode_tmap = encode_tmap_check;
+    env.allow_pair = getenv("ARKB_NO_PAIR") == nullptr;  // the same switches as the executor's lowering
     env.workspace = reinterpret_cast<char *>((uintptr_t)1 << 44);
     std::vector<std::vector<TagRecord>> records(plan.world_size, lay.published);
     for (auto &kv : lay.buffers)

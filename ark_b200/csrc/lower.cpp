@@ -475,7 +475,9 @@ struct Lowerer {
             const bool want = e ? atoi(e) != 0 : true;
             if (want && row_bytes >= 1024 && buf <= 96 * 1024 && a.rows >= 4 * proc.count()) {
                 // all row buffers that fit are kept in flight; warps first (they do the arithmetic), then depth
-                const int64_t total = (192 * 1024) / buf;
+                const int64_t wbytes = a.weight ? (a.cols * (a.weight_f32 ? 4 : (int64_t)dtype_size(in.dtype)) + 127) / 128 * 128 : 0;
+                a.weight_smem = a.weight && wbytes <= 64 * 1024 ? 1 : 0;
+                const int64_t total = (192 * 1024 - (a.weight_smem ? wbytes : 0)) / buf;
                 a.staged_bufs = (int32_t)std::max<int64_t>(1, std::min<int64_t>(3, total / 16));
                 a.staged_warps = (int32_t)std::min<int64_t>(16, total / a.staged_bufs);
             }
@@ -995,6 +997,18 @@ struct Lowerer {
             const int min_n = step;
             int tile_n = 256;
             int64_t want_splits = 1;
+            // tall tiles (one CTA per tile only; off unless ARKB_TALL=1, 2 = wherever they are possible): 256 x tile_n per
+            // CTA as two 128-row halves that share every B block, a third fewer operand bytes per flop at width 256.
+            // Measured on the 7B prefill shapes they gain nothing: a k-block of a half still takes 0.53 us (the ring holds
+            // 3 slots of 62 KiB instead of 4 of 46, so fewer bytes are in flight: the main loop follows the bytes in flight
+            // over the load latency, not the bytes loaded), and both accumulator buffers belong to one tile, so the
+            // epilogue (~5 us per half with direct stores) no longer overlaps the next tile: 2048 x 11008 x 4096 went from
+            // 195 to 265 us, 2048 x 4096 x 11008 from 157 to 149, the layer from 0.91 to 1.02 ms.
+            const char *tall_env = getenv("ARKB_TALL");
+            const bool tall_on = tall_env && atoi(tall_env) != 0;
+            const bool tall_forced = tall_env && atoi(tall_env) == 2;
+            const bool may_tall = tall_on && !prog.pair_mode && M > 128 && (!fuse_ar || M % ((int64_t)env.nranks * 256) == 0);
+            bool want_tall = false;
             {
                 // Time model of a tile (microseconds), fitted to measurements of 2048 x 4096 x 4096 at every width: a
                 // k-block takes the longest of its MMAs (0.4 us at width 256), of its operand loads (the CTA's A rows
@@ -1007,9 +1021,9 @@ struct Lowerer {
                 static const bool old_model = []() { const char *e = getenv("ARKB_TILE_MODEL"); return e && atoi(e) == 0; }();
                 static const bool splitk_on = []() { const char *e = getenv("ARKB_SPLITK_TILES"); return e ? atoi(e) != 0 : true; }();
                 const bool may_split = splitk_on && env.workspace && !fuse_ar && !(epi && epi_mode != 0) && (N % 4) == 0 && !old_model;
+                const int64_t kblocks = (K + 63) / 64;
+                double best = 1e30;
                 if (units256 < 8 * P) {
-                    const int64_t kblocks = (K + 63) / 64;
-                    double best = 1e30;
                     for (int c = 256; c >= min_n; c -= step) {
                         const int64_t units = bn * bc * tiles_m * ((N + c - 1) / c);
                         const double load = prog.pair_mode ? 1.35 * 1.42e-3 * (128 + c / 2.0) : 1.42e-3 * (128 + c);
@@ -1023,6 +1037,24 @@ struct Lowerer {
                             if (cost < best * (sp > 1 ? 0.9 : 1.0) - 1e-9) { best = cost; tile_n = c; want_splits = sp; }
                         }
                     }
+                } else {
+                    // many rounds: the widest tile (what the default above is); its cost, for the comparison with tall tiles
+                    const int64_t units = bn * bc * tiles_m * ((N + 255) / 256);
+                    const double load = prog.pair_mode ? 1.35 * 1.42e-3 * 256.0 : 1.42e-3 * 384.0;
+                    best = (double)((units + P - 1) / P) * ((double)kblocks * std::max(0.4, load) + 3.0);
+                }
+                if (may_tall && !old_model) {
+                    const int64_t tiles_m2 = (M + 255) / 256;
+                    double best_tall = 1e30;
+                    int tall_n = 256;
+                    for (int c = 256; c >= std::max(min_n, 64); c -= step) {
+                        const int64_t units = bn * bc * tiles_m2 * ((N + c - 1) / c);
+                        const double tk = std::max(std::max(0.8 * c / 256.0, 1.42e-3 * (256 + c)), 0.5);
+                        const int64_t waves = (units + P - 1) / P;
+                        const double cost = (double)waves * ((double)kblocks * tk + 2.0 + 4.0 * c / 256.0);  // fill, two half-tile epilogues
+                        if (cost < best_tall - 1e-9) { best_tall = cost; tall_n = c; }
+                    }
+                    if (best_tall < best * 0.95 || tall_forced) { want_tall = true; tile_n = tall_n; want_splits = 1; }
                 }
             }
             if (const char *e = getenv("ARKB_TILE_N")) {  // experiments: force the tile width (rounded to what the mode allows)
@@ -1032,6 +1064,11 @@ struct Lowerer {
             if (N < tile_n) tile_n = (int)((N + step - 1) / step * step);  // narrow outputs: one tile covers N
             g.tile_n = tile_n;
             g.plan_tiles = 0;
+            if (want_tall) {
+                g.tall = 1;
+                g.tile_m = 256;
+            }
+            const int64_t tiles_m = (M + g.tile_m - 1) / g.tile_m;
             g.tiles_m = (int32_t)tiles_m;
             g.tiles_n = (int32_t)((N + tile_n - 1) / tile_n);
             g.raster_group = (int32_t)std::min<int64_t>(tiles_m, 16);  // ~sqrt(#CTAs * tile_n / tile_m): least A+B bytes per wave
@@ -1121,7 +1158,7 @@ struct Lowerer {
         // ring: 16 KiB A block + this CTA's B block per stage, as many stages as fit in 192 KiB (at most 12)
         g.stage_b_bytes = (int32_t)(g.b_mn_major ? ((b_rows + 63) / 64) * 64 * 128 : b_rows * 128);
         if (swapped && g.kgroup > 1) g.stages = (int32_t)std::min<int64_t>(12, kSwappedRingBytes / (g.kgroup * (16 * 1024 + g.stage_b_bytes)));
-        else g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / (16 * 1024 + g.stage_b_bytes));
+        else g.stages = (int32_t)std::min<int64_t>(12, (192 * 1024) / ((g.tall ? 32 : 16) * 1024 + g.stage_b_bytes));
         // output through TMA stores of 32x32 blocks: needs 16-byte aligned rows and whole 32-column blocks per tile
         g.c_tma = (!swapped && g.c_vec && g.tile_n % 32 == 0 && (cst[3] * es) % 16 == 0 && (cst[2] * cst[3] * es) % 16 == 0 && !g.bias) ? 1 : 0;
         // The TMA-store epilogue (32x32 blocks through shared memory) keeps the accumulator hand-over short, which pays
@@ -1171,7 +1208,7 @@ struct Lowerer {
         if (fuse_ar) acc.opaque = true;  // tiles go to the peers' staging slots
         push(s, std::string("Matmul ") + op.name + " M=" + std::to_string(M) + " N=" + std::to_string(N) + " K=" +
                     std::to_string(K) + " tile_n=" + std::to_string(g.tile_n) + " units=" + std::to_string(g.n_units) +
-                    (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
+                    (g.tall ? " tall" : "") + (g.plan_tiles ? " plan-tiles" : "") + (g.act ? " act=" + std::to_string(g.act) : "") +
                     (g.a_mn_major ? " A:MN" : " A:K") + (g.b_mn_major ? " B:MN" : " B:K") + (swapped ? " swapped" : "") +
                     (g.peer_rows ? " tiles->peer slots" : "") + (epi ? (epi_mode == 2 ? " rope" : epi_mode == 1 ? " *operand" : " +operand") : "") +
                     " stages=" + std::to_string(g.stages) + (g.kgroup > 1 ? "x" + std::to_string(g.kgroup) + "kb" : "") + (g.splits > 1 ? " splitK=" + std::to_string(g.splits) : ""));
@@ -2394,7 +2431,8 @@ struct Lowerer {
                 case SK_ROWOP:
                     if (s.ro.staged_warps > 0) {
                         const size_t row = (size_t)s.ro.cols * dtype_size(s.ro.dtype);
-                        need = (size_t)s.ro.staged_warps * s.ro.staged_bufs * ((row + 127) / 128 * 128) + 1024;
+                        const size_t wrow = s.ro.weight_smem ? (size_t)s.ro.cols * (s.ro.weight_f32 ? 4 : dtype_size(s.ro.dtype)) : 0;
+                        need = (size_t)s.ro.staged_warps * s.ro.staged_bufs * ((row + 127) / 128 * 128) + (wrow + 127) / 128 * 128 + 1024;
                     } else {
                         need = 16 * 1024;
                     }

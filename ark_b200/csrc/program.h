@@ -110,7 +110,8 @@ struct RowOpArgs {
     const void *mask;      // optional additive mask, mask_rows x cols, row pitch mask_ld
     int64_t mask_ld;
     int32_t weight_f32;    // 1: `weight` holds fp32 values whatever the rows' type (the llama example keeps its norm weights in fp32)
-    int32_t pad;
+    int32_t weight_smem;   // staged form: the CTA copies the weight row into shared memory (behind the row buffers) once,
+                           // instead of every warp fetching it from L2 a vector at a time for every row
 };
 
 // Shared memory the loop kernel offers a matmul stage for operand ring slots when its epilogue needs no staging
@@ -161,7 +162,9 @@ struct GemmArgs {
     int32_t out_transposed;          // 1: operands are swapped (A = weights, B = activations); D[n][m] is stored to C[m][n]
     int32_t splits;                  // > 1: K is cut into `splits` ranges; unit = tile * splits + range, fp32 partials go to `ws`
     int32_t kper;                    // k-blocks per range (a multiple of kgroup); 0: ceil(k-blocks / splits)
-    int32_t pad2;
+    int32_t tall;                    // 1 (one CTA per tile only): the CTA owns 256 x tile_n tiles as two 128-row halves that share
+                                     // the B block of every ring slot (a third fewer operand bytes per flop at tile_n 256); the
+                                     // halves take both accumulator buffers, so the epilogue does not overlap the next tile
     float *ws;                       // split-K partials, layout [splits][batch][rows of C][cols of C]
     int32_t peer_rows;               // > 0: fused all_reduce, rows of C each rank sums (M / ranks)
     int32_t pad3;

@@ -292,3 +292,27 @@ def test_matmul_split_k_tiles_are_chosen():
     acc = O.matmul(O.to_f32(a, "fp16"), O.to_f32(w, "fp16"), "fp32", False, True)
     want = O.to_storage(O.binary("add", acc, O.to_f32(other, "fp16"), "fp32"), "fp16")
     assert_matmul_close(got, want, "fp16", "split-K + added operand")
+
+
+@pytest.mark.parametrize("dt", ["fp16", "bf16"])
+@pytest.mark.parametrize("mnk,ta,tb,fuse", [((600, 400, 320), False, True, None), ((512, 256, 1024), False, False, "relu"),
+                                            ((304, 264, 136), True, True, None)])
+def test_matmul_tall_tiles(monkeypatch, dt, mnk, ta, tb, fuse):
+    """Optional tile form of the one-CTA-per-tile matmul: 256 rows per CTA as two 128-row halves that share every
+    block of B and take one accumulator buffer each (rows past M arrive as zeros and are clipped by the epilogue)."""
+    monkeypatch.setenv("ARKB_NO_PAIR", "1")
+    monkeypatch.setenv("ARKB_TALL", "2")
+    m, n, k = mnk
+    rng = np.random.default_rng(77)
+    a, b = rand(rng, (k, m) if ta else (m, k), dt), rand(rng, (n, k) if tb else (k, n), dt)
+    ark.init()
+    t_a, t_b = ark.tensor(list(a.shape), NAME[dt]), ark.tensor(list(b.shape), NAME[dt])
+    if fuse:
+        with ark.PlannerContext(sync=False):
+            out = getattr(ark, fuse)(ark.matmul(t_a, t_b, transpose_input=ta, transpose_other=tb))
+    else:
+        out = ark.matmul(t_a, t_b, transpose_input=ta, transpose_other=tb)
+    plan = ark.Planner(0).plan()
+    assert " tall " in ark.plan_dump(str(plan))
+    (got,) = execute([out], {t_a: a, t_b: b}, plan=plan)
+    assert_matmul_close(got, O.matmul(a, b, dt, ta, tb, act=fuse), dt, f"tall {mnk}")
