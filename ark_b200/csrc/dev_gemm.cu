@@ -401,7 +401,7 @@ __device__ __noinline__ bool gemm_produce(const GemmRun &R, int warp) {
 }
 
 // MMA issue: one lane of warp 5 of the leader CTA.
-template <bool PAIR, bool GROUPED>
+template <bool PAIR, bool GROUPED, bool TALL>
 __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
     const GemmLocal &L = R.L;
     const GemmArgs &g = *R.g;
@@ -417,7 +417,8 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
     const int splits = R.splits, kper = R.kper;
     const uint32_t base_par = R.base_par, tmem_base = R.tmem_base;
     const unsigned int t0 = R.t0;
-    const int tall = PAIR ? 0 : R.tall, a_slot = R.a_slot;
+    constexpr int tall = TALL ? 1 : 0;
+    const int a_slot = R.a_slot;
     (void)a_slot;
     const CUtensorMap *tmA = &gmaps->tmA, *tmB = &gmaps->tmB, *tmC = &gmaps->tmC;
     (void)L; (void)g; (void)smem; (void)pp; (void)ctl; (void)st; (void)stage_idx; (void)lim; (void)STAGES; (void)G; (void)blk_b_bytes;
@@ -469,8 +470,8 @@ __device__ __noinline__ bool gemm_issue(const GemmRun &R) {
                     if constexpr (PAIR) umma_f16_pair(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                     else umma_f16(tmem_d, da + (uint64_t)(kk * a_adv), db + (uint64_t)(kk * b_adv), idesc, accum);
                 }
-                if constexpr (!PAIR) {
-                    if (tall) {  // rows 128..255 of the tile against the same B block (both layouts put them 16 KiB further on)
+                if constexpr (TALL) {
+                    {  // rows 128..255 of the tile against the same B block (both layouts put them 16 KiB further on)
                         const uint32_t sa2 = sa0 + kGemmABytes;
                         const uint64_t da2 = L.a_mn_major ? umma_desc(sa2, chunk_bytes, 1024) : umma_desc(sa2, 16, 1024);
 #pragma unroll
@@ -655,7 +656,14 @@ __device__ __noinline__ void run_gemm_t(const GemmArgs &g, const GemmArgs *gmaps
     if (warp == kProducerWarp || warp == kProducerWarpB) {
         if (lane == 0) gemm_produce<PAIR, GROUPED>(R, warp);
     } else if (warp == kMmaWarp) {
-        if (lane == 0 && R.crank == 0) gemm_issue<PAIR, GROUPED>(R);
+        if (lane == 0 && R.crank == 0) {
+            if constexpr (!PAIR && !GROUPED) {
+                if (R.tall) gemm_issue<false, false, true>(R);
+                else gemm_issue<false, false, false>(R);
+            } else {
+                gemm_issue<PAIR, GROUPED, false>(R);
+            }
+        }
     } else if (warp < kEpiWarps) {
         gemm_drain<PAIR>(R, warp, lane);
     }
