@@ -62,8 +62,8 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     qkv_side_by_side (fused-attention prefill only; None = decide here): projections run next to each other on a share
     of the processors each instead of one after the other on all of them: Wq, Wk, Wv on a third each when there are as
     many K/V heads as query heads, else Wk and Wv on a half each after Wq. That pays when a projection has too few
-    columns per rank to fill half the grid with 128 x 256 tiles (the 7B shape from tensor-parallel degree 4 on, the K/V
-    projections of the 70B shape from degree 2 on): a narrow tile costs as much per k-block as a wide one, so 49 CTAs
+    columns per rank to fill half the grid (a quarter for the K/V pair) with 128 x 256 tiles (the 7B shape from
+    tensor-parallel degree 4 on, the K/V projections of the 70B shape from degree 4 on): a narrow tile costs as much per k-block as a wide one, so 49 CTAs
     with 176-wide tiles finish a projection in the time 148 CTAs with 64-wide tiles need (measured on one rank's
     share of the 7B shape at degree 8: 98 -> 42 microseconds for the three).
     Returns the layer output [batch*seq, dim]."""
@@ -76,7 +76,9 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     decode = seq == 1 and k_cache is not None
     fused_prefill = causal and mask is None and k_cache is None and seq > 1
     if qkv_side_by_side is None:
-        qkv_side_by_side = -(-bt // 128) * -(-(kvl * hd) // 256) <= DEFAULT_NUM_SM // 2
+        # 128 x 256 tiles of one K/V projection against the share of the grid it would get (measured: the 70B shape at
+        # degree 2, 64 tiles per projection on a half each, gains nothing; at degree 8, 32 tiles, 2.6 %)
+        qkv_side_by_side = -(-bt // 128) * -(-(kvl * hd) // 256) <= DEFAULT_NUM_SM // (2 if kvl == hl else 4)
     side = fused_prefill and qkv_side_by_side
     third, half = DEFAULT_NUM_SM // 3, DEFAULT_NUM_SM // 2
     if kvl == hl:
