@@ -298,7 +298,7 @@ __device__ __noinline__ bool attn_issue(const AttnRun &R) {
 // ---- softmax and output -------------------------------------------------------------------------
 // Warp q + 8*half owns TMEM lanes 32q..32q+31 (the only ones a warp with index = q mod 4 can reach) = query rows
 // 32q.. of the tile, and columns 64*half..+63 of S and O. Thread = row.
-template <typename T>
+template <typename T, bool MASK>
 __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) {
     const PrefillAttnArgs &a = *R.a;
     AttnBars *B = R.bars;
@@ -343,6 +343,14 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
             continue;
         }
         const int last_key = a.causal ? min(a.Tkv - 1, qi + a.Tkv - a.Tq) : a.Tkv - 1;  // last key this row may see
+        // additive mask: this row's values, in units of the raw score (mask / scale), join the raw scores
+        const T *mrow = nullptr;
+        float inv_scale = 0.0f;
+        if constexpr (MASK) {
+            mrow = reinterpret_cast<const T *>(a.mask) + (int64_t)t.b * a.m_stride_b + (int64_t)t.h * a.m_stride_h +
+                   (int64_t)min(qi, a.Tq - 1) * a.m_stride_q;
+            inv_scale = 1.0f / a.scale;
+        }
         float m = -INFINITY, l = 0.0f;
         for (int j = 0; j < t.n_tiles; ++j, ++sc) {
             const int sb = sc & 1;
@@ -362,6 +370,25 @@ __device__ __noinline__ bool attn_softmax(const AttnRun &R, int warp, int lane) 
             tmem_ld_wait();
             // the raw scores stay in r0 / r1 as float bits until the exponentials (the scale is positive: the maximum
             // of the raw scores is the maximum of the scaled ones)
+            if constexpr (MASK) {
+#pragma unroll
+                for (int cc = 0; cc < 8; ++cc) {  // 8 keys per 16-byte vector of the mask row
+                    const int k0 = key0 + cc * 8;
+                    float mv[8];
+                    if (k0 + 7 < a.Tkv) {
+                        load_vec<T, 8>(mrow + k0, mv);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) mv[i] = k0 + i < a.Tkv ? to_f32(mrow[k0 + i]) : 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int idx = cc * 8 + i;
+                        if (idx < 32) r0[idx] = __float_as_uint(fmaf(mv[i], inv_scale, __uint_as_float(r0[idx])));
+                        else r1[idx - 32] = __float_as_uint(fmaf(mv[i], inv_scale, __uint_as_float(r1[idx - 32])));
+                    }
+                }
+            }
             if (masked) {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
@@ -481,8 +508,13 @@ __device__ __noinline__ void run_prefill_attn(const PrefillAttnArgs &a, const Pr
     } else if (warp == kMmaWarp) {
         if (lane == 0) attn_issue(R);
     } else if (warp < kEpiWarps || (warp >= 8 && warp < 12)) {
-        if (a.dtype == DT_BF16) attn_softmax<__nv_bfloat16>(R, warp, lane);
-        else attn_softmax<__half>(R, warp, lane);
+        if (a.mask) {
+            if (a.dtype == DT_BF16) attn_softmax<__nv_bfloat16, true>(R, warp, lane);
+            else attn_softmax<__half, true>(R, warp, lane);
+        } else {
+            if (a.dtype == DT_BF16) attn_softmax<__nv_bfloat16, false>(R, warp, lane);
+            else attn_softmax<__half, false>(R, warp, lane);
+        }
     }
     tc_fence_before();
     __syncthreads();

@@ -1381,11 +1381,25 @@ struct Lowerer {
         if (!(a.scale > 0.0f)) throw Error(E_UNSUPPORTED, "PrefillAttention: Scale must be positive");
         a.q_tiles = (int32_t)((Tq + 127) / 128);
         a.n_units = (int32_t)(B * Hq * a.q_tiles);
+        const TensorDesc *mask = op.reads.size() > 3 ? &op.reads[3] : nullptr;
+        if (mask) {
+            auto ms = mask->shape4();
+            auto mst = mask->strides4();
+            if (mask->dtype != q.dtype || ms[2] != Tq || ms[3] != Tkv || (ms[0] != 1 && ms[0] != B) || (ms[1] != 1 && ms[1] != Hq))
+                throw Error(E_UNSUPPORTED, "PrefillAttention: mask [B or 1, Hq or 1, Tq, Tkv] of the operands' type");
+            a.mask = tensor_ptr(*mask);
+            a.m_stride_q = mst[3];
+            a.m_stride_h = ms[1] == 1 ? 0 : mst[2] * mst[3];
+            a.m_stride_b = ms[0] == 1 ? 0 : mst[1] * mst[2] * mst[3];
+            if (!aligned16(a.mask) || a.m_stride_q % 8 || a.m_stride_h % 8 || a.m_stride_b % 8)
+                throw Error(E_UNSUPPORTED, "PrefillAttention: mask rows must be 16-byte aligned");
+        }
         acc_begin();
         rd(q); rd(k); rd(v);
+        if (mask) rd(*mask);
         wr(o);
         push(s, "PrefillAttention " + op.name + " B=" + std::to_string(B) + " heads=" + std::to_string(Hq) + "/" + std::to_string(Hkv) +
-                    " rows=" + std::to_string(Tq) + " keys=" + std::to_string(Tkv) + (a.causal ? " causal" : "") + " " + layout +
+                    " rows=" + std::to_string(Tq) + " keys=" + std::to_string(Tkv) + (a.causal ? " causal" : "") + (mask ? " +mask" : "") + " " + layout +
                     " units=" + std::to_string(a.n_units));
     }
 

@@ -253,6 +253,8 @@ struct PrefillAttnArgs {
     int32_t dtype;
     float scale;      // applied to q.k before the softmax
     int32_t n_units, q_tiles;
+    const void *mask; // optional additive mask [B or 1, Hq or 1, Tq, Tkv] of the operands' type, added to scale * q.k
+    int64_t m_stride_b, m_stride_h, m_stride_q;  // elements; 0 on a broadcast axis
 };
 
 struct GemmSimtArgs {

@@ -50,7 +50,7 @@ def layer_weights(cfg, dtype, world_size, prefix=""):
 
 
 def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None, causal=False,
-                  qkv_side_by_side=None):
+                  qkv_side_by_side=None, fused_attention=False):
     """One layer on `x` [batch*seq, dim].
 
     Prefill: `mask` [1, 1, seq, seq] (additive, -inf above the diagonal) and `rope` [1, seq, 1, head_dim]
@@ -58,7 +58,11 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     [batch, kv_heads_local, t_kv, head_dim] hold the keys/values attended to; `rope` is [1, 1, 1, head_dim].
     Prefill with causal=True (and no `mask` tensor; head_dim 128): the attention block is one fused stage that reads
     q, k, v in the [batch, seq, heads, head_dim] layout the projections leave and keeps the scores on chip, so the
-    four transposes, the scores tensor and the mask tensor of the reference's chain disappear.
+    four transposes, the scores tensor and the mask tensor of the reference's chain disappear. fused_attention=True
+    with a `mask` tensor: the same stage in its general form, the mask added to the scaled scores on chip (every key
+    tile is computed, the stage cannot know which ones the mask hides, unless causal=True is given as well: key tiles
+    past the diagonal are then skipped and the mask only acts below it); the default for a mask tensor stays the
+    reference's operator chain (matmul, scale + mask + softmax, matmul: examples/llama/model.py:403-444).
     qkv_side_by_side (fused-attention prefill only; None = decide here): projections run next to each other on a share
     of the processors each instead of one after the other on all of them: Wq, Wk, Wv on a third each when there are as
     many K/V heads as query heads, else Wk and Wv on a half each after Wq. That pays when a projection has too few
@@ -74,7 +78,7 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     # or two rows of activations the engine folds them into the weight-streaming stage (norm and gate*up while the
     # activations are staged, the residual add on the way out) and otherwise runs them one after the other.
     decode = seq == 1 and k_cache is not None
-    fused_prefill = causal and mask is None and k_cache is None and seq > 1
+    fused_prefill = ((causal and mask is None) or (fused_attention and mask is not None)) and k_cache is None and seq > 1
     if qkv_side_by_side is None:
         # 128 x 256 tiles of one K/V projection against the share of the grid it would get (measured: the 70B shape at
         # degree 2, 64 tiles per projection on a half each, gains nothing; at degree 8, 32 tiles, 2.6 %)
@@ -97,14 +101,15 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     scale = 1.0 / math.sqrt(hd)
     if fused_prefill:
         if hd != 128 or hl % kvl:
-            raise ValueError("causal=True needs head_dim 128 and a whole number of query heads per K/V head; pass a mask tensor otherwise")
+            raise ValueError("the fused attention stage needs head_dim 128 and a whole number of query heads per K/V head; "
+                             "pass a mask tensor (and fused_attention=False) otherwise")
         with PlannerContext(sync=False, processor_range=rk if side else None):
             k = ops.reshape(ops.matmul(h, w["wk"], transpose_other=True), [batch, seq, kvl, hd])
             if rope is not None:
                 k = ops.rope(k, rope)
         with PlannerContext(sync=False, processor_range=rv if side else None):
             v = ops.reshape(ops.matmul(h, w["wv"], transpose_other=True), [batch, seq, kvl, hd])
-        o = ops.prefill_attention(q, k, v, scale, causal=True, token_major=True)   # [b, seq, hl, hd]
+        o = ops.prefill_attention(q, k, v, scale, causal=causal, token_major=True, mask=mask)   # [b, seq, hl, hd]
         return _after_attention(ops.reshape(o, [bt, hl * hd]), x, w, cfg, rank, p)
     # [b, hl, seq, hd]; with one token per sequence the two layouts are the same memory
     q = ops.reshape(q, [batch, hl, 1, hd]) if seq == 1 else ops.transpose(q, [0, 2, 1, 3])

@@ -367,11 +367,13 @@ def decode_attention(q, k_cache, v_cache, scale=1.0, output=None, name="decode_a
     return res
 
 
-def prefill_attention(q, k, v, scale=1.0, causal=True, token_major=False, output=None, name="prefill_attention"):
+def prefill_attention(q, k, v, scale=1.0, causal=True, token_major=False, mask=None, output=None, name="prefill_attention"):
     """softmax(scale * q . k^T [+ causal mask]) . v for many query rows per head, head dimension 128:
     q [B, Hq, Tq, 128], k and v [B, Hkv, Tkv, 128] (Hq a multiple of Hkv: grouped-query attention), result as q.
     With token_major=True all four tensors are [B, T, H, 128], the layout the projection matmuls leave behind, so
-    no transpose is needed on either side. causal=True: row i attends to keys [0, i + Tkv - Tq].
+    no transpose is needed on either side. causal=True: row i attends to keys [0, i + Tkv - Tq] (key tiles past the
+    diagonal are skipped). mask: an additive mask [B or 1, Hq or 1, Tq, Tkv] of the operands' type (the tensor
+    examples/llama/model.py:419-420 adds to the scores), added to scale * q . k^T; every key tile is computed then.
     Engine extension: the reference example builds the block from two matmuls, a scale, a mask add and a softmax
     (examples/llama/model.py:336-444) and writes the [B, H, T, T] scores to memory twice; here the scores stay
     in tensor memory (S = q k^T and O = P v on tcgen05, online softmax in fp32, P rounded to the storage type)."""
@@ -379,9 +381,13 @@ def prefill_attention(q, k, v, scale=1.0, causal=True, token_major=False, output
     if len(q.shape) != 4 or len(k.shape) != 4 or list(k.shape) != list(v.shape) or q.shape[3] != 128 or k.shape[3] != 128 \
             or q.shape[0] != k.shape[0] or q.shape[hx] % k.shape[hx]:
         raise ModelError("prefill_attention: q [B, Hq, Tq, 128], k and v [B, Hkv, Tkv, 128], Hq a multiple of Hkv")
+    if mask is not None:
+        ms = [1] * (4 - len(mask.shape)) + list(mask.shape)
+        if ms[2] != q.shape[tx] or ms[3] != k.shape[tx] or ms[0] not in (1, q.shape[0]) or ms[1] not in (1, q.shape[hx]):
+            raise ModelError("prefill_attention: mask [B or 1, Hq or 1, Tq, Tkv]")
     out = _out_like(q.shape, q.dtype, output)
     res = _result_of(out)
-    _m().add_op("PrefillAttention", name, [q, k, v], [out], [res],
+    _m().add_op("PrefillAttention", name, [q, k, v] + ([mask] if mask is not None else []), [out], [res],
                 {"Scale": float(scale), "Causal": int(bool(causal)), "TokenMajor": int(bool(token_major))})
     return res
 

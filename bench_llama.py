@@ -87,8 +87,9 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
     ark.set_world_size(world)
     x = ark.tensor([batch * seq, cfg.dim], adt)
     rope = ark.tensor([1, seq, 1, hd], adt)
-    fused = attention == "fused" and not decode and hd == 128
-    mask = None if decode or fused else ark.tensor([1, 1, seq, seq], adt)
+    fused = attention in ("fused", "fused-mask") and not decode and hd == 128
+    with_mask = not decode and (not fused or attention == "fused-mask")
+    mask = ark.tensor([1, 1, seq, seq], adt) if with_mask else None
     layers, caches = [], []
     h = x
     for li in range(nlayers):
@@ -97,8 +98,8 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
         if decode:
             kc, vc = ark.tensor([batch, kvl, span, hd], adt), ark.tensor([batch, kvl, span, hd], adt)
             caches.append((kc, vc))
-        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc, causal=fused,
-                          qkv_side_by_side=qkv_side_by_side)
+        h = decoder_layer(h, w, cfg, batch, seq, rank, world, rope=rope, mask=mask, k_cache=kc, v_cache=vc, causal=fused and mask is None,
+                          qkv_side_by_side=qkv_side_by_side, fused_attention=fused and mask is not None)
         layers.append(w)
     ex = ark.Executor(local, 0, "llama", str(ark.Planner(local).plan()), loop_mode=False, allgather=ag)
     ex.compile()
@@ -184,7 +185,7 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
                                        f"x {seq} tokens, {t_kv} keys", "stages": n_stages},
                 "output_finite": finite}
         if not decode:
-            line["config"]["attention"] = "fused" if fused else "chain"
+            line["config"]["attention"] = ("fused, additive mask tensor" if mask is not None else "fused") if fused else "chain"
         if decode:
             gbs = wbytes / (ms * 1e-3) / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
@@ -206,8 +207,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--stage-times", action="store_true",
                     help="instead of timing, print when the CTAs entered and left every stage of the last of 3 iterations")
-    ap.add_argument("--attention", choices=["fused", "chain"], default="fused",
-                    help="prefill: one fused attention stage (scores on chip) or the reference's matmul/softmax/matmul chain")
+    ap.add_argument("--attention", choices=["fused", "fused-mask", "chain"], default="fused",
+                    help="prefill: one fused attention stage (scores on chip; causal from indices, or 'fused-mask': the mask "
+                         "tensor added on chip, every key tile computed) or the reference's matmul/softmax/matmul chain")
     ap.add_argument("--qkv", choices=["auto", "side", "sequential"], default="auto",
                     help="prefill with fused attention: Wq, Wk, Wv next to each other on a third of the processors each, "
                          "or one after the other on all of them (auto: side by side from tensor-parallel degree 4 on)")

@@ -123,6 +123,31 @@ def test_prefill_layer_with_fused_attention(dt, dim, heads, kv, batch, seq, side
     check(got, want, dt)
 
 
+@pytest.mark.parametrize("dt,heads,kv,causal", [("fp16", 4, 4, False), ("bf16", 8, 2, True)])
+def test_prefill_layer_with_mask_tensor_in_the_fused_stage(dt, heads, kv, causal):
+    """The reference's call (a mask tensor, examples/llama/model.py:419-420) with the attention block as one stage: the
+    mask is added on chip; with causal=True besides, key tiles past the diagonal are skipped. Reference: the oracle's
+    per-operator composition with the same mask tensor."""
+    cfg = LlamaConfig(dim=128 * heads, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
+    batch, seq = 2, 200
+    rng = np.random.default_rng(57)
+    w = make_weights(cfg, dt, 1, rng)
+    x = O.to_storage(rng.normal(0, 1, (batch * seq, cfg.dim)).astype(np.float32), dt)
+    rope = O.to_storage(rope_table(seq, cfg.head_dim), dt)
+    mask = O.to_storage(causal_mask(seq, dt), dt)
+    ark.init()
+    tw = layer_weights(cfg, NAME[dt], 1)
+    tx = ark.tensor([batch * seq, cfg.dim], NAME[dt])
+    tr, tm = ark.tensor([1, seq, 1, cfg.head_dim], NAME[dt]), ark.tensor([1, 1, seq, seq], NAME[dt])
+    ty = decoder_layer(tx, tw, cfg, batch, seq, 0, 1, rope=tr, mask=tm, causal=causal, fused_attention=True)
+    text = ark.plan_dump(str(ark.Planner(0).plan()))
+    assert "+mask" in text and "Softmax" not in text and "Transpose" not in text and (" causal" in text) == causal
+    feeds = {tx: x, tr: rope, tm: mask}
+    feeds.update({tw[k]: w[k] for k in w})
+    (got,) = execute([ty], feeds, loop_mode=True)
+    check(got, layer(x, [w], cfg, batch, seq, dt, rope=rope, causal=True), dt)
+
+
 @pytest.mark.parametrize("dt,heads,kv,batch", [("fp16", 4, 4, 1), ("bf16", 8, 1, 16)])
 def test_decode_layer_with_kv_cache(dt, heads, kv, batch):
     cfg = LlamaConfig(dim=512, n_heads=heads, n_kv_heads=kv, ffn_dim=1376)
@@ -203,6 +228,54 @@ def test_prefill_attention_against_float64(dt, b, hq, hkv, tq, tkv, causal, toke
     if causal:
         visible = np.arange(tkv)[None, :] <= (np.arange(tq)[:, None] + tkv - tq)
         s = np.where(visible[None, None], s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bhqt,bhtd->bhqd", p, vf)
+    gotf = O.to_f32(got, dt).astype(np.float64)
+    if token_major:
+        gotf = gotf.transpose(0, 2, 1, 3)
+    err = np.abs(gotf - want)
+    tol = 4e-3 if dt == "fp16" else 3e-2
+    assert float(err.max()) <= tol, (float(err.max()), np.unravel_index(err.argmax(), err.shape))
+    assert float(err.mean()) <= tol / 20, float(err.mean())
+
+
+@pytest.mark.parametrize("dt,b,hq,hkv,tq,tkv,mshape,token_major,causal", [
+    ("fp16", 1, 4, 4, 256, 256, (1, 1), False, False),  # the llama example's mask: one [T, T] tensor for every head
+    ("bf16", 2, 4, 2, 200, 328, (2, 4), True, False),   # one mask per sequence and head, ragged tiles, [B, T, H, 128] storage
+    ("fp16", 2, 2, 1, 136, 136, (2, 1), False, False),  # per sequence (padding masks), broadcast over the heads
+    ("fp16", 1, 2, 2, 384, 384, (1, 1), True, True),    # the caller also says causal: key tiles past the diagonal are skipped
+])
+def test_prefill_attention_with_additive_mask(dt, b, hq, hkv, tq, tkv, mshape, token_major, causal):
+    """The general form of the fused stage: an additive mask tensor (here the causal -inf triangle plus finite biases
+    plus, per sequence, a block of padded keys) joins scale * q k^T before the softmax; every key tile is computed.
+    Reference: softmax attention in float64 on the same rounded inputs and the same rounded mask."""
+    rng = np.random.default_rng(73)
+    shape = lambda h, t: (b, t, h, 128) if token_major else (b, h, t, 128)
+    q = O.to_storage(rng.normal(0, 1, shape(hq, tq)).astype(np.float32), dt)
+    k = O.to_storage(rng.normal(0, 1, shape(hkv, tkv)).astype(np.float32), dt)
+    v = O.to_storage(rng.normal(0, 1, shape(hkv, tkv)).astype(np.float32), dt)
+    mb, mh = mshape
+    m = rng.normal(0, 1, (mb, mh, tq, tkv)).astype(np.float32)
+    visible = np.arange(tkv)[None, :] <= (np.arange(tq)[:, None] + tkv - tq)
+    m = np.where(visible[None, None], m, -np.inf).astype(np.float32)
+    for i in range(mb):
+        m[i, :, :, 3 + 5 * i: 40 + 9 * i] = -np.inf       # a block of keys nobody sees (key 0 stays visible to every row)
+    m = O.to_storage(m, dt)
+    scale = 1.0 / np.sqrt(128.0)
+    ark.init()
+    tq_, tk_, tv_ = ark.tensor(list(q.shape), NAME[dt]), ark.tensor(list(k.shape), NAME[dt]), ark.tensor(list(v.shape), NAME[dt])
+    tm_ = ark.tensor(list(m.shape), NAME[dt])
+    out = ark.prefill_attention(tq_, tk_, tv_, scale, causal=causal, token_major=token_major, mask=tm_)
+    plan = ark.Planner(0).plan()
+    assert "+mask" in ark.plan_dump(str(plan))
+    (got,) = execute([out], {tq_: q, tk_: k, tv_: v, tm_: m}, loop_mode=True, plan=plan)
+    g = hq // hkv
+    qf, kf, vf = (O.to_f32(x, dt).astype(np.float64) for x in (q, k, v))
+    if token_major:
+        qf, kf, vf = (x.transpose(0, 2, 1, 3) for x in (qf, kf, vf))
+    kf, vf = np.repeat(kf, g, axis=1), np.repeat(vf, g, axis=1)
+    s = np.einsum("bhqd,bhtd->bhqt", qf, kf) * scale + O.to_f32(m, dt).astype(np.float64)
     p = np.exp(s - s.max(-1, keepdims=True))
     p /= p.sum(-1, keepdims=True)
     want = np.einsum("bhqt,bhtd->bhqd", p, vf)
