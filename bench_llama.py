@@ -182,7 +182,7 @@ def run_case(model, phase, rank=0, world=1, local=0, ag=None, host_group=None, l
         line = {"metric": f"llama_{args.model}_{args.phase}_tokens_per_s", "value": t / (ms * 1e-3), "unit": "tokens/s",
                 "n_gpus": world, "ms_per_step": ms, "layers": nlayers, "dtype": dt, "data": "synthetic",
                 "config": {"workload": f"llama2-{args.model}-shaped x{nlayers} layers, tp{world}, {args.phase} batch {batch} "
-                                       f"x {seq} tokens, {t_kv} keys", "stages": n_stages},
+                                       f"x {seq} tokens, {t_kv} keys", "stages": n_stages, "timed_iterations": args.iters},
                 "output_finite": finite}
         if not decode:
             line["config"]["attention"] = ("fused, additive mask tensor" if mask is not None else "fused") if fused else "chain"
