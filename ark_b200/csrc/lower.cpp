@@ -1007,7 +1007,7 @@ struct Lowerer {
             const char *tall_env = getenv("ARKB_TALL");
             const bool tall_on = tall_env && atoi(tall_env) != 0;
             const bool tall_forced = tall_env && atoi(tall_env) == 2;
-            const bool may_tall = tall_on && !prog.pair_mode && M > 128 && (!fuse_ar || M % ((int64_t)env.nranks * 256) == 0);
+            const bool may_tall = tall_on && !prog.pair_mode && M > 128 && !fuse_ar;  // not combined with the fused all_reduce (never run together)
             bool want_tall = false;
             {
                 // Time model of a tile (microseconds), fitted to measurements of 2048 x 4096 x 4096 at every width: a
