@@ -235,6 +235,32 @@ def test_causal_prefill_layer_lowers_to_one_attention_stage():
         decoder_layer(ark.tensor([256, 512], ark.fp16), layer_weights(cfg64, ark.fp16, 1), cfg64, 1, 256, 0, 1, causal=True)
 
 
+def test_prefill_attention_takes_a_mask_tensor():
+    """The general form of the fused stage: an additive mask [B or 1, Hq or 1, Tq, Tkv]; wrong shapes are refused when
+    the model is built, a mask of another type or with unaligned rows when the plan is lowered."""
+    ark.init()
+    q, k = ark.tensor([2, 4, 256, 128], ark.fp16), ark.tensor([2, 2, 384, 128], ark.fp16)
+    ark.prefill_attention(q, k, k, 0.1, causal=False, mask=ark.tensor([2, 1, 256, 384], ark.fp16))
+    text = ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    assert "PrefillAttention prefill_attention B=2 heads=4/2 rows=256 keys=384 +mask bhtd units=16" in text
+    for shape in ([1, 1, 256, 256], [3, 1, 256, 384], [2, 2, 256, 384]):
+        ark.init()
+        q, k = ark.tensor([2, 4, 256, 128], ark.fp16), ark.tensor([2, 2, 384, 128], ark.fp16)
+        with pytest.raises(ark.ModelError):
+            ark.prefill_attention(q, k, k, 0.1, causal=False, mask=ark.tensor(shape, ark.fp16))
+    ark.init()
+    q, k = ark.tensor([1, 4, 256, 128], ark.fp16), ark.tensor([1, 4, 260, 128], ark.fp16)
+    ark.prefill_attention(q, k, k, 0.1, causal=False, mask=ark.tensor([1, 1, 256, 260], ark.fp16))   # rows of 520 bytes
+    with pytest.raises(ark.UnsupportedError):
+        ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    ark.init()
+    q, k = ark.tensor([1, 4, 256, 128], ark.fp16), ark.tensor([1, 4, 256, 128], ark.fp16)
+    ark.prefill_attention(q, k, k, 0.1, causal=False, mask=ark.tensor([1, 1, 256, 256], ark.bf16))
+    with pytest.raises(ark.UnsupportedError):
+        ark.plan_dump(str(ark.Planner(0, num_sm=148).plan()))
+    ark.init()
+
+
 def test_narrow_prefill_projections_run_side_by_side():
     """At tensor-parallel degree 8 a rank's share of Wq, Wk and Wv is 512 columns: each runs on a third of the processors
     with wide tiles, no barrier between the three; the plan still keeps the barrier after the norm and before the
