@@ -50,7 +50,7 @@ def layer_weights(cfg, dtype, world_size, prefix=""):
 
 
 def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None, k_cache=None, v_cache=None, causal=False,
-                  qkv_side_by_side=None, fused_attention=False):
+                  qkv_side_by_side=None, fused_attention=False, num_sm=DEFAULT_NUM_SM):
     """One layer on `x` [batch*seq, dim].
 
     Prefill: `mask` [1, 1, seq, seq] (additive, -inf above the diagonal) and `rope` [1, seq, 1, head_dim]
@@ -69,7 +69,8 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     columns per rank to fill half the grid (a quarter for the K/V pair) with 128 x 256 tiles (the 7B shape from
     tensor-parallel degree 4 on, the K/V projections of the 70B shape from degree 4 on): a narrow tile costs as much per k-block as a wide one, so 49 CTAs
     with 176-wide tiles finish a projection in the time 148 CTAs with 64-wide tiles need (measured on one rank's
-    share of the 7B shape at degree 8: 98 -> 42 microseconds for the three).
+    share of the 7B shape at degree 8: 98 -> 42 microseconds for the three). num_sm: the processors the plan will be
+    made for (the Planner's num_sm), which the shares are cut from.
     Returns the layer output [batch*seq, dim]."""
     p = world_size
     hl, kvl, hd = cfg.n_heads // p, max(1, cfg.n_kv_heads // p), cfg.head_dim
@@ -82,9 +83,9 @@ def decoder_layer(x, w, cfg, batch, seq, rank, world_size, rope=None, mask=None,
     if qkv_side_by_side is None:
         # 128 x 256 tiles of one K/V projection against the share of the grid it would get (measured: the 70B shape at
         # degree 2, 64 tiles per projection on a half each, gains nothing; at degree 8, 32 tiles, 2.6 %)
-        qkv_side_by_side = -(-bt // 128) * -(-(kvl * hd) // 256) <= DEFAULT_NUM_SM // (2 if kvl == hl else 4)
+        qkv_side_by_side = -(-bt // 128) * -(-(kvl * hd) // 256) <= num_sm // (2 if kvl == hl else 4)
     side = fused_prefill and qkv_side_by_side
-    third, half = DEFAULT_NUM_SM // 3, DEFAULT_NUM_SM // 2
+    third, half = num_sm // 3, num_sm // 2
     if kvl == hl:
         rq, rk, rv = [0, third], [third, 2 * third], [2 * third, 3 * third]
     else:
