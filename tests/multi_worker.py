@@ -249,6 +249,8 @@ def main():
     ty = decoder_layer(tx, tw, cfg, batch, seq, rank, world, rope=tr, causal=True)
     text = ark.plan_dump(str(ark.Planner(local).plan()))
     assert "PrefillAttention" in text and text.count(" rope ") == 2 and "*operand" in text, text
+    # a rank's projections are narrow here: they run side by side on a third of the processors each
+    assert [l.split()[1] for l in text.splitlines() if " Matmul " in l][:3] == ["[0,49)", "[49,98)", "[98,147)"], text
     feeds = {tx: x, tr: rope}
     feeds.update({tw[k]: ws[rank][k] for k in tw})
     (got,) = run([ty], feeds)
