@@ -235,6 +235,25 @@ def test_causal_prefill_layer_lowers_to_one_attention_stage():
         decoder_layer(ark.tensor([256, 512], ark.fp16), layer_weights(cfg64, ark.fp16, 1), cfg64, 1, 256, 0, 1, causal=True)
 
 
+def test_tall_tiles_are_an_opt_in_of_the_one_cta_form(monkeypatch):
+    """ARKB_TALL (off by default: measured slower) gives a CTA 256-row tiles as two halves over one B block; only
+    without CTA pairs, and the ring then holds 32 KiB of A per slot."""
+    def dump():
+        ark.init()
+        a, b = ark.tensor([2048, 4096], ark.fp16), ark.tensor([4096, 4096], ark.fp16)
+        ark.matmul(a, b, transpose_other=True)
+        return ark.plan_dump(str(ark.Planner(0, num_sm=148).plan())).splitlines()[1]
+    assert " tall" not in dump() and "tile_n=256" in dump()            # pairs by default
+    monkeypatch.setenv("ARKB_NO_PAIR", "1")
+    assert " tall" not in dump() and "units=288" in dump() and "stages=4" in dump()
+    monkeypatch.setenv("ARKB_TALL", "2")
+    line = dump()
+    assert " tall " in line and "units=144" in line and "stages=3" in line, line
+    monkeypatch.delenv("ARKB_NO_PAIR")
+    assert " tall" not in dump()                                        # never with pairs
+    ark.init()
+
+
 def test_prefill_attention_takes_a_mask_tensor():
     """The general form of the fused stage: an additive mask [B or 1, Hq or 1, Tq, Tkv]; wrong shapes are refused when
     the model is built, a mask of another type or with unaligned rows when the plan is lowered."""
